@@ -1,0 +1,326 @@
+/* b200_kernels.h -- C ABI of libb200_kernels.so: the LLM-decode kernel hot path of
+ * sizzlecar/triton-rs (`triton-kernels` crate + the two int4 GEMM examples of
+ * `triton-dsl`) as pre-built sm_100a code.
+ *
+ * What a caller of the reference does today, per kernel:
+ *     K::<CONSTS>::mlir()                      crates/triton-dsl/src/codegen.rs:89-113
+ *     -> triton_sys::Context::compile          crates/triton-sys/src/lib.rs:139
+ *     -> cudarc launch_builder().arg(..)       crates/triton-runtime/examples/run_vec_add.rs:105-118
+ * with the arguments in signature order, a caller-chosen grid, and two trailing
+ * scratch pointers.  Here each kernel is ONE function with the same name (dtype
+ * generics spelled as _f16/_f32 suffixes, the scheme the reference prelude already
+ * uses, crates/triton-kernels/src/lib.rs:45-76), the same arguments in the same
+ * order and the same tensor layouts, followed by
+ *     - the extents the reference took from its launch grid (rows, tokens, batch),
+ *     - a CUDA stream.
+ * Grid, block, shared memory, tile sizes and scratch arguments are chosen inside.
+ *
+ * Conventions (modelled on crates/triton-sys/shim/triton_c.h:25-45,62-77: plain C
+ * types, no exceptions, status + message):
+ *   - every pointer is a raw device pointer (what cudarc's CudaSlice::device_ptr
+ *     yields) unless the name says `host`;
+ *   - return value: 0 = launched; < 0 = argument rejected on the host before any
+ *     launch (B200K_E_*); > 0 = the cudaError_t of a failed launch;
+ *   - b200k_last_error() returns a thread-local message for the last non-zero return;
+ *   - calls are asynchronous and stream-ordered; nothing synchronises the device;
+ *   - no kernel traps or asserts: device-side waits are bounded and report through
+ *     a status word;
+ *   - the library never falls back to host arithmetic.
+ *
+ * `half` below means IEEE binary16 stored as uint16_t.
+ */
+#ifndef B200_KERNELS_H
+#define B200_KERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef uint16_t b200k_half;
+typedef void *b200k_stream; /* cudaStream_t */
+
+enum {
+    B200K_OK = 0,
+    B200K_E_NULL = -1,        /* a required pointer is NULL */
+    B200K_E_SHAPE = -2,       /* extent not supported (e.g. K % 8 != 0, head_dim) */
+    B200K_E_ALIGN = -3,       /* pointer or stride alignment not supported */
+    B200K_E_WORKSPACE = -4,   /* workspace missing or too small */
+    B200K_E_DEVICE = -5,      /* current device is not sm_100 */
+    B200K_E_STATE = -6        /* handle misuse */
+};
+
+const char *b200k_last_error(void);
+const char *b200k_version(void);
+/* 0 when the current CUDA device can run this library (compute capability 10.x). */
+int b200k_device_check(void);
+
+/* ------------------------------------------------------------------------- */
+/* Workspace.  Split-K GEMM partials, split-KV attention partials and the MoE  */
+/* permutation buffers live in scratch memory.  The drop-in entry points below */
+/* draw it from one per-device default workspace that the library allocates on */
+/* first use (cudaMalloc, B200K_DEFAULT_WORKSPACE_BYTES) or that the caller     */
+/* installs with b200k_set_workspace (then the library allocates nothing).     */
+/* Calls that use the default workspace must not overlap on the device: issue  */
+/* them on one stream, or use the *_ws variants with a workspace per stream.   */
+/* ------------------------------------------------------------------------- */
+#define B200K_DEFAULT_WORKSPACE_BYTES ((size_t)256 << 20)
+int b200k_set_workspace(void *workspace, size_t bytes);
+size_t b200k_gemm_workspace_bytes(int m, int n, int k);
+size_t b200k_attention_workspace_bytes(int batch, int num_q_heads, int num_kv_heads,
+                                       int head_dim, int max_len);
+
+/* ------------------------------------------------------------------------- */
+/* int4 W4A16 GEMM                                                             */
+/* ------------------------------------------------------------------------- */
+
+/* Replaces w4a16_gptq_gemm_typed<f16,BM,BN,BK>
+ * (crates/triton-dsl/examples/w4a16_gptq_gemm_typed.rs:104-274; argument list :110-128).
+ *   C[m,n] = sum_k A[m,k] * (((qweight[k/8,n] >> 4(k%8)) & 15)
+ *                            - (((qzeros[k/G,n/8] >> 4(n%8)) & 15) + 1)) * scales[k/G,n]
+ * fp32 accumulate, dequantised weight rounded to fp16 before the product (:256-260),
+ * fp16 output.  Requires K % 8 == 0, N % 8 == 0, group_size % 8 == 0, K % group_size == 0.
+ * Any element strides are accepted; the tensor-core and GEMV paths are taken when
+ * stride_ak = stride_qwn = stride_sn = stride_qzn = stride_cn = 1 and the row
+ * strides keep 16-byte alignment, otherwise a strided CUDA-core path runs. */
+int w4a16_gptq_gemm_f16(const b200k_half *a, const int32_t *qweight, const b200k_half *scales,
+                        const int32_t *qzeros, b200k_half *c, int m_size, int n_size,
+                        int k_size, int group_size, int stride_am, int stride_ak,
+                        int stride_qwk, int stride_qwn, int stride_sk, int stride_sn,
+                        int stride_qzk, int stride_qzn, int stride_cm, int stride_cn,
+                        b200k_stream stream);
+
+/* Same contraction with the symmetric zero-point 8 and no qzeros tensor: the GEMM
+ * counterpart of dequant_int4_sym_to_fp16
+ * (crates/triton-dsl/examples/ferrum_dequant_int4_sym.rs:25-131, zero at :60).
+ * Argument list = the GPTQ one without qzeros and its two strides. */
+int w4a16_gptq_gemm_sym_f16(const b200k_half *a, const int32_t *qweight,
+                            const b200k_half *scales, b200k_half *c, int m_size, int n_size,
+                            int k_size, int group_size, int stride_am, int stride_ak,
+                            int stride_qwk, int stride_qwn, int stride_sk, int stride_sn,
+                            int stride_cm, int stride_cn, b200k_stream stream);
+
+/* Replaces awq_gemm_int4_typed<f16,BM,BN,BK>
+ * (crates/triton-dsl/examples/awq_gemm_int4_typed.rs:95-242; argument list :96-114).
+ * qweight [K, N/8], qzeros [K/G, N/8]; column n sits at nibble [0,4,1,5,2,6,3,7][n%8]
+ * (:137-151) in both; zeros are used as stored, no +1 (:202-205). */
+int awq_gemm_int4_f16(const b200k_half *a, const int32_t *qweight, const b200k_half *scales,
+                      const int32_t *qzeros, b200k_half *c, int m_size, int n_size, int k_size,
+                      int group_size, int stride_am, int stride_ak, int stride_qwk,
+                      int stride_qwn, int stride_sk, int stride_sn, int stride_qzk,
+                      int stride_qzn, int stride_cm, int stride_cn, b200k_stream stream);
+
+/* The same three GEMMs with an explicit workspace (b200k_gemm_workspace_bytes). */
+int w4a16_gptq_gemm_f16_ws(const b200k_half *a, const int32_t *qweight,
+                           const b200k_half *scales, const int32_t *qzeros, b200k_half *c,
+                           int m_size, int n_size, int k_size, int group_size, int stride_am,
+                           int stride_ak, int stride_qwk, int stride_qwn, int stride_sk,
+                           int stride_sn, int stride_qzk, int stride_qzn, int stride_cm,
+                           int stride_cn, void *workspace, size_t workspace_bytes,
+                           b200k_stream stream);
+int awq_gemm_int4_f16_ws(const b200k_half *a, const int32_t *qweight, const b200k_half *scales,
+                         const int32_t *qzeros, b200k_half *c, int m_size, int n_size,
+                         int k_size, int group_size, int stride_am, int stride_ak,
+                         int stride_qwk, int stride_qwn, int stride_sk, int stride_sn,
+                         int stride_qzk, int stride_qzn, int stride_cm, int stride_cn,
+                         void *workspace, size_t workspace_bytes, b200k_stream stream);
+
+/* Replaces dequant_int4_to_fp16<BLOCK>
+ * (crates/triton-dsl/examples/ferrum_dequant_int4.rs:28-139): GPTQ full-matrix
+ * dequant, output COLUMN-major out[col*K + k] (:80-89), zero = stored nibble with
+ * no +1 (:76). */
+int dequant_int4_to_fp16(const int32_t *qweight, const b200k_half *scales,
+                         const int32_t *qzeros, b200k_half *output, int k_dim, int n_dim,
+                         int group_size, int n_div_8, b200k_stream stream);
+/* Replaces dequant_int4_sym_to_fp16<BLOCK>
+ * (crates/triton-dsl/examples/ferrum_dequant_int4_sym.rs:25-131). */
+int dequant_int4_sym_to_fp16(const int32_t *qweight, const b200k_half *scales,
+                             b200k_half *output, int k_dim, int n_dim, int group_size,
+                             b200k_stream stream);
+
+/* Bit-exact unpack probes (no counterpart kernel in the reference; they expose the
+ * nibble orders its GEMMs use so that tests can compare them with ==):
+ *   gptq_qweight: [K/8,N] -> int8 [K,N]          (w4a16_gptq_gemm_typed.rs:167-173)
+ *   gptq_qzeros : [groups,N/8] -> int8 [groups,N], value + zero_offset   (:155-162,236)
+ *   awq         : [rows,N/8] -> int8 [rows,N]     (awq_gemm_int4_typed.rs:137-151) */
+int b200k_unpack_gptq_qweight(const int32_t *qweight, int8_t *out, int k_dim, int n_dim,
+                              b200k_stream stream);
+int b200k_unpack_gptq_qzeros(const int32_t *qzeros, int8_t *out, int groups, int n_dim,
+                             int zero_offset, b200k_stream stream);
+int b200k_unpack_awq(const int32_t *packed, int8_t *out, int rows, int n_dim,
+                     b200k_stream stream);
+
+/* ------------------------------------------------------------------------- */
+/* decode attention                                                            */
+/* ------------------------------------------------------------------------- */
+
+/* Replaces decode_attention_typed<T,HEAD_DIM,BLOCK_KV>
+ * (crates/triton-kernels/src/attention.rs:51-164): q [Hq,D], caches [seq,Hkv,D]
+ * seq-major, output [Hq,D]; kv_head = q_head / (Hq/Hkv) (:68-69); fp32 softmax.
+ * Positions >= valid_kv_len are excluded (the documented intent, :90-92,131-133). */
+int decode_attention_f16(const b200k_half *q, const b200k_half *k_cache,
+                         const b200k_half *v_cache, b200k_half *output, int num_q_heads,
+                         int num_kv_heads, int head_dim, int valid_kv_len, float scale,
+                         b200k_stream stream);
+int decode_attention_f32(const float *q, const float *k_cache, const float *v_cache,
+                         float *output, int num_q_heads, int num_kv_heads, int head_dim,
+                         int valid_kv_len, float scale, b200k_stream stream);
+
+/* Replaces decode_attention_hm_typed (attention.rs:182-273): head-major caches
+ * [Hkv,capacity,D], off = kv_head*capacity*D + pos*D + d (:216-230). */
+int decode_attention_hm_f16(const b200k_half *q, const b200k_half *k_cache,
+                            const b200k_half *v_cache, b200k_half *output, int num_q_heads,
+                            int num_kv_heads, int head_dim, int capacity, int valid_kv_len,
+                            float scale, b200k_stream stream);
+int decode_attention_hm_f32(const float *q, const float *k_cache, const float *v_cache,
+                            float *output, int num_q_heads, int num_kv_heads, int head_dim,
+                            int capacity, int valid_kv_len, float scale, b200k_stream stream);
+
+/* Replaces batched_decode_attention_f32 (attention.rs:291-368): q [B,Hq,D], caches
+ * [B,seq_len,Hkv,D] seq-major, one shared valid_kv_len.  The reference walks
+ * valid_kv_len / BLOCK_KV whole tiles (:324) and asks callers to pad; this entry
+ * covers all valid_kv_len positions, which is the same thing for padded callers. */
+int batched_decode_attention_f32(const float *q, const float *k_cache, const float *v_cache,
+                                 float *output, int batch_size, int num_q_heads,
+                                 int num_kv_heads, int head_dim, int seq_len,
+                                 int valid_kv_len, float scale, b200k_stream stream);
+
+/* The follow-up the reference names at attention.rs:287-289 (per-sequence lengths),
+ * on the head-major layout of decode_attention_hm: q [B,Hq,D], caches
+ * [B,Hkv,max_len,D], context_lens [B] int32, output [B,Hq,D].  No counterpart
+ * kernel in the reference.  Split-KV over a work list of fixed-size chunks, all q
+ * heads of a GQA group per KV read, then a combine pass. */
+int batched_decode_attention_hm_f16(const b200k_half *q, const b200k_half *k_cache,
+                                    const b200k_half *v_cache, const int32_t *context_lens,
+                                    b200k_half *output, int batch_size, int num_q_heads,
+                                    int num_kv_heads, int head_dim, int max_len, float scale,
+                                    b200k_stream stream);
+int batched_decode_attention_hm_f16_ws(const b200k_half *q, const b200k_half *k_cache,
+                                       const b200k_half *v_cache, const int32_t *context_lens,
+                                       b200k_half *output, int batch_size, int num_q_heads,
+                                       int num_kv_heads, int head_dim, int max_len,
+                                       float scale, void *workspace, size_t workspace_bytes,
+                                       b200k_stream stream);
+
+/* Replaces flash_decode_attn_phase1_f32<HEAD_DIM,BLOCK_KV> (attention.rs:508-585):
+ * split s of q head h covers chunk_blocks*block_kv positions from
+ * s*chunk_blocks*block_kv, chunk_blocks = (valid_kv_len/num_splits)/block_kv (:538);
+ * writes un-normalised partial_acc [Hq,S,D], partial_max [Hq,S], partial_sum [Hq,S]
+ * (:579-584).  block_kv is the reference's BLOCK_KV const generic. */
+int flash_decode_attn_phase1_f32(const float *q, const float *k_cache, const float *v_cache,
+                                 float *partial_acc, float *partial_max, float *partial_sum,
+                                 int num_q_heads, int num_kv_heads, int head_dim,
+                                 int valid_kv_len, int num_splits, float scale, int block_kv,
+                                 b200k_stream stream);
+/* Replaces batched_flash_decode_attn_phase1_f32 (attention.rs:663-747). */
+int batched_flash_decode_attn_phase1_f32(const float *q, const float *k_cache,
+                                         const float *v_cache, float *partial_acc,
+                                         float *partial_max, float *partial_sum,
+                                         int batch_size, int num_q_heads, int num_kv_heads,
+                                         int head_dim, int seq_len, int valid_kv_len,
+                                         int num_splits, float scale, int block_kv,
+                                         b200k_stream stream);
+/* Replaces flash_decode_attn_phase2_f32<HEAD_DIM,NUM_SPLITS_TILE> (attention.rs:599-642):
+ * M = max m_s; L = sum l_s e^(m_s-M); out = sum acc_s e^(m_s-M) / L.  The batched
+ * caller flattens batch into num_q_heads (:659-661). */
+int flash_decode_attn_phase2_f32(const float *partial_acc, const float *partial_max,
+                                 const float *partial_sum, float *output, int num_q_heads,
+                                 int head_dim, int num_splits, b200k_stream stream);
+
+/* Replaces paged_decode_attention_typed (attention.rs:399-490): pools
+ * [max_blocks,block_size,Hkv,D]; phys = block_table[pos/block_size] (:450-455). */
+int paged_decode_attention_f16(const b200k_half *q, const b200k_half *k_block_pool,
+                               const b200k_half *v_block_pool, const int32_t *block_table,
+                               b200k_half *output, int num_q_heads, int num_kv_heads,
+                               int head_dim, int valid_kv_len, int block_size, float scale,
+                               b200k_stream stream);
+
+/* ------------------------------------------------------------------------- */
+/* bandwidth-bound glue                                                        */
+/* ------------------------------------------------------------------------- */
+
+/* Replace rms_norm_f16 / rms_norm_f32 (crates/triton-kernels/src/norms.rs:125-150,
+ * 16-41): y = x * rsqrt(sum(x^2)*inv_n + eps) * w, reduction in fp32.  num_rows is
+ * the reference's launch grid. */
+int rms_norm_f16(const b200k_half *input, const b200k_half *weight, b200k_half *output,
+                 int row_size, float inv_n, float eps, int num_rows, b200k_stream stream);
+int rms_norm_f32(const float *input, const float *weight, float *output, int row_size,
+                 float inv_n, float eps, int num_rows, b200k_stream stream);
+
+/* Replace fused_add_rms_norm_f16 / _f32 (norms.rs:189-220, 85-115): r = x + res;
+ * residual_out = r; output = rms_norm(r) from the unrounded fp32 sum (:208-219). */
+int fused_add_rms_norm_f16(const b200k_half *input, const b200k_half *residual,
+                           const b200k_half *weight, b200k_half *output,
+                           b200k_half *residual_out, int hidden_size, float inv_n, float eps,
+                           int num_rows, b200k_stream stream);
+int fused_add_rms_norm_f32(const float *input, const float *residual, const float *weight,
+                           float *output, float *residual_out, int hidden_size, float inv_n,
+                           float eps, int num_rows, b200k_stream stream);
+
+/* Replace residual_add_f16/_f32 and residual_add_inplace_f16/_f32
+ * (crates/triton-kernels/src/elementwise.rs:62-74, 46-58, 95-107, 79-91). */
+int residual_add_f16(const b200k_half *a, const b200k_half *b, b200k_half *out, int n,
+                     b200k_stream stream);
+int residual_add_f32(const float *a, const float *b, float *out, int n, b200k_stream stream);
+int residual_add_inplace_f16(b200k_half *a, const b200k_half *b, int n, b200k_stream stream);
+int residual_add_inplace_f32(float *a, const float *b, int n, b200k_stream stream);
+
+/* Replace fused_silu_mul_f16/_f32 (elementwise.rs:169-184, 148-164) and
+ * fused_silu_mul_interleaved_f16/_f32 (:188-212, 225-250): silu(g) = g/(1+e^-g) in
+ * fp32; interleaved = row b of gate_up [B, 2*inter] holds gate then up (:199-206). */
+int fused_silu_mul_f16(const b200k_half *gate, const b200k_half *up, b200k_half *out, int n,
+                       b200k_stream stream);
+int fused_silu_mul_f32(const float *gate, const float *up, float *out, int n,
+                       b200k_stream stream);
+int fused_silu_mul_interleaved_f16(const b200k_half *gate_up, b200k_half *out, int inter,
+                                   int total, b200k_stream stream);
+int fused_silu_mul_interleaved_f32(const float *gate_up, float *out, int inter, int total,
+                                   b200k_stream stream);
+
+/* Replace rope_q_f32 / rope_k_f32 (crates/triton-kernels/src/positional.rs:24-80):
+ * one position, tables [D/2] already sliced; pairs (i, i+D/2) (:45-46).  num_heads is
+ * the reference's launch grid. */
+int rope_q_f32(const float *q, const float *cos_table, const float *sin_table, float *q_out,
+               int head_dim, int num_heads, b200k_stream stream);
+int rope_k_f32(const float *k, const float *cos_table, const float *sin_table, float *k_out,
+               int head_dim, int num_heads, b200k_stream stream);
+/* Replaces rope_full_f32 (positional.rs:94-129): x [tokens,heads,D], tables
+ * [max_pos,D/2], positions [tokens] int32.  num_tokens is grid / num_heads. */
+int rope_full_f32(const float *q, const float *cos_table, const float *sin_table,
+                  const int32_t *positions, float *q_out, int num_heads, int head_dim,
+                  int num_tokens, b200k_stream stream);
+/* fp16 edition of rope_full (tables stay fp32, arithmetic fp32, one rounding at the
+ * store); the reference ships f32 only. */
+int rope_full_f16(const b200k_half *q, const float *cos_table, const float *sin_table,
+                  const int32_t *positions, b200k_half *q_out, int num_heads, int head_dim,
+                  int num_tokens, b200k_stream stream);
+
+/* Replaces kv_cache_append_f32<BLOCK> (crates/triton-kernels/src/cache.rs:21-47):
+ * new_keys/values [B,H,D] -> caches [max_seq,H,D] at row cache_idx[b] (:38-46).
+ * batch is grid / num_heads. */
+int kv_cache_append_f32(const float *new_keys, const float *new_values, float *k_cache,
+                        float *v_cache, const int32_t *cache_idx, int num_heads, int head_dim,
+                        int batch, b200k_stream stream);
+/* Batched head-major fp16 edition for the cache layout of
+ * batched_decode_attention_hm_f16: caches [B,H,max_len,D], row (b,h) goes to
+ * [b,h,cache_idx[b],:].  No counterpart kernel in the reference. */
+int kv_cache_append_hm_f16(const b200k_half *new_keys, const b200k_half *new_values,
+                           b200k_half *k_cache, b200k_half *v_cache, const int32_t *cache_idx,
+                           int num_heads, int head_dim, int max_len, int batch,
+                           b200k_stream stream);
+/* rope_full on q and k + kv_cache_append_hm in one pass over a fused QKV row
+ * [B, (Hq+2Hkv)*D] (q heads, then k heads, then v heads): q_out [B,Hq,D] rotated,
+ * k rotated and v copied into the caches at positions[b].  Fusion of
+ * positional.rs:94-129 and cache.rs:21-47; no counterpart kernel in the reference. */
+int rope_kv_append_hm_f16(const b200k_half *qkv, const float *cos_table,
+                          const float *sin_table, const int32_t *positions,
+                          b200k_half *q_out, b200k_half *k_cache, b200k_half *v_cache,
+                          int num_q_heads, int num_kv_heads, int head_dim, int max_len,
+                          int batch, b200k_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_KERNELS_H */

@@ -1,0 +1,164 @@
+"""Decode attention through the C ABI against the CPU oracle."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close, golden
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def t(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def test_golden_attention(P):
+    g = golden("attention_hm")
+    b, hq, d = g["q"].shape
+    hkv, ml = g["k"].shape[1], g["k"].shape[2]
+    out = torch.empty((b, hq, d), dtype=torch.float16, device=DEV)
+    P.batched_decode_attention_hm_f16(t(g["q"]), t(g["k"]), t(g["v"]), t(g["lens"]), out, b, hq, hkv, d, ml,
+                                      1.0 / np.sqrt(d))
+    assert_close(out.float().cpu().numpy(), g["out"])
+
+
+@pytest.mark.parametrize("b,hq,hkv,ml,lens", [
+    (4, 32, 8, 1500, [1, 511, 513, 1500]),
+    (2, 8, 8, 300, [64, 300]),            # no grouping
+    (3, 16, 2, 2100, [2100, 1024, 1025]), # group of 8
+    (2, 4, 2, 96, [0, 96]),               # an empty sequence -> zero row
+])
+def test_batched_hm_ragged_with_poisoned_tail(P, oracle, b, hq, hkv, ml, lens):
+    rng = np.random.default_rng(sum(lens))
+    d = 128
+    q = rng.standard_normal((b, hq, d)).astype(np.float16)
+    k = rng.standard_normal((b, hkv, ml, d)).astype(np.float16)
+    v = rng.standard_normal((b, hkv, ml, d)).astype(np.float16)
+    lens = np.array(lens, dtype=np.int32)
+    for i in range(b):                       # positions >= len must never be read
+        k[i, :, lens[i]:] = np.nan
+        v[i, :, lens[i]:] = np.nan
+    out = torch.empty((b, hq, d), dtype=torch.float16, device=DEV)
+    args = (t(q), t(k), t(v), t(lens), out, b, hq, hkv, d, ml, 1.0 / np.sqrt(d))
+    P.batched_decode_attention_hm_f16(*args)
+    got = out.float().cpu().numpy()
+    for i in range(b):
+        if lens[i] == 0:
+            assert (got[i] == 0).all()
+        else:
+            ref = oracle.decode_attention_hm(q[i], k[i], v[i], int(lens[i]), 1.0 / np.sqrt(d))
+            assert_close(got[i], ref, what=f"seq {i} len {lens[i]}")
+    out2 = torch.empty_like(out)
+    P.batched_decode_attention_hm_f16(*args[:4], out2, *args[5:])
+    assert torch.equal(out, out2), "two runs differ"
+
+
+def test_batched_hm_oracle_c_mid_size(P, oracle_c):
+    # a size numpy would crawl through: checked with the C oracle
+    rng = np.random.default_rng(77)
+    b, hq, hkv, d, ml = 8, 32, 8, 128, 4096
+    q = rng.standard_normal((b, hq, d)).astype(np.float16)
+    k = rng.standard_normal((b, hkv, ml, d)).astype(np.float16)
+    v = rng.standard_normal((b, hkv, ml, d)).astype(np.float16)
+    lens = rng.integers(512, ml + 1, b).astype(np.int32)
+    out = torch.empty((b, hq, d), dtype=torch.float16, device=DEV)
+    P.batched_decode_attention_hm_f16(t(q), t(k), t(v), t(lens), out, b, hq, hkv, d, ml, 1.0 / np.sqrt(d))
+    ref = np.zeros((b, hq, d), np.float32)
+    q32 = np.ascontiguousarray(q.astype(np.float32))
+    p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    oracle_c.oc_batched_decode_attention_hm(p(q32), p(k), p(v), p(lens), p(ref), b, hq, hkv, d, ml,
+                                            ctypes.c_float(1.0 / np.sqrt(d)))
+    assert_close(out.float().cpu().numpy(), ref)
+
+
+def test_full_size_property_constant_values(P):
+    # BASELINE config 1 extents. Size-independent property: if every V row of a sequence is
+    # the same vector, the output is that vector for every head, whatever the scores are.
+    b, hq, hkv, d, ml = 32, 32, 8, 128, 8192
+    gen = torch.Generator(device=DEV).manual_seed(1)
+    q = torch.randn((b, hq, d), device=DEV, generator=gen).half()
+    k = torch.randn((b, hkv, ml, d), device=DEV, generator=gen).half()
+    vrow = torch.randn((b, hkv, 1, d), device=DEV, generator=gen).half()
+    v = vrow.expand(b, hkv, ml, d).contiguous()
+    lens = torch.randint(512, ml + 1, (b,), device=DEV, dtype=torch.int32, generator=gen)
+    out = torch.empty((b, hq, d), dtype=torch.float16, device=DEV)
+    P.batched_decode_attention_hm_f16(q, k, v, lens, out, b, hq, hkv, d, ml, 1.0 / np.sqrt(d))
+    want = vrow.expand(b, hkv, hq // hkv, d).reshape(b, hq, d).float()
+    assert ((out.float() - want).abs() <= 1e-2 + 1e-2 * want.abs()).all()
+
+
+def test_single_sequence_layouts(P, oracle):
+    rng = np.random.default_rng(31)
+    hq, hkv, d, L, cap = 32, 8, 128, 777, 800
+    q = rng.standard_normal((hq, d)).astype(np.float16)
+    ks = rng.standard_normal((cap, hkv, d)).astype(np.float16)
+    vs = rng.standard_normal((cap, hkv, d)).astype(np.float16)
+    ks[L:] = np.nan
+    vs[L:] = np.nan
+    scale = 1.0 / np.sqrt(d)
+    ref = oracle.decode_attention(q, ks, vs, hkv, L, scale)
+    out = torch.empty((hq, d), dtype=torch.float16, device=DEV)
+    P.decode_attention_f16(t(q), t(ks), t(vs), out, hq, hkv, d, L, scale)
+    assert_close(out.float().cpu().numpy(), ref, what="seq-major")
+    khm, vhm = ks.transpose(1, 0, 2).copy(), vs.transpose(1, 0, 2).copy()
+    P.decode_attention_hm_f16(t(q), t(khm), t(vhm), out, hq, hkv, d, cap, L, scale)
+    assert_close(out.float().cpu().numpy(), ref, what="head-major")
+    # f32 editions
+    o32 = torch.empty((hq, d), device=DEV)
+    P.decode_attention_f32(t(q.astype(np.float32)), t(ks.astype(np.float32)), t(vs.astype(np.float32)), o32, hq, hkv,
+                           d, L, scale)
+    assert_close(o32.cpu().numpy(), ref, 1e-4, 1e-5, what="seq-major f32")
+    P.decode_attention_hm_f32(t(q.astype(np.float32)), t(khm.astype(np.float32)), t(vhm.astype(np.float32)), o32, hq,
+                              hkv, d, cap, L, scale)
+    assert_close(o32.cpu().numpy(), ref, 1e-4, 1e-5, what="head-major f32")
+    # head_dim 64 takes the generic family
+    q64 = q[:, :64].copy()
+    k64, v64 = ks[:L, :, :64].copy(), vs[:L, :, :64].copy()
+    o64 = torch.empty((hq, 64), dtype=torch.float16, device=DEV)
+    P.decode_attention_f16(t(q64), t(k64), t(v64), o64, hq, hkv, 64, L, 0.125)
+    assert_close(o64.float().cpu().numpy(), oracle.decode_attention(q64, k64, v64, hkv, L, 0.125), what="d64")
+
+
+def test_paged(P, oracle):
+    rng = np.random.default_rng(41)
+    hq, hkv, d, bs, nblk, L = 16, 4, 128, 16, 40, 16 * 23
+    q = rng.standard_normal((hq, d)).astype(np.float16)
+    kp = rng.standard_normal((nblk, bs, hkv, d)).astype(np.float16)
+    vp = rng.standard_normal((nblk, bs, hkv, d)).astype(np.float16)
+    table = rng.permutation(nblk)[: L // bs].astype(np.int32)
+    out = torch.empty((hq, d), dtype=torch.float16, device=DEV)
+    P.paged_decode_attention_f16(t(q), t(kp), t(vp), t(table), out, hq, hkv, d, L, bs, 1 / np.sqrt(d))
+    assert_close(out.float().cpu().numpy(), oracle.paged_decode_attention(q, kp, vp, table, L, bs, 1 / np.sqrt(d)))
+
+
+def test_f32_batched_and_split_phases(P, oracle):
+    rng = np.random.default_rng(51)
+    b, hq, hkv, d, S, L = 3, 8, 2, 64, 200, 192
+    q = rng.standard_normal((b, hq, d)).astype(np.float32)
+    k = rng.standard_normal((b, S, hkv, d)).astype(np.float32)
+    v = rng.standard_normal((b, S, hkv, d)).astype(np.float32)
+    scale = 0.125
+    out = torch.empty((b, hq, d), device=DEV)
+    P.batched_decode_attention_f32(t(q), t(k), t(v), out, b, hq, hkv, d, S, L, scale)
+    ref = oracle.batched_decode_attention(q, k, v, L, scale)
+    assert_close(out.cpu().numpy(), ref, 1e-4, 1e-5)
+    splits, bkv = 3, 32
+    pa = torch.empty((b, hq, splits, d), device=DEV)
+    pm = torch.empty((b, hq, splits), device=DEV)
+    ps = torch.empty((b, hq, splits), device=DEV)
+    P.batched_flash_decode_attn_phase1_f32(t(q), t(k), t(v), pa, pm, ps, b, hq, hkv, d, S, L, splits, scale, bkv)
+    for i in range(b):
+        ra, rm, rs = oracle.flash_decode_phase1(q[i], k[i], v[i], hkv, L, splits, scale, bkv)
+        # the partials are un-normalised against each split's own max: compare after the merge
+        assert_close((pa[i].cpu().numpy() * np.exp(pm[i].cpu().numpy())[..., None]),
+                     ra * np.exp(rm)[..., None], 1e-3, 1e-4)
+    o2 = torch.empty((b, hq, d), device=DEV)
+    P.flash_decode_attn_phase2_f32(pa, pm, ps, o2, b * hq, d, splits)
+    assert_close(o2.cpu().numpy(), ref, 1e-4, 1e-5)
+    # single-sequence phase 1 + the oracle's phase 2
+    P.flash_decode_attn_phase1_f32(t(q[0]), t(k[0]), t(v[0]), pa[0], pm[0], ps[0], hq, hkv, d, L, splits, scale, bkv)
+    comb = oracle.flash_decode_phase2(pa[0].cpu().numpy(), pm[0].cpu().numpy(), ps[0].cpu().numpy())
+    assert_close(comb, ref[0], 1e-4, 1e-5)

@@ -1,0 +1,136 @@
+"""W4A16 GEMM (GPTQ, symmetric GPTQ, AWQ), dequant and unpack through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close, golden
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def t(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def make_case(oracle, fmt, m, k, n, g, seed, sym=False):
+    rng = np.random.default_rng(seed)
+    nib = rng.integers(0, 16, (k, n), dtype=np.int32)
+    zer = rng.integers(0, 16, (k // g, n), dtype=np.int32)
+    sc = rng.uniform(0.002, 0.02, (k // g, n)).astype(np.float16)
+    a = rng.standard_normal((m, k)).astype(np.float16)
+    if fmt == "gptq":
+        qw = oracle.pack_gptq_qweight(nib)
+        qz = None if sym else oracle.pack_rowpacked_straight(zer)
+    else:
+        qw, qz = oracle.pack_awq(nib), oracle.pack_awq(zer)
+    return a, qw, sc, qz
+
+
+def ref_gemm(oracle, fmt, a, qw, sc, qz, g):
+    if fmt == "gptq":
+        return oracle.w4a16_gptq_gemm(a, qw, sc, qz, g, zero_offset=1)
+    return oracle.awq_gemm_int4(a, qw, sc, qz, g)
+
+
+def run_gemm(P, fmt, a, qw, sc, qz, g):
+    if fmt == "gptq":
+        return P.gptq_gemm(t(a), t(qw), t(sc), None if qz is None else t(qz), g)
+    return P.awq_gemm(t(a), t(qw), t(sc), t(qz), g)
+
+
+def test_unpack_bit_exact(P, oracle):
+    rng = np.random.default_rng(11)
+    for words in (rng.integers(0, 2 ** 32, (64, 48), dtype=np.uint64).astype(np.uint32),
+                  np.full((16, 8), 0x76543210, dtype=np.uint32),
+                  np.full((8, 8), 0xF0000000, dtype=np.uint32)):
+        w = words.view(np.int32)
+        r, c = w.shape
+        out = torch.empty((r * 8, c), dtype=torch.int8, device=DEV)
+        P.b200k_unpack_gptq_qweight(t(w), out, r * 8, c)
+        assert (out.cpu().numpy() == oracle.unpack_gptq_qweight(w)).all()
+        out = torch.empty((r, c * 8), dtype=torch.int8, device=DEV)
+        P.b200k_unpack_gptq_qzeros(t(w), out, r, c * 8, 1)
+        assert (out.cpu().numpy() == oracle.unpack_rowpacked_straight(w) + 1).all()
+        P.b200k_unpack_awq(t(w), out, r, c * 8)
+        assert (out.cpu().numpy() == oracle.unpack_awq(w)).all()
+
+
+def test_dequant_kernels(P, oracle):
+    a, qw, sc, qz = make_case(oracle, "gptq", 1, 256, 72, 128, 12)
+    out = torch.empty((72, 256), dtype=torch.float16, device=DEV)
+    P.dequant_int4_to_fp16(t(qw), t(sc), t(qz), out, 256, 72, 128, 9)
+    assert (out.cpu().numpy() == oracle.dequant_int4_to_fp16(qw, sc, qz, 128)).all()
+    P.dequant_int4_sym_to_fp16(t(qw), t(sc), out, 256, 72, 128)
+    assert (out.cpu().numpy() == oracle.dequant_int4_sym_to_fp16(qw, sc, 128)).all()
+
+
+SHAPES = [
+    # (m, k, n, g)
+    (1, 128, 8, 128), (1, 4096, 4096, 128), (1, 512, 264, 64), (1, 14336, 512, 128),
+    (2, 256, 72, 128), (3, 512, 136, 128), (16, 4096, 512, 128), (17, 1024, 256, 128),
+    (64, 1024, 384, 128), (128, 512, 256, 128), (130, 256, 264, 32),
+]
+
+
+@pytest.mark.parametrize("fmt", ["gptq", "awq"])
+@pytest.mark.parametrize("m,k,n,g", SHAPES)
+def test_gemm_vs_oracle(P, oracle, fmt, m, k, n, g):
+    a, qw, sc, qz = make_case(oracle, fmt, m, k, n, g, seed=m * 7 + k + n)
+    c = run_gemm(P, fmt, a, qw, sc, qz, g)
+    assert_close(c.float().cpu().numpy(), ref_gemm(oracle, fmt, a, qw, sc, qz, g), what=f"{fmt} {m}x{k}x{n}")
+    c2 = run_gemm(P, fmt, a, qw, sc, qz, g)
+    assert torch.equal(c, c2), "two runs differ"
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 4096, 4096), (16, 4096, 512), (5, 256, 72)])
+def test_gptq_sym_equals_stored_seven(P, oracle, m, k, n):
+    a, qw, sc, _ = make_case(oracle, "gptq", m, k, n, 128, seed=99, sym=True)
+    qz7 = np.full((k // 128, n // 8), 0x77777777, dtype=np.int32)
+    c_sym = run_gemm(P, "gptq", a, qw, sc, None, 128)
+    c_7 = run_gemm(P, "gptq", a, qw, sc, qz7, 128)
+    assert torch.equal(c_sym, c_7)
+    assert_close(c_sym.float().cpu().numpy(), oracle.w4a16_gptq_gemm(a, qw, sc, None, 128))
+
+
+def test_gemm_strided_operands(P, oracle):
+    # transposed A and a C with a row pitch: the strided family
+    a, qw, sc, qz = make_case(oracle, "gptq", 6, 256, 72, 128, seed=5)
+    at = t(np.ascontiguousarray(a.T)).t()            # [6,256] view with strides (1, 6)
+    cbuf = torch.full((6, 100), 9.0, dtype=torch.float16, device=DEV)
+    c = cbuf[:, :72]
+    qwg, scg, qzg = t(qw), t(sc), t(qz)
+    P.w4a16_gptq_gemm_f16(at, qwg, scg, qzg, c, 6, 72, 256, 128, at.stride(0), at.stride(1), qwg.stride(0),
+                          qwg.stride(1), scg.stride(0), scg.stride(1), qzg.stride(0), qzg.stride(1), c.stride(0),
+                          c.stride(1))
+    assert_close(c.float().cpu().numpy(), oracle.w4a16_gptq_gemm(a, qw, sc, qz, 128))
+    assert (cbuf[:, 72:] == 9.0).all()
+
+
+def test_gemm_linearity_full_size(P, oracle):
+    # size-independent property at a Llama shape: C(a1 + a2) == C(a1) + C(a2) within fp16 rounding
+    rng = np.random.default_rng(21)
+    k, n, g = 4096, 6144, 128
+    qw = t(rng.integers(-2 ** 31, 2 ** 31, (k // 8, n), dtype=np.int64).astype(np.int32))
+    sc = t(rng.uniform(0.002, 0.02, (k // g, n)).astype(np.float16))
+    qz = t(rng.integers(-2 ** 31, 2 ** 31, (k // g, n // 8), dtype=np.int64).astype(np.int32))
+    for m in (1, 16):
+        a1 = torch.randn((m, k), device=DEV).half()
+        a2 = torch.randn((m, k), device=DEV).half()
+        s = (a1.float() + a2.float()).half()
+        c1 = P.gptq_gemm(a1, qw, sc, qz, g).float()
+        c2 = P.gptq_gemm(a2, qw, sc, qz, g).float()
+        cs = P.gptq_gemm(s, qw, sc, qz, g).float()
+        err = (cs - (c1 + c2)).abs()
+        assert (err <= 3e-2 + 1e-2 * (c1 + c2).abs()).all(), float(err.max())
+
+
+def test_golden_gemm(P):
+    g = golden("gptq_gemm")
+    c = P.gptq_gemm(t(g["a"]), t(g["qweight"]), t(g["scales"]), t(g["qzeros"]), 128)
+    assert_close(c.float().cpu().numpy(), g["c"])
+    c = P.gptq_gemm(t(g["a"]), t(g["qweight"]), t(g["scales"]), None, 128)
+    assert_close(c.float().cpu().numpy(), g["c_sym"])
+    w = golden("awq_gemm")
+    c = P.awq_gemm(t(w["a"]), t(w["qweight"]), t(w["scales"]), t(w["qzeros"]), 128)
+    assert_close(c.float().cpu().numpy(), w["c"])

@@ -1,0 +1,502 @@
+// W4A16 int4 GEMM: C-ABI entry points, dispatch between the kernel families, the
+// strided CUDA-core family (any strides, any M), the split-K GEMV family (M = 1),
+// the full-matrix dequant kernels and the bit-exact unpack probes.
+#include <cooperative_groups.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "gemm.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace b200k {
+
+bool gemm_layout_is_canonical(const GemmArgs &g) {
+    if (g.s_ak != 1 || g.s_qwn != 1 || g.s_sn != 1 || g.s_cn != 1) return false;
+    if (g.qzeros && g.s_qzn != 1) return false;
+    if (!aligned16(g.a) || !aligned16(g.qweight) || !aligned16(g.scales) || !aligned16(g.c)) return false;
+    if (g.qzeros && !aligned16(g.qzeros)) return false;
+    if (g.s_am % 8 || g.s_qwk % 4 || g.s_sk % 8 || g.s_cm % 8) return false;
+    if (g.qzeros && g.s_qzk % 4) return false;
+    return true;
+}
+
+// ---------------------------------------------------------------------------
+// strided family: one thread per output column, up to 8 rows of A per pass.
+// Follows the reference arithmetic literally: integer nibble - zero, fp32 product
+// with the scale, rounded to fp16, fp32 accumulate.
+// ---------------------------------------------------------------------------
+template <int FMT>
+__global__ void __launch_bounds__(128)
+gemm_strided_kernel(GemmArgs g) {
+    const int n = blockIdx.x * 128 + threadIdx.x;
+    const int m0 = blockIdx.y * 8;
+    if (n >= g.n) return;
+    const int rows = min(8, g.m - m0);
+    float acc[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) acc[r] = 0.f;
+    float scale = 0.f;
+    int zero = 8;
+    for (int k = 0; k < g.k; ++k) {
+        if (k % g.group == 0) {
+            const int grp = k / g.group;
+            scale = __half2float(g.scales[(long)grp * g.s_sk + (long)n * g.s_sn]);
+            if (g.qzeros) {
+                const uint32_t zw = (uint32_t)g.qzeros[(long)grp * g.s_qzk + (long)(n / 8) * g.s_qzn];
+                const int slot = FMT == FMT_AWQ ? awq_slot(n % 8) : n % 8;
+                zero = (int)((zw >> (4 * slot)) & 15u) + g.zero_offset;
+            }
+        }
+        int q;
+        if (FMT == FMT_GPTQ) {
+            const uint32_t w = (uint32_t)g.qweight[(long)(k / 8) * g.s_qwk + (long)n * g.s_qwn];
+            q = (int)((w >> (4 * (k % 8))) & 15u);
+        } else {
+            const uint32_t w = (uint32_t)g.qweight[(long)k * g.s_qwk + (long)(n / 8) * g.s_qwn];
+            q = (int)((w >> (4 * awq_slot(n % 8))) & 15u);
+        }
+        const float wv = __half2float(__float2half_rn((float)(q - zero) * scale));
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            if (r < rows) acc[r] += __half2float(g.a[(long)(m0 + r) * g.s_am + (long)k * g.s_ak]) * wv;
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+        if (r < rows) g.c[(long)(m0 + r) * g.s_cm + (long)n * g.s_cn] = __float2half_rn(acc[r]);
+}
+
+int gemm_strided_launch(const GemmArgs &g) {
+    dim3 grid(ceil_div(g.n, 128), ceil_div(g.m, 8));
+    if (g.format == FMT_GPTQ)
+        gemm_strided_kernel<FMT_GPTQ><<<grid, 128, 0, g.stream>>>(g);
+    else
+        gemm_strided_kernel<FMT_AWQ><<<grid, 128, 0, g.stream>>>(g);
+    return launch_status("w4a16 gemm (strided)");
+}
+
+// ---------------------------------------------------------------------------
+// GEMV family (M = 1): HBM-bound.  A cluster of KSPLIT CTAs shares one block of
+// columns and splits K by quantisation group; every warp streams whole groups
+// with 128-bit loads, multiplies in half2 against the activation vector held in
+// shared memory, flushes to fp32 once per packed row, applies the group scale in
+// fp32, and the cluster reduces through distributed shared memory in a fixed
+// order (deterministic, no scratch memory, no atomics).
+//
+//   GPTQ: a thread owns 4 adjacent columns (one uint4 = 4 words = 4 cols x 8 k).
+//   AWQ : a thread owns 8 adjacent columns (one word  = 8 cols x 1 k).
+// ---------------------------------------------------------------------------
+constexpr int GEMV_THREADS = 256;
+constexpr int GEMV_WARPS = GEMV_THREADS / 32;
+
+// x permuted per 8-group to (x0,x4,x1,x5,x2,x6,x3,x7): the order nib_lo/nib_hi pair up.
+__device__ __forceinline__ void stage_x_gptq(const __half *x, __half *xs, int k) {
+    for (int i = threadIdx.x; i < k / 8; i += blockDim.x) {
+        const uint4 u = *reinterpret_cast<const uint4 *>(x + i * 8);
+        uint4 p;
+        p.x = __byte_perm(u.x, u.z, 0x5410);  // (x0, x4)
+        p.y = __byte_perm(u.x, u.z, 0x7632);  // (x1, x5)
+        p.z = __byte_perm(u.y, u.w, 0x5410);  // (x2, x6)
+        p.w = __byte_perm(u.y, u.w, 0x7632);  // (x3, x7)
+        *reinterpret_cast<uint4 *>(xs + i * 8) = p;
+    }
+}
+
+__global__ void __launch_bounds__(GEMV_THREADS)
+gemv_gptq_kernel(GemmArgs g, int ksplit) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __half *xs = reinterpret_cast<__half *>(smem_raw);                        // [K] permuted
+    float *red = reinterpret_cast<float *>(smem_raw + (size_t)g.k * 2);      // [GEMV_WARPS/2][256]
+    cg::cluster_group cluster = cg::this_cluster();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int cw = warp & 1, kw = warp >> 1;         // 2 column-warps x 4 k-warps
+    constexpr int KW = GEMV_WARPS / 2;
+    const int col = blockIdx.x * 256 + cw * 128 + lane * 4;
+    const int kslot = blockIdx.y * KW + kw, kslots = ksplit * KW;
+    const int groups = g.k / g.group, rows_per_group = g.group / 8;
+
+    stage_x_gptq(g.a, xs, g.k);
+    __syncthreads();
+
+    float tot[4] = {0.f, 0.f, 0.f, 0.f};
+    if (col < g.n) {
+        for (int grp = kslot; grp < groups; grp += kslots) {
+            // scales and zero-points of the 4 columns for this group
+            const uint2 su = *reinterpret_cast<const uint2 *>(g.scales + (long)grp * g.s_sk + col);
+            const float2 s01 = h2_to_f2(su.x), s23 = h2_to_f2(su.y);
+            __half2 zlo[4], zhi[4];
+            if (g.qzeros) {
+                const uint32_t zw = (uint32_t)g.qzeros[(long)grp * g.s_qzk + col / 8] >> (4 * (col % 8));
+#pragma unroll
+                for (int c = 0; c < 4; ++c) zero_magic((int)((zw >> (4 * c)) & 15u) + g.zero_offset, zlo[c], zhi[c]);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) zero_magic(8, zlo[c], zhi[c]);
+            }
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            const int r0 = grp * rows_per_group;
+            const int32_t *wp = g.qweight + (long)r0 * g.s_qwk + col;
+#pragma unroll 4
+            for (int r = 0; r < rows_per_group; ++r) {
+                const uint4 w4 = ldg_nc_v4(wp + (long)r * g.s_qwk);
+                const uint4 xv = *reinterpret_cast<const uint4 *>(xs + (r0 + r) * 8);
+                const __half2 x04 = u2h2(xv.x), x15 = u2h2(xv.y), x26 = u2h2(xv.z), x37 = u2h2(xv.w);
+                const uint32_t ws[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint32_t w = ws[c], w8 = w >> 8;
+                    __half2 s = __hmul2(__hsub2(u2h2(nib_lo(w)), zlo[c]), x04);
+                    s = __hfma2(__hsub2(u2h2(nib_hi(w)), zhi[c]), x15, s);
+                    s = __hfma2(__hsub2(u2h2(nib_lo(w8)), zlo[c]), x26, s);
+                    s = __hfma2(__hsub2(u2h2(nib_hi(w8)), zhi[c]), x37, s);
+                    const float2 f = __half22float2(s);
+                    acc[c] += f.x + f.y;
+                }
+            }
+            tot[0] += acc[0] * s01.x;
+            tot[1] += acc[1] * s01.y;
+            tot[2] += acc[2] * s23.x;
+            tot[3] += acc[3] * s23.y;
+        }
+    }
+    // reduce the KW k-warps of this CTA (fixed order), then the cluster's CTAs
+    float4 *red4 = reinterpret_cast<float4 *>(red);
+    if (kw > 0) red4[(kw - 1) * 64 + cw * 32 + lane] = make_float4(tot[0], tot[1], tot[2], tot[3]);
+    __syncthreads();
+    if (kw == 0) {
+#pragma unroll
+        for (int j = 0; j < KW - 1; ++j) {
+            const float4 o = red4[j * 64 + cw * 32 + lane];
+            tot[0] += o.x; tot[1] += o.y; tot[2] += o.z; tot[3] += o.w;
+        }
+    }
+    __syncthreads();
+    if (kw == 0) red4[cw * 32 + lane] = make_float4(tot[0], tot[1], tot[2], tot[3]);
+    cluster.sync();
+    if (cluster.block_rank() == 0 && kw == 0 && col < g.n) {
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < ksplit; ++r) {
+            const float4 *peer = cluster.map_shared_rank(red4, r);
+            const float4 o = peer[cw * 32 + lane];
+            sum.x += o.x; sum.y += o.y; sum.z += o.z; sum.w += o.w;
+        }
+        uint2 o;
+        o.x = f2_to_h2(sum.x, sum.y);
+        o.y = f2_to_h2(sum.z, sum.w);
+        *reinterpret_cast<uint2 *>(g.c + col) = o;
+    }
+    cluster.sync();  // peers keep their shared memory alive until rank 0 has read it
+}
+
+__global__ void __launch_bounds__(GEMV_THREADS)
+gemv_awq_kernel(GemmArgs g, int ksplit) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __half *xs = reinterpret_cast<__half *>(smem_raw);                        // [K]
+    float *red = reinterpret_cast<float *>(smem_raw + (size_t)g.k * 2);      // [GEMV_WARPS][256]
+    cg::cluster_group cluster = cg::this_cluster();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int col = blockIdx.x * 256 + lane * 8;      // 8 columns per thread, 256 per warp
+    const int kslot = blockIdx.y * GEMV_WARPS + warp, kslots = ksplit * GEMV_WARPS;
+    const int groups = g.k / g.group;
+
+    for (int i = threadIdx.x; i < g.k / 8; i += blockDim.x)
+        *reinterpret_cast<uint4 *>(xs + i * 8) = *reinterpret_cast<const uint4 *>(g.a + i * 8);
+    __syncthreads();
+
+    float tot[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) tot[c] = 0.f;
+    if (col < g.n) {
+        for (int grp = kslot; grp < groups; grp += kslots) {
+            const uint4 su = *reinterpret_cast<const uint4 *>(g.scales + (long)grp * g.s_sk + col);
+            const uint32_t zw = (uint32_t)g.qzeros[(long)grp * g.s_qzk + col / 8];
+            // zero-points as half2 pairs in the word's own pair order, already in magic form:
+            //   pair 0 = nibbles (0,4) = columns (0,1); pair 1 = (1,5) = (2,3); pair 2 = (2,6) = (4,5); pair 3 = (3,7) = (6,7)
+            const uint32_t z8 = zw >> 8;
+            const __half2 zl0 = u2h2(nib_lo(zw)), zh1 = u2h2(nib_hi(zw)), zl2 = u2h2(nib_lo(z8)), zh3 = u2h2(nib_hi(z8));
+            float acc[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) acc[c] = 0.f;
+            const int k0 = grp * g.group;
+            const int32_t *wp = g.qweight + (long)k0 * g.s_qwk + col / 8;
+            for (int kk = 0; kk < g.group; kk += 8) {
+                uint32_t w[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) w[j] = (uint32_t)__ldg(wp + (long)(kk + j) * g.s_qwk);
+                const uint4 xv = *reinterpret_cast<const uint4 *>(xs + k0 + kk);
+                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+                __half2 s0 = __float2half2_rn(0.f), s1 = s0, s2 = s0, s3 = s0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const __half2 xp = u2h2(xw[j >> 1]);
+                    const __half2 xb = (j & 1) ? __high2half2(xp) : __low2half2(xp);
+                    const uint32_t wj = w[j], w8 = wj >> 8;
+                    s0 = __hfma2(__hsub2(u2h2(nib_lo(wj)), zl0), xb, s0);
+                    s1 = __hfma2(__hsub2(u2h2(nib_hi(wj)), zh1), xb, s1);
+                    s2 = __hfma2(__hsub2(u2h2(nib_lo(w8)), zl2), xb, s2);
+                    s3 = __hfma2(__hsub2(u2h2(nib_hi(w8)), zh3), xb, s3);
+                }
+                const float2 f0 = __half22float2(s0), f1 = __half22float2(s1), f2 = __half22float2(s2), f3 = __half22float2(s3);
+                acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+                acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+            }
+            const float2 sa = h2_to_f2(su.x), sb = h2_to_f2(su.y), sc = h2_to_f2(su.z), sd = h2_to_f2(su.w);
+            tot[0] += acc[0] * sa.x; tot[1] += acc[1] * sa.y; tot[2] += acc[2] * sb.x; tot[3] += acc[3] * sb.y;
+            tot[4] += acc[4] * sc.x; tot[5] += acc[5] * sc.y; tot[6] += acc[6] * sd.x; tot[7] += acc[7] * sd.y;
+        }
+    }
+    float4 *red4 = reinterpret_cast<float4 *>(red);  // [warp][lane][2] float4
+    if (warp > 0) {
+        red4[((warp - 1) * 32 + lane) * 2 + 0] = make_float4(tot[0], tot[1], tot[2], tot[3]);
+        red4[((warp - 1) * 32 + lane) * 2 + 1] = make_float4(tot[4], tot[5], tot[6], tot[7]);
+    }
+    __syncthreads();
+    if (warp == 0) {
+        for (int j = 0; j < GEMV_WARPS - 1; ++j) {
+            const float4 a = red4[(j * 32 + lane) * 2 + 0], b = red4[(j * 32 + lane) * 2 + 1];
+            tot[0] += a.x; tot[1] += a.y; tot[2] += a.z; tot[3] += a.w;
+            tot[4] += b.x; tot[5] += b.y; tot[6] += b.z; tot[7] += b.w;
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {
+        red4[lane * 2 + 0] = make_float4(tot[0], tot[1], tot[2], tot[3]);
+        red4[lane * 2 + 1] = make_float4(tot[4], tot[5], tot[6], tot[7]);
+    }
+    cluster.sync();
+    if (cluster.block_rank() == 0 && warp == 0 && col < g.n) {
+        float s[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) s[c] = 0.f;
+        for (int r = 0; r < ksplit; ++r) {
+            const float4 *peer = cluster.map_shared_rank(red4, r);
+            const float4 a = peer[lane * 2 + 0], b = peer[lane * 2 + 1];
+            s[0] += a.x; s[1] += a.y; s[2] += a.z; s[3] += a.w;
+            s[4] += b.x; s[5] += b.y; s[6] += b.z; s[7] += b.w;
+        }
+        uint4 o;
+        o.x = f2_to_h2(s[0], s[1]); o.y = f2_to_h2(s[2], s[3]);
+        o.z = f2_to_h2(s[4], s[5]); o.w = f2_to_h2(s[6], s[7]);
+        *reinterpret_cast<uint4 *>(g.c + col) = o;
+    }
+    cluster.sync();
+}
+
+int gemv_launch(const GemmArgs &g) {
+    const int groups = g.k / g.group;
+    const int colblocks = ceil_div(g.n, 256);
+    const int kwarps = g.format == FMT_GPTQ ? GEMV_WARPS / 2 : GEMV_WARPS;
+    // enough CTAs for ~2 per SM, cluster size a power of two <= 8, no warp without a group
+    int ksplit = 1;
+    while (ksplit < 8 && colblocks * ksplit < 2 * sm_count() && ksplit * 2 * kwarps <= groups) ksplit *= 2;
+    const size_t smem = (size_t)g.k * 2 + (size_t)GEMV_WARPS * 256 * sizeof(float);
+    auto kern = g.format == FMT_GPTQ ? gemv_gptq_kernel : gemv_awq_kernel;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail((int)e, "gemv: shared memory %zu: %s", smem, cudaGetErrorString(e));
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(colblocks, ksplit, 1);
+    cfg.blockDim = dim3(GEMV_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = g.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = ksplit;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, g, ksplit);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail((int)e, "gemv launch: %s", cudaGetErrorString(e));
+    }
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// full-matrix dequant (column-major output) and unpack probes
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+dequant_int4_kernel(const int32_t *__restrict__ qw, const __half *__restrict__ scales,
+                    const int32_t *__restrict__ qz, __half *__restrict__ out, int k_dim, int n_dim, int group,
+                    int n_div_8) {
+    const int col = blockIdx.x * blockDim.x + threadIdx.x;
+    const int prow = blockIdx.y;
+    if (col >= n_dim) return;
+    const int grp = prow * 8 / group;
+    const uint32_t w = (uint32_t)qw[(long)prow * n_dim + col];
+    const float s = __half2float(scales[(long)grp * n_dim + col]);
+    int zero = 8;
+    if (qz) zero = (int)(((uint32_t)qz[(long)grp * n_div_8 + (col >> 3)] >> ((col & 7) << 2)) & 15u);
+    __align__(16) __half o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = __float2half_rn((float)((int)((w >> (4 * i)) & 15u) - zero) * s);
+    __half *dst = out + (long)col * k_dim + prow * 8;
+    if ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+        *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(o);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dst[i] = o[i];
+    }
+}
+
+// mode 0: GPTQ qweight [R/8,N] -> [R,N]; mode 1: straight row-packed [R,N/8] -> [R,N] (+add);
+// mode 2: AWQ row-packed [R,N/8] -> [R,N]
+__global__ void __launch_bounds__(256)
+unpack_kernel(const int32_t *__restrict__ in, int8_t *__restrict__ out, int rows, int n, int mode, int add) {
+    const long total = (long)rows * n;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const int r = (int)(i / n), c = (int)(i - (long)r * n);
+        uint32_t w;
+        int slot;
+        if (mode == 0) {
+            w = (uint32_t)in[(long)(r / 8) * n + c];
+            slot = r % 8;
+        } else {
+            w = (uint32_t)in[(long)r * (n / 8) + c / 8];
+            slot = mode == 2 ? awq_slot(c % 8) : c % 8;
+        }
+        out[i] = (int8_t)(((w >> (4 * slot)) & 15u) + add);
+    }
+}
+
+static int unpack_launch(const char *name, const int32_t *in, int8_t *out, int rows, int n, int mode, int add,
+                         cudaStream_t st) {
+    B200K_REQUIRE(in && out, B200K_E_NULL, "%s: NULL pointer", name);
+    B200K_REQUIRE(rows >= 0 && n >= 0 && n % 8 == 0 && (mode != 0 || rows % 8 == 0), B200K_E_SHAPE,
+                  "%s: rows %d, n %d", name, rows, n);
+    const long total = (long)rows * n;
+    if (total == 0) return 0;
+    long blocks = (total + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    unpack_kernel<<<(int)blocks, 256, 0, st>>>(in, out, rows, n, mode, add);
+    return launch_status(name);
+}
+
+// ---------------------------------------------------------------------------
+// validation + dispatch
+// ---------------------------------------------------------------------------
+static int gemm_dispatch(const char *name, GemmArgs g, bool own_ws) {
+    B200K_REQUIRE(g.a && g.qweight && g.scales && g.c, B200K_E_NULL, "%s: NULL pointer", name);
+    B200K_REQUIRE(g.format == FMT_GPTQ || g.qzeros, B200K_E_NULL, "%s: qzeros is NULL", name);
+    B200K_REQUIRE(g.m >= 0 && g.n > 0 && g.k > 0, B200K_E_SHAPE, "%s: M %d, N %d, K %d", name, g.m, g.n, g.k);
+    B200K_REQUIRE(g.group > 0 && g.group % 8 == 0 && g.k % g.group == 0 && g.n % 8 == 0, B200K_E_SHAPE,
+                  "%s: need group_size %% 8 == 0, K %% group_size == 0, N %% 8 == 0 (K %d, N %d, group %d)", name,
+                  g.k, g.n, g.group);
+    if (g.m == 0) return 0;
+    const bool canon = gemm_layout_is_canonical(g);
+    const char *force = getenv("B200K_GEMM_PATH");  // tuning/testing override: strided | gemv | tc
+    if (force && !strcmp(force, "strided")) return gemm_strided_launch(g);
+    if (canon && g.m == 1 && g.k <= 65536 && !(force && !strcmp(force, "tc"))) return gemv_launch(g);
+    if (canon) {
+        if (!g.ws && own_ws) {
+            int rc = default_workspace(&g.ws, &g.ws_bytes);
+            if (rc) return rc;
+        }
+        int rc = gemm_tc_launch(g);
+        if (rc != 1) return rc;
+    }
+    return gemm_strided_launch(g);
+}
+
+}  // namespace b200k
+
+using namespace b200k;
+
+#define GEMM_ARGS_FILL(FMT, ZO)                                                                       \
+    GemmArgs g;                                                                                       \
+    g.a = (const __half *)a; g.qweight = qweight; g.scales = (const __half *)scales;                  \
+    g.c = (__half *)c; g.m = m_size; g.n = n_size; g.k = k_size; g.group = group_size;                \
+    g.s_am = stride_am; g.s_ak = stride_ak; g.s_qwk = stride_qwk; g.s_qwn = stride_qwn;               \
+    g.s_sk = stride_sk; g.s_sn = stride_sn; g.s_cm = stride_cm; g.s_cn = stride_cn;                   \
+    g.format = FMT; g.zero_offset = ZO; g.stream = to_stream(stream);
+
+extern "C" int w4a16_gptq_gemm_f16_ws(const b200k_half *a, const int32_t *qweight, const b200k_half *scales,
+                                      const int32_t *qzeros, b200k_half *c, int m_size, int n_size, int k_size,
+                                      int group_size, int stride_am, int stride_ak, int stride_qwk, int stride_qwn,
+                                      int stride_sk, int stride_sn, int stride_qzk, int stride_qzn, int stride_cm,
+                                      int stride_cn, void *workspace, size_t workspace_bytes, b200k_stream stream) {
+    GEMM_ARGS_FILL(FMT_GPTQ, 1)
+    B200K_REQUIRE(qzeros, B200K_E_NULL, "w4a16_gptq_gemm_f16: qzeros is NULL (use w4a16_gptq_gemm_sym_f16)");
+    g.qzeros = qzeros; g.s_qzk = stride_qzk; g.s_qzn = stride_qzn;
+    g.ws = workspace; g.ws_bytes = workspace_bytes;
+    return gemm_dispatch("w4a16_gptq_gemm_f16", g, workspace == nullptr);
+}
+extern "C" int w4a16_gptq_gemm_f16(const b200k_half *a, const int32_t *qweight, const b200k_half *scales,
+                                   const int32_t *qzeros, b200k_half *c, int m_size, int n_size, int k_size,
+                                   int group_size, int stride_am, int stride_ak, int stride_qwk, int stride_qwn,
+                                   int stride_sk, int stride_sn, int stride_qzk, int stride_qzn, int stride_cm,
+                                   int stride_cn, b200k_stream stream) {
+    return w4a16_gptq_gemm_f16_ws(a, qweight, scales, qzeros, c, m_size, n_size, k_size, group_size, stride_am,
+                                  stride_ak, stride_qwk, stride_qwn, stride_sk, stride_sn, stride_qzk, stride_qzn,
+                                  stride_cm, stride_cn, nullptr, 0, stream);
+}
+extern "C" int w4a16_gptq_gemm_sym_f16(const b200k_half *a, const int32_t *qweight, const b200k_half *scales,
+                                       b200k_half *c, int m_size, int n_size, int k_size, int group_size,
+                                       int stride_am, int stride_ak, int stride_qwk, int stride_qwn, int stride_sk,
+                                       int stride_sn, int stride_cm, int stride_cn, b200k_stream stream) {
+    GEMM_ARGS_FILL(FMT_GPTQ, 0)
+    g.qzeros = nullptr; g.s_qzk = 0; g.s_qzn = 1;
+    g.ws = nullptr; g.ws_bytes = 0;
+    return gemm_dispatch("w4a16_gptq_gemm_sym_f16", g, true);
+}
+extern "C" int awq_gemm_int4_f16_ws(const b200k_half *a, const int32_t *qweight, const b200k_half *scales,
+                                    const int32_t *qzeros, b200k_half *c, int m_size, int n_size, int k_size,
+                                    int group_size, int stride_am, int stride_ak, int stride_qwk, int stride_qwn,
+                                    int stride_sk, int stride_sn, int stride_qzk, int stride_qzn, int stride_cm,
+                                    int stride_cn, void *workspace, size_t workspace_bytes, b200k_stream stream) {
+    GEMM_ARGS_FILL(FMT_AWQ, 0)
+    g.qzeros = qzeros; g.s_qzk = stride_qzk; g.s_qzn = stride_qzn;
+    g.ws = workspace; g.ws_bytes = workspace_bytes;
+    return gemm_dispatch("awq_gemm_int4_f16", g, workspace == nullptr);
+}
+extern "C" int awq_gemm_int4_f16(const b200k_half *a, const int32_t *qweight, const b200k_half *scales,
+                                 const int32_t *qzeros, b200k_half *c, int m_size, int n_size, int k_size,
+                                 int group_size, int stride_am, int stride_ak, int stride_qwk, int stride_qwn,
+                                 int stride_sk, int stride_sn, int stride_qzk, int stride_qzn, int stride_cm,
+                                 int stride_cn, b200k_stream stream) {
+    return awq_gemm_int4_f16_ws(a, qweight, scales, qzeros, c, m_size, n_size, k_size, group_size, stride_am, stride_ak,
+                                stride_qwk, stride_qwn, stride_sk, stride_sn, stride_qzk, stride_qzn, stride_cm,
+                                stride_cn, nullptr, 0, stream);
+}
+
+static int dequant_launch(const char *name, const int32_t *qw, const __half *sc, const int32_t *qz, __half *out,
+                          int k_dim, int n_dim, int group, int n_div_8, bool need_qz, cudaStream_t st) {
+    B200K_REQUIRE(qw && sc && out && (!need_qz || qz), B200K_E_NULL, "%s: NULL pointer", name);
+    B200K_REQUIRE(k_dim > 0 && n_dim > 0 && k_dim % 8 == 0 && group > 0 && group % 8 == 0 && k_dim % group == 0,
+                  B200K_E_SHAPE, "%s: K %d, N %d, group %d", name, k_dim, n_dim, group);
+    dim3 grid(ceil_div(n_dim, 256), k_dim / 8);
+    dequant_int4_kernel<<<grid, 256, 0, st>>>(qw, sc, qz, out, k_dim, n_dim, group, n_div_8);
+    return launch_status(name);
+}
+extern "C" int dequant_int4_to_fp16(const int32_t *qweight, const b200k_half *scales, const int32_t *qzeros,
+                                    b200k_half *output, int k_dim, int n_dim, int group_size, int n_div_8,
+                                    b200k_stream stream) {
+    return dequant_launch("dequant_int4_to_fp16", qweight, (const __half *)scales, qzeros, (__half *)output, k_dim,
+                          n_dim, group_size, n_div_8, true, to_stream(stream));
+}
+extern "C" int dequant_int4_sym_to_fp16(const int32_t *qweight, const b200k_half *scales, b200k_half *output,
+                                        int k_dim, int n_dim, int group_size, b200k_stream stream) {
+    return dequant_launch("dequant_int4_sym_to_fp16", qweight, (const __half *)scales, nullptr, (__half *)output,
+                          k_dim, n_dim, group_size, 0, false, to_stream(stream));
+}
+
+extern "C" int b200k_unpack_gptq_qweight(const int32_t *qweight, int8_t *out, int k_dim, int n_dim, b200k_stream s) {
+    return unpack_launch("b200k_unpack_gptq_qweight", qweight, out, k_dim, n_dim, 0, 0, to_stream(s));
+}
+extern "C" int b200k_unpack_gptq_qzeros(const int32_t *qzeros, int8_t *out, int groups, int n_dim, int zero_offset,
+                                        b200k_stream s) {
+    return unpack_launch("b200k_unpack_gptq_qzeros", qzeros, out, groups, n_dim, 1, zero_offset, to_stream(s));
+}
+extern "C" int b200k_unpack_awq(const int32_t *packed, int8_t *out, int rows, int n_dim, b200k_stream s) {
+    return unpack_launch("b200k_unpack_awq", packed, out, rows, n_dim, 2, 0, to_stream(s));
+}
+
+extern "C" size_t b200k_gemm_workspace_bytes(int m, int n, int k) {
+    // counters (64 KiB) + split-K fp32 partials: at most 8 splits of [m, n]
+    (void)k;
+    if (m <= 0 || n <= 0) return 0;
+    return (size_t)65536 + (size_t)8 * (size_t)m * (size_t)n * sizeof(float);
+}

@@ -1,0 +1,67 @@
+// Shared description of one W4A16 GEMM call, handed from the C-ABI entry points to
+// the kernel families (strided CUDA-core, split-K GEMV, tcgen05 tensor-core).
+#pragma once
+#include "common.cuh"
+
+namespace b200k {
+
+enum WeightFormat { FMT_GPTQ = 0, FMT_AWQ = 1 };
+
+struct GemmArgs {
+    const __half *a;
+    const int32_t *qweight;
+    const __half *scales;
+    const int32_t *qzeros;  // nullptr: symmetric zero-point 8 (GPTQ only)
+    __half *c;
+    int m, n, k, group;
+    int s_am, s_ak, s_qwk, s_qwn, s_sk, s_sn, s_qzk, s_qzn, s_cm, s_cn;
+    int format;       // WeightFormat
+    int zero_offset;  // added to the stored zero nibble (GPTQ GEMM: 1, AWQ: 0)
+    void *ws;         // scratch (may be nullptr when the chosen path needs none)
+    size_t ws_bytes;
+    cudaStream_t stream;
+};
+
+// True when every inner stride is 1 and the row strides / pointers allow 16-byte access.
+bool gemm_layout_is_canonical(const GemmArgs &g);
+
+// Kernel families.  Each returns 0 on launch, a B200K_E_* / CUDA code on failure.
+int gemm_strided_launch(const GemmArgs &g);
+int gemv_launch(const GemmArgs &g);
+// Tensor-core path (tcgen05 + TMEM).  Returns 1 when the shape is outside what it
+// covers (the caller then takes another family).
+int gemm_tc_launch(const GemmArgs &g);
+
+// ---- nibble -> fp16 helpers (device) -----------------------------------------
+// For a 32-bit word w holding nibbles n0..n7 (n_i at bits 4i..4i+3):
+//   lo(w)      = (w & 0x000F000F) | 0x64006400  -> half2 (1024+n0, 1024+n4)
+//   hi(w)      = (w & 0x00F000F0) | 0x54005400  -> half2 (  64+n1,   64+n5)
+//   lo(w >> 8), hi(w >> 8)                      -> (n2, n6), (n3, n7)
+// Subtracting (1024+z) resp. (64+z) in fp16 is exact for z in 0..16, so the result
+// is the integer (n - z) with no rounding; one fp16 multiply by the scale then
+// rounds once, the same value as the reference's f32 product rounded to fp16
+// (w4a16_gptq_gemm_typed.rs:256-260): an integer of at most 5 bits times an 11-bit
+// significand is exact in fp32.
+__device__ __forceinline__ uint32_t nib_lo(uint32_t w) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, 0x000F000F, 0x64006400, 0xEA;" : "=r"(r) : "r"(w));
+    return r;
+}
+__device__ __forceinline__ uint32_t nib_hi(uint32_t w) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, 0x00F000F0, 0x54005400, 0xEA;" : "=r"(r) : "r"(w));
+    return r;
+}
+__device__ __forceinline__ __half2 u2h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
+__device__ __forceinline__ uint32_t h22u(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+
+// Magic zero constants for a zero-point z (0..16): (1024+z) and (64+z) in both halves.
+__device__ __forceinline__ void zero_magic(int z, __half2 &zlo, __half2 &zhi) {
+    zlo = __half2half2(__ushort_as_half((unsigned short)(0x6400 + z)));       // 1024 + z, ulp = 1
+    zhi = __half2half2(__float2half_rn(64.0f + (float)z));                    // 64 + z,  exact
+}
+
+// position of column j (0..7) inside an AWQ word (awq_gemm_int4_typed.rs:137-151)
+__host__ __device__ __forceinline__ int awq_slot(int j) { return (j >> 1) + ((j & 1) << 2); }
+
+}  // namespace b200k
