@@ -1,18 +1,22 @@
 // GQA decode attention over a KV cache.
 //
 // Two kernel families:
-//  * attn_split_f16 (head_dim 128, fp16): split-KV flash-decode.  One CTA per
-//    (sequence, kv head, chunk of CH positions) handles ALL q heads of the GQA group,
-//    so every K/V element is read from HBM once.  K/V rows are staged into shared
-//    memory by bulk asynchronous copies (cp.async.bulk, one 256-byte row per copy,
-//    mbarrier transaction counts) in a 4-deep ring; scores are computed one position
-//    per thread pair, the softmax statistics once per chunk, and the P.V product with
-//    16 lanes per row; partial (acc, max, sum) triples go to scratch and the last CTA
-//    of a (sequence, kv head) to arrive merges them (log-sum-exp).  Every mbarrier
-//    wait is bounded and reports through a status word.
+//  * attn_split_f16 (head_dim 128, fp16, GQA group size <= 8): split-KV flash-decode.
+//    One CTA per (sequence, kv head, chunk of positions) serves ALL q heads of the
+//    GQA group, so every K/V element is read from HBM once.  K/V rows are staged into
+//    shared memory by bulk asynchronous copies (cp.async.bulk, one 256-byte row per
+//    copy, mbarrier transaction counts) in a 3-deep ring of 64-position K+V tiles.
+//    The products run on mma.sync m16n8k16 in transposed form (positions fill the 16
+//    MMA rows, the group's q heads the 8 columns): one query token per sequence gives
+//    at most 8 useful rows, far below the 64/128-row tcgen05 tile, and the kernel is
+//    HBM-bound by a wide margin, so the warp-level MMA is the right-sized tool here.
+//    Online softmax state is per warp; the four warps and then the chunks of a
+//    (sequence, kv head) are merged by log-sum-exp, the latter by the last CTA to
+//    arrive.  Every mbarrier wait is bounded and reports through a status word.
 //  * attn_generic (any head_dim <= 256, fp16 or fp32): one CTA per (sequence, q head,
 //    split); backs the f32 entry points and the explicit phase-1 / phase-2 API.
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace b200k {
 
@@ -34,51 +38,16 @@ __device__ __forceinline__ long kv_row_offset(const KvLayout &L, int b, int kvh,
 }
 
 // ---------------------------------------------------------------------------
-// mbarrier + bulk-copy primitives (shared::cta addresses as 32-bit)
-// ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: gives up after ~1 s of SM clock and returns false.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (;;) {
-        for (int i = 0; i < 64; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (clock64() - t0 > 2000000000LL) return false;
-    }
-}
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
-
-// ---------------------------------------------------------------------------
 // split-KV fp16 family
 // ---------------------------------------------------------------------------
 constexpr int AT_D = 128;               // head_dim
-constexpr int AT_THREADS = 128;
+constexpr int AT_THREADS = 128;         // 4 warps; warp w owns rows [16w, 16w+16) of every tile
 constexpr int AT_TILE = 64;             // positions per stage
-constexpr int AT_STAGES = 4;
-constexpr int AT_ROW = AT_D * 2 + 16;   // padded row stride in shared memory (bytes)
-constexpr int AT_MAX_CH = 1024;         // largest chunk (positions)
+constexpr int AT_STAGES = 3;            // each stage holds a K tile and a V tile
+constexpr int AT_HALF_BYTES = AT_TILE * 128;   // one TMA box: 64 rows x 64 dims (128 bytes), 128-byte swizzle
+constexpr int AT_TILE_BYTES = 2 * AT_HALF_BYTES;
+constexpr int AT_MAX_CH = 2048;         // largest chunk (positions)
+constexpr int AT_NH = 8;                // head columns of one MMA (GQA group size <= 8)
 
 struct AttnSplitArgs {
     const __half *q;        // [B, Hq, D]
@@ -86,49 +55,73 @@ struct AttnSplitArgs {
     __half *out;            // [B, Hq, D]
     const int32_t *lens;    // per sequence, or nullptr -> len_scalar
     int len_scalar;
-    int hq, hkv;
-    int chunk;              // positions per CTA, multiple of AT_TILE, <= AT_MAX_CH
+    int hq, hkv, g;         // g = hq / hkv
+    int chunk;              // positions per CTA, multiple of AT_TILE
     float scale_log2e;      // softmax scale * log2(e)
-    KvLayout L;
+    int seq_major;          // tensor-map coordinate order: 0 = (d, pos, head, batch), 1 = (d, head, pos, batch)
+    const int32_t *block_table;  // paged pools: batch coordinate = block_table[pos / block_size], pos -> slot
+    int block_size, box_rows;    // rows per TMA box (64, or the block size of a paged pool when smaller)
     float *ws_acc;          // [B*Hkv*max_chunks, G, D]
     float *ws_ml;           // [B*Hkv*max_chunks, G, 2]  (max, sum)
     int *counters;          // [B*Hkv], zero between launches
     int *status;            // device status word (0 = ok)
 };
 
-template <int G>
 struct AttnSmem {
-    __align__(16) unsigned char stage[AT_STAGES][AT_TILE * AT_ROW];
-    __align__(16) float sp[AT_MAX_CH * G];    // scores, then probabilities, [pos][G]
-    __align__(16) float q[G * AT_D];          // q * scale * log2(e)
-    float red[AT_THREADS / 32][2 * G];
-    float m[G], l[G];
+    __align__(1024) unsigned char kv[AT_STAGES][2][2][AT_HALF_BYTES];   // [stage][K|V][dims 0-63 | 64-127][swizzled rows]
+    float m[AT_THREADS / 32][AT_NH], l[AT_THREADS / 32][AT_NH];
+    float wgt[AT_THREADS / 32][AT_NH], lsum[AT_NH], mfin[AT_NH];
     __align__(8) unsigned long long full[AT_STAGES];
     int abort_flag;
     int is_last;
 };
 
-template <int G>
-__global__ void __launch_bounds__(AT_THREADS)
-attn_split_f16_kernel(AttnSplitArgs A) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    AttnSmem<G> &S = *reinterpret_cast<AttnSmem<G> *>(smem_raw);
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t movm_t(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// The arithmetic runs transposed so that positions, not heads, fill the 16 rows of the
+// MMA:  S^T[pos, head] = K[pos, :] . Q^T[:, head]   (A = K tile as stored, B = Q)
+//       O^T[dim, head] += V^T[dim, pos] . P^T[pos, head]  (A = V tile via ldmatrix.trans,
+//                                                          B = P^T via movmatrix)
+// with up to 8 q heads of one GQA group in the 8 MMA columns.
+__global__ void __launch_bounds__(AT_THREADS, 2)
+attn_split_f16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                      AttnSplitArgs A) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    AttnSmem &S = *reinterpret_cast<AttnSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int chunk_id = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int G = A.g;
     const int len = A.lens ? A.lens[b] : A.len_scalar;
     const int nchunks = (len + A.chunk - 1) / A.chunk;
+    const long out_row0 = ((long)b * A.hq + (long)kvh * G) * AT_D;
     if (len <= 0) {
         // no keys: defined as a zero output row (the reference would divide 0 by 0)
         if (chunk_id == 0)
-            for (int i = tid; i < G * AT_D; i += AT_THREADS)
-                A.out[((long)b * A.hq + kvh * G) * AT_D + i] = __float2half_rn(0.f);
+            for (int i = tid; i < G * AT_D; i += AT_THREADS) A.out[out_row0 + i] = __float2half_rn(0.f);
         return;
     }
     if (chunk_id >= nchunks) return;
     const int p0 = chunk_id * A.chunk;
     const int npos = min(A.chunk, len - p0);
     const int ntiles = (npos + AT_TILE - 1) / AT_TILE;
-    const int total_tiles = 2 * ntiles;  // K tiles then V tiles
 
     if (tid == 0) {
         for (int s = 0; s < AT_STAGES; ++s) mbar_init(smem_u32(&S.full[s]), 1);
@@ -136,161 +129,180 @@ attn_split_f16_kernel(AttnSplitArgs A) {
         S.is_last = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int i = tid; i < G * AT_D; i += AT_THREADS)
-        S.q[i] = __half2float(A.q[((long)b * A.hq + kvh * G) * AT_D + i]) * A.scale_log2e;
     __syncthreads();
 
-    // producer: warp 0 issues the row copies of tile t into stage t % STAGES
+    // producer: one thread issues the four TMA boxes of tile t (K and V, two 64-dim halves each)
+    // into stage t % STAGES.  A box always carries 64 rows: rows past the sequence end hold
+    // whatever the cache holds there (or zeros past the tensor's extent); the consumer masks
+    // their scores and clears their V rows.
     auto issue_tile = [&](int t) {
-        const bool is_v = t >= ntiles;
-        const int tt = is_v ? t - ntiles : t;
-        const int rows = min(AT_TILE, npos - tt * AT_TILE);
-        const uint32_t bar = smem_u32(&S.full[t % AT_STAGES]);
-        if (lane == 0) mbar_expect_tx(bar, (uint32_t)rows * AT_D * 2);
-        __syncwarp();
-        const __half *base = is_v ? A.v : A.k;
-        for (int r = lane; r < rows; r += 32) {
-            const long off = kv_row_offset(A.L, b, kvh, p0 + tt * AT_TILE + r);
-            bulk_g2s(smem_u32(&S.stage[t % AT_STAGES][r * AT_ROW]), base + off, AT_D * 2, bar);
+        const int st = t % AT_STAGES;
+        const uint32_t bar = smem_u32(&S.full[st]);
+        mbar_expect_tx(bar, 2 * AT_TILE_BYTES);
+        for (int r0 = 0; r0 < AT_TILE; r0 += A.box_rows) {
+            int pos = p0 + t * AT_TILE + r0, bc = b;
+            if (A.block_table) {
+                // a box past the sequence end may index past the table: clamp to the last valid block
+                const int lb = min(pos, len - 1) / A.block_size;
+                bc = A.block_table[lb];
+                pos = pos % A.block_size;
+            }
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                const uint32_t kd = smem_u32(&S.kv[st][0][hf][r0 * 128]), vd = smem_u32(&S.kv[st][1][hf][r0 * 128]);
+                if (A.seq_major) {
+                    tma_load_4d(kd, &kmap, hf * 64, kvh, pos, bc, bar);
+                    tma_load_4d(vd, &vmap, hf * 64, kvh, pos, bc, bar);
+                } else {
+                    tma_load_4d(kd, &kmap, hf * 64, pos, kvh, bc, bar);
+                    tma_load_4d(vd, &vmap, hf * 64, pos, kvh, bc, bar);
+                }
+            }
         }
     };
-    if (warp == 0)
-        for (int t = 0; t < min(AT_STAGES, total_tiles); ++t) issue_tile(t);
+    if (tid == 0) {
+        tma_prefetch_desc(&kmap);
+        tma_prefetch_desc(&vmap);
+        for (int t = 0; t < min(AT_STAGES, ntiles); ++t) issue_tile(t);
+    }
 
-    // ---- K phase: thread (h = lane / 16, position = warp * 16 + lane % 16) ----
-    const int kp = warp * 16 + (lane & 15), kh = lane >> 4;
-    int t = 0;
-    for (; t < ntiles; ++t) {
+    // Q as the B operand: column n = head (lane / 4), k = dims 16*ks + 2*(lane%4) + {0,1} and +8
+    uint32_t qf[8][2];
+    {
+        const int h = lane >> 2;
+        const __half *qrow = A.q + out_row0 + (long)h * AT_D + 2 * (lane & 3);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            qf[ks][0] = h < G ? *reinterpret_cast<const uint32_t *>(qrow + ks * 16) : 0u;
+            qf[ks][1] = h < G ? *reinterpret_cast<const uint32_t *>(qrow + ks * 16 + 8) : 0u;
+        }
+    }
+    float oacc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) oacc[i][j] = 0.f;
+    float m0 = -1e30f, m1 = -1e30f, l0 = 0.f, l1 = 0.f;   // heads 2*(lane%4) and +1
+
+    // ldmatrix lane coordinates inside a tile, for this warp's 16 rows: row and 16-byte column
+    const int k_row = warp * 16 + (lane & 15), k_c = lane >> 4;                          // K: A fragment as stored
+    const int v_row = warp * 16 + ((lane >> 4) << 3) + (lane & 7), v_c = (lane >> 3) & 1; // V: A fragment transposed
+
+    for (int t = 0; t < ntiles; ++t) {
         const int st = t % AT_STAGES;
         if (!S.abort_flag && !mbar_wait_bounded(smem_u32(&S.full[st]), (t / AT_STAGES) & 1)) {
             S.abort_flag = 1;
             atomicExch(A.status, 1);
         }
-        float s[G];
+        const int rows_valid = npos - t * AT_TILE;     // < 64 only in the last tile of the sequence
+        if (rows_valid < AT_TILE) {
+            // P = 0 must multiply finite numbers: clear the V rows past the sequence end
+            for (int i = tid; i < (AT_TILE - rows_valid) * 16; i += AT_THREADS) {
+                const int r = rows_valid + (i >> 4), c = i & 15;
+                *reinterpret_cast<uint4 *>(&S.kv[st][1][c >> 3][r * 128 + (c & 7) * 16]) = make_uint4(0, 0, 0, 0);
+            }
+            __syncthreads();
+        }
+        const int row0 = t * AT_TILE + warp * 16;      // first position of this warp's slab (within the chunk)
+        if (row0 < npos) {
+            const uint32_t kb = smem_u32(&S.kv[st][0][0][0]);
+            const uint32_t vb = smem_u32(&S.kv[st][1][0][0]);
+            float s[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int g = 0; g < G; ++g) s[g] = 0.f;
-        const unsigned char *row = &S.stage[st][kp * AT_ROW];
+            for (int ks = 0; ks < 8; ++ks) {
+                uint32_t a0, a1, a2, a3;
+                ldsm_x4(kb + (ks >> 2) * AT_HALF_BYTES + swz128(k_row, (ks & 3) * 2 + k_c), a0, a1, a2, a3);
+                mma_16816(s, a0, a1, a2, a3, qf[ks][0], qf[ks][1]);
+            }
+            // s[0],s[1]: position row0 + lane/4, heads 2*(lane%4), +1;  s[2],s[3]: position + 8
+            const int pa = row0 + (lane >> 2);
+            const bool va = pa < npos, vb8 = pa + 8 < npos;
+            s[0] = va ? s[0] * A.scale_log2e : -1e30f;
+            s[1] = va ? s[1] * A.scale_log2e : -1e30f;
+            s[2] = vb8 ? s[2] * A.scale_log2e : -1e30f;
+            s[3] = vb8 ? s[3] * A.scale_log2e : -1e30f;
+            float t0 = fmaxf(s[0], s[2]), t1 = fmaxf(s[1], s[3]);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int j = 2 * i + kh;  // 16-byte column of the row
-            const uint4 kv = *reinterpret_cast<const uint4 *>(row + j * 16);
-            const float2 k0 = h2_to_f2(kv.x), k1 = h2_to_f2(kv.y), k2 = h2_to_f2(kv.z), k3 = h2_to_f2(kv.w);
+            for (int o = 4; o <= 16; o <<= 1) {
+                t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, o));
+                t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, o));
+            }
+            const float n0 = fmaxf(m0, t0), n1 = fmaxf(m1, t1);
+            const float al0 = exp2f(m0 - n0), al1 = exp2f(m1 - n1);
+            m0 = n0;
+            m1 = n1;
+            const float p0v = exp2f(s[0] - n0), p1v = exp2f(s[1] - n1), p2v = exp2f(s[2] - n0), p3v = exp2f(s[3] - n1);
+            l0 = l0 * al0 + p0v + p2v;
+            l1 = l1 * al1 + p1v + p3v;
+            if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float4 qa = *reinterpret_cast<const float4 *>(&S.q[g * AT_D + j * 8]);
-                const float4 qb = *reinterpret_cast<const float4 *>(&S.q[g * AT_D + j * 8 + 4]);
-                s[g] += qa.x * k0.x + qa.y * k0.y + qa.z * k1.x + qa.w * k1.y + qb.x * k2.x + qb.y * k2.y +
-                        qb.z * k3.x + qb.w * k3.y;
+                for (int mt = 0; mt < 8; ++mt) {
+                    oacc[mt][0] *= al0; oacc[mt][1] *= al1; oacc[mt][2] *= al0; oacc[mt][3] *= al1;
+                }
+            }
+            // P^T as the B operand: transpose the two 8x8 (position x head) blocks
+            const uint32_t b0 = movm_t(f2_to_h2(p0v, p1v));
+            const uint32_t b1 = movm_t(f2_to_h2(p2v, p3v));
+#pragma unroll
+            for (int mt = 0; mt < 8; ++mt) {
+                uint32_t a0, a1, a2, a3;
+                ldsm_x4_t(vb + (mt >> 2) * AT_HALF_BYTES + swz128(v_row, (mt & 3) * 2 + v_c), a0, a1, a2, a3);
+                mma_16816(oacc[mt], a0, a1, a2, a3, b0, b1);
             }
         }
-#pragma unroll
-        for (int g = 0; g < G; ++g) s[g] += __shfl_xor_sync(0xffffffffu, s[g], 16);
-        const int pos = t * AT_TILE + kp;  // within the chunk
-        if (kh == 0 && pos < npos) {
-#pragma unroll
-            for (int g = 0; g < G; ++g) S.sp[pos * G + g] = s[g];
-        }
-        __syncthreads();  // stage st is free again
-        if (warp == 0 && t + AT_STAGES < total_tiles) issue_tile(t + AT_STAGES);
+        __syncthreads();  // every warp is done with stage st
+        if (tid == 0 && t + AT_STAGES < ntiles) issue_tile(t + AT_STAGES);
     }
 
-    // ---- softmax statistics of the chunk ----
+    // ---- merge the 4 warps: sums over the position lanes, then across warps ----
+    // (the per-warp O^T partials reuse the K/V ring: every copy has landed and been consumed)
+    float (*So)[AT_D][AT_NH] = reinterpret_cast<float (*)[AT_D][AT_NH]>(&S.kv[0][0][0][0]);
+#pragma unroll
+    for (int o = 4; o <= 16; o <<= 1) {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+    }
     {
-        float mx[G], sum[G];
+        const int h = 2 * (lane & 3), dr = lane >> 2;
 #pragma unroll
-        for (int g = 0; g < G; ++g) mx[g] = -1e30f;
-        for (int p = tid; p < npos; p += AT_THREADS)
-#pragma unroll
-            for (int g = 0; g < G; ++g) mx[g] = fmaxf(mx[g], S.sp[p * G + g]);
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            mx[g] = warp_max(mx[g]);
-            if (lane == 0) S.red[warp][g] = mx[g];
+        for (int mt = 0; mt < 8; ++mt) {
+            *reinterpret_cast<float2 *>(&So[warp][mt * 16 + dr][h]) = make_float2(oacc[mt][0], oacc[mt][1]);
+            *reinterpret_cast<float2 *>(&So[warp][mt * 16 + dr + 8][h]) = make_float2(oacc[mt][2], oacc[mt][3]);
         }
-        __syncthreads();
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            float m = S.red[0][g];
-            for (int w = 1; w < AT_THREADS / 32; ++w) m = fmaxf(m, S.red[w][g]);
-            mx[g] = m;
-            sum[g] = 0.f;
+        if (lane < 4) {
+            S.m[warp][h] = m0; S.m[warp][h + 1] = m1;
+            S.l[warp][h] = l0; S.l[warp][h + 1] = l1;
         }
-        for (int p = tid; p < npos; p += AT_THREADS)
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float e = exp2f(S.sp[p * G + g] - mx[g]);
-                S.sp[p * G + g] = e;
-                sum[g] += e;
-            }
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            sum[g] = warp_sum(sum[g]);
-            if (lane == 0) S.red[warp][G + g] = sum[g];
-        }
-        __syncthreads();
-#pragma unroll
-        for (int g = 0; g < G; ++g)
-            if (tid == g) {  // mx[] is identical in every thread
-                float l = 0.f;
-                for (int w = 0; w < AT_THREADS / 32; ++w) l += S.red[w][G + g];
-                S.m[g] = mx[g];
-                S.l[g] = l;
-            }
     }
-
-    // ---- V phase: thread (group = tid / 16 takes positions = group mod 8, lane16 -> 8 dims) ----
-    float acc[G][8];
-#pragma unroll
-    for (int g = 0; g < G; ++g)
-#pragma unroll
-        for (int d = 0; d < 8; ++d) acc[g][d] = 0.f;
-    const int vg = tid >> 4, vl = tid & 15;
-    for (; t < total_tiles; ++t) {
-        const int st = t % AT_STAGES, tt = t - ntiles;
-        if (!S.abort_flag && !mbar_wait_bounded(smem_u32(&S.full[st]), (t / AT_STAGES) & 1)) {
-            S.abort_flag = 1;
-            atomicExch(A.status, 1);
+    __syncthreads();
+    if (tid < AT_NH) {
+        float M = S.m[0][tid];
+        for (int w = 1; w < AT_THREADS / 32; ++w) M = fmaxf(M, S.m[w][tid]);
+        float Ls = 0.f;
+        for (int w = 0; w < AT_THREADS / 32; ++w) {
+            const float wg = exp2f(S.m[w][tid] - M);
+            S.wgt[w][tid] = wg;
+            Ls += S.l[w][tid] * wg;
         }
-        const int rows = min(AT_TILE, npos - tt * AT_TILE);
-#pragma unroll 2
-        for (int r = vg; r < rows; r += 8) {
-            const uint4 vv = *reinterpret_cast<const uint4 *>(&S.stage[st][r * AT_ROW + vl * 16]);
-            const float2 v0 = h2_to_f2(vv.x), v1 = h2_to_f2(vv.y), v2 = h2_to_f2(vv.z), v3 = h2_to_f2(vv.w);
-            const float *pp = &S.sp[(tt * AT_TILE + r) * G];
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float p = pp[g];
-                acc[g][0] += p * v0.x; acc[g][1] += p * v0.y; acc[g][2] += p * v1.x; acc[g][3] += p * v1.y;
-                acc[g][4] += p * v2.x; acc[g][5] += p * v2.y; acc[g][6] += p * v3.x; acc[g][7] += p * v3.y;
-            }
-        }
-        __syncthreads();
-        if (warp == 0 && t + AT_STAGES < total_tiles) issue_tile(t + AT_STAGES);
-    }
-
-    // ---- reduce the 8 position groups through shared memory (reuses the stage ring) ----
-    float *red = reinterpret_cast<float *>(&S.stage[0][0]);  // [8][G][D]
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-        *reinterpret_cast<float4 *>(&red[(vg * G + g) * AT_D + vl * 8]) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
-        *reinterpret_cast<float4 *>(&red[(vg * G + g) * AT_D + vl * 8 + 4]) = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
+        S.mfin[tid] = M;
+        S.lsum[tid] = Ls;
     }
     __syncthreads();
     const long item = ((long)b * A.hkv + kvh) * gridDim.x + chunk_id;
     for (int i = tid; i < G * AT_D; i += AT_THREADS) {
+        const int g = i / AT_D, d = i - g * AT_D;
         float o = 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o += red[j * G * AT_D + i];
-        if (nchunks == 1) {
-            A.out[((long)b * A.hq + kvh * G) * AT_D + i] = __float2half_rn(o / S.l[i / AT_D]);
-        } else {
+        for (int w = 0; w < AT_THREADS / 32; ++w) o += So[w][d][g] * S.wgt[w][g];
+        if (nchunks == 1)
+            A.out[out_row0 + i] = __float2half_rn(o / S.lsum[g]);
+        else
             A.ws_acc[item * G * AT_D + i] = o;
-        }
     }
     if (nchunks == 1) return;
     if (tid < G) {
-        A.ws_ml[(item * G + tid) * 2 + 0] = S.m[tid];
-        A.ws_ml[(item * G + tid) * 2 + 1] = S.l[tid];
+        A.ws_ml[(item * G + tid) * 2 + 0] = S.mfin[tid];
+        A.ws_ml[(item * G + tid) * 2 + 1] = S.lsum[tid];
     }
     __threadfence();
     __syncthreads();
@@ -301,24 +313,32 @@ attn_split_f16_kernel(AttnSplitArgs A) {
     __syncthreads();
     if (!S.is_last) return;
     __threadfence();
-    // ---- merge: out = sum_c acc_c 2^(m_c - M) / sum_c l_c 2^(m_c - M) ----
+    // ---- last CTA of this (sequence, kv head): out = sum_c acc_c 2^(m_c - M) / sum_c l_c 2^(m_c - M) ----
     const long item0 = ((long)b * A.hkv + kvh) * gridDim.x;
     for (int i = tid; i < G * AT_D; i += AT_THREADS) {
         const int g = i / AT_D;
         float M = -1e30f;
         for (int c = 0; c < nchunks; ++c) M = fmaxf(M, __ldcg(&A.ws_ml[((item0 + c) * G + g) * 2]));
-        float L = 0.f, o = 0.f;
+        float Lt = 0.f, o = 0.f;
         for (int c = 0; c < nchunks; ++c) {
             const float w = exp2f(__ldcg(&A.ws_ml[((item0 + c) * G + g) * 2]) - M);
-            L += __ldcg(&A.ws_ml[((item0 + c) * G + g) * 2 + 1]) * w;
+            Lt += __ldcg(&A.ws_ml[((item0 + c) * G + g) * 2 + 1]) * w;
             o += __ldcg(&A.ws_acc[(item0 + c) * G * AT_D + i]) * w;
         }
-        A.out[((long)b * A.hq + kvh * G) * AT_D + i] = __float2half_rn(o / L);
+        A.out[out_row0 + i] = __float2half_rn(o / Lt);
     }
     if (tid == 0) A.counters[b * A.hkv + kvh] = 0;  // ready for the next launch
 }
 
-// Scratch layout: [status 256 B][counters B*Hkv ints, padded to 256 B][ml][acc]
+// Scratch layout (fixed offsets, so that the counters of one call shape can never be
+// overwritten by the partials of another):
+//   [0, 256)        status word
+//   [256, 64 KiB)   arrival counters, one per (sequence, kv head); zero between launches
+//   [64 KiB, 128 KiB) reserved for the GEMM family's counters
+//   [128 KiB, ...)  (max, sum) pairs, then the un-normalised accumulators
+constexpr size_t WS_COUNTERS_OFF = 256;
+constexpr size_t WS_DATA_OFF = 128 * 1024;
+constexpr int ATTN_MAX_COUNTERS = (64 * 1024 - 256) / 4;
 struct AttnWs {
     int *status;
     int *counters;
@@ -329,11 +349,9 @@ struct AttnWs {
 static AttnWs attn_ws_layout(void *base, int batch, int hkv, int g, int max_chunks) {
     AttnWs w;
     unsigned char *p = (unsigned char *)base;
-    size_t off = 0;
-    w.status = (int *)(p + off);
-    off += 256;
-    w.counters = (int *)(p + off);
-    off += (((size_t)batch * hkv * sizeof(int)) + 255) / 256 * 256;
+    w.status = (int *)p;
+    w.counters = (int *)(p + WS_COUNTERS_OFF);
+    size_t off = WS_DATA_OFF;
     const size_t items = (size_t)batch * hkv * max_chunks;
     w.ml = (float *)(p + off);
     off += ((items * g * 2 * sizeof(float)) + 255) / 256 * 256;
@@ -351,34 +369,25 @@ static int pick_chunk(int batch, int hkv, int max_len) {
     return chunk;
 }
 
+enum KvMode { KV_HEAD_MAJOR = 0, KV_SEQ_MAJOR = 1, KV_PAGED = 2 };
 struct AttnCall {
     const __half *q, *k, *v;
     __half *out;
     const int32_t *lens;
     int len_scalar;
-    int batch, hq, hkv, d, max_len;
+    int batch, hq, hkv, d;
+    int max_len;        // longest sequence the grid must cover
+    int mode;           // KvMode
+    long pos_extent;    // extent of the position axis the TMA may touch (rows past it read as zero)
+    long row_pitch;     // head-major: capacity (rows per head); seq-major: seq_len (rows per sequence)
+    const int32_t *block_table;
+    int block_size;
     float scale;
-    KvLayout L;
     void *ws;
     size_t ws_bytes;
     bool own_ws;
     cudaStream_t stream;
 };
-
-template <int G>
-static int attn_split_launch_g(const AttnSplitArgs &A, dim3 grid, cudaStream_t st) {
-    const size_t smem = sizeof(AttnSmem<G>);
-    static bool attr_set[16] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 16 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_split_f16_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return fail((int)e, "attention: shared memory %zu: %s", smem, cudaGetErrorString(e));
-        attr_set[dev] = true;
-    }
-    attn_split_f16_kernel<G><<<grid, AT_THREADS, smem, st>>>(A);
-    return launch_status("decode attention (split-KV)");
-}
 
 static int attn_split_launch(const char *name, AttnCall c) {
     const int g = c.hq / c.hkv;
@@ -389,22 +398,57 @@ static int attn_split_launch(const char *name, AttnCall c) {
         if (rc) return rc;
     }
     B200K_REQUIRE(c.ws, B200K_E_WORKSPACE, "%s: workspace is NULL", name);
+    B200K_REQUIRE(c.batch * c.hkv <= ATTN_MAX_COUNTERS, B200K_E_SHAPE, "%s: batch * num_kv_heads = %d exceeds %d", name,
+                  c.batch * c.hkv, ATTN_MAX_COUNTERS);
     AttnWs w = attn_ws_layout(c.ws, c.batch, c.hkv, g, max_chunks);
     B200K_REQUIRE(w.bytes <= c.ws_bytes, B200K_E_WORKSPACE, "%s: workspace %zu bytes, need %zu", name, c.ws_bytes, w.bytes);
     AttnSplitArgs A;
     A.q = c.q; A.k = c.k; A.v = c.v; A.out = c.out; A.lens = c.lens; A.len_scalar = c.len_scalar;
-    A.hq = c.hq; A.hkv = c.hkv; A.chunk = chunk;
+    A.hq = c.hq; A.hkv = c.hkv; A.g = g; A.chunk = chunk;
     A.scale_log2e = c.scale * 1.4426950408889634f;
-    A.L = c.L;
+    A.seq_major = c.mode != KV_HEAD_MAJOR;
+    A.block_table = c.mode == KV_PAGED ? c.block_table : nullptr;
+    A.block_size = c.block_size;
+    A.box_rows = c.mode == KV_PAGED && c.block_size < AT_TILE ? c.block_size : AT_TILE;
     A.ws_acc = w.acc; A.ws_ml = w.ml; A.counters = w.counters; A.status = w.status;
-    dim3 grid(max_chunks, c.hkv, c.batch);
-    switch (g) {
-        case 1: return attn_split_launch_g<1>(A, grid, c.stream);
-        case 2: return attn_split_launch_g<2>(A, grid, c.stream);
-        case 4: return attn_split_launch_g<4>(A, grid, c.stream);
-        case 8: return attn_split_launch_g<8>(A, grid, c.stream);
+
+    // tensor maps: innermost dimension = head_dim, then by ascending stride
+    const uint64_t row = AT_D * 2;
+    uint64_t dims[4], strides[3];
+    uint32_t box[4];
+    dims[0] = AT_D;
+    box[0] = 64;
+    if (c.mode == KV_HEAD_MAJOR) {          // [B, Hkv, pitch, D]
+        dims[1] = (uint64_t)c.pos_extent; dims[2] = c.hkv; dims[3] = c.batch;
+        strides[0] = row; strides[1] = (uint64_t)c.row_pitch * row; strides[2] = (uint64_t)c.hkv * c.row_pitch * row;
+        box[1] = AT_TILE; box[2] = 1; box[3] = 1;
+    } else if (c.mode == KV_SEQ_MAJOR) {    // [B, pitch, Hkv, D]
+        dims[1] = c.hkv; dims[2] = (uint64_t)c.pos_extent; dims[3] = c.batch;
+        strides[0] = row; strides[1] = (uint64_t)c.hkv * row; strides[2] = (uint64_t)c.row_pitch * c.hkv * row;
+        box[1] = 1; box[2] = AT_TILE; box[3] = 1;
+    } else {                                // [blocks, block_size, Hkv, D]
+        dims[1] = c.hkv; dims[2] = c.block_size; dims[3] = 1u << 24;
+        strides[0] = row; strides[1] = (uint64_t)c.hkv * row; strides[2] = (uint64_t)c.block_size * c.hkv * row;
+        box[1] = 1; box[2] = A.box_rows; box[3] = 1;
     }
-    return 1;
+    CUtensorMap kmap, vmap;
+    int rc = make_tensor_map(&kmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, c.k, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    rc = make_tensor_map(&vmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, c.v, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+
+    const size_t smem = sizeof(AttnSmem) + 1024;
+    static bool attr_set[16] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 16 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(attn_split_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail((int)e, "attention: shared memory %zu: %s", smem, cudaGetErrorString(e));
+        attr_set[dev] = true;
+    }
+    dim3 grid(max_chunks, c.hkv, c.batch);
+    attn_split_f16_kernel<<<grid, AT_THREADS, smem, c.stream>>>(kmap, vmap, A);
+    return launch_status("decode attention (split-KV)");
 }
 
 // ---------------------------------------------------------------------------
@@ -543,13 +587,10 @@ static int attn_common_checks(const char *name, const void *q, const void *k, co
     return 0;
 }
 
-static bool split_ok(int hq, int hkv, int d, const void *q, const void *k, const void *v, const void *out,
-                     const KvLayout &L) {
+static bool split_ok(int hq, int hkv, int d, const void *q, const void *k, const void *v, const void *out) {
     const int g = hq / hkv;
-    if (d != AT_D || !(g == 1 || g == 2 || g == 4 || g == 8)) return false;
-    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return false;
-    if (L.stride_b % 8 || L.stride_h % 8 || L.stride_p % 8 || L.block_stride % 8) return false;
-    return true;
+    if (d != AT_D || g > AT_NH) return false;
+    return aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out);
 }
 
 }  // namespace b200k
@@ -559,17 +600,23 @@ using namespace b200k;
 // ---- fp16 single-sequence entry points ---------------------------------------
 static int decode_f16_common(const char *name, const b200k_half *q, const b200k_half *k, const b200k_half *v,
                              b200k_half *out, int hq, int hkv, int d, int len, float scale, const KvLayout &L,
-                             int cap_for_chunks, b200k_stream stream) {
+                             int mode, long row_pitch, b200k_stream stream) {
     int rc = attn_common_checks(name, q, k, v, out, hq, hkv, d, len);
     if (rc) return rc;
-    if (split_ok(hq, hkv, d, q, k, v, out, L)) {
+    bool fast = split_ok(hq, hkv, d, q, k, v, out);
+    if (mode == KV_PAGED) {
+        const int bs = L.block_size;   // whole TMA boxes: a power of two from 8 to 64, or a multiple of 64
+        fast = fast && ((bs >= 8 && bs < 64 && (bs & (bs - 1)) == 0) || bs % 64 == 0);
+    }
+    if (fast) {
         AttnCall c = {};
         c.q = (const __half *)q; c.k = (const __half *)k; c.v = (const __half *)v; c.out = (__half *)out;
         c.lens = nullptr; c.len_scalar = len; c.batch = 1; c.hq = hq; c.hkv = hkv; c.d = d;
-        c.max_len = cap_for_chunks; c.scale = scale; c.L = L; c.ws = nullptr; c.own_ws = true;
+        c.max_len = len; c.mode = mode; c.pos_extent = len; c.row_pitch = row_pitch;
+        c.block_table = L.block_table; c.block_size = L.block_size;
+        c.scale = scale; c.ws = nullptr; c.own_ws = true;
         c.stream = to_stream(stream);
-        rc = attn_split_launch(name, c);
-        if (rc != 1) return rc;
+        return attn_split_launch(name, c);
     }
     return attn_generic_launch<__half>(name, q, k, v, out, 1, hq, hkv, d, len, scale, L, to_stream(stream));
 }
@@ -579,7 +626,7 @@ extern "C" int decode_attention_f16(const b200k_half *q, const b200k_half *k_cac
                                     int valid_kv_len, float scale, b200k_stream stream) {
     KvLayout L = {0, head_dim, (long)num_kv_heads * head_dim, nullptr, 0, 0};
     return decode_f16_common("decode_attention_f16", q, k_cache, v_cache, output, num_q_heads, num_kv_heads, head_dim,
-                             valid_kv_len, scale, L, valid_kv_len, stream);
+                             valid_kv_len, scale, L, KV_SEQ_MAJOR, valid_kv_len, stream);
 }
 extern "C" int decode_attention_hm_f16(const b200k_half *q, const b200k_half *k_cache, const b200k_half *v_cache,
                                        b200k_half *output, int num_q_heads, int num_kv_heads, int head_dim,
@@ -588,7 +635,7 @@ extern "C" int decode_attention_hm_f16(const b200k_half *q, const b200k_half *k_
                   capacity, valid_kv_len);
     KvLayout L = {0, (long)capacity * head_dim, head_dim, nullptr, 0, 0};
     return decode_f16_common("decode_attention_hm_f16", q, k_cache, v_cache, output, num_q_heads, num_kv_heads,
-                             head_dim, valid_kv_len, scale, L, valid_kv_len, stream);
+                             head_dim, valid_kv_len, scale, L, KV_HEAD_MAJOR, capacity, stream);
 }
 extern "C" int paged_decode_attention_f16(const b200k_half *q, const b200k_half *k_block_pool,
                                           const b200k_half *v_block_pool, const int32_t *block_table,
@@ -599,7 +646,7 @@ extern "C" int paged_decode_attention_f16(const b200k_half *q, const b200k_half 
     KvLayout L = {0, head_dim, (long)num_kv_heads * head_dim, block_table, block_size,
                   (long)block_size * num_kv_heads * head_dim};
     return decode_f16_common("paged_decode_attention_f16", q, k_block_pool, v_block_pool, output, num_q_heads,
-                             num_kv_heads, head_dim, valid_kv_len, scale, L, valid_kv_len, stream);
+                             num_kv_heads, head_dim, valid_kv_len, scale, L, KV_PAGED, block_size, stream);
 }
 
 // ---- fp16 batched, per-sequence lengths ---------------------------------------
@@ -614,13 +661,13 @@ extern "C" int batched_decode_attention_hm_f16_ws(const b200k_half *q, const b20
                   "%s: num_q_heads %d, num_kv_heads %d", name, num_q_heads, num_kv_heads);
     B200K_REQUIRE(batch_size >= 0 && max_len > 0, B200K_E_SHAPE, "%s: batch %d, max_len %d", name, batch_size, max_len);
     if (batch_size == 0) return 0;
-    KvLayout L = {(long)num_kv_heads * max_len * head_dim, (long)max_len * head_dim, head_dim, nullptr, 0, 0};
-    B200K_REQUIRE(split_ok(num_q_heads, num_kv_heads, head_dim, q, k_cache, v_cache, output, L), B200K_E_SHAPE,
-                  "%s: needs head_dim 128, group size 1/2/4/8 and 16-byte aligned tensors", name);
+    B200K_REQUIRE(split_ok(num_q_heads, num_kv_heads, head_dim, q, k_cache, v_cache, output), B200K_E_SHAPE,
+                  "%s: needs head_dim 128, GQA group size <= 8 and 16-byte aligned tensors", name);
     AttnCall c = {};
     c.q = (const __half *)q; c.k = (const __half *)k_cache; c.v = (const __half *)v_cache; c.out = (__half *)output;
     c.lens = context_lens; c.len_scalar = 0; c.batch = batch_size; c.hq = num_q_heads; c.hkv = num_kv_heads;
-    c.d = head_dim; c.max_len = max_len; c.scale = scale; c.L = L;
+    c.d = head_dim; c.max_len = max_len; c.mode = KV_HEAD_MAJOR; c.pos_extent = max_len; c.row_pitch = max_len;
+    c.scale = scale;
     c.ws = workspace; c.ws_bytes = workspace_bytes; c.own_ws = workspace == nullptr;
     c.stream = to_stream(stream);
     return attn_split_launch(name, c);

@@ -163,9 +163,9 @@ binary_kernel(const T *__restrict__ a, const T *__restrict__ b, T *__restrict__ 
 
 template <typename T, int OP>
 static int binary_launch(const char *name, const T *a, const T *b, T *out, int n, cudaStream_t st) {
-    B200K_REQUIRE(a && b && out, B200K_E_NULL, "%s: NULL pointer", name);
     B200K_REQUIRE(n >= 0, B200K_E_SHAPE, "%s: n = %d", name, n);
-    if (n == 0) return 0;
+    if (n == 0) return 0;  // nothing to do; empty buffers may legitimately be NULL
+    B200K_REQUIRE(a && b && out, B200K_E_NULL, "%s: NULL pointer", name);
     const bool vec = aligned16(a) && aligned16(b) && aligned16(out);
     const int work = ceil_div(n, Elem<T>::VEC);
     int blocks = ceil_div(work, 256);

@@ -4,6 +4,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace b200k {
 
@@ -65,6 +66,38 @@ int default_workspace(void **ptr, size_t *bytes) {
     }
     *ptr = g_ws[dev];
     *bytes = g_ws_bytes[dev];
+    return 0;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int make_tensor_map(CUtensorMap *map, CUtensorMapDataType dtype, int rank, const void *base, const uint64_t *dims,
+                    const uint64_t *strides_bytes, const uint32_t *box, CUtensorMapSwizzle swizzle) {
+    static EncodeTiledFn encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
+            cudaGetLastError();
+            return fail(B200K_E_DEVICE, "cuTensorMapEncodeTiled is not available from the driver");
+        }
+        encode = (EncodeTiledFn)fn;
+    }
+    cuuint64_t gdim[5], gstr[4];
+    cuuint32_t bdim[5], estr[5];
+    for (int i = 0; i < rank; ++i) {
+        gdim[i] = dims[i];
+        bdim[i] = box[i];
+        estr[i] = 1;
+        if (i > 0) gstr[i - 1] = strides_bytes[i - 1];
+    }
+    CUresult r = encode(map, dtype, (cuuint32_t)rank, const_cast<void *>(base), gdim, gstr, bdim, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200K_E_ALIGN, "tensor map rejected by the driver (CUresult %d)", (int)r);
     return 0;
 }
 
