@@ -1,0 +1,394 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A16 decode hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+A step is one pass of the Llama-3-8B-shape W4A16 decode layer chain (rms_norm -> QKV int4
+GEMM -> RoPE + kv append -> GQA decode attention -> o_proj -> add+rms_norm -> gate_up int4
+-> silu_mul -> down int4 -> add) over one batch of 64 sequences with 4096 tokens of context
+each, on synthetic seeded data.  Prints ONE JSON line.  With N > 1 (under torchrun) the
+layer is tensor-parallel over N ranks (column-parallel QKV / gate_up, row-parallel o / down
+with an all-reduce, attention by KV head); the batch is fixed, so scaling is strong.
+
+`--impl reference` times the CPU restatement of the same chain (the reference has no CPU
+implementation and cannot be built here) on the host cores, on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import importlib
+import json
+import os
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+BATCH, CTX = 64, 4096
+N_SETS = 4                    # distinct weight + KV sets rotated step by step (4 x 1.2 GB >> L2)
+METRIC = "layer tok/s (Llama-3-8B-shape W4A16 decode layer, batch 64, ctx 4096)"
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d["hbm_gbs"], d.get("bf16_tflops", 1590.0), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+# --------------------------------------------------------------------------------------
+# CPU legs (the only place the oracle is executed by this file)
+# --------------------------------------------------------------------------------------
+def load_oracle_c():
+    so = ROOT / "oracle" / "liboracle_c.so"
+    if not so.exists():
+        subprocess.run(["make", "-C", str(ROOT / "oracle")], check=True)
+    return ctypes.CDLL(str(so))
+
+
+def cpu_layer_case(rng, batch, ctx):
+    """Seeded inputs of the layer chain at the benchmark's extents, `batch` sequences."""
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import oracle as o
+    H, hq, hkv, d, I, G = 4096, 32, 8, 128, 14336, 128
+    ml = ctx + 1
+
+    def gptq(k, n):
+        return (rng.integers(-2 ** 31, 2 ** 31, (k // 8, n), dtype=np.int64).astype(np.int32),
+                rng.uniform(0.002, 0.02, (k // G, n)).astype(np.float16),
+                np.full((k // G, n // 8), 0x77777777, dtype=np.int32))
+    cos, sin = o.rope_tables(ml, d, 500000.0)
+    case = dict(H=H, hq=hq, hkv=hkv, d=d, I=I, G=G, ml=ml, cos=cos, sin=sin,
+                ln1=rng.uniform(0.5, 1.5, H).astype(np.float16), ln2=rng.uniform(0.5, 1.5, H).astype(np.float16),
+                qkv=gptq(H, (hq + 2 * hkv) * d), o=gptq(hq * d, H), gate_up=gptq(H, 2 * I), down=gptq(I, H),
+                hidden=rng.standard_normal((batch, H)).astype(np.float16),
+                pos=np.full(batch, ctx, dtype=np.int32))
+    # the cache of 4 sequences, repeated: same arithmetic cost, a quarter of the set-up time
+    base_k = rng.standard_normal((min(batch, 4), hkv, ml, d), dtype=np.float32).astype(np.float16)
+    base_v = rng.standard_normal((min(batch, 4), hkv, ml, d), dtype=np.float32).astype(np.float16)
+    reps = -(-batch // base_k.shape[0])
+    case["kc"] = np.ascontiguousarray(np.tile(base_k, (reps, 1, 1, 1))[:batch])
+    case["vc"] = np.ascontiguousarray(np.tile(base_v, (reps, 1, 1, 1))[:batch])
+    return case
+
+
+def cpu_layer_run(oc, c):
+    batch = c["hidden"].shape[0]
+    out = np.zeros((batch, c["H"]), np.float32)
+    ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    args = [ptr(c["hidden"]), ptr(out), batch, c["H"], c["hq"], c["hkv"], c["d"], c["I"], c["G"], 1,
+            ctypes.c_float(1e-5), ptr(c["ln1"]), ptr(c["ln2"])]
+    for name in ("qkv", "o", "gate_up", "down"):
+        args += [ptr(x) for x in c[name]]
+    args += [ptr(c["cos"]), ptr(c["sin"]), ptr(c["pos"]), ptr(c["kc"]), ptr(c["vc"]), c["ml"]]
+    t0 = time.perf_counter()
+    oc.oc_decode_layer(*args)
+    return time.perf_counter() - t0, out
+
+
+def cpu_baseline(sample_batch=BATCH, reps=3):
+    oc = load_oracle_c()
+    oc.oc_num_threads.restype = ctypes.c_int
+    cores = oc.oc_num_threads()
+    case = cpu_layer_case(np.random.default_rng(4), sample_batch, CTX)
+    cpu_layer_run(oc, case)                      # warm-up (page in, thread pool)
+    ts = [cpu_layer_run(oc, case)[0] for _ in range(reps)]
+    best = min(ts)
+    return {"value": sample_batch / best, "unit": "tok/s", "cores": cores, "kind": "port",
+            "sample": f"{sample_batch} of {BATCH} sequences, ctx {CTX}, full layer chain, best of {reps}"}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    oc = load_oracle_c()
+    oc.oc_num_threads.restype = ctypes.c_int
+    cores = oc.oc_num_threads()
+    sample = BATCH
+    case = cpu_layer_case(np.random.default_rng(4), sample, CTX)
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_layer_run(oc, case)
+    ts = [cpu_layer_run(oc, case)[0] for _ in range(args.steps)]
+    ms = 1e3 * sum(ts) / len(ts)
+    value = sample / (ms / 1e3)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
+        "config": {"workload": "C4 decode layer chain, batch 64, ctx 4096 (each step: the whole batch)",
+                   "note": "CPU restatement of the reference kernels' arithmetic (oracle/oracle_c.c, OpenMP); "
+                           "the reference has no CPU path and its Rust/Triton toolchain is absent"},
+        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": cores, "kind": "port",
+                         "sample": f"{sample} of {BATCH} sequences per step, ctx {CTX}, full layer chain"},
+        "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc = index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        for ln in out.strip().splitlines():
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    pkg = importlib.import_module("triton-rs_b200")
+    P = pkg.prelude
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch N > 1 through torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    pkg.lib().call("b200k_device_check")
+
+    shape = pkg.LayerShape()
+    ls = shape.local(world)
+    H, d, G = shape.hidden, shape.head_dim, shape.group_size
+    ml = CTX + 1
+    gen = torch.Generator(device=dev).manual_seed(1234)      # same seed on every rank: identical full weights
+
+    def rand_i32(*s):
+        return torch.randint(-2 ** 31, 2 ** 31 - 1, s, device=dev, dtype=torch.int32, generator=gen)
+
+    def gptq(k, n):
+        # nibbles uniform 0..15; symmetric zero-point 8 = stored nibble 7 under the GPTQ GEMM's +1 rule
+        return (rand_i32(k // 8, n), (torch.rand((k // G, n), device=dev, generator=gen) * 0.018 + 0.002).half(),
+                torch.full((k // G, n // 8), 0x77777777, device=dev, dtype=torch.int32))
+
+    sys.path.insert(0, str(ROOT / "oracle"))
+    half = d // 2
+    inv_freq = 1.0 / (shape.rope_theta ** (torch.arange(half, dtype=torch.float64) * 2.0 / d))
+    ang = torch.arange(ml, dtype=torch.float64)[:, None] * inv_freq[None, :]
+    cos, sin = torch.cos(ang).float().to(dev), torch.sin(ang).float().to(dev)
+
+    layers = []
+    for _ in range(N_SETS):
+        full = {"qkv": gptq(H, (shape.num_q_heads + 2 * shape.num_kv_heads) * d), "o": gptq(shape.num_q_heads * d, H),
+                "gate_up": gptq(H, 2 * shape.intermediate), "down": gptq(shape.intermediate, H)}
+        w = pkg.shard_layer_weights(full, shape, rank, world) if world > 1 else full
+        del full
+        ln1 = (torch.rand(H, device=dev, generator=gen) + 0.5).half()
+        ln2 = (torch.rand(H, device=dev, generator=gen) + 0.5).half()
+        kc = torch.randn((BATCH, ls.num_kv_heads, ml, d), device=dev, generator=gen, dtype=torch.float16)
+        vc = torch.randn((BATCH, ls.num_kv_heads, ml, d), device=dev, generator=gen, dtype=torch.float16)
+        layers.append(pkg.DecodeLayer(ls, w, ln1, ln2, cos, sin, max_batch=BATCH, max_len=ml, use_graph=(world == 1),
+                                      k_cache=kc, v_cache=vc))
+    hidden = torch.randn((BATCH, H), device=dev, generator=gen, dtype=torch.float16)
+    positions = torch.full((BATCH,), CTX, device=dev, dtype=torch.int32)
+    out = torch.empty_like(hidden)
+    stream = torch.cuda.current_stream()
+
+    # ---- one step -----------------------------------------------------------------------
+    part = torch.empty_like(hidden)
+    part2 = torch.empty_like(hidden)
+
+    def step_single(i):
+        layers[i % N_SETS].forward(hidden, positions, out=out)
+
+    def step_tp_eager(i):
+        L = layers[i % N_SETS]
+        L.forward_stage(0, hidden=hidden, positions=positions, partial=part, batch=BATCH)
+        dist.all_reduce(part)
+        L.forward_stage(1, hidden=hidden, reduced=part, partial=part2, batch=BATCH)
+        dist.all_reduce(part2)
+        L.forward_stage(2, reduced=part2, out=out, batch=BATCH)
+
+    tp_graphs = []
+    if world > 1:
+        for i in range(N_SETS):           # first-use set-up outside any capture
+            step_tp_eager(i)
+        torch.cuda.synchronize()
+        try:
+            for i in range(N_SETS):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    step_tp_eager(i)
+                tp_graphs.append(g)
+        except Exception:                 # capture of the collective not possible: stay eager
+            tp_graphs = []
+            torch.cuda.synchronize()
+
+    def step(i):
+        if world == 1:
+            step_single(i)
+        elif tp_graphs:
+            tp_graphs[i % N_SETS].replay()
+        else:
+            step_tp_eager(i)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3) + N_SETS):    # graph capture happens on first use of each set
+        step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for i in range(args.steps):
+        step(i)
+    ev1.record()
+    barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    if world > 1:
+        tt = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms_total = float(tt.item())
+    ms_step = ms_total / args.steps
+
+    # ---- end to end through the C ABI with host buffers (N = 1: one call; N > 1: staged) ----
+    hh = hidden.cpu().pin_memory()
+    hp = positions.cpu().pin_memory()
+    ho = torch.empty((BATCH, H), dtype=torch.float16).pin_memory()
+
+    def e2e_step(i):
+        if world == 1:
+            layers[i % N_SETS].forward_host(hh, hp, ho)
+        else:
+            hidden.copy_(hh, non_blocking=True)
+            positions.copy_(hp, non_blocking=True)
+            step(i)
+            ho.copy_(out, non_blocking=True)
+        stream.synchronize()              # the caller reads the result before the next decode step
+
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_step(i)
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    if world > 1:
+        tt = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_ms = float(tt.item())
+
+    # ---- the dominant kernel (decode attention) timed alone on the same rotating caches ----
+    q = torch.randn((BATCH, ls.num_q_heads, d), device=dev, generator=gen, dtype=torch.float16)
+    lens = torch.full((BATCH,), ml, device=dev, dtype=torch.int32)
+    ao = torch.empty_like(q)
+    scale = 1.0 / float(np.sqrt(d))
+
+    def attn(i):
+        L = layers[i % N_SETS]
+        P.batched_decode_attention_hm_f16(q, L.k_cache, L.v_cache, lens, ao, BATCH, ls.num_q_heads, ls.num_kv_heads, d,
+                                          ml, scale)
+    for i in range(N_SETS):
+        attn(i)
+    torch.cuda.synchronize()
+    n_at = max(args.steps, 8)
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_at)]
+    for i, (a, b) in enumerate(evs):
+        a.record(); attn(i); b.record()
+    torch.cuda.synchronize()
+    attn_ms = sum(a.elapsed_time(b) for a, b in evs) / n_at
+    clocks = sampler.stop() if rank == 0 else None
+
+    status = ctypes.c_int(-1)
+    pkg.lib().call("b200k_device_status", ctypes.addressof(status), stream.cuda_stream)
+
+    if rank == 0:
+        hbm_peak, tf_peak, peak_kind = peaks()
+        attn_bytes = 2 * BATCH * ls.num_kv_heads * ml * d * 2 + 2 * BATCH * ls.num_q_heads * d * 2
+        achieved = attn_bytes / (attn_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": BATCH / (ms_step * 1e-3), "unit": "tok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage, int4 weights, f32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": "C4: Llama-3-8B-shape W4A16 (GPTQ) decode layer chain, batch 64, ctx 4096",
+                       "parallelism": f"tp{world}" if world > 1 else "single GPU",
+                       "l2": f"inputs larger than L2: {N_SETS} weight+KV sets rotated, "
+                             f"{(2 * BATCH * ls.num_kv_heads * ml * d * 2) / 1e9:.2f} GB of KV per step",
+                       "graph": bool(world == 1 or tp_graphs), "device_status": status.value},
+            "e2e": {"value": BATCH / (e2e_ms * 1e-3), "unit": "tok/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": BATCH * H * 2 + BATCH * 4, "d2h_bytes_per_step": BATCH * H * 2},
+            "gpu_launches": (layers[0].launches_per_forward) * args.steps,
+            "roofline": {"kernel": "attn_split_f16_kernel", "bound": "hbm", "achieved": achieved, "peak": hbm_peak,
+                         "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": None,
+                         "algorithmic_bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms},
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -320,6 +320,76 @@ int rope_kv_append_hm_f16(const b200k_half *qkv, const float *cos_table,
                           int num_q_heads, int num_kv_heads, int head_dim, int max_len,
                           int batch, b200k_stream stream);
 
+/* ------------------------------------------------------------------------- */
+/* decode layer chain                                                          */
+/* ------------------------------------------------------------------------- */
+/* The reference holds the kernels but not the loop that strings them together: its
+ * consumer calls about a dozen launches per layer in the order shown by
+ * crates/triton-core/examples/ferrum_integration_demo.rs:52-108.  This handle is that
+ * call sequence for one Llama-shape decode layer, kept inside the library so that it
+ * can be captured once in a CUDA graph and replayed:
+ *   rms_norm -> QKV int4 GEMM -> RoPE + kv_cache_append -> decode attention -> o_proj
+ *   -> [all-reduce] -> residual add + rms_norm -> gate_up int4 GEMM -> silu_mul ->
+ *   down int4 GEMM -> [all-reduce] -> residual add
+ * All extents are the LOCAL ones of a tensor-parallel rank (q heads, kv heads and
+ * intermediate columns already divided by the world size); weights are GPTQ
+ * (qzeros NULL = symmetric zero-point 8) or AWQ, caller-owned and not copied.
+ * No counterpart in the reference. */
+typedef struct b200k_layer b200k_layer;
+typedef struct b200k_layer_config {
+    int hidden;          /* model width H */
+    int num_q_heads;     /* local */
+    int num_kv_heads;    /* local */
+    int head_dim;        /* 128 */
+    int intermediate;    /* local */
+    int group_size;
+    int weight_format;   /* 0 = GPTQ, 1 = AWQ */
+    int max_batch;
+    int max_len;         /* KV cache rows per (sequence, kv head) */
+    float rms_eps;
+    int use_graph;       /* capture the chain in a CUDA graph on first use per batch size */
+    int reserved[5];     /* zero */
+} b200k_layer_config;
+
+int b200k_layer_create(const b200k_layer_config *config, b200k_layer **out_layer);
+void b200k_layer_destroy(b200k_layer *layer);
+/* which: 0 = qkv [H, (Hq+2Hkv)*D], 1 = o [Hq*D, H], 2 = gate_up [H, 2*I] (gate columns then
+ * up columns), 3 = down [I, H].  Packed layouts as in the GEMM entry points. */
+int b200k_layer_set_weight(b200k_layer *layer, int which, const int32_t *qweight,
+                           const b200k_half *scales, const int32_t *qzeros);
+/* ln1/ln2 [H] fp16; cos/sin [max_pos, D/2] fp32 (rope_full_f32's tables). */
+int b200k_layer_set_norms_rope(b200k_layer *layer, const b200k_half *ln1, const b200k_half *ln2,
+                               const float *cos_table, const float *sin_table);
+/* caches [max_batch, num_kv_heads, max_len, D] fp16 head-major, caller-owned. */
+int b200k_layer_set_kv_cache(b200k_layer *layer, b200k_half *k_cache, b200k_half *v_cache);
+/* Peer-to-peer all-reduce for the two row-parallel GEMMs; comm may be NULL (single GPU). */
+struct b200k_comm;
+int b200k_layer_set_comm(b200k_layer *layer, struct b200k_comm *comm);
+
+/* Whole layer on device buffers: hidden_in/out [batch, H] fp16, positions [batch] int32
+ * (the row each sequence appends at; attention then covers positions[b]+1 rows). */
+int b200k_layer_forward(b200k_layer *layer, const b200k_half *hidden_in, const int32_t *positions,
+                        b200k_half *hidden_out, int batch, b200k_stream stream);
+/* The same through HOST buffers (pinned memory for full copy speed): copies the inputs
+ * in, runs the layer, copies the result out, all on `stream`; returns after enqueueing. */
+int b200k_layer_forward_host(b200k_layer *layer, const b200k_half *host_hidden_in,
+                             const int32_t *host_positions, b200k_half *host_hidden_out,
+                             int batch, b200k_stream stream);
+/* The chain in three pieces, for callers that run their own collective (e.g. NCCL)
+ * between them.  stage 0: up to and including o_proj, partial sums into partial_out
+ * [batch,H]; stage 1: takes the reduced o_proj output in reduced_in, up to and including
+ * the down GEMM, partial sums into partial_out; stage 2: final residual add of
+ * reduced_in into hidden_out. */
+int b200k_layer_forward_stage(b200k_layer *layer, int stage, const b200k_half *hidden_in,
+                              const int32_t *positions, const b200k_half *reduced_in,
+                              b200k_half *partial_out, b200k_half *hidden_out, int batch,
+                              b200k_stream stream);
+/* Number of kernel launches one forward call issues (for launch accounting). */
+int b200k_layer_launches_per_forward(const b200k_layer *layer);
+/* Reads the device status word of the default workspace (0 = no bounded wait ever gave up).
+ * Synchronises the stream. */
+int b200k_device_status(int *host_status_out, b200k_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -278,11 +278,12 @@ kv_append_kernel(const T *__restrict__ nk, const T *__restrict__ nv, T *__restri
 __global__ void __launch_bounds__(256)
 rope_kv_append_kernel(const __half *__restrict__ qkv, const float *__restrict__ cos_t,
                       const float *__restrict__ sin_t, const int32_t *__restrict__ positions,
-                      __half *__restrict__ q_out, __half *__restrict__ kc, __half *__restrict__ vc, int hq,
-                      int hkv, int d, int max_len) {
+                      __half *__restrict__ q_out, __half *__restrict__ kc, __half *__restrict__ vc,
+                      int32_t *__restrict__ lens_out, int hq, int hkv, int d, int max_len) {
     const int b = blockIdx.x;
     const int half = d / 2;
     const int pos = positions[b];
+    if (lens_out && threadIdx.x == 0) lens_out[b] = pos + 1;   // rows attention covers after this append
     const __half *row = qkv + (size_t)b * (hq + 2 * hkv) * d;
     const float *cr = cos_t + (size_t)pos * half, *sr = sin_t + (size_t)pos * half;
     const int rot_pairs = (hq + hkv) * half;
@@ -308,6 +309,19 @@ rope_kv_append_kernel(const __half *__restrict__ qkv, const float *__restrict__ 
             *reinterpret_cast<__half2 *>(vc + (((size_t)b * hkv + h) * max_len + pos) * d + p) = v;
         }
     }
+}
+
+int rope_kv_append_lens_launch(const __half *qkv, const float *cos_t, const float *sin_t, const int32_t *positions,
+                               __half *q_out, __half *kc, __half *vc, int32_t *lens_out, int hq, int hkv, int d,
+                               int max_len, int batch, cudaStream_t st) {
+    B200K_REQUIRE(qkv && cos_t && sin_t && positions && q_out && kc && vc, B200K_E_NULL,
+                  "rope_kv_append_hm_f16: NULL pointer");
+    B200K_REQUIRE(hq > 0 && hkv > 0 && d > 0 && d % 2 == 0 && max_len > 0 && batch >= 0, B200K_E_SHAPE,
+                  "rope_kv_append_hm_f16: Hq %d, Hkv %d, D %d, max_len %d, batch %d", hq, hkv, d, max_len, batch);
+    if (batch == 0) return 0;
+    rope_kv_append_kernel<<<batch, 256, 0, st>>>(qkv, cos_t, sin_t, positions, q_out, kc, vc, lens_out, hq, hkv, d,
+                                                 max_len);
+    return launch_status("rope_kv_append_hm_f16");
 }
 
 }  // namespace b200k
@@ -426,15 +440,7 @@ extern "C" int rope_kv_append_hm_f16(const b200k_half *qkv, const float *cos_tab
                                      const int32_t *positions, b200k_half *q_out, b200k_half *k_cache,
                                      b200k_half *v_cache, int num_q_heads, int num_kv_heads, int head_dim, int max_len,
                                      int batch, b200k_stream s) {
-    B200K_REQUIRE(qkv && cos_table && sin_table && positions && q_out && k_cache && v_cache, B200K_E_NULL,
-                  "rope_kv_append_hm_f16: NULL pointer");
-    B200K_REQUIRE(num_q_heads > 0 && num_kv_heads > 0 && head_dim > 0 && head_dim % 2 == 0 && max_len > 0 &&
-                      batch >= 0,
-                  B200K_E_SHAPE, "rope_kv_append_hm_f16: Hq %d, Hkv %d, D %d, max_len %d, batch %d", num_q_heads,
-                  num_kv_heads, head_dim, max_len, batch);
-    if (batch == 0) return 0;
-    rope_kv_append_kernel<<<batch, 256, 0, to_stream(s)>>>((const __half *)qkv, cos_table, sin_table, positions,
-                                                           (__half *)q_out, (__half *)k_cache, (__half *)v_cache,
-                                                           num_q_heads, num_kv_heads, head_dim, max_len);
-    return launch_status("rope_kv_append_hm_f16");
+    return rope_kv_append_lens_launch((const __half *)qkv, cos_table, sin_table, positions, (__half *)q_out,
+                                      (__half *)k_cache, (__half *)v_cache, nullptr, num_q_heads, num_kv_heads,
+                                      head_dim, max_len, batch, to_stream(s));
 }
