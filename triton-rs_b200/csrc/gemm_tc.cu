@@ -1,6 +1,407 @@
-// Tensor-core W4A16 GEMM (tcgen05 + TMEM).  Placeholder until the kernel lands: reports
-// "shape not covered" so that the dispatcher takes the strided family.
+// Tensor-core W4A16 GEMM for sm_100a: tcgen05.mma with the accumulator in TMEM.
+//
+// The product is computed transposed, C^T[n, m] = sum_k W^T[n, k] * A^T[k, m], so that
+// the 128 rows of the MMA are 128 weight columns and the MMA's N extent is the token
+// tile (16..256): a decode batch of 16-64 tokens then wastes nothing of the 128-row
+// instruction, and the dequantised weight tile is the A operand.
+//
+// Per CTA: one 128-column slab of the weight, one token tile, one K split.  Roles:
+//   warp 0      TMA producer: packed int4 words (no swizzle) and the activation tile
+//               (128-byte swizzle) of K block kb into ring stage kb % STAGES
+//   warps 2..5  dequant: nibbles -> fp16 in registers (magic-number trick, exact
+//               (q - zero), one fp16 multiply by the scale = the reference's rounding),
+//               written as the UMMA operand tile in the 128-byte-swizzled canonical
+//               layout -- K-major for GPTQ (a word holds 8 consecutive k of one column =
+//               one 16-byte chunk of a row), MN-major for AWQ (a word holds 8 adjacent
+//               columns of one k = one 16-byte chunk of a k-row)
+//   warp 1      one thread issues 4 x tcgen05.mma (K = 16 each) per K block and commits
+//               to the stage's "consumed" barrier
+//   warps 2..5  epilogue: tcgen05.ld of the 128 x TT fp32 accumulator, fp16 store; with a
+//               K split the CTAs of a cluster exchange partial tiles through distributed
+//               shared memory and each reduces a share of the rows in a fixed order
+// Every wait on an mbarrier is bounded; a wait that gives up sets a status word and the
+// kernel drains and frees its TMEM as usual.
+#include <cooperative_groups.h>
+
 #include "gemm.cuh"
+#include "tma.cuh"
+
+namespace cg = cooperative_groups;
+
 namespace b200k {
-int gemm_tc_launch(const GemmArgs &) { return 1; }
+
+constexpr int TC_BN = 128;        // weight columns per CTA = MMA M
+constexpr int TC_BK = 64;         // K per stage = one 128-byte swizzle row of fp16
+constexpr int TC_THREADS = 192;
+constexpr int TC_A_BYTES = TC_BN * TC_BK * 2;   // 16 KiB dequantised tile
+constexpr int TC_RAW_BYTES = TC_BN * TC_BK / 2; // 4 KiB packed tile
+
+struct TcArgs {
+    const __half *scales;
+    const int32_t *qzeros;
+    __half *c;
+    int m, n, k, group;
+    int s_sk, s_qzk, s_cm;
+    int zero_offset;
+    int tt;            // token tile = MMA N (16, 32, 64, 128, 256)
+    int stages;
+    int ksplit;        // cluster size along K
+    int kb_per_split;  // K blocks per split
+    int *status;
+};
+
+// ---- tcgen05 wrappers -------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
+// Addresses and offsets are in 16-byte units.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor, kind::f16: D = f32, A = B = f16, A major as given, B K-major.
+__host__ __device__ __forceinline__ uint32_t umma_idesc(int m, int n, int a_mn_major) {
+    return (1u << 4) | ((uint32_t)a_mn_major << 15) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap amap, TcArgs P) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int S = P.stages, TT = P.tt;
+    const int b_bytes = TT * TC_BK * 2;
+    unsigned char *a_tile = smem;                              // [S][16 KiB]
+    unsigned char *b_tile = a_tile + (size_t)S * TC_A_BYTES;   // [S][TT * 128]
+    unsigned char *raw = b_tile + (size_t)S * b_bytes;         // [S][4 KiB]
+    unsigned long long *bars = reinterpret_cast<unsigned long long *>(raw + (size_t)S * TC_RAW_BYTES);
+    // bars[0..S) full (TMA landed), [S..2S) dq_full (operand tile written), [2S..3S) consumed (MMAs retired), [3S] accumulator ready
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * S + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * TC_BN, m0 = blockIdx.y * TT;
+    const int kb_total = P.k / TC_BK;
+    const int kb_begin = blockIdx.z * P.kb_per_split;
+    const int kb_end = min(kb_total, kb_begin + P.kb_per_split);
+    const int nkb = max(0, kb_end - kb_begin);
+    uint32_t tmem_cols = 32;
+    while ((int)tmem_cols < TT) tmem_cols <<= 1;
+
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(smem_u32(&bars[s]), 1);
+            mbar_init(smem_u32(&bars[S + s]), 128);
+            mbar_init(smem_u32(&bars[2 * S + s]), 1);
+        }
+        mbar_init(smem_u32(&bars[3 * S]), 1);
+        *abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == 0) {
+        tmem_alloc(smem_u32(tmem_slot), tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_acc = *tmem_slot;
+
+    auto wait = [&](int bar_idx, uint32_t parity) {
+        if (*abort_flag) return;
+        if (!mbar_wait_bounded(smem_u32(&bars[bar_idx]), parity)) {
+            *abort_flag = 1;
+            atomicExch(P.status, 2);
+        }
+    };
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            tma_prefetch_desc(&wmap);
+            tma_prefetch_desc(&amap);
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % S, kb = kb_begin + i;
+                if (i >= S) wait(2 * S + s, ((i / S) - 1) & 1);
+                const uint32_t bar = smem_u32(&bars[s]);
+                mbar_expect_tx(bar, TC_RAW_BYTES + b_bytes);
+                if (FMT == FMT_GPTQ)
+                    tma_load_2d(smem_u32(raw + (size_t)s * TC_RAW_BYTES), &wmap, n0, kb * (TC_BK / 8), bar);
+                else
+                    tma_load_2d(smem_u32(raw + (size_t)s * TC_RAW_BYTES), &wmap, n0 / 8, kb * TC_BK, bar);
+                tma_load_2d(smem_u32(b_tile + (size_t)s * b_bytes), &amap, kb * TC_BK, m0, bar);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(TC_BN, TT, FMT == FMT_AWQ ? 1 : 0);
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % S;
+                wait(S + s, (i / S) & 1);
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(a_tile + (size_t)s * TC_A_BYTES);
+                const uint32_t b_addr = smem_u32(b_tile + (size_t)s * b_bytes);
+#pragma unroll
+                for (int j = 0; j < TC_BK / 16; ++j) {
+                    uint64_t da, db;
+                    if (FMT == FMT_GPTQ)
+                        da = umma_desc(a_addr + j * 32, 16, 1024);           // K-major: 8-row groups 1 KiB apart
+                    else
+                        da = umma_desc(a_addr + j * 2048, 8192, 1024);       // MN-major: 64-column halves 8 KiB apart, 8-k groups 1 KiB apart
+                    db = umma_desc(b_addr + j * 32, 16, 1024);
+                    tc_mma_f16(tmem_acc, da, db, idesc, (i > 0 || j > 0) ? 1u : 0u);
+                }
+                tc_commit(smem_u32(&bars[2 * S + s]));   // stage s may be refilled once these MMAs retire
+            }
+            tc_commit(smem_u32(&bars[3 * S]));           // accumulator complete
+        }
+    } else {
+        // ---------------- dequant warps (128 threads) ----------------
+        const int t = tid - 64;
+        if (FMT == FMT_GPTQ) {
+            const int n = n0 + t;                      // this thread's weight column = operand row t
+            const bool live = n < P.n;
+            int cur_group = -1;
+            __half2 s2 = __float2half2_rn(0.f), zlo = s2, zhi = s2;
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % S, kb = kb_begin + i;
+                const int grp = kb * TC_BK / P.group;
+                if (grp != cur_group) {
+                    cur_group = grp;
+                    int z = 8;
+                    if (live) {
+                        s2 = __half2half2(P.scales[(long)grp * P.s_sk + n]);
+                        if (P.qzeros)
+                            z = (int)(((uint32_t)P.qzeros[(long)grp * P.s_qzk + n / 8] >> (4 * (n % 8))) & 15u) + P.zero_offset;
+                    }
+                    zero_magic(z, zlo, zhi);
+                }
+                wait(s, (i / S) & 1);                                   // packed words landed
+                if (i >= S) wait(2 * S + s, ((i / S) - 1) & 1);         // operand tile no longer read by the tensor core
+                const uint32_t *rw = reinterpret_cast<const uint32_t *>(raw + (size_t)s * TC_RAW_BYTES);
+                unsigned char *arow = a_tile + (size_t)s * TC_A_BYTES + t * 128;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint32_t w = rw[j * TC_BN + t], w8 = w >> 8;
+                    const uint32_t v04 = h22u(__hmul2(__hsub2(u2h2(nib_lo(w)), zlo), s2));
+                    const uint32_t v15 = h22u(__hmul2(__hsub2(u2h2(nib_hi(w)), zhi), s2));
+                    const uint32_t v26 = h22u(__hmul2(__hsub2(u2h2(nib_lo(w8)), zlo), s2));
+                    const uint32_t v37 = h22u(__hmul2(__hsub2(u2h2(nib_hi(w8)), zhi), s2));
+                    uint4 o;
+                    o.x = __byte_perm(v04, v15, 0x5410);   // k0 k1
+                    o.y = __byte_perm(v26, v37, 0x5410);   // k2 k3
+                    o.z = __byte_perm(v04, v15, 0x7632);   // k4 k5
+                    o.w = __byte_perm(v26, v37, 0x7632);   // k6 k7
+                    *reinterpret_cast<uint4 *>(arow + ((j ^ (t & 7)) << 4)) = o;
+                }
+                fence_proxy_async();
+                mbar_arrive(smem_u32(&bars[S + s]));
+            }
+        } else {
+            const int n8 = t & 15, kr = t >> 4;        // 16 words per k row; this thread: word n8 of rows kr, kr+8, ...
+            const int n = n0 + n8 * 8;
+            const bool live = n < P.n;
+            int cur_group = -1;
+            __half2 s01, s23, s45, s67, z01, z23, z45, z67;
+            s01 = s23 = s45 = s67 = z01 = z23 = z45 = z67 = __float2half2_rn(0.f);
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % S, kb = kb_begin + i;
+                const int grp = kb * TC_BK / P.group;
+                if (grp != cur_group) {
+                    cur_group = grp;
+                    if (live) {
+                        const uint4 su = *reinterpret_cast<const uint4 *>(P.scales + (long)grp * P.s_sk + n);
+                        s01 = u2h2(su.x); s23 = u2h2(su.y); s45 = u2h2(su.z); s67 = u2h2(su.w);
+                        const uint32_t zw = (uint32_t)P.qzeros[(long)grp * P.s_qzk + n / 8], z8 = zw >> 8;
+                        z01 = u2h2(nib_lo(zw)); z23 = u2h2(nib_hi(zw)); z45 = u2h2(nib_lo(z8)); z67 = u2h2(nib_hi(z8));
+                    }
+                }
+                wait(s, (i / S) & 1);
+                if (i >= S) wait(2 * S + s, ((i / S) - 1) & 1);
+                const uint32_t *rw = reinterpret_cast<const uint32_t *>(raw + (size_t)s * TC_RAW_BYTES);
+                unsigned char *ahalf = a_tile + (size_t)s * TC_A_BYTES + (n8 >> 3) * 8192;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int kk = kr + 8 * j;
+                    const uint32_t w = rw[kk * 16 + n8], w8 = w >> 8;
+                    uint4 o;
+                    o.x = h22u(__hmul2(__hsub2(u2h2(nib_lo(w)), z01), s01));    // columns 0,1 (nibbles 0,4)
+                    o.y = h22u(__hmul2(__hsub2(u2h2(nib_hi(w)), z23), s23));    // columns 2,3 (nibbles 1,5)
+                    o.z = h22u(__hmul2(__hsub2(u2h2(nib_lo(w8)), z45), s45));   // columns 4,5 (nibbles 2,6)
+                    o.w = h22u(__hmul2(__hsub2(u2h2(nib_hi(w8)), z67), s67));   // columns 6,7 (nibbles 3,7)
+                    *reinterpret_cast<uint4 *>(ahalf + kk * 128 + (((n8 & 7) ^ (kk & 7)) << 4)) = o;
+                }
+                fence_proxy_async();
+                mbar_arrive(smem_u32(&bars[S + s]));
+            }
+        }
+        // ---------------- epilogue: TMEM -> registers -> C (or the split-K exchange) ----------------
+        if (nkb > 0) {
+            wait(3 * S, 0);
+            tc_fence_after();
+        }
+        const int q = warp & 3;                       // TMEM lane quadrant this warp may read
+        const int row = q * 32 + lane;                // accumulator row = weight column n0 + row
+        const int n = n0 + row;
+        float *red = reinterpret_cast<float *>(a_tile);   // [TT][128] fp32, reuses the ring (all MMAs have retired)
+        for (int c0 = 0; c0 < TT; c0 += 16) {
+            uint32_t r[16];
+            if (nkb > 0) {
+                tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + c0, r);
+                tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) r[j] = 0u;
+            }
+            if (P.ksplit == 1) {
+                if (n < P.n) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int m = m0 + c0 + j;
+                        if (m < P.m) P.c[(long)m * P.s_cm + n] = __float2half_rn(__uint_as_float(r[j]));
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) red[(c0 + j) * TC_BN + row] = __uint_as_float(r[j]);
+            }
+        }
+    }
+
+    if (P.ksplit > 1) {
+        // every CTA of the cluster holds a partial [TT][128] tile; CTA r reduces rows r, r+ksplit, ...
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        if (warp >= 2) {
+            const int row = tid - 64, n = n0 + row;
+            float *red = reinterpret_cast<float *>(a_tile);
+            const int rank = (int)cluster.block_rank();
+            for (int mm = rank; mm < TT; mm += P.ksplit) {
+                const int m = m0 + mm;
+                if (m >= P.m) break;
+                float acc = 0.f;
+                for (int r = 0; r < P.ksplit; ++r) acc += cluster.map_shared_rank(red, r)[mm * TC_BN + row];
+                if (n < P.n) P.c[(long)m * P.s_cm + n] = __float2half_rn(acc);
+            }
+        }
+        cluster.sync();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_acc, tmem_cols);
+}
+
+static int pick_tt(int m) {
+    if (m <= 16) return 16;
+    if (m <= 32) return 32;
+    if (m <= 64) return 64;
+    if (m <= 128) return 128;
+    return 256;
+}
+
+int gemm_tc_launch(const GemmArgs &g) {
+    if (g.k % TC_BK || g.group % TC_BK || g.n % 8) return 1;
+    if (g.format == FMT_AWQ && !g.qzeros) return 1;
+    const int tt = pick_tt(g.m);
+    const int col_tiles = ceil_div(g.n, TC_BN), tok_tiles = ceil_div(g.m, tt);
+    const int kb_total = g.k / TC_BK;
+    int ksplit = 1;
+    if (tt <= 64)
+        while (ksplit < 8 && col_tiles * tok_tiles * ksplit < sm_count() && kb_total / (ksplit * 2) >= 4) ksplit *= 2;
+    const int kb_per_split = ceil_div(kb_total, ksplit);
+    const int stage_bytes = TC_A_BYTES + tt * TC_BK * 2 + TC_RAW_BYTES;
+    int stages = (200 * 1024) / stage_bytes;
+    if (stages > 6) stages = 6;
+    if (stages > kb_per_split) stages = kb_per_split < 2 ? 2 : kb_per_split;
+    if (ksplit > 1 && stages * TC_A_BYTES < tt * TC_BN * 4) return 1;   // exchange tile must fit in the ring
+    const size_t smem = (size_t)stages * stage_bytes + (3 * stages + 1) * 8 + 16 + 1024;
+
+    // tensor maps: packed weight words (no swizzle) and activations (128-byte swizzle)
+    CUtensorMap wmap, amap;
+    int rc;
+    if (g.format == FMT_GPTQ) {
+        const uint64_t dims[2] = {(uint64_t)g.n, (uint64_t)(g.k / 8)}, str[1] = {(uint64_t)g.s_qwk * 4};
+        const uint32_t box[2] = {TC_BN, TC_BK / 8};
+        rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, g.qweight, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+    } else {
+        const uint64_t dims[2] = {(uint64_t)(g.n / 8), (uint64_t)g.k}, str[1] = {(uint64_t)g.s_qwk * 4};
+        const uint32_t box[2] = {TC_BN / 8, TC_BK};
+        rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, g.qweight, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+    }
+    if (rc) return 1;
+    {
+        const uint64_t dims[2] = {(uint64_t)g.k, (uint64_t)g.m}, str[1] = {(uint64_t)g.s_am * 2};
+        const uint32_t box[2] = {TC_BK, (uint32_t)tt};
+        rc = make_tensor_map(&amap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    }
+    if (rc) return 1;   // layout the TMA cannot describe: the strided family takes it
+
+    TcArgs P;
+    P.scales = g.scales; P.qzeros = g.qzeros; P.c = g.c;
+    P.m = g.m; P.n = g.n; P.k = g.k; P.group = g.group;
+    P.s_sk = g.s_sk; P.s_qzk = g.s_qzk; P.s_cm = g.s_cm;
+    P.zero_offset = g.zero_offset;
+    P.tt = tt; P.stages = stages; P.ksplit = ksplit; P.kb_per_split = kb_per_split;
+    P.status = (int *)g.ws;   // status word at the start of the scratch buffer
+    if (!P.status) return fail(B200K_E_WORKSPACE, "w4a16 gemm (tensor core): workspace is NULL");
+
+    auto kern = g.format == FMT_GPTQ ? gemm_tc_kernel<FMT_GPTQ> : gemm_tc_kernel<FMT_AWQ>;
+    static size_t attr_smem[2][16] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 16 && attr_smem[g.format][dev] < smem) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return fail((int)e, "w4a16 gemm (tensor core): shared memory: %s", cudaGetErrorString(e));
+        attr_smem[g.format][dev] = 227 * 1024;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(col_tiles, tok_tiles, ksplit);
+    cfg.blockDim = dim3(TC_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = g.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = ksplit;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, wmap, amap, P);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail((int)e, "w4a16 gemm (tensor core) launch: %s", cudaGetErrorString(e));
+    }
+    return 0;
+}
+
 }  // namespace b200k
