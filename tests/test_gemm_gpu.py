@@ -89,7 +89,11 @@ def test_gptq_sym_equals_stored_seven(P, oracle, m, k, n):
     qz7 = np.full((k // 128, n // 8), 0x77777777, dtype=np.int32)
     c_sym = run_gemm(P, "gptq", a, qw, sc, None, 128)
     c_7 = run_gemm(P, "gptq", a, qw, sc, qz7, 128)
-    assert torch.equal(c_sym, c_7)
+    if n % 32 == 0:
+        assert torch.equal(c_sym, c_7)       # same kernel family, same arithmetic
+    else:
+        # a qzeros row pitch that is not a multiple of 16 bytes takes the strided family
+        assert_close(c_7.float().cpu().numpy(), c_sym.float().cpu().numpy(), 2e-3, 2e-3)
     assert_close(c_sym.float().cpu().numpy(), oracle.w4a16_gptq_gemm(a, qw, sc, None, 128))
 
 

@@ -101,6 +101,28 @@ __device__ __forceinline__ void stage_x_gptq(const __half *x, __half *xs, int k)
     }
 }
 
+__device__ __forceinline__ uint32_t ldg_nc_u32(const void *p) {
+    uint32_t r;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(r) : "l"(p));
+    return r;
+}
+
+// One 8-k word of one column against the permuted activation chunk: 4 half2 products
+// summed in half2 (8 terms of |q - z| <= 16), widened to fp32 by the caller.
+__device__ __forceinline__ float gptq_word_dot(uint32_t w, __half2 zlo, __half2 zhi, __half2 x04, __half2 x15,
+                                               __half2 x26, __half2 x37) {
+    const uint32_t w8 = w >> 8;
+    __half2 s = __hmul2(__hsub2(u2h2(nib_lo(w)), zlo), x04);
+    s = __hfma2(__hsub2(u2h2(nib_hi(w)), zhi), x15, s);
+    s = __hfma2(__hsub2(u2h2(nib_lo(w8)), zlo), x26, s);
+    s = __hfma2(__hsub2(u2h2(nib_hi(w8)), zhi), x37, s);
+    const float2 f = __half22float2(s);
+    return f.x + f.y;
+}
+
+// RPG = packed rows per quantisation group when known at compile time (16 for group 128):
+// the whole group's weights are then requested before anything waits on them.
+template <int RPG>
 __global__ void __launch_bounds__(GEMV_THREADS)
 gemv_gptq_kernel(GemmArgs g, int ksplit) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -112,44 +134,61 @@ gemv_gptq_kernel(GemmArgs g, int ksplit) {
     constexpr int KW = GEMV_WARPS / 2;
     const int col = blockIdx.x * 256 + cw * 128 + lane * 4;
     const int kslot = blockIdx.y * KW + kw, kslots = ksplit * KW;
-    const int groups = g.k / g.group, rows_per_group = g.group / 8;
+    const int groups = g.k / g.group, rows_per_group = RPG > 0 ? RPG : g.group / 8;
+    const bool live = col < g.n;
+
+    // first group's weights, scales and zero-points are in flight before the activation vector is staged
+    constexpr int NW = RPG > 0 ? RPG : 1;
+    uint4 wreg[NW];
+    uint2 su = make_uint2(0, 0);
+    uint32_t zw = 0;
+    auto request = [&](int grp) {
+        if (g.qzeros) zw = ldg_nc_u32(g.qzeros + (long)grp * g.s_qzk + col / 8);
+        su = *reinterpret_cast<const uint2 *>(g.scales + (long)grp * g.s_sk + col);
+        if (RPG > 0) {
+            const int32_t *wp = g.qweight + (long)grp * RPG * g.s_qwk + col;
+#pragma unroll
+            for (int r = 0; r < NW; ++r) wreg[r] = ldg_nc_v4(wp + (long)r * g.s_qwk);
+        }
+    };
+    if (live && kslot < groups) request(kslot);
 
     stage_x_gptq(g.a, xs, g.k);
     __syncthreads();
 
     float tot[4] = {0.f, 0.f, 0.f, 0.f};
-    if (col < g.n) {
+    if (live) {
         for (int grp = kslot; grp < groups; grp += kslots) {
-            // scales and zero-points of the 4 columns for this group
-            const uint2 su = *reinterpret_cast<const uint2 *>(g.scales + (long)grp * g.s_sk + col);
+            if (grp != kslot) request(grp);
             const float2 s01 = h2_to_f2(su.x), s23 = h2_to_f2(su.y);
             __half2 zlo[4], zhi[4];
-            if (g.qzeros) {
-                const uint32_t zw = (uint32_t)g.qzeros[(long)grp * g.s_qzk + col / 8] >> (4 * (col % 8));
+            const uint32_t zsh = zw >> (4 * (col % 8));
 #pragma unroll
-                for (int c = 0; c < 4; ++c) zero_magic((int)((zw >> (4 * c)) & 15u) + g.zero_offset, zlo[c], zhi[c]);
-            } else {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) zero_magic(8, zlo[c], zhi[c]);
-            }
+            for (int c = 0; c < 4; ++c)
+                zero_magic(g.qzeros ? (int)((zsh >> (4 * c)) & 15u) + g.zero_offset : 8, zlo[c], zhi[c]);
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             const int r0 = grp * rows_per_group;
-            const int32_t *wp = g.qweight + (long)r0 * g.s_qwk + col;
-#pragma unroll 4
-            for (int r = 0; r < rows_per_group; ++r) {
-                const uint4 w4 = ldg_nc_v4(wp + (long)r * g.s_qwk);
-                const uint4 xv = *reinterpret_cast<const uint4 *>(xs + (r0 + r) * 8);
-                const __half2 x04 = u2h2(xv.x), x15 = u2h2(xv.y), x26 = u2h2(xv.z), x37 = u2h2(xv.w);
-                const uint32_t ws[4] = {w4.x, w4.y, w4.z, w4.w};
+            if (RPG > 0) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const uint32_t w = ws[c], w8 = w >> 8;
-                    __half2 s = __hmul2(__hsub2(u2h2(nib_lo(w)), zlo[c]), x04);
-                    s = __hfma2(__hsub2(u2h2(nib_hi(w)), zhi[c]), x15, s);
-                    s = __hfma2(__hsub2(u2h2(nib_lo(w8)), zlo[c]), x26, s);
-                    s = __hfma2(__hsub2(u2h2(nib_hi(w8)), zhi[c]), x37, s);
-                    const float2 f = __half22float2(s);
-                    acc[c] += f.x + f.y;
+                for (int r = 0; r < NW; ++r) {
+                    const uint4 xv = *reinterpret_cast<const uint4 *>(xs + (r0 + r) * 8);
+                    const __half2 x04 = u2h2(xv.x), x15 = u2h2(xv.y), x26 = u2h2(xv.z), x37 = u2h2(xv.w);
+                    acc[0] += gptq_word_dot(wreg[r].x, zlo[0], zhi[0], x04, x15, x26, x37);
+                    acc[1] += gptq_word_dot(wreg[r].y, zlo[1], zhi[1], x04, x15, x26, x37);
+                    acc[2] += gptq_word_dot(wreg[r].z, zlo[2], zhi[2], x04, x15, x26, x37);
+                    acc[3] += gptq_word_dot(wreg[r].w, zlo[3], zhi[3], x04, x15, x26, x37);
+                }
+            } else {
+                const int32_t *wp = g.qweight + (long)r0 * g.s_qwk + col;
+#pragma unroll 4
+                for (int r = 0; r < rows_per_group; ++r) {
+                    const uint4 w4 = ldg_nc_v4(wp + (long)r * g.s_qwk);
+                    const uint4 xv = *reinterpret_cast<const uint4 *>(xs + (r0 + r) * 8);
+                    const __half2 x04 = u2h2(xv.x), x15 = u2h2(xv.y), x26 = u2h2(xv.z), x37 = u2h2(xv.w);
+                    acc[0] += gptq_word_dot(w4.x, zlo[0], zhi[0], x04, x15, x26, x37);
+                    acc[1] += gptq_word_dot(w4.y, zlo[1], zhi[1], x04, x15, x26, x37);
+                    acc[2] += gptq_word_dot(w4.z, zlo[2], zhi[2], x04, x15, x26, x37);
+                    acc[3] += gptq_word_dot(w4.w, zlo[3], zhi[3], x04, x15, x26, x37);
                 }
             }
             tot[0] += acc[0] * s01.x;
@@ -172,7 +211,7 @@ gemv_gptq_kernel(GemmArgs g, int ksplit) {
     __syncthreads();
     if (kw == 0) red4[cw * 32 + lane] = make_float4(tot[0], tot[1], tot[2], tot[3]);
     cluster.sync();
-    if (cluster.block_rank() == 0 && kw == 0 && col < g.n) {
+    if (cluster.block_rank() == 0 && kw == 0 && live) {
         float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int r = 0; r < ksplit; ++r) {
             const float4 *peer = cluster.map_shared_rank(red4, r);
@@ -197,6 +236,26 @@ gemv_awq_kernel(GemmArgs g, int ksplit) {
     const int col = blockIdx.x * 256 + lane * 8;      // 8 columns per thread, 256 per warp
     const int kslot = blockIdx.y * GEMV_WARPS + warp, kslots = ksplit * GEMV_WARPS;
     const int groups = g.k / g.group;
+    const bool live = col < g.n;
+    constexpr int BATCH = 32;                         // k rows requested before any is used
+
+    uint32_t w[BATCH];
+    uint4 su = make_uint4(0, 0, 0, 0);
+    uint32_t zw = 0;
+    auto request_meta = [&](int grp) {
+        zw = ldg_nc_u32(g.qzeros + (long)grp * g.s_qzk + col / 8);
+        su = *reinterpret_cast<const uint4 *>(g.scales + (long)grp * g.s_sk + col);
+    };
+    auto request_rows = [&](int k0) {
+        const int32_t *wp = g.qweight + (long)k0 * g.s_qwk + col / 8;
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j) w[j] = ldg_nc_u32(wp + (long)j * g.s_qwk);
+    };
+    const bool batched = g.group % BATCH == 0;
+    if (live && kslot < groups) {
+        request_meta(kslot);
+        if (batched) request_rows(kslot * g.group);
+    }
 
     for (int i = threadIdx.x; i < g.k / 8; i += blockDim.x)
         *reinterpret_cast<uint4 *>(xs + i * 8) = *reinterpret_cast<const uint4 *>(g.a + i * 8);
@@ -205,41 +264,50 @@ gemv_awq_kernel(GemmArgs g, int ksplit) {
     float tot[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) tot[c] = 0.f;
-    if (col < g.n) {
+    if (live) {
         for (int grp = kslot; grp < groups; grp += kslots) {
-            const uint4 su = *reinterpret_cast<const uint4 *>(g.scales + (long)grp * g.s_sk + col);
-            const uint32_t zw = (uint32_t)g.qzeros[(long)grp * g.s_qzk + col / 8];
+            if (grp != kslot) request_meta(grp);
             // zero-points as half2 pairs in the word's own pair order, already in magic form:
             //   pair 0 = nibbles (0,4) = columns (0,1); pair 1 = (1,5) = (2,3); pair 2 = (2,6) = (4,5); pair 3 = (3,7) = (6,7)
             const uint32_t z8 = zw >> 8;
             const __half2 zl0 = u2h2(nib_lo(zw)), zh1 = u2h2(nib_hi(zw)), zl2 = u2h2(nib_lo(z8)), zh3 = u2h2(nib_hi(z8));
+            const uint4 sg = su;
             float acc[8];
 #pragma unroll
             for (int c = 0; c < 8; ++c) acc[c] = 0.f;
             const int k0 = grp * g.group;
-            const int32_t *wp = g.qweight + (long)k0 * g.s_qwk + col / 8;
-            for (int kk = 0; kk < g.group; kk += 8) {
-                uint32_t w[8];
+            for (int kk = 0; kk < g.group; kk += BATCH) {
+                const int nrows = min(BATCH, g.group - kk);
+                if (!batched) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) w[j] = (uint32_t)__ldg(wp + (long)(kk + j) * g.s_qwk);
-                const uint4 xv = *reinterpret_cast<const uint4 *>(xs + k0 + kk);
-                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
-                __half2 s0 = __float2half2_rn(0.f), s1 = s0, s2 = s0, s3 = s0;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const __half2 xp = u2h2(xw[j >> 1]);
-                    const __half2 xb = (j & 1) ? __high2half2(xp) : __low2half2(xp);
-                    const uint32_t wj = w[j], w8 = wj >> 8;
-                    s0 = __hfma2(__hsub2(u2h2(nib_lo(wj)), zl0), xb, s0);
-                    s1 = __hfma2(__hsub2(u2h2(nib_hi(wj)), zh1), xb, s1);
-                    s2 = __hfma2(__hsub2(u2h2(nib_lo(w8)), zl2), xb, s2);
-                    s3 = __hfma2(__hsub2(u2h2(nib_hi(w8)), zh3), xb, s3);
+                    for (int j = 0; j < BATCH; ++j)
+                        if (j < nrows) w[j] = ldg_nc_u32(g.qweight + (long)(k0 + kk + j) * g.s_qwk + col / 8);
+                } else if (!(grp == kslot && kk == 0)) {
+                    request_rows(k0 + kk);
                 }
-                const float2 f0 = __half22float2(s0), f1 = __half22float2(s1), f2 = __half22float2(s2), f3 = __half22float2(s3);
-                acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
-                acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+#pragma unroll
+                for (int j8 = 0; j8 < BATCH; j8 += 8) {
+                    if (j8 < nrows) {
+                        const uint4 xv = *reinterpret_cast<const uint4 *>(xs + k0 + kk + j8);
+                        const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+                        __half2 s0 = __float2half2_rn(0.f), s1 = s0, s2 = s0, s3 = s0;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const __half2 xp = u2h2(xw[j >> 1]);
+                            const __half2 xb = (j & 1) ? __high2half2(xp) : __low2half2(xp);
+                            const uint32_t wj = w[j8 + j], w8 = wj >> 8;
+                            s0 = __hfma2(__hsub2(u2h2(nib_lo(wj)), zl0), xb, s0);
+                            s1 = __hfma2(__hsub2(u2h2(nib_hi(wj)), zh1), xb, s1);
+                            s2 = __hfma2(__hsub2(u2h2(nib_lo(w8)), zl2), xb, s2);
+                            s3 = __hfma2(__hsub2(u2h2(nib_hi(w8)), zh3), xb, s3);
+                        }
+                        const float2 f0 = __half22float2(s0), f1 = __half22float2(s1), f2 = __half22float2(s2), f3 = __half22float2(s3);
+                        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+                        acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+                    }
+                }
             }
-            const float2 sa = h2_to_f2(su.x), sb = h2_to_f2(su.y), sc = h2_to_f2(su.z), sd = h2_to_f2(su.w);
+            const float2 sa = h2_to_f2(sg.x), sb = h2_to_f2(sg.y), sc = h2_to_f2(sg.z), sd = h2_to_f2(sg.w);
             tot[0] += acc[0] * sa.x; tot[1] += acc[1] * sa.y; tot[2] += acc[2] * sb.x; tot[3] += acc[3] * sb.y;
             tot[4] += acc[4] * sc.x; tot[5] += acc[5] * sc.y; tot[6] += acc[6] * sd.x; tot[7] += acc[7] * sd.y;
         }
@@ -263,7 +331,7 @@ gemv_awq_kernel(GemmArgs g, int ksplit) {
         red4[lane * 2 + 1] = make_float4(tot[4], tot[5], tot[6], tot[7]);
     }
     cluster.sync();
-    if (cluster.block_rank() == 0 && warp == 0 && col < g.n) {
+    if (cluster.block_rank() == 0 && warp == 0 && live) {
         float s[8];
 #pragma unroll
         for (int c = 0; c < 8; ++c) s[c] = 0.f;
@@ -289,7 +357,7 @@ int gemv_launch(const GemmArgs &g) {
     int ksplit = 1;
     while (ksplit < 8 && colblocks * ksplit < 2 * sm_count() && ksplit * 2 * kwarps <= groups) ksplit *= 2;
     const size_t smem = (size_t)g.k * 2 + (size_t)GEMV_WARPS * 256 * sizeof(float);
-    auto kern = g.format == FMT_GPTQ ? gemv_gptq_kernel : gemv_awq_kernel;
+    auto kern = g.format == FMT_GPTQ ? (g.group == 128 ? gemv_gptq_kernel<16> : gemv_gptq_kernel<0>) : gemv_awq_kernel;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail((int)e, "gemv: shared memory %zu: %s", smem, cudaGetErrorString(e));

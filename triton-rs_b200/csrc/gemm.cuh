@@ -55,10 +55,11 @@ __device__ __forceinline__ uint32_t nib_hi(uint32_t w) {
 __device__ __forceinline__ __half2 u2h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
 __device__ __forceinline__ uint32_t h22u(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
 
-// Magic zero constants for a zero-point z (0..16): (1024+z) and (64+z) in both halves.
+// Magic zero constants for a zero-point z (0..16): (1024+z) and (64+z) in both halves,
+// built with integer arithmetic on the fp16 bit patterns (ulp is 1 at 1024 and 1/16 at 64).
 __device__ __forceinline__ void zero_magic(int z, __half2 &zlo, __half2 &zhi) {
-    zlo = __half2half2(__ushort_as_half((unsigned short)(0x6400 + z)));       // 1024 + z, ulp = 1
-    zhi = __half2half2(__float2half_rn(64.0f + (float)z));                    // 64 + z,  exact
+    zlo = u2h2((uint32_t)(0x6400 + z) * 0x10001u);
+    zhi = u2h2((uint32_t)(0x5400 + (z << 4)) * 0x10001u);
 }
 
 // position of column j (0..7) inside an AWQ word (awq_gemm_int4_typed.rs:137-151)

@@ -22,6 +22,7 @@
 // Every wait on an mbarrier is bounded; a wait that gives up sets a status word and the
 // kernel drains and frees its TMEM as usual.
 #include <cooperative_groups.h>
+#include <stdlib.h>
 
 #include "gemm.cuh"
 #include "tma.cuh"
@@ -32,9 +33,16 @@ namespace b200k {
 
 constexpr int TC_BN = 128;        // weight columns per CTA = MMA M
 constexpr int TC_BK = 64;         // K per stage = one 128-byte swizzle row of fp16
-constexpr int TC_THREADS = 192;
+constexpr int TC_DQ_WARPS = 8;    // dequant / epilogue warps, in TC_DQ_GROUPS groups that take alternate K blocks
+constexpr int TC_DQ_GROUPS = 2;
+constexpr int TC_GROUP_WARPS = TC_DQ_WARPS / TC_DQ_GROUPS;
+constexpr int TC_DQ_WARP0 = 3;    // warps 0, 1, 2: weight producer, MMA issuer, activation producer
+constexpr int TC_THREADS = 32 * (TC_DQ_WARP0 + TC_DQ_WARPS);
 constexpr int TC_A_BYTES = TC_BN * TC_BK * 2;   // 16 KiB dequantised tile
-constexpr int TC_RAW_BYTES = TC_BN * TC_BK / 2; // 4 KiB packed tile
+constexpr int TC_W_BYTES = TC_BN * TC_BK / 2;   // 4 KiB packed weight words of one K block
+constexpr int TC_SC_BYTES = TC_BN * 2;          // the block's scale row (one group) for the 128 columns
+constexpr int TC_ZP_BYTES = TC_BN / 2;          // and its 16 packed zero-point words
+constexpr int TC_RAW_BYTES = TC_W_BYTES + TC_SC_BYTES + TC_ZP_BYTES + 64;   // 4.5 KiB ring slot
 
 struct TcArgs {
     const __half *scales;
@@ -44,7 +52,10 @@ struct TcArgs {
     int s_sk, s_qzk, s_cm;
     int zero_offset;
     int tt;            // token tile = MMA N (16, 32, 64, 128, 256)
-    int stages;
+    int dq_stages;     // SD: ring of dequantised operand tiles (on-chip producer and consumer: shallow)
+    int act_stages;    // SA: ring of activation tiles (TMA from L2: deep enough to cover its latency)
+    int raw_stages;    // R: ring of packed-weight tiles; deepest, because 4 KiB per K block is all
+                       //    the HBM traffic there is and enough of it must be in flight
     int ksplit;        // cluster size along K
     int kb_per_split;  // K blocks per split
     int *status;
@@ -93,19 +104,40 @@ __host__ __device__ __forceinline__ uint32_t umma_idesc(int m, int n, int a_mn_m
     return (1u << 4) | ((uint32_t)a_mn_major << 15) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// Position in a ring of `n` slots: slot index and the parity of the phase in flight.
+struct Ring {
+    int n, slot;
+    uint32_t phase;
+    __device__ __forceinline__ Ring(int n_) : n(n_), slot(0), phase(0) {}
+    __device__ __forceinline__ void next() {
+        if (++slot == n) {
+            slot = 0;
+            phase ^= 1u;
+        }
+    }
+};
+
 template <int FMT>
-__global__ void __launch_bounds__(TC_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap amap, TcArgs P) {
+__global__ void __launch_bounds__(TC_THREADS, 2)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap amap,
+               const __grid_constant__ CUtensorMap smap, const __grid_constant__ CUtensorMap zmap, TcArgs P) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    const int S = P.stages, TT = P.tt;
+    const int SD = P.dq_stages, SA = P.act_stages, R = P.raw_stages, TT = P.tt;
     const int b_bytes = TT * TC_BK * 2;
-    unsigned char *a_tile = smem;                              // [S][16 KiB]
-    unsigned char *b_tile = a_tile + (size_t)S * TC_A_BYTES;   // [S][TT * 128]
-    unsigned char *raw = b_tile + (size_t)S * b_bytes;         // [S][4 KiB]
-    unsigned long long *bars = reinterpret_cast<unsigned long long *>(raw + (size_t)S * TC_RAW_BYTES);
-    // bars[0..S) full (TMA landed), [S..2S) dq_full (operand tile written), [2S..3S) consumed (MMAs retired), [3S] accumulator ready
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * S + 1);
+    unsigned char *a_tile = smem;                               // [SD][16 KiB]
+    unsigned char *b_tile = a_tile + (size_t)SD * TC_A_BYTES;   // [SA][TT * 128]
+    unsigned char *raw = b_tile + (size_t)SA * b_bytes;         // [R][4 KiB]
+    unsigned long long *bars = reinterpret_cast<unsigned long long *>(raw + (size_t)R * TC_RAW_BYTES);
+    // barrier map
+    const int B_ACTF = 0;               // [SA] activation tile landed (TMA)
+    const int B_ACTE = SA;              // [SA] activation tile consumed (tcgen05.commit)
+    const int B_DQF = 2 * SA;           // [SD] operand tile written (one arrival per dequant warp)
+    const int B_DQE = 2 * SA + SD;      // [SD] operand tile consumed (tcgen05.commit)
+    const int B_RAWF = 2 * SA + 2 * SD;       // [R] packed words landed (TMA)
+    const int B_RAWE = 2 * SA + 2 * SD + R;   // [R] packed words read (one arrival per dequant warp)
+    const int B_ACC = 2 * SA + 2 * SD + 2 * R;  // accumulator complete
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + B_ACC + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -118,12 +150,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     while ((int)tmem_cols < TT) tmem_cols <<= 1;
 
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) {
-            mbar_init(smem_u32(&bars[s]), 1);
-            mbar_init(smem_u32(&bars[S + s]), 128);
-            mbar_init(smem_u32(&bars[2 * S + s]), 1);
+        for (int s = 0; s < SA; ++s) {
+            mbar_init(smem_u32(&bars[B_ACTF + s]), 1);
+            mbar_init(smem_u32(&bars[B_ACTE + s]), 1);
         }
-        mbar_init(smem_u32(&bars[3 * S]), 1);
+        for (int s = 0; s < SD; ++s) {
+            mbar_init(smem_u32(&bars[B_DQF + s]), TC_GROUP_WARPS);
+            mbar_init(smem_u32(&bars[B_DQE + s]), 1);
+        }
+        for (int r = 0; r < R; ++r) {
+            mbar_init(smem_u32(&bars[B_RAWF + r]), 1);
+            mbar_init(smem_u32(&bars[B_RAWE + r]), TC_GROUP_WARPS);
+        }
+        mbar_init(smem_u32(&bars[B_ACC]), 1);
         *abort_flag = 0;
         mbar_init_fence();
     }
@@ -145,32 +184,54 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     };
 
     if (warp == 0) {
-        // ---------------- TMA producer ----------------
+        // ---------------- TMA producer, packed weights: R blocks ahead ----------------
         if (lane == 0) {
+            const int group_shift = 31 - __clz(P.group);   // group sizes on this path are powers of two
             tma_prefetch_desc(&wmap);
-            tma_prefetch_desc(&amap);
-            for (int i = 0; i < nkb; ++i) {
-                const int s = i % S, kb = kb_begin + i;
-                if (i >= S) wait(2 * S + s, ((i / S) - 1) & 1);
-                const uint32_t bar = smem_u32(&bars[s]);
-                mbar_expect_tx(bar, TC_RAW_BYTES + b_bytes);
+            tma_prefetch_desc(&smap);
+            if (P.qzeros) tma_prefetch_desc(&zmap);
+            Ring rr(R);
+            for (int i = 0; i < nkb; ++i, rr.next()) {
+                const int r = rr.slot, kb = kb_begin + i;
+                if (i >= R) wait(B_RAWE + r, rr.phase ^ 1u);
+                const uint32_t bar = smem_u32(&bars[B_RAWF + r]);
+                const uint32_t dst = smem_u32(raw + (size_t)r * TC_RAW_BYTES);
+                mbar_expect_tx(bar, TC_W_BYTES + TC_SC_BYTES + (P.qzeros ? TC_ZP_BYTES : 0));
                 if (FMT == FMT_GPTQ)
-                    tma_load_2d(smem_u32(raw + (size_t)s * TC_RAW_BYTES), &wmap, n0, kb * (TC_BK / 8), bar);
+                    tma_load_2d(dst, &wmap, n0, kb * (TC_BK / 8), bar);
                 else
-                    tma_load_2d(smem_u32(raw + (size_t)s * TC_RAW_BYTES), &wmap, n0 / 8, kb * TC_BK, bar);
-                tma_load_2d(smem_u32(b_tile + (size_t)s * b_bytes), &amap, kb * TC_BK, m0, bar);
+                    tma_load_2d(dst, &wmap, n0 / 8, kb * TC_BK, bar);
+                // the block's quantisation group rides along: scale row and packed zero-points
+                const int grp = (kb * TC_BK) >> group_shift;
+                tma_load_2d(dst + TC_W_BYTES, &smap, n0, grp, bar);
+                if (P.qzeros) tma_load_2d(dst + TC_W_BYTES + TC_SC_BYTES, &zmap, n0 / 8, grp, bar);
+            }
+        }
+    } else if (warp == 2) {
+        // ---------------- TMA producer, activation tiles: SA blocks ahead ----------------
+        if (lane == 0) {
+            tma_prefetch_desc(&amap);
+            Ring ra(SA);
+            for (int i = 0; i < nkb; ++i, ra.next()) {
+                const int s = ra.slot;
+                if (i >= SA) wait(B_ACTE + s, ra.phase ^ 1u);
+                const uint32_t bar = smem_u32(&bars[B_ACTF + s]);
+                mbar_expect_tx(bar, b_bytes);
+                tma_load_2d(smem_u32(b_tile + (size_t)s * b_bytes), &amap, (kb_begin + i) * TC_BK, m0, bar);
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(TC_BN, TT, FMT == FMT_AWQ ? 1 : 0);
-            for (int i = 0; i < nkb; ++i) {
-                const int s = i % S;
-                wait(S + s, (i / S) & 1);
+            Ring ra(SA), rd(SD);
+            for (int i = 0; i < nkb; ++i, ra.next(), rd.next()) {
+                const int sd = rd.slot, sa = ra.slot;
+                wait(B_ACTF + sa, ra.phase);
+                wait(B_DQF + sd, rd.phase);
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(a_tile + (size_t)s * TC_A_BYTES);
-                const uint32_t b_addr = smem_u32(b_tile + (size_t)s * b_bytes);
+                const uint32_t a_addr = smem_u32(a_tile + (size_t)sd * TC_A_BYTES);
+                const uint32_t b_addr = smem_u32(b_tile + (size_t)sa * b_bytes);
 #pragma unroll
                 for (int j = 0; j < TC_BK / 16; ++j) {
                     uint64_t da, db;
@@ -181,40 +242,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                     db = umma_desc(b_addr + j * 32, 16, 1024);
                     tc_mma_f16(tmem_acc, da, db, idesc, (i > 0 || j > 0) ? 1u : 0u);
                 }
-                tc_commit(smem_u32(&bars[2 * S + s]));   // stage s may be refilled once these MMAs retire
+                // both tiles may be refilled once these MMAs retire
+                tc_commit(smem_u32(&bars[B_DQE + sd]));
+                tc_commit(smem_u32(&bars[B_ACTE + sa]));
             }
-            tc_commit(smem_u32(&bars[3 * S]));           // accumulator complete
+            tc_commit(smem_u32(&bars[B_ACC]));            // accumulator complete
         }
     } else {
-        // ---------------- dequant warps (128 threads) ----------------
-        const int t = tid - 64;
-        if (FMT == FMT_GPTQ) {
-            const int n = n0 + t;                      // this thread's weight column = operand row t
-            const bool live = n < P.n;
-            int cur_group = -1;
-            __half2 s2 = __float2half2_rn(0.f), zlo = s2, zhi = s2;
-            for (int i = 0; i < nkb; ++i) {
-                const int s = i % S, kb = kb_begin + i;
-                const int grp = kb * TC_BK / P.group;
-                if (grp != cur_group) {
-                    cur_group = grp;
-                    int z = 8;
-                    if (live) {
-                        s2 = __half2half2(P.scales[(long)grp * P.s_sk + n]);
-                        if (P.qzeros)
-                            z = (int)(((uint32_t)P.qzeros[(long)grp * P.s_qzk + n / 8] >> (4 * (n % 8))) & 15u) + P.zero_offset;
-                    }
-                    zero_magic(z, zlo, zhi);
-                }
-                wait(s, (i / S) & 1);                                   // packed words landed
-                if (i >= S) wait(2 * S + s, ((i / S) - 1) & 1);         // operand tile no longer read by the tensor core
-                const uint32_t *rw = reinterpret_cast<const uint32_t *>(raw + (size_t)s * TC_RAW_BYTES);
+        // ---------------- dequant warps: two groups of 128 threads, group g takes K blocks g, g+2, ... ----------------
+        // (the waits, fences and arrivals of one block then overlap the arithmetic of the other group's block)
+        const int tg = tid - 32 * TC_DQ_WARP0;
+        const int grp_id = tg >> 7, t = tg & 127;
+        Ring rr(R), rd(SD);
+        if (grp_id == 1) { rr.next(); rd.next(); }
+        for (int i = grp_id; i < nkb; i += TC_DQ_GROUPS) {
+            const int s = rd.slot, r = rr.slot;
+            wait(B_RAWF + r, rr.phase);                               // packed words, scales, zero-points landed
+            const unsigned char *slot = raw + (size_t)r * TC_RAW_BYTES;
+            const uint32_t *rw = reinterpret_cast<const uint32_t *>(slot);
+            uint32_t w[8];
+            if (FMT == FMT_GPTQ) {
+                // thread t = weight column t (operand row t): its 8 words are the 8 16-byte chunks of the row
+                const __half2 s2 = __half2half2(reinterpret_cast<const __half *>(slot + TC_W_BYTES)[t]);
+                int z = 8;
+                if (P.qzeros)
+                    z = (int)((reinterpret_cast<const uint32_t *>(slot + TC_W_BYTES + TC_SC_BYTES)[t >> 3] >> (4 * (t & 7))) & 15u) +
+                        P.zero_offset;
+                __half2 zlo, zhi;
+                zero_magic(z, zlo, zhi);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) w[j] = rw[j * TC_BN + t];
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars[B_RAWE + r]));  // this warp is done with the packed tile
+                if (i >= SD) wait(B_DQE + s, rd.phase ^ 1u);              // operand tile no longer read by the tensor core
                 unsigned char *arow = a_tile + (size_t)s * TC_A_BYTES + t * 128;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    const uint32_t w = rw[j * TC_BN + t], w8 = w >> 8;
-                    const uint32_t v04 = h22u(__hmul2(__hsub2(u2h2(nib_lo(w)), zlo), s2));
-                    const uint32_t v15 = h22u(__hmul2(__hsub2(u2h2(nib_hi(w)), zhi), s2));
+                    const uint32_t w8 = w[j] >> 8;
+                    const uint32_t v04 = h22u(__hmul2(__hsub2(u2h2(nib_lo(w[j])), zlo), s2));
+                    const uint32_t v15 = h22u(__hmul2(__hsub2(u2h2(nib_hi(w[j])), zhi), s2));
                     const uint32_t v26 = h22u(__hmul2(__hsub2(u2h2(nib_lo(w8)), zlo), s2));
                     const uint32_t v37 = h22u(__hmul2(__hsub2(u2h2(nib_hi(w8)), zhi), s2));
                     uint4 o;
@@ -224,76 +290,67 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                     o.w = __byte_perm(v26, v37, 0x7632);   // k6 k7
                     *reinterpret_cast<uint4 *>(arow + ((j ^ (t & 7)) << 4)) = o;
                 }
-                fence_proxy_async();
-                mbar_arrive(smem_u32(&bars[S + s]));
-            }
-        } else {
-            const int n8 = t & 15, kr = t >> 4;        // 16 words per k row; this thread: word n8 of rows kr, kr+8, ...
-            const int n = n0 + n8 * 8;
-            const bool live = n < P.n;
-            int cur_group = -1;
-            __half2 s01, s23, s45, s67, z01, z23, z45, z67;
-            s01 = s23 = s45 = s67 = z01 = z23 = z45 = z67 = __float2half2_rn(0.f);
-            for (int i = 0; i < nkb; ++i) {
-                const int s = i % S, kb = kb_begin + i;
-                const int grp = kb * TC_BK / P.group;
-                if (grp != cur_group) {
-                    cur_group = grp;
-                    if (live) {
-                        const uint4 su = *reinterpret_cast<const uint4 *>(P.scales + (long)grp * P.s_sk + n);
-                        s01 = u2h2(su.x); s23 = u2h2(su.y); s45 = u2h2(su.z); s67 = u2h2(su.w);
-                        const uint32_t zw = (uint32_t)P.qzeros[(long)grp * P.s_qzk + n / 8], z8 = zw >> 8;
-                        z01 = u2h2(nib_lo(zw)); z23 = u2h2(nib_hi(zw)); z45 = u2h2(nib_lo(z8)); z67 = u2h2(nib_hi(z8));
-                    }
-                }
-                wait(s, (i / S) & 1);
-                if (i >= S) wait(2 * S + s, ((i / S) - 1) & 1);
-                const uint32_t *rw = reinterpret_cast<const uint32_t *>(raw + (size_t)s * TC_RAW_BYTES);
+            } else {
+                // thread t: word column n8 = t % 16 (8 weight columns), k rows t / 16 + 8 j
+                const int n8 = t & 15, kr = t >> 4;
+                const uint4 su = reinterpret_cast<const uint4 *>(slot + TC_W_BYTES)[n8];
+                const __half2 s01 = u2h2(su.x), s23 = u2h2(su.y), s45 = u2h2(su.z), s67 = u2h2(su.w);
+                const uint32_t zw = reinterpret_cast<const uint32_t *>(slot + TC_W_BYTES + TC_SC_BYTES)[n8], z8 = zw >> 8;
+                const __half2 z01 = u2h2(nib_lo(zw)), z23 = u2h2(nib_hi(zw)), z45 = u2h2(nib_lo(z8)), z67 = u2h2(nib_hi(z8));
+#pragma unroll
+                for (int j = 0; j < 8; ++j) w[j] = rw[(kr + 8 * j) * 16 + n8];
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars[B_RAWE + r]));
+                if (i >= SD) wait(B_DQE + s, rd.phase ^ 1u);
                 unsigned char *ahalf = a_tile + (size_t)s * TC_A_BYTES + (n8 >> 3) * 8192;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const int kk = kr + 8 * j;
-                    const uint32_t w = rw[kk * 16 + n8], w8 = w >> 8;
+                    const uint32_t w8 = w[j] >> 8;
                     uint4 o;
-                    o.x = h22u(__hmul2(__hsub2(u2h2(nib_lo(w)), z01), s01));    // columns 0,1 (nibbles 0,4)
-                    o.y = h22u(__hmul2(__hsub2(u2h2(nib_hi(w)), z23), s23));    // columns 2,3 (nibbles 1,5)
-                    o.z = h22u(__hmul2(__hsub2(u2h2(nib_lo(w8)), z45), s45));   // columns 4,5 (nibbles 2,6)
-                    o.w = h22u(__hmul2(__hsub2(u2h2(nib_hi(w8)), z67), s67));   // columns 6,7 (nibbles 3,7)
+                    o.x = h22u(__hmul2(__hsub2(u2h2(nib_lo(w[j])), z01), s01));   // columns 0,1 (nibbles 0,4)
+                    o.y = h22u(__hmul2(__hsub2(u2h2(nib_hi(w[j])), z23), s23));   // columns 2,3 (nibbles 1,5)
+                    o.z = h22u(__hmul2(__hsub2(u2h2(nib_lo(w8)), z45), s45));     // columns 4,5 (nibbles 2,6)
+                    o.w = h22u(__hmul2(__hsub2(u2h2(nib_hi(w8)), z67), s67));     // columns 6,7 (nibbles 3,7)
                     *reinterpret_cast<uint4 *>(ahalf + kk * 128 + (((n8 & 7) ^ (kk & 7)) << 4)) = o;
                 }
-                fence_proxy_async();
-                mbar_arrive(smem_u32(&bars[S + s]));
             }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars[B_DQF + s]));
+            rr.next(); rr.next();
+            rd.next(); rd.next();
         }
         // ---------------- epilogue: TMEM -> registers -> C (or the split-K exchange) ----------------
         if (nkb > 0) {
-            wait(3 * S, 0);
+            wait(B_ACC, 0);
             tc_fence_after();
         }
         const int q = warp & 3;                       // TMEM lane quadrant this warp may read
+        const int chunk0 = (warp - TC_DQ_WARP0) >> 2; // the two warps of a quadrant alternate 16-column chunks
         const int row = q * 32 + lane;                // accumulator row = weight column n0 + row
         const int n = n0 + row;
         float *red = reinterpret_cast<float *>(a_tile);   // [TT][128] fp32, reuses the ring (all MMAs have retired)
-        for (int c0 = 0; c0 < TT; c0 += 16) {
-            uint32_t r[16];
+        for (int c0 = chunk0 * 16; c0 < TT; c0 += 32) {
+            uint32_t rr[16];
             if (nkb > 0) {
-                tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + c0, r);
+                tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + c0, rr);
                 tmem_ld_wait();
             } else {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) r[j] = 0u;
+                for (int j = 0; j < 16; ++j) rr[j] = 0u;
             }
             if (P.ksplit == 1) {
                 if (n < P.n) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int m = m0 + c0 + j;
-                        if (m < P.m) P.c[(long)m * P.s_cm + n] = __float2half_rn(__uint_as_float(r[j]));
+                        if (m < P.m) P.c[(long)m * P.s_cm + n] = __float2half_rn(__uint_as_float(rr[j]));
                     }
                 }
             } else {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) red[(c0 + j) * TC_BN + row] = __uint_as_float(r[j]);
+                for (int j = 0; j < 16; ++j) red[(c0 + j) * TC_BN + row] = __uint_as_float(rr[j]);
             }
         }
     }
@@ -302,11 +359,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         // every CTA of the cluster holds a partial [TT][128] tile; CTA r reduces rows r, r+ksplit, ...
         cg::cluster_group cluster = cg::this_cluster();
         cluster.sync();
-        if (warp >= 2) {
-            const int row = tid - 64, n = n0 + row;
+        if (warp >= TC_DQ_WARP0) {
+            const int t = tid - 32 * TC_DQ_WARP0, row = t & (TC_BN - 1), sub = t >> 7;
+            const int n = n0 + row;
             float *red = reinterpret_cast<float *>(a_tile);
             const int rank = (int)cluster.block_rank();
-            for (int mm = rank; mm < TT; mm += P.ksplit) {
+            for (int mm = rank + sub * P.ksplit; mm < TT; mm += 2 * P.ksplit) {
                 const int m = m0 + mm;
                 if (m >= P.m) break;
                 float acc = 0.f;
@@ -330,24 +388,53 @@ static int pick_tt(int m) {
 }
 
 int gemm_tc_launch(const GemmArgs &g) {
-    if (g.k % TC_BK || g.group % TC_BK || g.n % 8) return 1;
+    if (g.k % TC_BK || g.group % TC_BK || (g.group & (g.group - 1)) || g.n % 8) return 1;
     if (g.format == FMT_AWQ && !g.qzeros) return 1;
+    if (g.qzeros && (g.s_qzk % 4 || !aligned16(g.qzeros))) return 1;   // zero-point rows travel by TMA: 16-byte pitch
     const int tt = pick_tt(g.m);
     const int col_tiles = ceil_div(g.n, TC_BN), tok_tiles = ceil_div(g.m, tt);
     const int kb_total = g.k / TC_BK;
+    const int tiles = col_tiles * tok_tiles;
+    // Shared memory: two CTAs per SM while the token tile is small, one otherwise.
+    const int ctas_per_sm = tt <= 64 ? 2 : 1;
+    const int budget = (ctas_per_sm == 2 ? 111 : 222) * 1024;
+    const int act_bytes = tt * TC_BK * 2;
+    int dq_stages = tt == 64 ? 2 : (tt == 256 ? 2 : 3);
+    int act_stages = tt <= 32 ? 8 : (tt == 64 ? 6 : (tt == 128 ? 6 : 4));
+    if (const char *e = getenv("B200K_TC_DQ_STAGES")) dq_stages = atoi(e);     // tuning overrides
+    if (const char *e = getenv("B200K_TC_ACT_STAGES")) act_stages = atoi(e);
+    int raw_stages = (budget - dq_stages * TC_A_BYTES - act_stages * act_bytes - 1024) / TC_RAW_BYTES;
+    if (raw_stages > 16) raw_stages = 16;
+    if (raw_stages < 2) return 1;
+    // K split (cluster size 1..8): fill the machine's CTA slots in whole waves, keep >= 4 K blocks per CTA
+    const int slots = sm_count() * ctas_per_sm;
     int ksplit = 1;
-    if (tt <= 64)
-        while (ksplit < 8 && col_tiles * tok_tiles * ksplit < sm_count() && kb_total / (ksplit * 2) >= 4) ksplit *= 2;
-    const int kb_per_split = ceil_div(kb_total, ksplit);
-    const int stage_bytes = TC_A_BYTES + tt * TC_BK * 2 + TC_RAW_BYTES;
-    int stages = (200 * 1024) / stage_bytes;
-    if (stages > 6) stages = 6;
-    if (stages > kb_per_split) stages = kb_per_split < 2 ? 2 : kb_per_split;
-    if (ksplit > 1 && stages * TC_A_BYTES < tt * TC_BN * 4) return 1;   // exchange tile must fit in the ring
-    const size_t smem = (size_t)stages * stage_bytes + (3 * stages + 1) * 8 + 16 + 1024;
+    if (tt <= 64) {
+        double best = -1.0;
+        for (int ks = 1; ks <= 8; ++ks) {
+            if (ks > 1 && kb_total / ks < 4) break;
+            if (ks > 1 && dq_stages * TC_A_BYTES < tt * TC_BN * 4) break;   // exchange tile must fit in the operand ring
+            const long ctas = (long)tiles * ks;
+            const long waves = (ctas + slots - 1) / slots;
+            double eff = (double)ctas / (double)(waves * slots);
+            if (ctas < slots / 2) eff *= 0.5;    // far too few CTAs: prefer more splits
+            if (eff > best + 0.02) { best = eff; ksplit = ks; }
+        }
+    }
+    if (const char *e = getenv("B200K_TC_KSPLIT")) {   // tuning override
+        const int v = atoi(e);
+        if (v >= 1 && v <= 8 && (v == 1 || dq_stages * TC_A_BYTES >= tt * TC_BN * 4)) ksplit = v;
+    }
+    if (const char *e = getenv("B200K_TC_RAW_STAGES")) {
+        const int v = atoi(e);
+        if (v >= 2 && v <= raw_stages) raw_stages = v;
+    }
+    const size_t smem = (size_t)dq_stages * TC_A_BYTES + (size_t)act_stages * act_bytes +
+                        (size_t)raw_stages * TC_RAW_BYTES + (2 * act_stages + 2 * dq_stages + 2 * raw_stages + 1) * 8 +
+                        16 + 1024;
 
     // tensor maps: packed weight words (no swizzle) and activations (128-byte swizzle)
-    CUtensorMap wmap, amap;
+    CUtensorMap wmap, amap, smap, zmap;
     int rc;
     if (g.format == FMT_GPTQ) {
         const uint64_t dims[2] = {(uint64_t)g.n, (uint64_t)(g.k / 8)}, str[1] = {(uint64_t)g.s_qwk * 4};
@@ -365,13 +452,27 @@ int gemm_tc_launch(const GemmArgs &g) {
         rc = make_tensor_map(&amap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
     }
     if (rc) return 1;   // layout the TMA cannot describe: the strided family takes it
+    {
+        const uint64_t dims[2] = {(uint64_t)g.n, (uint64_t)(g.k / g.group)}, str[1] = {(uint64_t)g.s_sk * 2};
+        const uint32_t box[2] = {TC_BN, 1};
+        rc = make_tensor_map(&smap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.scales, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+    }
+    if (rc) return 1;
+    zmap = smap;
+    if (g.qzeros) {
+        const uint64_t dims[2] = {(uint64_t)(g.n / 8), (uint64_t)(g.k / g.group)}, str[1] = {(uint64_t)g.s_qzk * 4};
+        const uint32_t box[2] = {TC_BN / 8, 1};
+        rc = make_tensor_map(&zmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, g.qzeros, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc) return 1;
+    }
 
     TcArgs P;
     P.scales = g.scales; P.qzeros = g.qzeros; P.c = g.c;
     P.m = g.m; P.n = g.n; P.k = g.k; P.group = g.group;
     P.s_sk = g.s_sk; P.s_qzk = g.s_qzk; P.s_cm = g.s_cm;
     P.zero_offset = g.zero_offset;
-    P.tt = tt; P.stages = stages; P.ksplit = ksplit; P.kb_per_split = kb_per_split;
+    P.tt = tt; P.dq_stages = dq_stages; P.act_stages = act_stages; P.raw_stages = raw_stages; P.ksplit = ksplit;
+    P.kb_per_split = ceil_div(kb_total, ksplit);
     P.status = (int *)g.ws;   // status word at the start of the scratch buffer
     if (!P.status) return fail(B200K_E_WORKSPACE, "w4a16 gemm (tensor core): workspace is NULL");
 
@@ -396,7 +497,7 @@ int gemm_tc_launch(const GemmArgs &g) {
     attr[0].val.clusterDim.z = ksplit;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, wmap, amap, P);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, wmap, amap, smap, zmap, P);
     if (e != cudaSuccess) {
         cudaGetLastError();
         return fail((int)e, "w4a16 gemm (tensor core) launch: %s", cudaGetErrorString(e));

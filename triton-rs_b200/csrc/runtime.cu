@@ -128,6 +128,11 @@ extern "C" int b200k_set_workspace(void *workspace, size_t bytes) {
     B200K_REQUIRE(workspace != nullptr, B200K_E_NULL, "set_workspace: workspace is NULL");
     B200K_REQUIRE(aligned16(workspace) && bytes >= (1u << 20), B200K_E_WORKSPACE,
                   "set_workspace: need a 16-byte aligned buffer of at least 1 MiB");
+    // status word and arrival counters (first 128 KiB) start at zero; kernels leave them at zero
+    if (cudaMemset(workspace, 0, 128 * 1024) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(B200K_E_WORKSPACE, "set_workspace: cannot clear the buffer (is it device memory?)");
+    }
     std::lock_guard<std::mutex> lk(g_mu);
     if (g_ws[dev] && g_ws_owned[dev]) cudaFree(g_ws[dev]);
     g_ws[dev] = workspace;
