@@ -131,7 +131,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     unsigned long long *bars = reinterpret_cast<unsigned long long *>(raw + (size_t)R * TC_RAW_BYTES);
     // barrier map
     const int B_ACTF = 0;               // [SA] activation tile landed (TMA)
-    const int B_ACTE = SA;              // [SA] activation tile consumed (tcgen05.commit)
+    const int B_ACTE = SA;              // [SA] activation tile consumed (released by the dequant group that sees its MMAs retired)
     const int B_DQF = 2 * SA;           // [SD] operand tile written (one arrival per dequant warp)
     const int B_DQE = 2 * SA + SD;      // [SD] operand tile consumed (tcgen05.commit)
     const int B_RAWF = 2 * SA + 2 * SD;       // [R] packed words landed (TMA)
@@ -222,29 +222,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
+        // One thread; its per-block work is the critical path at small token tiles, so it waits on
+        // one barrier (an operand tile is published only after its activation tile has landed) and
+        // commits to one barrier per block.
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(TC_BN, TT, FMT == FMT_AWQ ? 1 : 0);
+            const uint64_t da0 = FMT == FMT_GPTQ ? umma_desc(smem_u32(a_tile), 16, 1024)       // K-major: 8-row groups 1 KiB apart
+                                                 : umma_desc(smem_u32(a_tile), 8192, 1024);    // MN-major: 64-column halves 8 KiB apart, 8-k groups 1 KiB apart
+            const uint64_t db0 = umma_desc(smem_u32(b_tile), 16, 1024);
+            const uint32_t a_step = (FMT == FMT_GPTQ ? 32 : 2048) >> 4;     // descriptor address units of 16 bytes
             Ring ra(SA), rd(SD);
             for (int i = 0; i < nkb; ++i, ra.next(), rd.next()) {
                 const int sd = rd.slot, sa = ra.slot;
-                wait(B_ACTF + sa, ra.phase);
                 wait(B_DQF + sd, rd.phase);
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(a_tile + (size_t)sd * TC_A_BYTES);
-                const uint32_t b_addr = smem_u32(b_tile + (size_t)sa * b_bytes);
+                const uint64_t da = da0 + (uint64_t)((sd * TC_A_BYTES) >> 4);
+                const uint64_t db = db0 + (uint64_t)((sa * b_bytes) >> 4);
 #pragma unroll
-                for (int j = 0; j < TC_BK / 16; ++j) {
-                    uint64_t da, db;
-                    if (FMT == FMT_GPTQ)
-                        da = umma_desc(a_addr + j * 32, 16, 1024);           // K-major: 8-row groups 1 KiB apart
-                    else
-                        da = umma_desc(a_addr + j * 2048, 8192, 1024);       // MN-major: 64-column halves 8 KiB apart, 8-k groups 1 KiB apart
-                    db = umma_desc(b_addr + j * 32, 16, 1024);
-                    tc_mma_f16(tmem_acc, da, db, idesc, (i > 0 || j > 0) ? 1u : 0u);
-                }
-                // both tiles may be refilled once these MMAs retire
-                tc_commit(smem_u32(&bars[B_DQE + sd]));
-                tc_commit(smem_u32(&bars[B_ACTE + sa]));
+                for (int j = 0; j < TC_BK / 16; ++j)
+                    tc_mma_f16(tmem_acc, da + (uint64_t)(j * a_step), db + (uint64_t)(j * 2), idesc, (i > 0 || j > 0) ? 1u : 0u);
+                tc_commit(smem_u32(&bars[B_DQE + sd]));   // operand tile (and, through it, the activation tile) reusable once these retire
             }
             tc_commit(smem_u32(&bars[B_ACC]));            // accumulator complete
         }
@@ -252,9 +249,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         // ---------------- dequant warps: two groups of 128 threads, group g takes K blocks g, g+2, ... ----------------
         // (the waits, fences and arrivals of one block then overlap the arithmetic of the other group's block)
         const int tg = tid - 32 * TC_DQ_WARP0;
-        const int grp_id = tg >> 7, t = tg & 127;
-        Ring rr(R), rd(SD);
-        if (grp_id == 1) { rr.next(); rd.next(); }
+        const int grp_id = tg >> 7, t = tg & 127, warp_in_group = t >> 5;
+        Ring rr(R), rd(SD), ra(SA), ra_old(SA);   // ra: this block's activation slot; ra_old: that of block i - SD
+        if (grp_id == 1) { rr.next(); rd.next(); ra.next(); }
+        if ((SD ^ grp_id) & 1) ra_old.next();   // the first block this group sees retire is block 0 or block 1
         for (int i = grp_id; i < nkb; i += TC_DQ_GROUPS) {
             const int s = rd.slot, r = rr.slot;
             wait(B_RAWF + r, rr.phase);                               // packed words, scales, zero-points landed
@@ -274,7 +272,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 for (int j = 0; j < 8; ++j) w[j] = rw[j * TC_BN + t];
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bars[B_RAWE + r]));  // this warp is done with the packed tile
-                if (i >= SD) wait(B_DQE + s, rd.phase ^ 1u);              // operand tile no longer read by the tensor core
+                if (i >= SD) {
+                    wait(B_DQE + s, rd.phase ^ 1u);   // block i - SD retired: its operand tile is free, and so is its activation tile
+                    if (warp_in_group == 0 && lane == 0) mbar_arrive(smem_u32(&bars[B_ACTE + ra_old.slot]));
+                    ra_old.next(); ra_old.next();
+                }
                 unsigned char *arow = a_tile + (size_t)s * TC_A_BYTES + t * 128;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
@@ -301,7 +303,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 for (int j = 0; j < 8; ++j) w[j] = rw[(kr + 8 * j) * 16 + n8];
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bars[B_RAWE + r]));
-                if (i >= SD) wait(B_DQE + s, rd.phase ^ 1u);
+                if (i >= SD) {
+                    wait(B_DQE + s, rd.phase ^ 1u);   // block i - SD retired: its operand tile is free, and so is its activation tile
+                    if (warp_in_group == 0 && lane == 0) mbar_arrive(smem_u32(&bars[B_ACTE + ra_old.slot]));
+                    ra_old.next(); ra_old.next();
+                }
                 unsigned char *ahalf = a_tile + (size_t)s * TC_A_BYTES + (n8 >> 3) * 8192;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
@@ -317,9 +323,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             }
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bars[B_DQF + s]));
+            if (lane == 0) {
+                wait(B_ACTF + ra.slot, ra.phase);     // the MMA issuer waits on B_DQF alone
+                mbar_arrive(smem_u32(&bars[B_DQF + s]));
+            }
             rr.next(); rr.next();
             rd.next(); rd.next();
+            ra.next(); ra.next();
         }
         // ---------------- epilogue: TMEM -> registers -> C (or the split-K exchange) ----------------
         if (nkb > 0) {
@@ -406,20 +416,16 @@ int gemm_tc_launch(const GemmArgs &g) {
     int raw_stages = (budget - dq_stages * TC_A_BYTES - act_stages * act_bytes - 1024) / TC_RAW_BYTES;
     if (raw_stages > 16) raw_stages = 16;
     if (raw_stages < 2) return 1;
-    // K split (cluster size 1..8): fill the machine's CTA slots in whole waves, keep >= 4 K blocks per CTA
-    const int slots = sm_count() * ctas_per_sm;
+    // K split (cluster of 1, 2, 4 or 8 CTAs along K).  A CTA costs ~6 us of fill, drain and exchange
+    // whatever its length, so: the fewest CTAs that still occupy most SMs; one more doubling only when
+    // the machine is at most once covered and every CTA keeps a long K range.
     int ksplit = 1;
     if (tt <= 64) {
-        double best = -1.0;
-        for (int ks = 1; ks <= 8; ++ks) {
-            if (ks > 1 && kb_total / ks < 4) break;
-            if (ks > 1 && dq_stages * TC_A_BYTES < tt * TC_BN * 4) break;   // exchange tile must fit in the operand ring
-            const long ctas = (long)tiles * ks;
-            const long waves = (ctas + slots - 1) / slots;
-            double eff = (double)ctas / (double)(waves * slots);
-            if (ctas < slots / 2) eff *= 0.5;    // far too few CTAs: prefer more splits
-            if (eff > best + 0.02) { best = eff; ksplit = ks; }
-        }
+        const int sms = sm_count();
+        while (ksplit < 8 && tiles * ksplit < (sms * 7) / 8 && kb_total / (ksplit * 2) >= 4 &&
+               dq_stages * TC_A_BYTES >= tt * TC_BN * 4)
+            ksplit *= 2;
+        if (ksplit < 8 && ksplit > 1 && tiles * ksplit <= sms && kb_total / (ksplit * 2) >= 24) ksplit *= 2;
     }
     if (const char *e = getenv("B200K_TC_KSPLIT")) {   // tuning override
         const int v = atoi(e);
