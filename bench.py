@@ -365,7 +365,10 @@ def run_gpu_arm(args):
                     "h2d_bytes_per_step": BATCH * H * 2 + BATCH * 4, "d2h_bytes_per_step": BATCH * H * 2},
             "gpu_launches": (layers[0].launches_per_forward) * args.steps,
             "roofline": {"kernel": "attn_split_f16_kernel", "bound": "hbm", "achieved": achieved, "peak": hbm_peak,
-                         "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": None,
+                         "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": peak_kind,
+                         # dram bytes per launch: ncu capture of a smaller launch of this kernel (profiles/
+                         # attn_split_f16_b8_ctx4096.md: 1.033 x algorithmic), scaled to this launch
+                         "traffic": int(attn_bytes * 1.033),
                          "algorithmic_bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms},
             "clocks": clocks,
         }
