@@ -204,6 +204,26 @@ int batched_decode_attention_hm_f16_ws(const b200k_half *q, const b200k_half *k_
                                        float scale, void *workspace, size_t workspace_bytes,
                                        b200k_stream stream);
 
+/* batched_decode_attention_hm_f16 for callers that must not allocate device memory: an engine
+ * that has handed the whole GPU to its own arena, a plugin running inside someone else's
+ * allocator, or a host that may not call cudaMalloc once serving has started.  It has no
+ * counterpart in the reference.  The split-KV partials go to a fixed array that is part of the
+ * library image (B200K_NOALLOC_SCRATCH_BYTES per GPU, resident from library load to process exit)
+ * instead of the workspace; the call performs no cudaMalloc, cudaFree or other allocating call.
+ *   - Shapes whose scratch need (b200k_attention_workspace_bytes) exceeds the array are rejected
+ *     with B200K_E_WORKSPACE and a message naming both sizes; nothing is launched.
+ *   - The first call on each device looks the array's address up (that device must be current):
+ *     make that call before any stream capture begins.
+ *   - All calls on a device share the one array.  Its arrival counters are left at zero by every
+ *     call, so back-to-back calls on one stream are fine; calls that may run at the same time
+ *     on the same GPU (different streams) race on it and must not be made. */
+#define B200K_NOALLOC_SCRATCH_BYTES (8u << 20)
+int batched_decode_attention_hm_f16_noalloc(const b200k_half *q, const b200k_half *k_cache,
+                                            const b200k_half *v_cache, const int32_t *context_lens,
+                                            b200k_half *output, int batch_size, int num_q_heads,
+                                            int num_kv_heads, int head_dim, int max_len, float scale,
+                                            b200k_stream stream);
+
 /* Replaces flash_decode_attn_phase1_f32<HEAD_DIM,BLOCK_KV> (attention.rs:508-585):
  * split s of q head h covers chunk_blocks*block_kv positions from
  * s*chunk_blocks*block_kv, chunk_blocks = (valid_kv_len/num_splits)/block_kv (:538);

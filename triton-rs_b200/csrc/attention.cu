@@ -679,6 +679,47 @@ extern "C" int batched_decode_attention_hm_f16(const b200k_half *q, const b200k_
     return batched_decode_attention_hm_f16_ws(q, k_cache, v_cache, context_lens, output, batch_size, num_q_heads,
                                               num_kv_heads, head_dim, max_len, scale, nullptr, 0, stream);
 }
+// ---- the same kernel for callers that cannot allocate ---------------------------------
+// Scratch for the split-KV partials lives in this file-scope device array instead of a
+// cudaMalloc'd workspace.  Every GPU that loads the library holds it until the process exits.
+// In host code the array's name is only a stand-in; the device address is looked up once per
+// device with cudaGetSymbolAddress and handed to the kernel like any other workspace.
+static __device__ __align__(256) unsigned char g_attn_static_scratch[B200K_NOALLOC_SCRATCH_BYTES];
+
+extern "C" int batched_decode_attention_hm_f16_noalloc(const b200k_half *q, const b200k_half *k_cache,
+                                                       const b200k_half *v_cache, const int32_t *context_lens,
+                                                       b200k_half *output, int batch_size, int num_q_heads,
+                                                       int num_kv_heads, int head_dim, int max_len, float scale,
+                                                       b200k_stream stream) {
+    const char *name = "batched_decode_attention_hm_f16_noalloc";
+    static void *scratch_of_device[16] = {};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 16) {
+        cudaGetLastError();
+        return fail(B200K_E_DEVICE, "%s: no usable current device", name);
+    }
+    if (!scratch_of_device[dev]) {
+        // first call on this device: resolve the array's device address (no allocation happens)
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_attn_static_scratch);
+        if (e != cudaSuccess || !p) {
+            cudaGetLastError();
+            return fail((int)(e != cudaSuccess ? e : cudaErrorInvalidSymbol), "%s: cudaGetSymbolAddress: %s", name,
+                        cudaGetErrorString(e));
+        }
+        scratch_of_device[dev] = p;
+    }
+    const size_t need = b200k_attention_workspace_bytes(batch_size, num_q_heads, num_kv_heads, head_dim, max_len);
+    B200K_REQUIRE(need <= (size_t)B200K_NOALLOC_SCRATCH_BYTES, B200K_E_WORKSPACE,
+                  "%s: this call needs %zu bytes of scratch, the built-in array holds %zu (batch %d, kv heads %d, "
+                  "max_len %d): use batched_decode_attention_hm_f16_ws with a caller-owned workspace",
+                  name, need, (size_t)B200K_NOALLOC_SCRATCH_BYTES, batch_size, num_kv_heads, max_len);
+    return batched_decode_attention_hm_f16_ws(q, k_cache, v_cache, context_lens, output, batch_size, num_q_heads,
+                                              num_kv_heads, head_dim, max_len, scale, scratch_of_device[dev],
+                                              (size_t)B200K_NOALLOC_SCRATCH_BYTES, stream);
+}
+
 extern "C" size_t b200k_attention_workspace_bytes(int batch, int num_q_heads, int num_kv_heads, int head_dim,
                                                   int max_len) {
     if (batch <= 0 || num_kv_heads <= 0 || num_q_heads <= 0 || max_len <= 0 || head_dim != AT_D) return 0;
