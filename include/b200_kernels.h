@@ -258,6 +258,37 @@ int paged_decode_attention_f16(const b200k_half *q, const b200k_half *k_block_po
                                b200k_stream stream);
 
 /* ------------------------------------------------------------------------- */
+/* fused MoE                                                                   */
+/* ------------------------------------------------------------------------- */
+/* The reference has no MoE kernel (a search of its tree finds two comment mentions,
+ * crates/triton-dsl/examples/awq_gemm_int4_typed.rs:63 and
+ * crates/triton-kernels/src/elementwise.rs:222); these entry points follow its conventions for
+ * the parts: GPTQ layout and +1 zero rule of w4a16_gptq_gemm_typed, half-split gate|up rows of
+ * fused_silu_mul_interleaved (elementwise.rs:199-206).
+ *
+ * moe_route_topk_f32: fp32 softmax over experts, top-k (ties: lowest expert index), weights
+ * renormalised to sum 1.  topk_ids [T,k] int32, topk_weights [T,k] fp32.
+ * moe_permute: pair p = t*k + j.  counts [E], offsets [E+1], sorted_pairs [T*k] = pair indices by
+ * expert then by pair index, inverse [T*k] = position of each pair in that order.
+ * fused_moe_gptq_f16: x [T,H] fp16, router_logits [T,E] fp32, stacked expert weights
+ * w13_qweight [E, H/8, 2I] (gate columns then up columns), w13_scales [E, H/G, 2I],
+ * w2_qweight [E, I/8, H], w2_scales [E, I/G, H]; qzeros [E, K/G, N/8] or NULL for the symmetric
+ * zero-point 8; out[t] = sum_j w[t,j] * (silu(g) * u) W2_e.  workspace NULL = default workspace
+ * (fused_moe_workspace_bytes says how much is used). */
+int moe_route_topk_f32(const float *router_logits, int32_t *topk_ids, float *topk_weights,
+                       int num_tokens, int num_experts, int top_k, b200k_stream stream);
+int moe_permute(const int32_t *topk_ids, int32_t *counts, int32_t *offsets, int32_t *sorted_pairs,
+                int32_t *inverse, int num_pairs, int num_experts, b200k_stream stream);
+size_t fused_moe_workspace_bytes(int num_tokens, int hidden, int num_experts, int top_k,
+                                 int intermediate);
+int fused_moe_gptq_f16(const b200k_half *x, const float *router_logits, const int32_t *w13_qweight,
+                       const b200k_half *w13_scales, const int32_t *w13_qzeros,
+                       const int32_t *w2_qweight, const b200k_half *w2_scales,
+                       const int32_t *w2_qzeros, b200k_half *out, int num_tokens, int hidden,
+                       int num_experts, int top_k, int intermediate, int group_size,
+                       void *workspace, size_t workspace_bytes, b200k_stream stream);
+
+/* ------------------------------------------------------------------------- */
 /* bandwidth-bound glue                                                        */
 /* ------------------------------------------------------------------------- */
 

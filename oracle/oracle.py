@@ -360,16 +360,15 @@ def fused_silu_mul_interleaved(gate_up, inter):
 # the reference's conventions for its parts: GPTQ layout, half-split gate|up)
 # ---------------------------------------------------------------------------
 def moe_route(logits, top_k):
-    """fp32 softmax over experts, top-k by probability (ties: lowest expert index
-    first), weights renormalised to sum 1.  Returns (topk_ids [T,k] int32,
-    topk_w [T,k] fp32)."""
+    """fp32 softmax over experts, top-k (ties: lowest expert index first), weights
+    renormalised to sum 1.  Experts are ranked by logit: softmax is monotonic, so this
+    is the top-k of the softmax, and the ranking does not depend on how exp rounds.
+    Returns (topk_ids [T,k] int32, topk_w [T,k] fp32)."""
     x = logits.astype(np.float32)
     m = x.max(axis=1, keepdims=True)
-    p = np.exp(x - m)
-    p = p / p.sum(axis=1, keepdims=True, dtype=np.float32)
-    # stable argsort on -p keeps the lowest index first among equals
-    order = np.argsort(-p, axis=1, kind="stable")[:, :top_k]
-    w = np.take_along_axis(p, order, axis=1)
+    # stable argsort on -x keeps the lowest index first among equals
+    order = np.argsort(-x, axis=1, kind="stable")[:, :top_k]
+    w = np.exp(np.take_along_axis(x, order, axis=1) - m)     # softmax numerators; the denominator cancels
     w = w / w.sum(axis=1, keepdims=True, dtype=np.float32)
     return order.astype(np.int32), w.astype(np.float32)
 

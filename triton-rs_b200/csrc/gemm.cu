@@ -478,7 +478,8 @@ using namespace b200k;
     g.c = (__half *)c; g.m = m_size; g.n = n_size; g.k = k_size; g.group = group_size;                \
     g.s_am = stride_am; g.s_ak = stride_ak; g.s_qwk = stride_qwk; g.s_qwn = stride_qwn;               \
     g.s_sk = stride_sk; g.s_sn = stride_sn; g.s_cm = stride_cm; g.s_cn = stride_cn;                   \
-    g.format = FMT; g.zero_offset = ZO; g.stream = to_stream(stream);
+    g.format = FMT; g.zero_offset = ZO; g.stream = to_stream(stream);                                 \
+    g.seg_offsets = nullptr; g.num_segments = 0;
 
 extern "C" int w4a16_gptq_gemm_f16_ws(const b200k_half *a, const int32_t *qweight, const b200k_half *scales,
                                       const int32_t *qzeros, b200k_half *c, int m_size, int n_size, int k_size,

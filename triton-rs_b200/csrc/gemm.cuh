@@ -17,6 +17,11 @@ struct GemmArgs {
     int s_am, s_ak, s_qwk, s_qwn, s_sk, s_sn, s_qzk, s_qzn, s_cm, s_cn;
     int format;       // WeightFormat
     int zero_offset;  // added to the stored zero nibble (GPTQ GEMM: 1, AWQ: 0)
+    // grouped mode (fused MoE): `a` and `c` hold num_segments row segments back to back, segment e =
+    // rows [seg_offsets[e], seg_offsets[e+1]) (device array), multiplied by weight matrix e of a stack
+    // [num_segments, K/8 (or K), ...] laid out contiguously; m = total rows.  nullptr: ordinary GEMM.
+    const int *seg_offsets;
+    int num_segments;
     void *ws;         // scratch (may be nullptr when the chosen path needs none)
     size_t ws_bytes;
     cudaStream_t stream;

@@ -59,6 +59,9 @@ struct TcArgs {
     int ksplit;        // cluster size along K
     int kb_per_split;  // K blocks per split
     int *status;
+    const int *seg_offsets;   // grouped mode: row segments of A / C, one weight matrix per segment (blockIdx.z)
+    int w_rows_per_seg;       // rows of the packed weight tensor per segment (K/8 for GPTQ, K for AWQ)
+    int g_rows_per_seg;       // rows of the scale / zero tensors per segment (K / group)
 };
 
 // ---- tcgen05 wrappers -------------------------------------------------------------
@@ -141,9 +144,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * TC_BN, m0 = blockIdx.y * TT;
+    const int n0 = blockIdx.x * TC_BN;
+    int m0 = blockIdx.y * TT, m_end = P.m, w_row0 = 0, g_row0 = 0;
+    if (P.seg_offsets) {
+        // grouped mode: this CTA works on segment blockIdx.z with that segment's weights; no K split
+        const int e = blockIdx.z;
+        m0 += P.seg_offsets[e];
+        m_end = P.seg_offsets[e + 1];
+        if (m0 >= m_end) return;            // uniform across the CTA, before any barrier or TMEM allocation
+        w_row0 = e * P.w_rows_per_seg;
+        g_row0 = e * P.g_rows_per_seg;
+    }
     const int kb_total = P.k / TC_BK;
-    const int kb_begin = blockIdx.z * P.kb_per_split;
+    const int kb_begin = P.seg_offsets ? 0 : blockIdx.z * P.kb_per_split;
     const int kb_end = min(kb_total, kb_begin + P.kb_per_split);
     const int nkb = max(0, kb_end - kb_begin);
     uint32_t tmem_cols = 32;
@@ -198,13 +211,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 const uint32_t dst = smem_u32(raw + (size_t)r * TC_RAW_BYTES);
                 mbar_expect_tx(bar, TC_W_BYTES + TC_SC_BYTES + (P.qzeros ? TC_ZP_BYTES : 0));
                 if (FMT == FMT_GPTQ)
-                    tma_load_2d(dst, &wmap, n0, kb * (TC_BK / 8), bar);
+                    tma_load_2d(dst, &wmap, n0, w_row0 + kb * (TC_BK / 8), bar);
                 else
-                    tma_load_2d(dst, &wmap, n0 / 8, kb * TC_BK, bar);
+                    tma_load_2d(dst, &wmap, n0 / 8, w_row0 + kb * TC_BK, bar);
                 // the block's quantisation group rides along: scale row and packed zero-points
                 const int grp = (kb * TC_BK) >> group_shift;
-                tma_load_2d(dst + TC_W_BYTES, &smap, n0, grp, bar);
-                if (P.qzeros) tma_load_2d(dst + TC_W_BYTES + TC_SC_BYTES, &zmap, n0 / 8, grp, bar);
+                tma_load_2d(dst + TC_W_BYTES, &smap, n0, g_row0 + grp, bar);
+                if (P.qzeros) tma_load_2d(dst + TC_W_BYTES + TC_SC_BYTES, &zmap, n0 / 8, g_row0 + grp, bar);
             }
         }
     } else if (warp == 2) {
@@ -355,7 +368,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int m = m0 + c0 + j;
-                        if (m < P.m) P.c[(long)m * P.s_cm + n] = __float2half_rn(__uint_as_float(rr[j]));
+                        if (m < m_end) P.c[(long)m * P.s_cm + n] = __float2half_rn(__uint_as_float(rr[j]));
                     }
                 }
             } else {
@@ -376,7 +389,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             const int rank = (int)cluster.block_rank();
             for (int mm = rank + sub * P.ksplit; mm < TT; mm += 2 * P.ksplit) {
                 const int m = m0 + mm;
-                if (m >= P.m) break;
+                if (m >= m_end) break;
                 float acc = 0.f;
                 for (int r = 0; r < P.ksplit; ++r) acc += cluster.map_shared_rank(red, r)[mm * TC_BN + row];
                 if (n < P.n) P.c[(long)m * P.s_cm + n] = __float2half_rn(acc);
@@ -401,7 +414,10 @@ int gemm_tc_launch(const GemmArgs &g) {
     if (g.k % TC_BK || g.group % TC_BK || (g.group & (g.group - 1)) || g.n % 8) return 1;
     if (g.format == FMT_AWQ && !g.qzeros) return 1;
     if (g.qzeros && (g.s_qzk % 4 || !aligned16(g.qzeros))) return 1;   // zero-point rows travel by TMA: 16-byte pitch
-    const int tt = pick_tt(g.m);
+    const bool grouped = g.seg_offsets != nullptr;
+    // grouped: the token tile follows the average segment; the grid covers the worst case (every row in
+    // one segment) and CTAs past their segment's end return at once
+    const int tt = pick_tt(grouped ? ceil_div(g.m, g.num_segments) : g.m);
     const int col_tiles = ceil_div(g.n, TC_BN), tok_tiles = ceil_div(g.m, tt);
     const int kb_total = g.k / TC_BK;
     const int tiles = col_tiles * tok_tiles;
@@ -420,7 +436,7 @@ int gemm_tc_launch(const GemmArgs &g) {
     // whatever its length, so: the fewest CTAs that still occupy most SMs; one more doubling only when
     // the machine is at most once covered and every CTA keeps a long K range.
     int ksplit = 1;
-    if (tt <= 64) {
+    if (tt <= 64 && !grouped) {
         const int sms = sm_count();
         while (ksplit < 8 && tiles * ksplit < (sms * 7) / 8 && kb_total / (ksplit * 2) >= 4 &&
                dq_stages * TC_A_BYTES >= tt * TC_BN * 4)
@@ -442,12 +458,13 @@ int gemm_tc_launch(const GemmArgs &g) {
     // tensor maps: packed weight words (no swizzle) and activations (128-byte swizzle)
     CUtensorMap wmap, amap, smap, zmap;
     int rc;
+    const uint64_t nseg = grouped ? (uint64_t)g.num_segments : 1;
     if (g.format == FMT_GPTQ) {
-        const uint64_t dims[2] = {(uint64_t)g.n, (uint64_t)(g.k / 8)}, str[1] = {(uint64_t)g.s_qwk * 4};
+        const uint64_t dims[2] = {(uint64_t)g.n, (uint64_t)(g.k / 8) * nseg}, str[1] = {(uint64_t)g.s_qwk * 4};
         const uint32_t box[2] = {TC_BN, TC_BK / 8};
         rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, g.qweight, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
     } else {
-        const uint64_t dims[2] = {(uint64_t)(g.n / 8), (uint64_t)g.k}, str[1] = {(uint64_t)g.s_qwk * 4};
+        const uint64_t dims[2] = {(uint64_t)(g.n / 8), (uint64_t)g.k * nseg}, str[1] = {(uint64_t)g.s_qwk * 4};
         const uint32_t box[2] = {TC_BN / 8, TC_BK};
         rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, g.qweight, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
     }
@@ -459,14 +476,14 @@ int gemm_tc_launch(const GemmArgs &g) {
     }
     if (rc) return 1;   // layout the TMA cannot describe: the strided family takes it
     {
-        const uint64_t dims[2] = {(uint64_t)g.n, (uint64_t)(g.k / g.group)}, str[1] = {(uint64_t)g.s_sk * 2};
+        const uint64_t dims[2] = {(uint64_t)g.n, (uint64_t)(g.k / g.group) * nseg}, str[1] = {(uint64_t)g.s_sk * 2};
         const uint32_t box[2] = {TC_BN, 1};
         rc = make_tensor_map(&smap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.scales, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
     }
     if (rc) return 1;
     zmap = smap;
     if (g.qzeros) {
-        const uint64_t dims[2] = {(uint64_t)(g.n / 8), (uint64_t)(g.k / g.group)}, str[1] = {(uint64_t)g.s_qzk * 4};
+        const uint64_t dims[2] = {(uint64_t)(g.n / 8), (uint64_t)(g.k / g.group) * nseg}, str[1] = {(uint64_t)g.s_qzk * 4};
         const uint32_t box[2] = {TC_BN / 8, 1};
         rc = make_tensor_map(&zmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, g.qzeros, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
         if (rc) return 1;
@@ -479,6 +496,9 @@ int gemm_tc_launch(const GemmArgs &g) {
     P.zero_offset = g.zero_offset;
     P.tt = tt; P.dq_stages = dq_stages; P.act_stages = act_stages; P.raw_stages = raw_stages; P.ksplit = ksplit;
     P.kb_per_split = ceil_div(kb_total, ksplit);
+    P.seg_offsets = g.seg_offsets;
+    P.w_rows_per_seg = g.format == FMT_GPTQ ? g.k / 8 : g.k;
+    P.g_rows_per_seg = g.k / g.group;
     P.status = (int *)g.ws;   // status word at the start of the scratch buffer
     if (!P.status) return fail(B200K_E_WORKSPACE, "w4a16 gemm (tensor core): workspace is NULL");
 
@@ -492,7 +512,7 @@ int gemm_tc_launch(const GemmArgs &g) {
         attr_smem[g.format][dev] = 227 * 1024;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(col_tiles, tok_tiles, ksplit);
+    cfg.gridDim = dim3(col_tiles, tok_tiles, grouped ? g.num_segments : ksplit);
     cfg.blockDim = dim3(TC_THREADS, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = g.stream;
@@ -500,7 +520,7 @@ int gemm_tc_launch(const GemmArgs &g) {
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = ksplit;
+    attr[0].val.clusterDim.z = grouped ? 1 : ksplit;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, wmap, amap, smap, zmap, P);

@@ -1,0 +1,263 @@
+// Fused MoE (top-k routing, token permute, grouped int4 expert GEMMs, silu_mul, weighted
+// un-permute).  The reference has no such kernel; the pieces follow its conventions: GPTQ
+// weight layout of w4a16_gptq_gemm_typed, and the half-split gate|up layout of
+// fused_silu_mul_interleaved (gate = first half of a row, up = second half).
+//
+// Bit-exact contract (the tests compare indices with ==): experts are ranked by router logit,
+// highest first, ties to the lowest expert index (softmax is monotonic, so this is the top-k
+// of the softmax without depending on how exp rounds); pair p = token*k + j; the segmented
+// list orders pairs by expert, then by pair index.
+#include "gemm.cuh"
+
+namespace b200k {
+
+constexpr int MOE_MAX_E = 64;
+constexpr int MOE_MAX_K = 8;
+
+// one thread per token
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const float *__restrict__ logits, int32_t *__restrict__ ids, float *__restrict__ wts, int tokens,
+                 int experts, int top_k) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= tokens) return;
+    const float *x = logits + (long)t * experts;
+    float m = x[0];
+    for (int e = 1; e < experts; ++e) m = fmaxf(m, x[e]);
+    int sel[MOE_MAX_K];
+    float p[MOE_MAX_K], psum = 0.f;
+    for (int j = 0; j < top_k; ++j) {
+        int best = -1;
+        float bv = 0.f;
+        for (int e = 0; e < experts; ++e) {
+            bool taken = false;
+            for (int i = 0; i < j; ++i) taken |= (sel[i] == e);
+            if (taken) continue;
+            const float v = x[e];
+            if (best < 0 || v > bv) {   // strict: the lowest index wins a tie
+                best = e;
+                bv = v;
+            }
+        }
+        sel[j] = best;
+        p[j] = expf(bv - m);            // softmax numerator; the denominator cancels in the renormalisation
+        psum += p[j];
+    }
+    for (int j = 0; j < top_k; ++j) {
+        ids[(long)t * top_k + j] = sel[j];
+        wts[(long)t * top_k + j] = p[j] / psum;
+    }
+}
+
+// Single CTA: counts, offsets, stable segmented order and its inverse.
+__global__ void __launch_bounds__(1024)
+moe_permute_kernel(const int32_t *__restrict__ ids, int pairs, int experts, int32_t *__restrict__ counts,
+                   int32_t *__restrict__ offsets, int32_t *__restrict__ sorted_pairs, int32_t *__restrict__ inv) {
+    __shared__ int s_count[MOE_MAX_E];
+    __shared__ int s_off[MOE_MAX_E + 1];
+    __shared__ int s_run[MOE_MAX_E];          // pairs of each expert placed so far
+    __shared__ int s_warp[32][MOE_MAX_E];     // per-warp counts of the current chunk
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    if (tid < experts) s_count[tid] = 0;
+    __syncthreads();
+    for (int p = tid; p < pairs; p += blockDim.x) atomicAdd(&s_count[ids[p]], 1);   // integer counts: order-independent
+    __syncthreads();
+    if (tid == 0) {
+        int acc = 0;
+        for (int e = 0; e < experts; ++e) {
+            s_off[e] = acc;
+            acc += s_count[e];
+        }
+        s_off[experts] = acc;
+    }
+    if (tid < experts) s_run[tid] = 0;
+    __syncthreads();
+    if (tid <= experts) offsets[tid] = s_off[tid];
+    if (tid < experts) counts[tid] = s_count[tid];
+    // chunks of blockDim pairs in pair order; inside a chunk the rank of a pair among those of its expert is
+    // (pairs of that expert in lower warps) + (in lower lanes of its warp)
+    for (int base = 0; base < pairs; base += blockDim.x) {
+        const int p = base + tid;
+        const int e = p < pairs ? ids[p] : -1;
+        int my_rank = 0;
+        for (int x = 0; x < experts; ++x) {
+            const unsigned mask = __ballot_sync(0xffffffffu, e == x);
+            if (lane == 0) s_warp[warp][x] = __popc(mask);
+            if (e == x) my_rank = __popc(mask & ((1u << lane) - 1u));
+        }
+        __syncthreads();
+        if (e >= 0) {
+            int before = 0;
+            for (int w = 0; w < warp; ++w) before += s_warp[w][e];
+            const int pos = s_off[e] + s_run[e] + before + my_rank;
+            sorted_pairs[pos] = p;
+            inv[p] = pos;
+        }
+        __syncthreads();
+        if (tid < experts) {
+            int tot = 0;
+            for (int w = 0; w < nwarps; ++w) tot += s_warp[w][tid];
+            s_run[tid] += tot;
+        }
+        __syncthreads();
+    }
+}
+
+// x_perm[i, :] = x[sorted_pairs[i] / k, :]   (16 bytes per thread)
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(const __half *__restrict__ x, const int32_t *__restrict__ sorted_pairs, __half *__restrict__ xp,
+                  int pairs, int hidden, int top_k) {
+    const int hv = hidden / 8;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < (long)pairs * hv; i += (long)gridDim.x * blockDim.x) {
+        const int row = (int)(i / hv), c = (int)(i - (long)row * hv);
+        const int tok = sorted_pairs[row] / top_k;
+        reinterpret_cast<uint4 *>(xp)[(long)row * hv + c] = reinterpret_cast<const uint4 *>(x)[(long)tok * hv + c];
+    }
+}
+
+// out[t, :] = sum_j w[t, j] * y_perm[inv[t*k + j], :]   (fp32 sum in slot order, fp16 out)
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const __half *__restrict__ yp, const int32_t *__restrict__ inv, const float *__restrict__ wts,
+                   __half *__restrict__ out, int tokens, int hidden, int top_k) {
+    const int hv = hidden / 8;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < (long)tokens * hv; i += (long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / hv), c = (int)(i - (long)t * hv);
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int j = 0; j < top_k; ++j) {
+            const float w = wts[(long)t * top_k + j];
+            const uint4 v = reinterpret_cast<const uint4 *>(yp)[(long)inv[(long)t * top_k + j] * hv + c];
+            const float2 a = h2_to_f2(v.x), b = h2_to_f2(v.y), cc = h2_to_f2(v.z), d = h2_to_f2(v.w);
+            acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * b.x; acc[3] += w * b.y;
+            acc[4] += w * cc.x; acc[5] += w * cc.y; acc[6] += w * d.x; acc[7] += w * d.y;
+        }
+        uint4 o;
+        o.x = f2_to_h2(acc[0], acc[1]); o.y = f2_to_h2(acc[2], acc[3]);
+        o.z = f2_to_h2(acc[4], acc[5]); o.w = f2_to_h2(acc[6], acc[7]);
+        reinterpret_cast<uint4 *>(out)[(long)t * hv + c] = o;
+    }
+}
+
+struct MoeWs {
+    int32_t *ids, *counts, *offsets, *sorted_pairs, *inv;
+    float *wts;
+    __half *xp, *gu, *act, *yp;
+    size_t bytes;
+};
+static MoeWs moe_ws_layout(void *base, int tokens, int hidden, int experts, int top_k, int inter) {
+    MoeWs w;
+    unsigned char *p = (unsigned char *)base;
+    size_t off = 128 * 1024;   // status word and the counter regions of the other kernels stay untouched
+    auto take = [&](size_t bytes) {
+        unsigned char *r = p + off;
+        off += (bytes + 255) / 256 * 256;
+        return r;
+    };
+    const size_t pairs = (size_t)tokens * top_k;
+    w.ids = (int32_t *)take(pairs * 4);
+    w.wts = (float *)take(pairs * 4);
+    w.counts = (int32_t *)take((size_t)experts * 4);
+    w.offsets = (int32_t *)take((size_t)(experts + 1) * 4);
+    w.sorted_pairs = (int32_t *)take(pairs * 4);
+    w.inv = (int32_t *)take(pairs * 4);
+    w.xp = (__half *)take(pairs * hidden * 2);
+    w.gu = (__half *)take(pairs * 2 * (size_t)inter * 2);
+    w.act = (__half *)take(pairs * (size_t)inter * 2);
+    w.yp = (__half *)take(pairs * hidden * 2);
+    w.bytes = off;
+    return w;
+}
+
+static int grid_for(long work) {
+    long blocks = (work + 255) / 256;
+    const long cap = (long)sm_count() * 16;
+    return (int)(blocks > cap ? cap : blocks);
+}
+
+}  // namespace b200k
+
+using namespace b200k;
+
+extern "C" int moe_route_topk_f32(const float *router_logits, int32_t *topk_ids, float *topk_weights, int num_tokens,
+                                  int num_experts, int top_k, b200k_stream stream) {
+    B200K_REQUIRE(num_tokens >= 0 && num_experts >= 1 && num_experts <= MOE_MAX_E && top_k >= 1 &&
+                      top_k <= MOE_MAX_K && top_k <= num_experts,
+                  B200K_E_SHAPE, "moe_route_topk_f32: tokens %d, experts %d (<= %d), top_k %d (<= %d)", num_tokens,
+                  num_experts, MOE_MAX_E, top_k, MOE_MAX_K);
+    if (num_tokens == 0) return 0;
+    B200K_REQUIRE(router_logits && topk_ids && topk_weights, B200K_E_NULL, "moe_route_topk_f32: NULL pointer");
+    moe_route_kernel<<<ceil_div(num_tokens, 256), 256, 0, to_stream(stream)>>>(router_logits, topk_ids, topk_weights,
+                                                                              num_tokens, num_experts, top_k);
+    return launch_status("moe_route_topk_f32");
+}
+
+extern "C" int moe_permute(const int32_t *topk_ids, int32_t *counts, int32_t *offsets, int32_t *sorted_pairs,
+                           int32_t *inverse, int num_pairs, int num_experts, b200k_stream stream) {
+    B200K_REQUIRE(num_pairs >= 0 && num_experts >= 1 && num_experts <= MOE_MAX_E, B200K_E_SHAPE,
+                  "moe_permute: pairs %d, experts %d (<= %d)", num_pairs, num_experts, MOE_MAX_E);
+    B200K_REQUIRE(topk_ids && counts && offsets && sorted_pairs && inverse, B200K_E_NULL, "moe_permute: NULL pointer");
+    moe_permute_kernel<<<1, 1024, 0, to_stream(stream)>>>(topk_ids, num_pairs, num_experts, counts, offsets,
+                                                         sorted_pairs, inverse);
+    return launch_status("moe_permute");
+}
+
+extern "C" size_t fused_moe_workspace_bytes(int num_tokens, int hidden, int num_experts, int top_k, int intermediate) {
+    if (num_tokens <= 0 || hidden <= 0 || num_experts <= 0 || top_k <= 0 || intermediate <= 0) return 0;
+    return moe_ws_layout(nullptr, num_tokens, hidden, num_experts, top_k, intermediate).bytes;
+}
+
+extern "C" int fused_moe_gptq_f16(const b200k_half *x, const float *router_logits, const int32_t *w13_qweight,
+                                  const b200k_half *w13_scales, const int32_t *w13_qzeros, const int32_t *w2_qweight,
+                                  const b200k_half *w2_scales, const int32_t *w2_qzeros, b200k_half *out,
+                                  int num_tokens, int hidden, int num_experts, int top_k, int intermediate,
+                                  int group_size, void *workspace, size_t workspace_bytes, b200k_stream stream) {
+    const char *name = "fused_moe_gptq_f16";
+    B200K_REQUIRE(x && router_logits && w13_qweight && w13_scales && w2_qweight && w2_scales && out, B200K_E_NULL,
+                  "%s: NULL pointer", name);
+    B200K_REQUIRE(num_tokens >= 0 && num_experts >= 1 && num_experts <= MOE_MAX_E && top_k >= 1 &&
+                      top_k <= MOE_MAX_K && top_k <= num_experts && hidden > 0 && hidden % 64 == 0 &&
+                      intermediate > 0 && intermediate % 64 == 0 && group_size >= 64 &&
+                      (group_size & (group_size - 1)) == 0 && hidden % group_size == 0 &&
+                      intermediate % group_size == 0,
+                  B200K_E_SHAPE, "%s: unsupported extents (tokens %d, hidden %d, experts %d, top_k %d, inter %d, group %d)",
+                  name, num_tokens, hidden, num_experts, top_k, intermediate, group_size);
+    if (num_tokens == 0) return 0;
+    if (!workspace) {
+        int rc = default_workspace(&workspace, &workspace_bytes);
+        if (rc) return rc;
+    }
+    MoeWs w = moe_ws_layout(workspace, num_tokens, hidden, num_experts, top_k, intermediate);
+    B200K_REQUIRE(w.bytes <= workspace_bytes, B200K_E_WORKSPACE, "%s: workspace %zu bytes, need %zu", name,
+                  workspace_bytes, w.bytes);
+    cudaStream_t st = to_stream(stream);
+    const int pairs = num_tokens * top_k;
+    int rc;
+    if ((rc = moe_route_topk_f32(router_logits, w.ids, w.wts, num_tokens, num_experts, top_k, stream))) return rc;
+    if ((rc = moe_permute(w.ids, w.counts, w.offsets, w.sorted_pairs, w.inv, pairs, num_experts, stream))) return rc;
+    moe_gather_kernel<<<grid_for((long)pairs * hidden / 8), 256, 0, st>>>((const __half *)x, w.sorted_pairs, w.xp, pairs,
+                                                                          hidden, top_k);
+    if ((rc = launch_status(name))) return rc;
+
+    GemmArgs g = {};
+    g.format = FMT_GPTQ; g.group = group_size; g.stream = st; g.ws = workspace; g.ws_bytes = workspace_bytes;
+    g.seg_offsets = w.offsets; g.num_segments = num_experts;
+    g.s_ak = g.s_qwn = g.s_sn = g.s_qzn = g.s_cn = 1;
+    // up-projection: [pairs, H] x W13_e [H, 2I] -> [pairs, 2I]
+    g.a = w.xp; g.qweight = w13_qweight; g.scales = (const __half *)w13_scales; g.qzeros = w13_qzeros; g.c = w.gu;
+    g.m = pairs; g.n = 2 * intermediate; g.k = hidden;
+    g.s_am = hidden; g.s_qwk = g.n; g.s_sk = g.n; g.s_qzk = g.n / 8; g.s_cm = g.n;
+    g.zero_offset = w13_qzeros ? 1 : 0;
+    rc = gemm_tc_launch(g);
+    if (rc) return rc == 1 ? fail(B200K_E_SHAPE, "%s: expert GEMM shape not covered by the tensor-core path", name) : rc;
+    if ((rc = fused_silu_mul_interleaved_f16((const b200k_half *)w.gu, (b200k_half *)w.act, intermediate,
+                                             pairs * intermediate, stream)))
+        return rc;
+    // down-projection: [pairs, I] x W2_e [I, H] -> [pairs, H]
+    g.a = w.act; g.qweight = w2_qweight; g.scales = (const __half *)w2_scales; g.qzeros = w2_qzeros; g.c = w.yp;
+    g.n = hidden; g.k = intermediate;
+    g.s_am = intermediate; g.s_qwk = g.n; g.s_sk = g.n; g.s_qzk = g.n / 8; g.s_cm = g.n;
+    g.zero_offset = w2_qzeros ? 1 : 0;
+    rc = gemm_tc_launch(g);
+    if (rc) return rc == 1 ? fail(B200K_E_SHAPE, "%s: expert GEMM shape not covered by the tensor-core path", name) : rc;
+    moe_combine_kernel<<<grid_for((long)num_tokens * hidden / 8), 256, 0, st>>>(w.yp, w.inv, w.wts, (__half *)out,
+                                                                                num_tokens, hidden, top_k);
+    return launch_status(name);
+}
