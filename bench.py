@@ -178,6 +178,87 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def component_metrics(pkg, torch, dev, gen):
+    """The other parts of the compound metric: W4A16 GEMM TFLOP/s and GB/s (configs 0 and 2), decode
+    attention GB/s (config 1), fused MoE (config 3).  Small kernels are replayed from a CUDA graph over
+    rotating weight buffers (> 400 MB in total) so that every launch streams from HBM."""
+    P = pkg.prelude
+    hbm_peak, tf_peak, _ = peaks()
+
+    def graph_time(fn, calls, reps=5):
+        st = torch.cuda.Stream()
+        with torch.cuda.stream(st):
+            for _ in range(3):
+                fn()
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=st):
+            for _ in range(calls):
+                fn()
+        gr.replay()
+        torch.cuda.synchronize()
+        best = 1e30
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); gr.replay(); b.record()
+            torch.cuda.synchronize()
+            best = min(best, a.elapsed_time(b) / calls)
+        return best   # ms per call
+
+    def ri(*s):
+        return torch.randint(-2 ** 31, 2 ** 31 - 1, s, device=dev, dtype=torch.int32, generator=gen)
+
+    out = {}
+    G = 128
+    for fmt, m, k, n in [("gptq", 16, 4096, 4096), ("gptq", 1, 4096, 4096), ("awq", 1, 4096, 28672),
+                         ("awq", 16, 4096, 28672), ("awq", 128, 4096, 6144), ("awq", 1024, 4096, 6144),
+                         ("awq", 1024, 14336, 4096)]:
+        nbuf = max(2, int(400e6 // (k * n // 2)))
+        qws = [ri(k // 8, n) if fmt == "gptq" else ri(k, n // 8) for _ in range(nbuf)]
+        sc = (torch.rand((k // G, n), device=dev, generator=gen) * 0.018 + 0.002).half()
+        qz = ri(k // G, n // 8)
+        a = torch.randn((m, k), device=dev, generator=gen, dtype=torch.float16)
+        c = torch.empty((m, n), device=dev, dtype=torch.float16)
+        i = [0]
+
+        def fn():
+            i[0] = (i[0] + 1) % nbuf
+            (P.gptq_gemm if fmt == "gptq" else P.awq_gemm)(a, qws[i[0]], sc, qz, G, out=c)
+        ms = graph_time(fn, 2 * nbuf)
+        byts = k * n // 2 + (k // G) * n * 2 + (k // G) * n // 2 + 2 * m * k + 2 * m * n
+        out[f"{fmt}_gemm_m{m}_k{k}_n{n}"] = {
+            "us": ms * 1e3, "GB/s": byts / ms / 1e6, "TFLOP/s": 2 * m * k * n / ms / 1e9,
+            "frac_hbm": byts / ms / 1e6 / hbm_peak, "frac_tensor": 2 * m * k * n / ms / 1e9 / tf_peak,
+            "timing": "cold (rotating weight buffers), CUDA-graph replay"}
+        del qws
+    # config 1: decode attention, batch 32, lengths U[512, 8192]
+    b, hq, hkv, d, ml = 32, 32, 8, 128, 8192
+    q = torch.randn((b, hq, d), device=dev, generator=gen, dtype=torch.float16)
+    kc = torch.randn((b, hkv, ml, d), device=dev, generator=gen, dtype=torch.float16)
+    vc = torch.randn((b, hkv, ml, d), device=dev, generator=gen, dtype=torch.float16)
+    lens = torch.randint(512, ml + 1, (b,), device=dev, dtype=torch.int32, generator=gen)
+    ao = torch.empty_like(q)
+    ms = graph_time(lambda: P.batched_decode_attention_hm_f16(q, kc, vc, lens, ao, b, hq, hkv, d, ml, 1.0 / float(np.sqrt(d))), 4)
+    byts = 4096 * int(lens.sum()) + 2 * b * hq * d * 2
+    out["decode_attention_c1"] = {"us": ms * 1e3, "GB/s": byts / ms / 1e6, "frac_hbm": byts / ms / 1e6 / hbm_peak,
+                                  "sum_len": int(lens.sum()), "timing": "inputs (537 MB) larger than L2"}
+    del kc, vc
+    # config 3: fused MoE, Mixtral-8x7B shape
+    T, E, kk, H, I = 512, 8, 2, 4096, 14336
+    w13q, w2q = ri(E, H // 8, 2 * I), ri(E, I // 8, H)
+    w13s = (torch.rand((E, H // G, 2 * I), device=dev, generator=gen) * 0.018 + 0.002).half()
+    w2s = (torch.rand((E, I // G, H), device=dev, generator=gen) * 0.018 + 0.002).half()
+    x = torch.randn((T, H), device=dev, generator=gen, dtype=torch.float16)
+    lg = torch.randn((T, E), device=dev, generator=gen)
+    mo = torch.empty((T, H), dtype=torch.float16, device=dev)
+    ms = graph_time(lambda: P.fused_moe_gptq_f16(x, lg, w13q, w13s, None, w2q, w2s, None, mo, T, H, E, kk, I, G, None, 0), 2)
+    flops = T * kk * (2 * H * 2 * I + 2 * I * H)
+    out["fused_moe_c3"] = {"us": ms * 1e3, "TFLOP/s": flops / ms / 1e9, "frac_tensor": flops / ms / 1e9 / tf_peak,
+                           "weight_GB/s": 726663168 / ms / 1e6,
+                           "timing": "weights (727 MB) larger than L2"}
+    return out
+
+
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -344,6 +425,8 @@ def run_gpu_arm(args):
     attn_ms = sum(a.elapsed_time(b) for a, b in evs) / n_at
     clocks = sampler.stop() if rank == 0 else None
 
+    components = component_metrics(pkg, torch, dev, gen) if world == 1 and not args.no_components else None
+
     status = ctypes.c_int(-1)
     pkg.lib().call("b200k_device_status", ctypes.addressof(status), stream.cuda_stream)
 
@@ -372,6 +455,8 @@ def run_gpu_arm(args):
                          "algorithmic_bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms},
             "clocks": clocks,
         }
+        if components is not None:
+            line["components"] = components
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline()
         print(json.dumps(line))
@@ -386,6 +471,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--no-components", action="store_true", help="skip the per-kernel figures (configs 0-3)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
