@@ -50,7 +50,13 @@ def load_oracle_c():
     so = ROOT / "oracle" / "liboracle_c.so"
     if not so.exists():
         subprocess.run(["make", "-C", str(ROOT / "oracle")], check=True)
-    return ctypes.CDLL(str(so))
+    oc = ctypes.CDLL(str(so))
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    oc.oc_set_num_threads(cores)        # all host cores, whatever OMP_NUM_THREADS the launcher exported
+    return oc
 
 
 def cpu_layer_case(rng, batch, ctx):
@@ -137,45 +143,58 @@ def run_reference_arm(args):
 # GPU arm
 # --------------------------------------------------------------------------------------
 class ClockSampler:
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle reasons of one GPU, read (never set) through NVML every few milliseconds by a
+    background thread while the timed regions run."""
+    BITS = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
-    def __init__(self, index):
-        self.index, self.proc = index, None
+    def __init__(self, torch, index):
+        self.samples, self.reasons, self.max_mhz, self._stop, self._thr = [], set(), None, False, None
+        self.err = None
+        try:
+            import threading
+            import pynvml
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            try:
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            self.nv = pynvml
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self._thr = threading.Thread(target=self._run, daemon=True)
+        except Exception as e:      # no NVML: the line says so instead of inventing numbers
+            self.err = f"{type(e).__name__}: {e}"
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop:
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for name, bit in self.BITS.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception as e:
+                self.err = f"{type(e).__name__}: {e}"
+                return
+            time.sleep(0.004)
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "25", "-i", str(self.index)], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+        if self._thr:
+            self._thr.start()
 
     def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
-        for ln in out.strip().splitlines():
-            f = [x.strip() for x in ln.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1])); mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        self._stop = True
+        if self._thr:
+            self._thr.join(timeout=2)
+        sm = sorted(self.samples)
+        out = {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+               "samples": len(sm)}
+        if self.err:
+            out["note"] = self.err
+        return out
 
 
 def component_metrics(pkg, torch, dev, gen):
@@ -272,8 +291,15 @@ def run_gpu_arm(args):
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch N > 1 through torch.distributed.run")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    def note(msg):
+        if os.environ.get("BENCH_VERBOSE"):
+            print(f"[rank {rank}] {time.strftime('%H:%M:%S')} {msg}", file=sys.stderr, flush=True)
+
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        # a collective that cannot complete ends with an error after 5 minutes instead of waiting for ever
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
+        note("process group up")
     pkg.lib().call("b200k_device_check")
 
     shape = pkg.LayerShape()
@@ -330,9 +356,12 @@ def run_gpu_arm(args):
 
     tp_graphs = []
     if world > 1:
+        note("layers built")
         for i in range(N_SETS):           # first-use set-up outside any capture
             step_tp_eager(i)
         torch.cuda.synchronize()
+        note("eager steps done")
+    if world > 1 and not os.environ.get("BENCH_NO_TP_GRAPH"):
         try:
             for i in range(N_SETS):
                 g = torch.cuda.CUDAGraph()
@@ -356,12 +385,14 @@ def run_gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    note(f"tp graphs: {len(tp_graphs)}")
+    sampler = ClockSampler(torch, local)
+    if rank == 0:
+        sampler.start()              # samples every 25 ms from warm-up to the last timed kernel
     for i in range(max(args.warmup, 3) + N_SETS):    # graph capture happens on first use of each set
         step(i)
     barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    note("warm-up done")
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     ev0.record()
@@ -370,6 +401,7 @@ def run_gpu_arm(args):
     ev1.record()
     barrier()
     ms_total = ev0.elapsed_time(ev1)
+    note(f"timed region done: {ms_total / args.steps:.3f} ms/step")
     if world > 1:
         tt = torch.tensor([ms_total], device=dev)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
@@ -391,9 +423,12 @@ def run_gpu_arm(args):
             ho.copy_(out, non_blocking=True)
         stream.synchronize()              # the caller reads the result before the next decode step
 
+    note("e2e warm-up")
     for i in range(3):
         e2e_step(i)
+    note("e2e warm-up steps issued")
     barrier()
+    note("e2e timed")
     t0 = time.perf_counter()
     for i in range(args.steps):
         e2e_step(i)
@@ -404,6 +439,7 @@ def run_gpu_arm(args):
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         e2e_ms = float(tt.item())
 
+    note(f"e2e done: {e2e_ms:.3f} ms/step")
     # ---- the dominant kernel (decode attention) timed alone on the same rotating caches ----
     q = torch.randn((BATCH, ls.num_q_heads, d), device=dev, generator=gen, dtype=torch.float16)
     lens = torch.full((BATCH,), ml, device=dev, dtype=torch.int32)
@@ -423,7 +459,9 @@ def run_gpu_arm(args):
         a.record(); attn(i); b.record()
     torch.cuda.synchronize()
     attn_ms = sum(a.elapsed_time(b) for a, b in evs) / n_at
+    note("attention timed")
     clocks = sampler.stop() if rank == 0 else None
+    note("sampler stopped")
 
     components = component_metrics(pkg, torch, dev, gen) if world == 1 and not args.no_components else None
 
@@ -461,7 +499,13 @@ def run_gpu_arm(args):
             line["cpu_baseline"] = cpu_baseline()
         print(json.dumps(line))
     if world > 1:
-        dist.destroy_process_group()
+        # Tearing the process group down while CUDA graphs that captured its collectives are alive
+        # can block for ever; every rank is done, so leave without the teardown.
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():

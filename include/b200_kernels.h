@@ -127,6 +127,13 @@ int awq_gemm_int4_f16_ws(const b200k_half *a, const int32_t *qweight, const b200
                          int stride_qzk, int stride_qzn, int stride_cm, int stride_cn,
                          void *workspace, size_t workspace_bytes, b200k_stream stream);
 
+/* Launch plan of the tensor-core GEMM family for a shape, without launching anything (usable without a
+ * GPU): host_plan_out[8] = {token tile, dequant groups, operand-ring depth, activation-ring depth,
+ * weight-ring depth, K split, K blocks per split, output tiles}.  Lets host-side tests check the kernel's
+ * barrier protocol for the exact ring depths that would be used.  No counterpart in the reference. */
+int b200k_gemm_tc_plan(int m_size, int n_size, int k_size, int group_size, int awq,
+                       int *host_plan_out);
+
 /* Replaces dequant_int4_to_fp16<BLOCK>
  * (crates/triton-dsl/examples/ferrum_dequant_int4.rs:28-139): GPTQ full-matrix
  * dequant, output COLUMN-major out[col*K + k] (:80-89), zero = stored nibble with

@@ -34,6 +34,15 @@ int oc_num_threads(void) {
 #endif
 }
 
+/* torchrun exports OMP_NUM_THREADS=1: callers that want every core say so here. */
+void oc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 static inline float r16(float x) { return (float)(f16)x; }
 
 /* nibble position of column j (0..7) inside a packed word.

@@ -69,7 +69,7 @@ SHAPES = [
     # (m, k, n, g)
     (1, 128, 8, 128), (1, 4096, 4096, 128), (1, 512, 264, 64), (1, 14336, 512, 128),
     (2, 256, 72, 128), (3, 512, 136, 128), (16, 4096, 512, 128), (17, 1024, 256, 128),
-    (64, 1024, 384, 128), (128, 512, 256, 128), (130, 256, 264, 32),
+    (64, 1024, 384, 128), (128, 512, 256, 128), (130, 256, 264, 32), (300, 1024, 256, 128), (1024, 512, 128, 128),
 ]
 
 

@@ -1,0 +1,78 @@
+"""Host-side model of the tensor-core GEMM's barrier protocol (three rings, NG dequant groups, one MMA
+issuer), run for the exact ring depths the library would launch with.  A ring-depth combination that
+can deadlock shows up here, on the CPU, as agents left waiting."""
+import ctypes
+
+import pytest
+
+
+def simulate(NG, SD, SA, R, nkb):
+    done = {}
+
+    def completed(b):
+        return done.get(b, 0)
+
+    def wprod():
+        for i in range(nkb):
+            if i >= R:
+                yield ("wait", ("RAWE", i % R), i // R - 1)
+            yield ("arrive", ("RAWF", i % R))
+
+    def aprod():
+        for i in range(nkb):
+            if i >= SA:
+                yield ("wait", ("ACTE", i % SA), i // SA - 1)
+            yield ("arrive", ("ACTF", i % SA))
+
+    def mma():
+        for i in range(nkb):
+            yield ("wait", ("DQF", i % SD), i // SD)
+            yield ("arrive", ("DQE", i % SD))
+
+    def group(g):
+        old = ((g - SD) % NG + NG) % NG
+        for i in range(g, nkb, NG):
+            yield ("wait", ("RAWF", i % R), i // R)
+            yield ("arrive", ("RAWE", i % R))
+            if i >= SD:
+                yield ("wait", ("DQE", i % SD), i // SD - 1)
+                assert old == i - SD
+                yield ("arrive", ("ACTE", old % SA))      # block i - SD retired: its activation slot is free
+                old += NG
+            yield ("wait", ("ACTF", i % SA), i // SA)      # published only once the activation tile has landed
+            yield ("arrive", ("DQF", i % SD))
+
+    agents = [wprod(), aprod(), mma()] + [group(g) for g in range(NG)]
+    pending = [next(a, None) for a in agents]
+    progress = True
+    while progress:
+        progress = False
+        for k, a in enumerate(agents):
+            while pending[k] is not None:
+                op = pending[k]
+                if op[0] == "wait":
+                    if completed(op[1]) <= op[2]:
+                        break
+                else:
+                    done[op[1]] = completed(op[1]) + 1
+                pending[k] = next(a, None)
+                progress = True
+    return [p for p in pending if p is not None]
+
+
+def test_model_detects_a_known_bad_configuration():
+    assert simulate(4, 5, 3, 10, 64)            # activation ring shallower than the operand ring: stuck at the tail
+    assert not simulate(4, 5, 5, 13, 64)
+
+
+@pytest.mark.parametrize("awq", [0, 1])
+@pytest.mark.parametrize("m", [2, 16, 17, 33, 64, 100, 128, 300, 1024, 4096])
+@pytest.mark.parametrize("k,n", [(4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096), (256, 128), (64, 64)])
+def test_launch_plans_cannot_deadlock(pkg, m, k, n, awq):
+    plan = (ctypes.c_int * 8)()
+    pkg.lib().call("b200k_gemm_tc_plan", m, n, k, 64 if k == 64 else 128, awq, ctypes.addressof(plan))
+    tt, ng, sd, sa, r, ksplit, kb_per_split, tiles = list(plan)
+    assert tt in (16, 32, 64, 128, 256) and ng in (2, 4) and 1 <= ksplit <= 8
+    assert sd >= ng and sa >= sd and r >= 2
+    for nkb in {kb_per_split, max(1, (k // 64) - kb_per_split * (ksplit - 1)), 1, 2, 3, 7}:
+        assert not simulate(ng, sd, sa, r, nkb), (plan[:], nkb)

@@ -479,7 +479,7 @@ using namespace b200k;
     g.s_am = stride_am; g.s_ak = stride_ak; g.s_qwk = stride_qwk; g.s_qwn = stride_qwn;               \
     g.s_sk = stride_sk; g.s_sn = stride_sn; g.s_cm = stride_cm; g.s_cn = stride_cn;                   \
     g.format = FMT; g.zero_offset = ZO; g.stream = to_stream(stream);                                 \
-    g.seg_offsets = nullptr; g.num_segments = 0;
+    g.seg_offsets = nullptr; g.num_segments = 0; g.plan_out = nullptr;
 
 extern "C" int w4a16_gptq_gemm_f16_ws(const b200k_half *a, const int32_t *qweight, const b200k_half *scales,
                                       const int32_t *qzeros, b200k_half *c, int m_size, int n_size, int k_size,
@@ -560,6 +560,23 @@ extern "C" int b200k_unpack_gptq_qzeros(const int32_t *qzeros, int8_t *out, int 
 }
 extern "C" int b200k_unpack_awq(const int32_t *packed, int8_t *out, int rows, int n_dim, b200k_stream s) {
     return unpack_launch("b200k_unpack_awq", packed, out, rows, n_dim, 2, 0, to_stream(s));
+}
+
+extern "C" int b200k_gemm_tc_plan(int m_size, int n_size, int k_size, int group_size, int awq, int *host_plan_out) {
+    B200K_REQUIRE(host_plan_out, B200K_E_NULL, "b200k_gemm_tc_plan: NULL pointer");
+    GemmArgs g = {};
+    g.m = m_size; g.n = n_size; g.k = k_size; g.group = group_size;
+    g.format = awq ? FMT_AWQ : FMT_GPTQ;
+    g.s_ak = g.s_qwn = g.s_sn = g.s_qzn = g.s_cn = 1;
+    g.s_am = k_size; g.s_cm = n_size; g.s_sk = n_size; g.s_qzk = n_size / 8;
+    g.s_qwk = awq ? n_size / 8 : n_size;
+    // dummy, 16-byte aligned, never dereferenced: the plan is computed before any tensor map or launch
+    g.a = (const __half *)16; g.qweight = (const int32_t *)16; g.scales = (const __half *)16;
+    g.qzeros = (const int32_t *)16; g.c = (__half *)16;
+    g.plan_out = host_plan_out;
+    for (int i = 0; i < 8; ++i) host_plan_out[i] = 0;
+    const int rc = gemm_tc_launch(g);
+    return rc == 1 ? fail(B200K_E_SHAPE, "b200k_gemm_tc_plan: shape not covered by the tensor-core family") : rc;
 }
 
 extern "C" size_t b200k_gemm_workspace_bytes(int m, int n, int k) {

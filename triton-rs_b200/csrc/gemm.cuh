@@ -22,6 +22,7 @@ struct GemmArgs {
     // [num_segments, K/8 (or K), ...] laid out contiguously; m = total rows.  nullptr: ordinary GEMM.
     const int *seg_offsets;
     int num_segments;
+    int *plan_out;    // host pointer: when set, the tensor-core family writes its launch plan there and launches nothing
     void *ws;         // scratch (may be nullptr when the chosen path needs none)
     size_t ws_bytes;
     cudaStream_t stream;

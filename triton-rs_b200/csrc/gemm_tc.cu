@@ -33,11 +33,11 @@ namespace b200k {
 
 constexpr int TC_BN = 128;        // weight columns per CTA = MMA M
 constexpr int TC_BK = 64;         // K per stage = one 128-byte swizzle row of fp16
-constexpr int TC_DQ_WARPS = 8;    // dequant / epilogue warps, in TC_DQ_GROUPS groups that take alternate K blocks
-constexpr int TC_DQ_GROUPS = 2;
-constexpr int TC_GROUP_WARPS = TC_DQ_WARPS / TC_DQ_GROUPS;
+constexpr int TC_GROUP_WARPS = 4;  // dequant / epilogue warps come in groups of 4 (128 threads = 128 operand rows);
+                                   // NG groups take K blocks round-robin: 2 groups (two CTAs per SM) for small token
+                                   // tiles, 4 groups for large ones, where the tensor pipe would otherwise wait for operands
 constexpr int TC_DQ_WARP0 = 3;    // warps 0, 1, 2: weight producer, MMA issuer, activation producer
-constexpr int TC_THREADS = 32 * (TC_DQ_WARP0 + TC_DQ_WARPS);
+constexpr int tc_threads(int ng) { return 32 * (TC_DQ_WARP0 + TC_GROUP_WARPS * ng); }
 constexpr int TC_A_BYTES = TC_BN * TC_BK * 2;   // 16 KiB dequantised tile
 constexpr int TC_W_BYTES = TC_BN * TC_BK / 2;   // 4 KiB packed weight words of one K block
 constexpr int TC_SC_BYTES = TC_BN * 2;          // the block's scale row (one group) for the 128 columns
@@ -120,8 +120,8 @@ struct Ring {
     }
 };
 
-template <int FMT>
-__global__ void __launch_bounds__(TC_THREADS, 2)
+template <int FMT, int NG>
+__global__ void __launch_bounds__(tc_threads(NG), NG == 2 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap amap,
                const __grid_constant__ CUtensorMap smap, const __grid_constant__ CUtensorMap zmap, TcArgs P) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -259,14 +259,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             tc_commit(smem_u32(&bars[B_ACC]));            // accumulator complete
         }
     } else {
-        // ---------------- dequant warps: two groups of 128 threads, group g takes K blocks g, g+2, ... ----------------
+        // ---------------- dequant warps: NG groups of 128 threads, group g takes K blocks g, g+NG, ... ----------------
         // (the waits, fences and arrivals of one block then overlap the arithmetic of the other group's block)
         const int tg = tid - 32 * TC_DQ_WARP0;
         const int grp_id = tg >> 7, t = tg & 127, warp_in_group = t >> 5;
         Ring rr(R), rd(SD), ra(SA), ra_old(SA);   // ra: this block's activation slot; ra_old: that of block i - SD
-        if (grp_id == 1) { rr.next(); rd.next(); ra.next(); }
-        if ((SD ^ grp_id) & 1) ra_old.next();   // the first block this group sees retire is block 0 or block 1
-        for (int i = grp_id; i < nkb; i += TC_DQ_GROUPS) {
+        for (int j = 0; j < grp_id; ++j) { rr.next(); rd.next(); ra.next(); }
+        // the first block this group sees retire is block (grp_id - SD) mod NG
+        for (int j = 0, first_old = ((grp_id - SD) % NG + NG) % NG; j < first_old; ++j) ra_old.next();
+        for (int i = grp_id; i < nkb; i += NG) {
             const int s = rd.slot, r = rr.slot;
             wait(B_RAWF + r, rr.phase);                               // packed words, scales, zero-points landed
             const unsigned char *slot = raw + (size_t)r * TC_RAW_BYTES;
@@ -288,7 +289,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 if (i >= SD) {
                     wait(B_DQE + s, rd.phase ^ 1u);   // block i - SD retired: its operand tile is free, and so is its activation tile
                     if (warp_in_group == 0 && lane == 0) mbar_arrive(smem_u32(&bars[B_ACTE + ra_old.slot]));
-                    ra_old.next(); ra_old.next();
+#pragma unroll
+                    for (int j = 0; j < NG; ++j) ra_old.next();
                 }
                 unsigned char *arow = a_tile + (size_t)s * TC_A_BYTES + t * 128;
 #pragma unroll
@@ -319,7 +321,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 if (i >= SD) {
                     wait(B_DQE + s, rd.phase ^ 1u);   // block i - SD retired: its operand tile is free, and so is its activation tile
                     if (warp_in_group == 0 && lane == 0) mbar_arrive(smem_u32(&bars[B_ACTE + ra_old.slot]));
-                    ra_old.next(); ra_old.next();
+#pragma unroll
+                    for (int j = 0; j < NG; ++j) ra_old.next();
                 }
                 unsigned char *ahalf = a_tile + (size_t)s * TC_A_BYTES + (n8 >> 3) * 8192;
 #pragma unroll
@@ -340,9 +343,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 wait(B_ACTF + ra.slot, ra.phase);     // the MMA issuer waits on B_DQF alone
                 mbar_arrive(smem_u32(&bars[B_DQF + s]));
             }
-            rr.next(); rr.next();
-            rd.next(); rd.next();
-            ra.next(); ra.next();
+#pragma unroll
+            for (int j = 0; j < NG; ++j) { rr.next(); rd.next(); ra.next(); }
         }
         // ---------------- epilogue: TMEM -> registers -> C (or the split-K exchange) ----------------
         if (nkb > 0) {
@@ -350,11 +352,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             tc_fence_after();
         }
         const int q = warp & 3;                       // TMEM lane quadrant this warp may read
-        const int chunk0 = (warp - TC_DQ_WARP0) >> 2; // the two warps of a quadrant alternate 16-column chunks
+        const int chunk0 = (warp - TC_DQ_WARP0) >> 2; // the NG warps of a quadrant take 16-column chunks round-robin
         const int row = q * 32 + lane;                // accumulator row = weight column n0 + row
         const int n = n0 + row;
         float *red = reinterpret_cast<float *>(a_tile);   // [TT][128] fp32, reuses the ring (all MMAs have retired)
-        for (int c0 = chunk0 * 16; c0 < TT; c0 += 32) {
+        for (int c0 = chunk0 * 16; c0 < TT; c0 += 16 * NG) {
             uint32_t rr[16];
             if (nkb > 0) {
                 tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + c0, rr);
@@ -387,7 +389,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             const int n = n0 + row;
             float *red = reinterpret_cast<float *>(a_tile);
             const int rank = (int)cluster.block_rank();
-            for (int mm = rank + sub * P.ksplit; mm < TT; mm += 2 * P.ksplit) {
+            for (int mm = rank + sub * P.ksplit; mm < TT; mm += NG * P.ksplit) {
                 const int m = m0 + mm;
                 if (m >= m_end) break;
                 float acc = 0.f;
@@ -425,31 +427,44 @@ int gemm_tc_launch(const GemmArgs &g) {
     const int ctas_per_sm = tt <= 64 ? 2 : 1;
     const int budget = (ctas_per_sm == 2 ? 111 : 222) * 1024;
     const int act_bytes = tt * TC_BK * 2;
-    int dq_stages = tt == 64 ? 2 : (tt == 256 ? 2 : 3);
-    int act_stages = tt <= 32 ? 8 : (tt == 64 ? 6 : (tt == 128 ? 6 : 4));
+    const int ng = tt <= 64 ? 2 : 4;                 // dequant groups
+    int dq_stages = tt <= 32 ? 3 : (tt == 64 ? 2 : (tt == 128 ? 5 : 4));
+    int act_stages = tt <= 32 ? 8 : (tt == 64 ? 6 : (tt == 128 ? 5 : 4));
     if (const char *e = getenv("B200K_TC_DQ_STAGES")) dq_stages = atoi(e);     // tuning overrides
     if (const char *e = getenv("B200K_TC_ACT_STAGES")) act_stages = atoi(e);
+    // An activation slot is handed back when the operand tile SD blocks later is recycled, so the last SD
+    // blocks never hand theirs back: the activation ring must be at least as deep as the operand ring, and
+    // the operand ring as deep as there are dequant groups.
+    if (dq_stages < ng) dq_stages = ng;
+    if (act_stages < dq_stages) act_stages = dq_stages;
     int raw_stages = (budget - dq_stages * TC_A_BYTES - act_stages * act_bytes - 1024) / TC_RAW_BYTES;
     if (raw_stages > 16) raw_stages = 16;
     if (raw_stages < 2) return 1;
+    if (const char *e = getenv("B200K_TC_RAW_STAGES")) {
+        const int v = atoi(e);
+        if (v >= 2 && v <= raw_stages) raw_stages = v;
+    }
     // K split (cluster of 1, 2, 4 or 8 CTAs along K).  A CTA costs ~6 us of fill, drain and exchange
     // whatever its length, so: the fewest CTAs that still occupy most SMs; one more doubling only when
     // the machine is at most once covered and every CTA keeps a long K range.
+    // The exchange tile ([tt][128] fp32) reuses the three rings, idle by then.
+    const size_t ring_bytes = (size_t)dq_stages * TC_A_BYTES + (size_t)act_stages * act_bytes + (size_t)raw_stages * TC_RAW_BYTES;
+    const bool can_split = !grouped && ring_bytes >= (size_t)tt * TC_BN * 4;
     int ksplit = 1;
-    if (tt <= 64 && !grouped) {
+    if (can_split) {
         const int sms = sm_count();
-        while (ksplit < 8 && tiles * ksplit < (sms * 7) / 8 && kb_total / (ksplit * 2) >= 4 &&
-               dq_stages * TC_A_BYTES >= tt * TC_BN * 4)
-            ksplit *= 2;
+        while (ksplit < 8 && tiles * ksplit < (sms * 7) / 8 && kb_total / (ksplit * 2) >= 4) ksplit *= 2;
         if (ksplit < 8 && ksplit > 1 && tiles * ksplit <= sms && kb_total / (ksplit * 2) >= 24) ksplit *= 2;
     }
     if (const char *e = getenv("B200K_TC_KSPLIT")) {   // tuning override
         const int v = atoi(e);
-        if (v >= 1 && v <= 8 && (v == 1 || dq_stages * TC_A_BYTES >= tt * TC_BN * 4)) ksplit = v;
+        if (v >= 1 && v <= 8 && (v == 1 || can_split)) ksplit = v;
     }
-    if (const char *e = getenv("B200K_TC_RAW_STAGES")) {
-        const int v = atoi(e);
-        if (v >= 2 && v <= raw_stages) raw_stages = v;
+    if (g.plan_out) {
+        int *o = g.plan_out;
+        o[0] = tt; o[1] = ng; o[2] = dq_stages; o[3] = act_stages; o[4] = raw_stages; o[5] = ksplit;
+        o[6] = ceil_div(kb_total, ksplit); o[7] = tok_tiles * col_tiles;
+        return 0;
     }
     const size_t smem = (size_t)dq_stages * TC_A_BYTES + (size_t)act_stages * act_bytes +
                         (size_t)raw_stages * TC_RAW_BYTES + (2 * act_stages + 2 * dq_stages + 2 * raw_stages + 1) * 8 +
@@ -502,18 +517,19 @@ int gemm_tc_launch(const GemmArgs &g) {
     P.status = (int *)g.ws;   // status word at the start of the scratch buffer
     if (!P.status) return fail(B200K_E_WORKSPACE, "w4a16 gemm (tensor core): workspace is NULL");
 
-    auto kern = g.format == FMT_GPTQ ? gemm_tc_kernel<FMT_GPTQ> : gemm_tc_kernel<FMT_AWQ>;
-    static size_t attr_smem[2][16] = {};
+    auto kern = g.format == FMT_GPTQ ? (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2> : gemm_tc_kernel<FMT_GPTQ, 4>)
+                                     : (ng == 2 ? gemm_tc_kernel<FMT_AWQ, 2> : gemm_tc_kernel<FMT_AWQ, 4>);
+    static bool attr_set[2][2][16] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 16 && attr_smem[g.format][dev] < smem) {
+    if (dev >= 0 && dev < 16 && !attr_set[g.format][ng == 4][dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return fail((int)e, "w4a16 gemm (tensor core): shared memory: %s", cudaGetErrorString(e));
-        attr_smem[g.format][dev] = 227 * 1024;
+        attr_set[g.format][ng == 4][dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(col_tiles, tok_tiles, grouped ? g.num_segments : ksplit);
-    cfg.blockDim = dim3(TC_THREADS, 1, 1);
+    cfg.blockDim = dim3(tc_threads(ng), 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = g.stream;
     cudaLaunchAttribute attr[1];

@@ -273,21 +273,21 @@ kv_append_kernel(const T *__restrict__ nk, const T *__restrict__ nv, T *__restri
     }
 }
 
-// rope(q), rope(k) + append of k, v from a fused QKV row; one CTA per batch row,
+// rope(q), rope(k) + append of k, v from a fused QKV row; grid = (chunks of a row, batch rows),
 // one thread per (head, pair) for q/k and per element pair for v.
 __global__ void __launch_bounds__(256)
 rope_kv_append_kernel(const __half *__restrict__ qkv, const float *__restrict__ cos_t,
                       const float *__restrict__ sin_t, const int32_t *__restrict__ positions,
                       __half *__restrict__ q_out, __half *__restrict__ kc, __half *__restrict__ vc,
                       int32_t *__restrict__ lens_out, int hq, int hkv, int d, int max_len) {
-    const int b = blockIdx.x;
+    const int b = blockIdx.y;
     const int half = d / 2;
     const int pos = positions[b];
-    if (lens_out && threadIdx.x == 0) lens_out[b] = pos + 1;   // rows attention covers after this append
+    if (lens_out && threadIdx.x == 0 && blockIdx.x == 0) lens_out[b] = pos + 1;   // rows attention covers after this append
     const __half *row = qkv + (size_t)b * (hq + 2 * hkv) * d;
     const float *cr = cos_t + (size_t)pos * half, *sr = sin_t + (size_t)pos * half;
     const int rot_pairs = (hq + hkv) * half;
-    for (int i = threadIdx.x; i < rot_pairs + hkv * half; i += blockDim.x) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < rot_pairs + hkv * half; i += gridDim.x * blockDim.x) {
         if (i < rot_pairs) {
             const int h = i / half, p = i - h * half;
             const float c = cr[p], s = sr[p];
@@ -319,8 +319,9 @@ int rope_kv_append_lens_launch(const __half *qkv, const float *cos_t, const floa
     B200K_REQUIRE(hq > 0 && hkv > 0 && d > 0 && d % 2 == 0 && max_len > 0 && batch >= 0, B200K_E_SHAPE,
                   "rope_kv_append_hm_f16: Hq %d, Hkv %d, D %d, max_len %d, batch %d", hq, hkv, d, max_len, batch);
     if (batch == 0) return 0;
-    rope_kv_append_kernel<<<batch, 256, 0, st>>>(qkv, cos_t, sin_t, positions, q_out, kc, vc, lens_out, hq, hkv, d,
-                                                 max_len);
+    const int items = (hq + 2 * hkv) * (d / 2);
+    rope_kv_append_kernel<<<dim3(ceil_div(items, 256), batch), 256, 0, st>>>(qkv, cos_t, sin_t, positions, q_out, kc, vc,
+                                                                             lens_out, hq, hkv, d, max_len);
     return launch_status("rope_kv_append_hm_f16");
 }
 
