@@ -322,6 +322,10 @@ def run_gpu_arm(args):
     ang = torch.arange(ml, dtype=torch.float64)[:, None] * inv_freq[None, :]
     cos, sin = torch.cos(ang).float().to(dev), torch.sin(ang).float().to(dev)
 
+    # N > 1: the library's own peer-to-peer all-reduce inside its captured layer chain;
+    # BENCH_TP_COMM=nccl runs the staged chain with NCCL all-reduces between the stages instead
+    own_comm = world > 1 and os.environ.get("BENCH_TP_COMM", "p2p") == "p2p"
+    comm = pkg.Comm.from_process_group(BATCH * H * 2) if own_comm else None
     layers = []
     for _ in range(N_SETS):
         full = {"qkv": gptq(H, (shape.num_q_heads + 2 * shape.num_kv_heads) * d), "o": gptq(shape.num_q_heads * d, H),
@@ -332,8 +336,10 @@ def run_gpu_arm(args):
         ln2 = (torch.rand(H, device=dev, generator=gen) + 0.5).half()
         kc = torch.randn((BATCH, ls.num_kv_heads, ml, d), device=dev, generator=gen, dtype=torch.float16)
         vc = torch.randn((BATCH, ls.num_kv_heads, ml, d), device=dev, generator=gen, dtype=torch.float16)
-        layers.append(pkg.DecodeLayer(ls, w, ln1, ln2, cos, sin, max_batch=BATCH, max_len=ml, use_graph=(world == 1),
-                                      k_cache=kc, v_cache=vc))
+        layers.append(pkg.DecodeLayer(ls, w, ln1, ln2, cos, sin, max_batch=BATCH, max_len=ml,
+                                      use_graph=(world == 1 or own_comm), k_cache=kc, v_cache=vc))
+        if comm is not None:
+            layers[-1].set_comm(comm)
     hidden = torch.randn((BATCH, H), device=dev, generator=gen, dtype=torch.float16)
     positions = torch.full((BATCH,), CTX, device=dev, dtype=torch.int32)
     out = torch.empty_like(hidden)
@@ -355,13 +361,13 @@ def run_gpu_arm(args):
         L.forward_stage(2, reduced=part2, out=out, batch=BATCH)
 
     tp_graphs = []
-    if world > 1:
+    if world > 1 and not own_comm:
         note("layers built")
         for i in range(N_SETS):           # first-use set-up outside any capture
             step_tp_eager(i)
         torch.cuda.synchronize()
         note("eager steps done")
-    if world > 1 and not os.environ.get("BENCH_NO_TP_GRAPH"):
+    if world > 1 and not own_comm and not os.environ.get("BENCH_NO_TP_GRAPH"):
         try:
             for i in range(N_SETS):
                 g = torch.cuda.CUDAGraph()
@@ -373,7 +379,7 @@ def run_gpu_arm(args):
             torch.cuda.synchronize()
 
     def step(i):
-        if world == 1:
+        if world == 1 or own_comm:
             step_single(i)
         elif tp_graphs:
             tp_graphs[i % N_SETS].replay()
@@ -385,6 +391,7 @@ def run_gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    barrier()                        # ranks enter the first exchange together (its wait is bounded to about a second)
     note(f"tp graphs: {len(tp_graphs)}")
     sampler = ClockSampler(torch, local)
     if rank == 0:
@@ -414,7 +421,7 @@ def run_gpu_arm(args):
     ho = torch.empty((BATCH, H), dtype=torch.float16).pin_memory()
 
     def e2e_step(i):
-        if world == 1:
+        if world == 1 or own_comm:
             layers[i % N_SETS].forward_host(hh, hp, ho)
         else:
             hidden.copy_(hh, non_blocking=True)
@@ -481,7 +488,9 @@ def run_gpu_arm(args):
                        "parallelism": f"tp{world}" if world > 1 else "single GPU",
                        "l2": f"inputs larger than L2: {N_SETS} weight+KV sets rotated, "
                              f"{(2 * BATCH * ls.num_kv_heads * ml * d * 2) / 1e9:.2f} GB of KV per step",
-                       "graph": bool(world == 1 or tp_graphs), "device_status": status.value},
+                       "all_reduce": None if world == 1 else ("own one-shot kernel over NVLink peer memory" if own_comm else "NCCL"),
+                       "graph": bool(world == 1 or own_comm or tp_graphs), "device_status": status.value,
+                       "comm_status": comm.status() if comm is not None else None},
             "e2e": {"value": BATCH / (e2e_ms * 1e-3), "unit": "tok/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": BATCH * H * 2 + BATCH * 4, "d2h_bytes_per_step": BATCH * H * 2},
             "gpu_launches": (layers[0].launches_per_forward) * args.steps,

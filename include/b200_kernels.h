@@ -420,8 +420,30 @@ int b200k_layer_set_norms_rope(b200k_layer *layer, const b200k_half *ln1, const 
                                const float *cos_table, const float *sin_table);
 /* caches [max_batch, num_kv_heads, max_len, D] fp16 head-major, caller-owned. */
 int b200k_layer_set_kv_cache(b200k_layer *layer, b200k_half *k_cache, b200k_half *v_cache);
-/* Peer-to-peer all-reduce for the two row-parallel GEMMs; comm may be NULL (single GPU). */
+/* ---- tensor-parallel exchange: one-shot all-reduce over NVLink peer memory -----------------------
+ * No counterpart in the reference, which is single-GPU (its consumer would call NCCL).  One process
+ * per GPU.  Each rank creates an exchange buffer (flags + two slots of slot_bytes), publishes its
+ * 64-byte CUDA IPC handle, and maps the handles of all ranks (host_all_handles = world x 64 bytes in
+ * rank order; how they travel between processes is the caller's business, e.g. an all-gather over
+ * the process group).  world <= 8, one node.
+ * b200k_comm_allreduce_f16 sums `count` fp16 values (multiple of 8) held in slot `slot` of every
+ * rank, fp32 accumulation in rank order, every rank gets identical bits in `output` (local memory).
+ * `input` non-NULL is first copied into the slot; NULL means the producer wrote the slot directly
+ * (b200k_comm_slot).  Every rank must make the same sequence of calls; use slots alternately (a slot
+ * may be rewritten once a LATER all-reduce has been enqueued behind the one that read it).  The
+ * kernel waits for its peers at most about a second, then sets the status word (b200k_comm_status
+ * != 0) and leaves `output` unwritten.  Plain peer loads and stores only. */
 struct b200k_comm;
+int b200k_comm_create(int rank, int world, size_t slot_bytes, struct b200k_comm **out_comm);
+int b200k_comm_ipc_handle(struct b200k_comm *comm, void *host_handle_64_bytes);
+int b200k_comm_open_peers(struct b200k_comm *comm, const void *host_all_handles);
+int b200k_comm_slot(struct b200k_comm *comm, int slot, b200k_half **host_out_ptr);
+int b200k_comm_allreduce_f16(struct b200k_comm *comm, int slot, const b200k_half *input, b200k_half *output,
+                             size_t count, b200k_stream stream);
+int b200k_comm_status(struct b200k_comm *comm, int *host_status_out, b200k_stream stream);
+void b200k_comm_destroy(struct b200k_comm *comm);
+/* Attach to a layer: the o and down GEMMs then write into slots 0 and 1 and the layer chain runs the
+ * two all-reduces itself (12 launches).  NULL detaches (single GPU). */
 int b200k_layer_set_comm(b200k_layer *layer, struct b200k_comm *comm);
 
 /* Whole layer on device buffers: hidden_in/out [batch, H] fp16, positions [batch] int32

@@ -1,0 +1,136 @@
+"""Peer-to-peer all-reduce and the tensor-parallel layer chain on real GPUs.
+
+One process per GPU (children of the test), rendezvous on 127.0.0.1.  The two-rank cases
+need two visible GPUs and are skipped otherwise; the one-rank case runs everywhere.
+The all-reduce must be bit-exact: fp32 sum of the ranks' fp16 values in rank order, one rounding."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from conftest import ROOT
+
+pytestmark = pytest.mark.gpu
+
+
+def _expected(parts):
+    acc = np.zeros(parts[0].shape, dtype=np.float32)
+    for p in parts:                       # rank order, fp32 accumulate, one rounding to fp16
+        acc = acc + p.astype(np.float32)
+    return acc.astype(np.float16)
+
+
+def test_allreduce_single_rank(pkg):
+    dev = "cuda:0"
+    n = 4096 + 8
+    comm = pkg.Comm(0, 1, n * 2, exchange=None)
+    x = torch.randn(n, device=dev, dtype=torch.float16)
+    out = torch.zeros_like(x)
+    for slot in (0, 1, 0):
+        comm.all_reduce(slot, out, n, input=x)
+        torch.cuda.synchronize()
+        assert torch.equal(out, x)
+    assert comm.status() == 0
+    with pytest.raises(pkg.B200KError):
+        comm.all_reduce(0, torch.zeros(n + 512, device=dev, dtype=torch.float16), n + 512, input=None)   # larger than a slot
+    with pytest.raises(pkg.B200KError):
+        comm.all_reduce(2, out, n, input=x)              # no such slot
+    comm.close()
+
+
+def _rank_main(rank, world, port, q):
+    try:
+        sys.path.insert(0, str(ROOT))
+        sys.path.insert(0, str(ROOT / "oracle"))
+        sys.path.insert(0, str(ROOT / "tests"))
+        import importlib
+        import torch.distributed as dist
+        import oracle as o
+        from test_layer_gpu import make_layer
+        pkg = importlib.import_module("triton-rs_b200")
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+
+        def t(a):
+            return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+        # ---- all-reduce alone: several sizes, both slots, staged input and in-place slot ----
+        n_max = 64 * 4096
+        comm = pkg.Comm.from_process_group(n_max * 2)
+        rng = np.random.default_rng(7)
+        for it, n in enumerate([8, 4096, 64 * 4096, 1000 * 8, 64 * 4096]):
+            parts = [rng.standard_normal(n).astype(np.float16) for _ in range(world)]   # same stream of numbers on every rank
+            out = torch.zeros(n, device=dev, dtype=torch.float16)
+            dist.barrier()                # the kernel waits for its peers for about a second only
+            comm.all_reduce(it & 1, out, n, input=t(parts[rank]))
+            torch.cuda.synchronize()
+            got = out.cpu().numpy()
+            assert np.array_equal(got.view(np.uint16), _expected(parts).view(np.uint16)), f"all-reduce n={n}"
+        assert comm.status() == 0
+
+        # ---- tensor-parallel layer (own all-reduce inside the captured chain) against the oracle ----
+        rng = np.random.default_rng(17)
+        B, H, hq, hkv, d, I, G, ml = 3, 256, 4, 2, 128, 512, 128, 40
+        p = make_layer(o, rng, H, hq, hkv, d, I, G, ml)
+        shape = pkg.LayerShape(H, hq, hkv, d, I, G, 1e-5)
+        ls = shape.local(world)
+        full = {k: tuple(None if x is None else t(x) for x in p[k]) for k in ("qkv", "o", "gate_up", "down")}
+        w = pkg.shard_layer_weights(full, shape, rank, world)
+        kc = rng.standard_normal((B, hkv, ml, d)).astype(np.float16)
+        vc = rng.standard_normal((B, hkv, ml, d)).astype(np.float16)
+        per = hkv // world
+        layer = pkg.DecodeLayer(ls, w, t(p["ln1"]), t(p["ln2"]), t(p["cos"]), t(p["sin"]), max_batch=4, max_len=ml,
+                                use_graph=True, k_cache=t(kc[:, rank * per:(rank + 1) * per]),
+                                v_cache=t(vc[:, rank * per:(rank + 1) * per]))
+        layer.set_comm(comm)
+        assert layer.launches_per_forward == 12
+        for step, pos in enumerate([[5, 0, 38], [6, 1, 39], [7, 2, 3]]):     # later steps replay the captured graph
+            pos = np.array(pos, dtype=np.int32)
+            hidden = rng.standard_normal((B, H)).astype(np.float16)
+            ref = o.decode_layer(hidden, p, kc, vc, pos)
+            dist.barrier()
+            out = layer.forward(t(hidden), t(pos))
+            torch.cuda.synchronize()
+            got = out.float().cpu().numpy()
+            err = np.abs(got - ref).max()
+            assert np.isfinite(got).all() and np.allclose(got, ref, rtol=2e-2, atol=2e-2), f"tp layer step {step}: {err}"
+            gathered = [None] * world
+            dist.all_gather_object(gathered, got.tobytes())
+            assert all(g == gathered[0] for g in gathered), "ranks disagree"
+        assert comm.status() == 0
+        dist.barrier()
+        layer.close()
+        comm.close()
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        q.put((rank, "".join(traceback.format_exception(e))))
+
+
+@pytest.mark.timeout(300)
+def test_two_ranks_allreduce_and_tp_layer():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world, port = 2, 29731
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = {}
+    try:
+        for _ in range(world):
+            r, msg = q.get(timeout=240)
+            results[r] = msg
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    assert all(v == "ok" for v in results.values()), results

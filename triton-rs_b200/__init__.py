@@ -7,4 +7,4 @@ prelude over torch-owned device memory (`prelude`), and holds the build recipe
 """
 from ._lib import B200KError, Library, lib, parse_header  # noqa: F401
 from . import prelude  # noqa: F401
-from .layer import DecodeLayer, LayerShape, shard_columns, shard_layer_weights, shard_rows  # noqa: F401
+from .layer import Comm, DecodeLayer, LayerShape, shard_columns, shard_layer_weights, shard_rows  # noqa: F401

@@ -10,7 +10,10 @@ namespace b200k {
 int rope_kv_append_lens_launch(const __half *qkv, const float *cos_t, const float *sin_t, const int32_t *positions,
                                __half *q_out, __half *kc, __half *vc, int32_t *lens_out, int hq, int hkv, int d,
                                int max_len, int batch, cudaStream_t st);
-int comm_allreduce_f16(struct ::b200k_comm *comm, __half *buf, size_t count, cudaStream_t st);
+// peer-to-peer all-reduce (comm.cu): the partial sums sit in slot `slot` of every rank's exchange buffer
+int comm_allreduce_f16(struct ::b200k_comm *comm, int slot, __half *out, size_t count, cudaStream_t st);
+__half *comm_slot(struct ::b200k_comm *comm, int slot);
+size_t comm_slot_capacity(struct ::b200k_comm *comm);
 }  // namespace b200k
 
 struct b200k_layer {
@@ -79,10 +82,18 @@ static int stage2(b200k_layer *L, const b200k_half *dn_red, b200k_half *out, int
 static int chain(b200k_layer *L, const b200k_half *hidden, const int32_t *positions, b200k_half *out, int b,
                  b200k_stream st) {
     int rc;
-    if ((rc = stage0(L, hidden, positions, L->o, b, st))) return rc;
-    if (L->comm && (rc = comm_allreduce_f16(L->comm, (__half *)L->o, (size_t)b * L->cfg.hidden, to_stream(st)))) return rc;
-    if ((rc = stage1(L, hidden, L->o, L->dn, b, st))) return rc;
-    if (L->comm && (rc = comm_allreduce_f16(L->comm, (__half *)L->dn, (size_t)b * L->cfg.hidden, to_stream(st)))) return rc;
+    const size_t count = (size_t)b * L->cfg.hidden;
+    if (!L->comm) {
+        if ((rc = stage0(L, hidden, positions, L->o, b, st))) return rc;
+        if ((rc = stage1(L, hidden, L->o, L->dn, b, st))) return rc;
+        return stage2(L, L->dn, out, b, st);
+    }
+    // tensor parallel: the row-parallel GEMMs write their partial sums into the exchange buffer the
+    // peers can read; the all-reduce leaves the full sum in the local buffer the next stage reads
+    if ((rc = stage0(L, hidden, positions, (b200k_half *)comm_slot(L->comm, 0), b, st))) return rc;
+    if ((rc = comm_allreduce_f16(L->comm, 0, (__half *)L->o, count, to_stream(st)))) return rc;
+    if ((rc = stage1(L, hidden, L->o, (b200k_half *)comm_slot(L->comm, 1), b, st))) return rc;
+    if ((rc = comm_allreduce_f16(L->comm, 1, (__half *)L->dn, count, to_stream(st)))) return rc;
     return stage2(L, L->dn, out, b, st);
 }
 
@@ -177,6 +188,9 @@ extern "C" int b200k_layer_set_kv_cache(b200k_layer *L, b200k_half *k_cache, b20
 }
 extern "C" int b200k_layer_set_comm(b200k_layer *L, struct b200k_comm *comm) {
     B200K_REQUIRE(L, B200K_E_NULL, "b200k_layer_set_comm: layer is NULL");
+    B200K_REQUIRE(!comm || comm_slot_capacity(comm) >= (size_t)L->cfg.max_batch * L->cfg.hidden * 2, B200K_E_SHAPE,
+                  "b200k_layer_set_comm: exchange slots of %zu bytes are smaller than max_batch x hidden fp16 (%zu bytes)",
+                  comm_slot_capacity(comm), (size_t)L->cfg.max_batch * L->cfg.hidden * 2);
     L->comm = comm;
     drop_graphs(L);
     return 0;

@@ -91,6 +91,60 @@ def shard_layer_weights(weights, shape: LayerShape, rank, world, fmt="gptq"):
     }
 
 
+class Comm:
+    """Exchange buffer of one tensor-parallel rank for the library's peer-to-peer all-reduce.
+
+    `exchange(handle: bytes) -> list[bytes]` must return the 64-byte handles of all ranks in rank order
+    (an all-gather between the processes, one per GPU, of one node)."""
+
+    def __init__(self, rank: int, world: int, slot_bytes: int, exchange):
+        self._L = lib()
+        self.rank, self.world, self.slot_bytes = rank, world, slot_bytes
+        handle = ctypes.c_void_p()
+        self._L.call("b200k_comm_create", rank, world, slot_bytes, ctypes.addressof(handle))
+        self.handle = handle.value
+        mine = ctypes.create_string_buffer(64)
+        self._L.call("b200k_comm_ipc_handle", self.handle, ctypes.addressof(mine))
+        handles = [bytes(mine.raw)] if world == 1 else list(exchange(bytes(mine.raw)))
+        if len(handles) != world or any(len(h) != 64 for h in handles):
+            raise ValueError("exchange() must return one 64-byte handle per rank")
+        blob = ctypes.create_string_buffer(b"".join(handles), 64 * world)
+        self._L.call("b200k_comm_open_peers", self.handle, ctypes.addressof(blob))
+
+    @classmethod
+    def from_process_group(cls, slot_bytes: int, group=None):
+        """One rank per GPU over an initialised torch.distributed process group (handles travel as
+        Python objects through the group's all-gather)."""
+        import torch.distributed as dist
+
+        def exchange(h):
+            out = [None] * dist.get_world_size(group)
+            dist.all_gather_object(out, h, group=group)
+            return out
+        return cls(dist.get_rank(group), dist.get_world_size(group), slot_bytes, exchange)
+
+    def slot(self, slot: int) -> int:
+        """Device address of slot 0 or 1 of this rank's buffer."""
+        p = ctypes.c_void_p()
+        self._L.call("b200k_comm_slot", self.handle, slot, ctypes.addressof(p))
+        return p.value
+
+    def all_reduce(self, slot: int, output, count: int, input=None, stream=None):
+        st = stream if stream is not None else torch.cuda.current_stream().cuda_stream
+        self._L.call("b200k_comm_allreduce_f16", self.handle, slot, input, output, count, st)
+        return output
+
+    def status(self) -> int:
+        v = ctypes.c_int(-1)
+        self._L.call("b200k_comm_status", self.handle, ctypes.addressof(v), torch.cuda.current_stream().cuda_stream)
+        return v.value
+
+    def close(self):
+        if self.handle:
+            self._L.raw("b200k_comm_destroy")(self.handle)
+            self.handle = None
+
+
 class DecodeLayer:
     """One decode layer on one GPU (one tensor-parallel rank)."""
     ORDER = ("qkv", "o", "gate_up", "down")
@@ -120,6 +174,11 @@ class DecodeLayer:
     def set_kv_cache(self, k_cache, v_cache):
         self.k_cache, self.v_cache = k_cache, v_cache
         self._L.call("b200k_layer_set_kv_cache", self.handle, k_cache, v_cache)
+
+    def set_comm(self, comm: "Comm | None"):
+        """Attach the exchange buffer: forward() then runs the two all-reduces of a tensor-parallel layer itself."""
+        self.comm = comm
+        self._L.call("b200k_layer_set_comm", self.handle, comm.handle if comm is not None else None)
 
     def _stream(self, stream):
         return stream if stream is not None else torch.cuda.current_stream().cuda_stream
