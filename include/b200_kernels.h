@@ -128,8 +128,9 @@ int awq_gemm_int4_f16_ws(const b200k_half *a, const int32_t *qweight, const b200
                          void *workspace, size_t workspace_bytes, b200k_stream stream);
 
 /* Launch plan of the tensor-core GEMM family for a shape, without launching anything (usable without a
- * GPU): host_plan_out[8] = {token tile, dequant groups, operand-ring depth, activation-ring depth,
- * weight-ring depth, K split, K blocks per split, output tiles}.  Lets host-side tests check the kernel's
+ * GPU): host_plan_out[10] = {token tile, dequant groups, operand-ring depth, activation-ring depth,
+ * weight-ring depth, K split, K blocks per split, output tiles, MMA-issuing warps, 1 if the dequantised
+ * operand tile lives in tensor memory (0: shared memory)}.  Lets host-side tests check the kernel's
  * barrier protocol for the exact ring depths that would be used.  No counterpart in the reference. */
 int b200k_gemm_tc_plan(int m_size, int n_size, int k_size, int group_size, int awq,
                        int *host_plan_out);
@@ -405,7 +406,8 @@ typedef struct b200k_layer_config {
     int max_batch;
     int max_len;         /* KV cache rows per (sequence, kv head) */
     float rms_eps;
-    int use_graph;       /* capture the chain in a CUDA graph on first use per batch size */
+    int use_graph;       /* capture the call in a CUDA graph on first use per (batch size, buffer addresses):
+                          * a decode loop that reuses its buffers replays one graph, copies included */
     int reserved[5];     /* zero */
 } b200k_layer_config;
 

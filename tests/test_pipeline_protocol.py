@@ -1,12 +1,12 @@
-"""Host-side model of the tensor-core GEMM's barrier protocol (three rings, NG dequant groups, one MMA
-issuer), run for the exact ring depths the library would launch with.  A ring-depth combination that
+"""Host-side model of the tensor-core GEMM's barrier protocol (three rings, NG dequant groups, one or two
+MMA issuers that take the K blocks alternately), run for the exact ring depths the library would launch with.  A ring-depth combination that
 can deadlock shows up here, on the CPU, as agents left waiting."""
 import ctypes
 
 import pytest
 
 
-def simulate(NG, SD, SA, R, nkb):
+def simulate(NG, SD, SA, R, nkb, NMMA=1):
     done = {}
 
     def completed(b):
@@ -24,8 +24,8 @@ def simulate(NG, SD, SA, R, nkb):
                 yield ("wait", ("ACTE", i % SA), i // SA - 1)
             yield ("arrive", ("ACTF", i % SA))
 
-    def mma():
-        for i in range(nkb):
+    def mma(w):
+        for i in range(w, nkb, NMMA):
             yield ("wait", ("DQF", i % SD), i // SD)
             yield ("arrive", ("DQE", i % SD))
 
@@ -42,7 +42,7 @@ def simulate(NG, SD, SA, R, nkb):
             yield ("wait", ("ACTF", i % SA), i // SA)      # published only once the activation tile has landed
             yield ("arrive", ("DQF", i % SD))
 
-    agents = [wprod(), aprod(), mma()] + [group(g) for g in range(NG)]
+    agents = [wprod(), aprod()] + [mma(w) for w in range(NMMA)] + [group(g) for g in range(NG)]
     pending = [next(a, None) for a in agents]
     progress = True
     while progress:
@@ -69,10 +69,12 @@ def test_model_detects_a_known_bad_configuration():
 @pytest.mark.parametrize("m", [2, 16, 17, 33, 64, 100, 128, 300, 1024, 4096])
 @pytest.mark.parametrize("k,n", [(4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096), (256, 128), (64, 64)])
 def test_launch_plans_cannot_deadlock(pkg, m, k, n, awq):
-    plan = (ctypes.c_int * 8)()
+    plan = (ctypes.c_int * 10)()
     pkg.lib().call("b200k_gemm_tc_plan", m, n, k, 64 if k == 64 else 128, awq, ctypes.addressof(plan))
-    tt, ng, sd, sa, r, ksplit, kb_per_split, tiles = list(plan)
+    tt, ng, sd, sa, r, ksplit, kb_per_split, tiles, nmma, in_tmem = list(plan)
     assert tt in (16, 32, 64, 128, 256) and ng in (2, 4) and 1 <= ksplit <= 8
-    assert sd >= ng and sa >= sd and r >= 2
+    assert sd >= ng and sa >= sd and r >= 2 and nmma in (1, 2) and in_tmem in (0, 1)
+    if in_tmem:       # tensor memory: 256 columns per CTA when two CTAs share an SM, 512 otherwise
+        assert max(32, nmma * tt) + 32 * sd <= (256 if tt <= 64 else 512)
     for nkb in {kb_per_split, max(1, (k // 64) - kb_per_split * (ksplit - 1)), 1, 2, 3, 7}:
-        assert not simulate(ng, sd, sa, r, nkb), (plan[:], nkb)
+        assert not simulate(ng, sd, sa, r, nkb, nmma), (plan[:], nkb)

@@ -574,7 +574,7 @@ extern "C" int b200k_gemm_tc_plan(int m_size, int n_size, int k_size, int group_
     g.a = (const __half *)16; g.qweight = (const int32_t *)16; g.scales = (const __half *)16;
     g.qzeros = (const int32_t *)16; g.c = (__half *)16;
     g.plan_out = host_plan_out;
-    for (int i = 0; i < 8; ++i) host_plan_out[i] = 0;
+    for (int i = 0; i < 10; ++i) host_plan_out[i] = 0;
     const int rc = gemm_tc_launch(g);
     return rc == 1 ? fail(B200K_E_SHAPE, "b200k_gemm_tc_plan: shape not covered by the tensor-core family") : rc;
 }

@@ -36,7 +36,7 @@ constexpr int TC_BK = 64;         // K per stage = one 128-byte swizzle row of f
 constexpr int TC_GROUP_WARPS = 4;  // dequant / epilogue warps come in groups of 4 (128 threads = 128 operand rows);
                                    // NG groups take K blocks round-robin: 2 groups (two CTAs per SM) for small token
                                    // tiles, 4 groups for large ones, where the tensor pipe would otherwise wait for operands
-constexpr int TC_DQ_WARP0 = 3;    // warps 0, 1, 2: weight producer, MMA issuer, activation producer
+constexpr int TC_DQ_WARP0 = 4;    // warps 0..3: weight producer, MMA issuer, second MMA issuer (small token tiles), activation producer
 constexpr int tc_threads(int ng) { return 32 * (TC_DQ_WARP0 + TC_GROUP_WARPS * ng); }
 constexpr int TC_A_BYTES = TC_BN * TC_BK * 2;   // 16 KiB dequantised tile
 constexpr int TC_W_BYTES = TC_BN * TC_BK / 2;   // 4 KiB packed weight words of one K block
@@ -87,6 +87,28 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t desc_a, uin
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// The same with the A operand read from tensor memory: 128 lanes = 128 operand rows, 8 columns of
+// 32 bits = 16 fp16 values of K per row.
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 columns of this warp's 32 lanes: register j of lane l -> TMEM (lane base + l, column base + j)
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -120,7 +142,15 @@ struct Ring {
     }
 };
 
-template <int FMT, int NG>
+// TS: the dequantised operand tile goes to tensor memory (tcgen05.st) instead of shared memory and the
+// MMA reads it from there.  GPTQ only: a thread that owns weight column n holds, word by word, 8
+// consecutive k of that column, which is exactly one TMEM lane (operand row) and 4 columns of it.
+// It saves the 16 KiB shared-memory write and the 16 KiB read the tensor pipe would make per K block.
+// NMMA = 2: two issuing warps, each with its own accumulator, take the K blocks alternately (block i goes
+// to issuer i % 2, which is also dequant group i % 2 when there are two groups); the epilogue adds the two
+// accumulators.  At token tiles of 16..64 one thread cannot issue 4 MMAs, wait and commit fast enough to
+// keep up with the operand stream; at 128 and above the MMAs themselves take longer than their issue.
+template <int FMT, int NG, bool TS, int NMMA>
 __global__ void __launch_bounds__(tc_threads(NG), NG == 2 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap amap,
                const __grid_constant__ CUtensorMap smap, const __grid_constant__ CUtensorMap zmap, TcArgs P) {
@@ -128,8 +158,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int SD = P.dq_stages, SA = P.act_stages, R = P.raw_stages, TT = P.tt;
     const int b_bytes = TT * TC_BK * 2;
-    unsigned char *a_tile = smem;                               // [SD][16 KiB]
-    unsigned char *b_tile = a_tile + (size_t)SD * TC_A_BYTES;   // [SA][TT * 128]
+    unsigned char *a_tile = smem;                               // [SD][16 KiB] (absent when the operand tile lives in TMEM)
+    unsigned char *b_tile = a_tile + (TS ? 0 : (size_t)SD * TC_A_BYTES);   // [SA][TT * 128]
     unsigned char *raw = b_tile + (size_t)SA * b_bytes;         // [R][4 KiB]
     unsigned long long *bars = reinterpret_cast<unsigned long long *>(raw + (size_t)R * TC_RAW_BYTES);
     // barrier map
@@ -159,8 +189,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     const int kb_begin = P.seg_offsets ? 0 : blockIdx.z * P.kb_per_split;
     const int kb_end = min(kb_total, kb_begin + P.kb_per_split);
     const int nkb = max(0, kb_end - kb_begin);
+    // TMEM columns: NMMA fp32 accumulators [128 lanes][TT]; with TS, SD operand tiles of 32 columns behind them
+    const uint32_t a_col0 = NMMA * TT < 32 ? 32 : NMMA * TT;
     uint32_t tmem_cols = 32;
-    while ((int)tmem_cols < TT) tmem_cols <<= 1;
+    while (tmem_cols < (TS ? a_col0 + 32u * SD : (uint32_t)TT)) tmem_cols <<= 1;
 
     if (tid == 0) {
         for (int s = 0; s < SA; ++s) {
@@ -175,7 +207,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             mbar_init(smem_u32(&bars[B_RAWF + r]), 1);
             mbar_init(smem_u32(&bars[B_RAWE + r]), TC_GROUP_WARPS);
         }
-        mbar_init(smem_u32(&bars[B_ACC]), 1);
+        mbar_init(smem_u32(&bars[B_ACC]), NMMA);
         *abort_flag = 0;
         mbar_init_fence();
     }
@@ -189,8 +221,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     const uint32_t tmem_acc = *tmem_slot;
 
     auto wait = [&](int bar_idx, uint32_t parity) {
-        if (*abort_flag) return;
-        if (!mbar_wait_bounded(smem_u32(&bars[bar_idx]), parity)) {
+        const uint32_t bar = smem_u32(&bars[bar_idx]);
+        if (mbar_try_wait(bar, parity)) return;      // the common case costs one instruction
+        if (*abort_flag) return;                     // some wait already gave up: drain without waiting again
+        if (!mbar_wait_bounded(bar, parity)) {
             *abort_flag = 1;
             atomicExch(P.status, 2);
         }
@@ -220,7 +254,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 if (P.qzeros) tma_load_2d(dst + TC_W_BYTES + TC_SC_BYTES, &zmap, n0 / 8, g_row0 + grp, bar);
             }
         }
-    } else if (warp == 2) {
+    } else if (warp == 3) {
         // ---------------- TMA producer, activation tiles: SA blocks ahead ----------------
         if (lane == 0) {
             tma_prefetch_desc(&amap);
@@ -233,36 +267,47 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 tma_load_2d(smem_u32(b_tile + (size_t)s * b_bytes), &amap, (kb_begin + i) * TC_BK, m0, bar);
             }
         }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        // One thread; its per-block work is the critical path at small token tiles, so it waits on
-        // one barrier (an operand tile is published only after its activation tile has landed) and
+    } else if (warp == 1 || warp == 2) {
+        // ---------------- MMA issuers ----------------
+        // One thread per issuing warp; its per-block work is the critical path at small token tiles, so it
+        // waits on one barrier (an operand tile is published only after its activation tile has landed) and
         // commits to one barrier per block.
-        if (lane == 0) {
+        const int mw = warp - 1;
+        if (lane == 0 && mw < NMMA) {
             const uint32_t idesc = umma_idesc(TC_BN, TT, FMT == FMT_AWQ ? 1 : 0);
             const uint64_t da0 = FMT == FMT_GPTQ ? umma_desc(smem_u32(a_tile), 16, 1024)       // K-major: 8-row groups 1 KiB apart
                                                  : umma_desc(smem_u32(a_tile), 8192, 1024);    // MN-major: 64-column halves 8 KiB apart, 8-k groups 1 KiB apart
             const uint64_t db0 = umma_desc(smem_u32(b_tile), 16, 1024);
             const uint32_t a_step = (FMT == FMT_GPTQ ? 32 : 2048) >> 4;     // descriptor address units of 16 bytes
+            const uint32_t acc = tmem_acc + mw * TT;
             Ring ra(SA), rd(SD);
-            for (int i = 0; i < nkb; ++i, ra.next(), rd.next()) {
+            for (int j = 0; j < mw; ++j) { ra.next(); rd.next(); }
+            for (int i = mw; i < nkb; i += NMMA) {
                 const int sd = rd.slot, sa = ra.slot;
                 wait(B_DQF + sd, rd.phase);
                 tc_fence_after();
                 const uint64_t da = da0 + (uint64_t)((sd * TC_A_BYTES) >> 4);
                 const uint64_t db = db0 + (uint64_t)((sa * b_bytes) >> 4);
 #pragma unroll
-                for (int j = 0; j < TC_BK / 16; ++j)
-                    tc_mma_f16(tmem_acc, da + (uint64_t)(j * a_step), db + (uint64_t)(j * 2), idesc, (i > 0 || j > 0) ? 1u : 0u);
+                for (int j = 0; j < TC_BK / 16; ++j) {
+                    if (TS)
+                        tc_mma_f16_ts(acc, tmem_acc + a_col0 + sd * 32 + j * 8, db + (uint64_t)(j * 2), idesc,
+                                      (i >= NMMA || j > 0) ? 1u : 0u);
+                    else
+                        tc_mma_f16(acc, da + (uint64_t)(j * a_step), db + (uint64_t)(j * 2), idesc, (i >= NMMA || j > 0) ? 1u : 0u);
+                }
                 tc_commit(smem_u32(&bars[B_DQE + sd]));   // operand tile (and, through it, the activation tile) reusable once these retire
+#pragma unroll
+                for (int j = 0; j < NMMA; ++j) { ra.next(); rd.next(); }
             }
-            tc_commit(smem_u32(&bars[B_ACC]));            // accumulator complete
+            tc_commit(smem_u32(&bars[B_ACC]));            // this issuer's accumulator complete (immediately, if it had no block)
         }
     } else {
         // ---------------- dequant warps: NG groups of 128 threads, group g takes K blocks g, g+NG, ... ----------------
         // (the waits, fences and arrivals of one block then overlap the arithmetic of the other group's block)
         const int tg = tid - 32 * TC_DQ_WARP0;
-        const int grp_id = tg >> 7, t = tg & 127, warp_in_group = t >> 5;
+        // t = operand row; the hardware warp's TMEM lane quadrant is warp % 4, and a group is 4 consecutive warps
+        const int grp_id = tg >> 7, t = ((warp & 3) << 5) | lane, warp_in_group = (tg & 127) >> 5;
         Ring rr(R), rd(SD), ra(SA), ra_old(SA);   // ra: this block's activation slot; ra_old: that of block i - SD
         for (int j = 0; j < grp_id; ++j) { rr.next(); rd.next(); ra.next(); }
         // the first block this group sees retire is block (grp_id - SD) mod NG
@@ -288,11 +333,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 if (lane == 0) mbar_arrive(smem_u32(&bars[B_RAWE + r]));  // this warp is done with the packed tile
                 if (i >= SD) {
                     wait(B_DQE + s, rd.phase ^ 1u);   // block i - SD retired: its operand tile is free, and so is its activation tile
+                    if (TS) tc_fence_after();         // the tensor-memory store below is ordered after the MMAs that read the tile
                     if (warp_in_group == 0 && lane == 0) mbar_arrive(smem_u32(&bars[B_ACTE + ra_old.slot]));
 #pragma unroll
                     for (int j = 0; j < NG; ++j) ra_old.next();
                 }
                 unsigned char *arow = a_tile + (size_t)s * TC_A_BYTES + t * 128;
+                uint32_t v[32];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const uint32_t w8 = w[j] >> 8;
@@ -305,7 +352,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                     o.y = __byte_perm(v26, v37, 0x5410);   // k2 k3
                     o.z = __byte_perm(v04, v15, 0x7632);   // k4 k5
                     o.w = __byte_perm(v26, v37, 0x7632);   // k6 k7
-                    *reinterpret_cast<uint4 *>(arow + ((j ^ (t & 7)) << 4)) = o;
+                    if (TS) {
+                        v[4 * j] = o.x; v[4 * j + 1] = o.y; v[4 * j + 2] = o.z; v[4 * j + 3] = o.w;
+                    } else {
+                        *reinterpret_cast<uint4 *>(arow + ((j ^ (t & 7)) << 4)) = o;
+                    }
+                }
+                if (TS) {
+                    // lane t of tensor memory = operand row t; columns = this block's 64 k, two per column
+                    tmem_st32(tmem_acc + ((uint32_t)(t & 96) << 16) + a_col0 + s * 32, v);
+                    tmem_st_wait();
+                    tc_fence_before();
                 }
             } else {
                 // thread t: word column n8 = t % 16 (8 weight columns), k rows t / 16 + 8 j
@@ -337,7 +394,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                     *reinterpret_cast<uint4 *>(ahalf + kk * 128 + (((n8 & 7) ^ (kk & 7)) << 4)) = o;
                 }
             }
-            fence_proxy_async();
+            if (!TS) fence_proxy_async();
             __syncwarp();
             if (lane == 0) {
                 wait(B_ACTF + ra.slot, ra.phase);     // the MMA issuer waits on B_DQF alone
@@ -355,11 +412,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         const int chunk0 = (warp - TC_DQ_WARP0) >> 2; // the NG warps of a quadrant take 16-column chunks round-robin
         const int row = q * 32 + lane;                // accumulator row = weight column n0 + row
         const int n = n0 + row;
-        float *red = reinterpret_cast<float *>(a_tile);   // [TT][128] fp32, reuses the ring (all MMAs have retired)
+        float *red = reinterpret_cast<float *>(smem);     // [TT][128] fp32, reuses the rings (all copies landed, all MMAs retired)
         for (int c0 = chunk0 * 16; c0 < TT; c0 += 16 * NG) {
             uint32_t rr[16];
             if (nkb > 0) {
                 tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + c0, rr);
+                if (NMMA == 2 && nkb > 1) {
+                    uint32_t r2[16];
+                    tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + TT + c0, r2);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) rr[j] = __float_as_uint(__uint_as_float(rr[j]) + __uint_as_float(r2[j]));
+                }
                 tmem_ld_wait();
             } else {
 #pragma unroll
@@ -387,7 +451,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         if (warp >= TC_DQ_WARP0) {
             const int t = tid - 32 * TC_DQ_WARP0, row = t & (TC_BN - 1), sub = t >> 7;
             const int n = n0 + row;
-            float *red = reinterpret_cast<float *>(a_tile);
+            float *red = reinterpret_cast<float *>(smem);
             const int rank = (int)cluster.block_rank();
             for (int mm = rank + sub * P.ksplit; mm < TT; mm += NG * P.ksplit) {
                 const int m = m0 + mm;
@@ -428,16 +492,32 @@ int gemm_tc_launch(const GemmArgs &g) {
     const int budget = (ctas_per_sm == 2 ? 111 : 222) * 1024;
     const int act_bytes = tt * TC_BK * 2;
     const int ng = tt <= 64 ? 2 : 4;                 // dequant groups
-    int dq_stages = tt <= 32 ? 3 : (tt == 64 ? 2 : (tt == 128 ? 5 : 4));
-    int act_stages = tt <= 32 ? 8 : (tt == 64 ? 6 : (tt == 128 ? 5 : 4));
+    // operand tile in tensor memory (GPTQ) or in shared memory (AWQ; B200K_TC_OPERAND=smem forces it)
+    bool ts = g.format == FMT_GPTQ;
+    if (const char *e = getenv("B200K_TC_OPERAND")) ts = ts && e[0] != 's';
+    const int a_bytes = ts ? 0 : TC_A_BYTES;
+    int dq_stages, act_stages;
+    const int nmma = (ts && tt <= 64) ? 2 : 1;   // issuing warps (each with its own accumulator)
+    if (ts) {   // operand tiles cost 32 TMEM columns each: 256 columns per CTA with two CTAs per SM, 512 with one
+        dq_stages = 4;                                   // shallow: an activation tile is requested act - dq blocks ahead
+        act_stages = tt <= 64 ? 8 : (tt == 128 ? 6 : 4);
+    } else {
+        dq_stages = tt <= 32 ? 3 : (tt == 64 ? 2 : (tt == 128 ? 5 : 4));
+        act_stages = tt <= 32 ? 8 : (tt == 64 ? 6 : (tt == 128 ? 5 : 4));
+    }
     if (const char *e = getenv("B200K_TC_DQ_STAGES")) dq_stages = atoi(e);     // tuning overrides
     if (const char *e = getenv("B200K_TC_ACT_STAGES")) act_stages = atoi(e);
     // An activation slot is handed back when the operand tile SD blocks later is recycled, so the last SD
     // blocks never hand theirs back: the activation ring must be at least as deep as the operand ring, and
     // the operand ring as deep as there are dequant groups.
     if (dq_stages < ng) dq_stages = ng;
+    if (ts) {
+        const int cols = (ctas_per_sm == 2 ? 256 : 512) - (nmma * tt < 32 ? 32 : nmma * tt);
+        if (dq_stages > cols / 32) dq_stages = cols / 32;
+        if (dq_stages < ng) return 1;
+    }
     if (act_stages < dq_stages) act_stages = dq_stages;
-    int raw_stages = (budget - dq_stages * TC_A_BYTES - act_stages * act_bytes - 1024) / TC_RAW_BYTES;
+    int raw_stages = (budget - dq_stages * a_bytes - act_stages * act_bytes - 1024) / TC_RAW_BYTES;
     if (raw_stages > 16) raw_stages = 16;
     if (raw_stages < 2) return 1;
     if (const char *e = getenv("B200K_TC_RAW_STAGES")) {
@@ -448,7 +528,7 @@ int gemm_tc_launch(const GemmArgs &g) {
     // whatever its length, so: the fewest CTAs that still occupy most SMs; one more doubling only when
     // the machine is at most once covered and every CTA keeps a long K range.
     // The exchange tile ([tt][128] fp32) reuses the three rings, idle by then.
-    const size_t ring_bytes = (size_t)dq_stages * TC_A_BYTES + (size_t)act_stages * act_bytes + (size_t)raw_stages * TC_RAW_BYTES;
+    const size_t ring_bytes = (size_t)dq_stages * a_bytes + (size_t)act_stages * act_bytes + (size_t)raw_stages * TC_RAW_BYTES;
     const bool can_split = !grouped && ring_bytes >= (size_t)tt * TC_BN * 4;
     int ksplit = 1;
     if (can_split) {
@@ -463,10 +543,10 @@ int gemm_tc_launch(const GemmArgs &g) {
     if (g.plan_out) {
         int *o = g.plan_out;
         o[0] = tt; o[1] = ng; o[2] = dq_stages; o[3] = act_stages; o[4] = raw_stages; o[5] = ksplit;
-        o[6] = ceil_div(kb_total, ksplit); o[7] = tok_tiles * col_tiles;
+        o[6] = ceil_div(kb_total, ksplit); o[7] = tok_tiles * col_tiles; o[8] = nmma; o[9] = ts ? 1 : 0;
         return 0;
     }
-    const size_t smem = (size_t)dq_stages * TC_A_BYTES + (size_t)act_stages * act_bytes +
+    const size_t smem = (size_t)dq_stages * a_bytes + (size_t)act_stages * act_bytes +
                         (size_t)raw_stages * TC_RAW_BYTES + (2 * act_stages + 2 * dq_stages + 2 * raw_stages + 1) * 8 +
                         16 + 1024;
 
@@ -517,15 +597,17 @@ int gemm_tc_launch(const GemmArgs &g) {
     P.status = (int *)g.ws;   // status word at the start of the scratch buffer
     if (!P.status) return fail(B200K_E_WORKSPACE, "w4a16 gemm (tensor core): workspace is NULL");
 
-    auto kern = g.format == FMT_GPTQ ? (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2> : gemm_tc_kernel<FMT_GPTQ, 4>)
-                                     : (ng == 2 ? gemm_tc_kernel<FMT_AWQ, 2> : gemm_tc_kernel<FMT_AWQ, 4>);
-    static bool attr_set[2][2][16] = {};
+    auto kern = g.format == FMT_AWQ ? (ng == 2 ? gemm_tc_kernel<FMT_AWQ, 2, false, 1> : gemm_tc_kernel<FMT_AWQ, 4, false, 1>)
+                : ts ? (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1>)
+                     : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, false, 1> : gemm_tc_kernel<FMT_GPTQ, 4, false, 1>);
+    static bool attr_set[3][2][16] = {};
+    const int variant = g.format == FMT_AWQ ? 1 : (ts ? 2 : 0);
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 16 && !attr_set[g.format][ng == 4][dev]) {
+    if (dev >= 0 && dev < 16 && !attr_set[variant][ng == 4][dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return fail((int)e, "w4a16 gemm (tensor core): shared memory: %s", cudaGetErrorString(e));
-        attr_set[g.format][ng == 4][dev] = true;
+        attr_set[variant][ng == 4][dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(col_tiles, tok_tiles, grouped ? g.num_segments : ksplit);

@@ -1,6 +1,7 @@
 // One Llama-shape W4A16 decode layer as a fixed call sequence over the library's own
 // entry points, optionally captured in a CUDA graph.  Host-side C++ only; every
 // arithmetic step is one of the kernels declared in b200_kernels.h.
+#include <array>
 #include <map>
 #include <vector>
 
@@ -28,7 +29,9 @@ struct b200k_layer {
     // activations (device), sized for max_batch
     b200k_half *x_in, *n1, *qkv, *qrot, *att, *o, *h1, *n2, *gu, *act, *dn, *y_out;
     int32_t *pos, *lens;
-    std::map<int, cudaGraphExec_t> graphs;   // batch -> captured chain over the internal buffers
+    // (batch, input, positions, output, host buffers?) -> captured chain.  The caller's pointers are part of the
+    // captured nodes, so a decode loop that reuses its buffers replays one graph with no staging copies.
+    std::map<std::array<uintptr_t, 5>, cudaGraphExec_t> graphs;
     cudaStream_t cap_stream;                 // capture happens here: the caller's stream may be the legacy default stream
     int launches;
 };
@@ -153,14 +156,16 @@ extern "C" int b200k_layer_create(const b200k_layer_config *config, b200k_layer 
 
 extern "C" void b200k_layer_destroy(b200k_layer *L) {
     if (!L) return;
-    for (auto &kv : L->graphs) cudaGraphExecDestroy(kv.second);
+    for (auto &kv : L->graphs)
+        if (kv.second) cudaGraphExecDestroy(kv.second);
     if (L->cap_stream) cudaStreamDestroy(L->cap_stream);
     cudaFree(L->x_in);  // base of the single allocation
     delete L;
 }
 
 static void drop_graphs(b200k_layer *L) {
-    for (auto &kv : L->graphs) cudaGraphExecDestroy(kv.second);
+    for (auto &kv : L->graphs)
+        if (kv.second) cudaGraphExecDestroy(kv.second);
     L->graphs.clear();
 }
 
@@ -199,42 +204,64 @@ extern "C" int b200k_layer_launches_per_forward(const b200k_layer *L) {
     return L ? L->launches + (L->comm ? 2 : 0) : 0;
 }
 
-// Runs the chain over the internal staging buffers (x_in, pos -> y_out), through a graph
-// when enabled.  Stable pointers make the captured graph valid for every later call.
-static int run_internal(b200k_layer *L, int batch, b200k_stream stream) {
+// The whole call as it would be issued eagerly: for host buffers the copies in and out around the chain.
+static int issue(b200k_layer *L, const b200k_half *hidden_in, const int32_t *positions, b200k_half *hidden_out, int batch,
+                 bool host, b200k_stream stream) {
+    if (!host) return chain(L, hidden_in, positions, hidden_out, batch, stream);
     cudaStream_t st = to_stream(stream);
-    if (!L->cfg.use_graph) return chain(L, L->x_in, L->pos, L->y_out, batch, stream);
-    auto it = L->graphs.find(batch);
-    if (it == L->graphs.end()) {
-        // one eager pass first: first-use set-up (default workspace, function attributes) must
-        // not happen inside a capture
-        int rc = chain(L, L->x_in, L->pos, L->y_out, batch, stream);
-        if (rc) return rc;
-        cudaGraph_t graph = nullptr;
-        cudaError_t e;
-        if (!L->cap_stream) {
-            e = cudaStreamCreateWithFlags(&L->cap_stream, cudaStreamNonBlocking);
-            if (e != cudaSuccess) return fail((int)e, "layer: stream create: %s", cudaGetErrorString(e));
-        }
-        e = cudaStreamBeginCapture(L->cap_stream, cudaStreamCaptureModeThreadLocal);
-        if (e != cudaSuccess) return fail((int)e, "layer: begin capture: %s", cudaGetErrorString(e));
-        rc = chain(L, L->x_in, L->pos, L->y_out, batch, (b200k_stream)L->cap_stream);
-        e = cudaStreamEndCapture(L->cap_stream, &graph);
-        if (rc) {
-            if (graph) cudaGraphDestroy(graph);
-            return rc;
-        }
-        if (e != cudaSuccess) return fail((int)e, "layer: end capture: %s", cudaGetErrorString(e));
-        cudaGraphExec_t exec = nullptr;
-        e = cudaGraphInstantiate(&exec, graph, 0);
-        cudaGraphDestroy(graph);
-        if (e != cudaSuccess) return fail((int)e, "layer: graph instantiate: %s", cudaGetErrorString(e));
-        L->graphs[batch] = exec;
-        return 0;  // the eager pass above already produced this call's result
-    }
-    cudaError_t e = cudaGraphLaunch(it->second, st);
-    if (e != cudaSuccess) return fail((int)e, "layer: graph launch: %s", cudaGetErrorString(e));
+    const size_t hb = (size_t)batch * L->cfg.hidden * 2;
+    cudaError_t e = cudaMemcpyAsync(L->x_in, hidden_in, hb, cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(L->pos, positions, (size_t)batch * 4, cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) return fail((int)e, "layer: copy in: %s", cudaGetErrorString(e));
+    int rc = chain(L, L->x_in, L->pos, L->y_out, batch, stream);
+    if (rc) return rc;
+    e = cudaMemcpyAsync(hidden_out, L->y_out, hb, cudaMemcpyDeviceToHost, st);
+    if (e != cudaSuccess) return fail((int)e, "layer: copy out: %s", cudaGetErrorString(e));
     return 0;
+}
+
+constexpr size_t MAX_GRAPHS = 64;   // distinct (batch, buffers) combinations kept; beyond that calls run eagerly
+
+// Runs one call, through a captured graph when enabled.  The first call with a given batch and set of
+// buffers runs eagerly (first-use set-up such as the default workspace and function attributes must not
+// happen inside a capture) and captures the same sequence for the calls that follow.
+static int run(b200k_layer *L, const b200k_half *hidden_in, const int32_t *positions, b200k_half *hidden_out, int batch,
+               bool host, b200k_stream stream) {
+    if (!L->cfg.use_graph) return issue(L, hidden_in, positions, hidden_out, batch, host, stream);
+    const std::array<uintptr_t, 5> key = {(uintptr_t)batch, (uintptr_t)hidden_in, (uintptr_t)positions, (uintptr_t)hidden_out,
+                                          (uintptr_t)host};
+    auto it = L->graphs.find(key);
+    if (it != L->graphs.end()) {
+        if (!it->second) return issue(L, hidden_in, positions, hidden_out, batch, host, stream);   // capture was not possible
+        cudaError_t e = cudaGraphLaunch(it->second, to_stream(stream));
+        if (e != cudaSuccess) return fail((int)e, "layer: graph launch: %s", cudaGetErrorString(e));
+        return 0;
+    }
+    int rc = issue(L, hidden_in, positions, hidden_out, batch, host, stream);
+    if (rc || L->graphs.size() >= MAX_GRAPHS) return rc;
+    cudaGraph_t graph = nullptr;
+    cudaError_t e;
+    if (!L->cap_stream) {
+        e = cudaStreamCreateWithFlags(&L->cap_stream, cudaStreamNonBlocking);
+        if (e != cudaSuccess) return fail((int)e, "layer: stream create: %s", cudaGetErrorString(e));
+    }
+    e = cudaStreamBeginCapture(L->cap_stream, cudaStreamCaptureModeThreadLocal);
+    if (e != cudaSuccess) return fail((int)e, "layer: begin capture: %s", cudaGetErrorString(e));
+    rc = issue(L, hidden_in, positions, hidden_out, batch, host, (b200k_stream)L->cap_stream);
+    e = cudaStreamEndCapture(L->cap_stream, &graph);
+    if (rc || e != cudaSuccess) {
+        // e.g. copies from pageable host memory cannot be captured: this set of buffers stays eager
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        L->graphs[key] = nullptr;
+        return 0;   // the eager pass above already produced this call's result
+    }
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) return fail((int)e, "layer: graph instantiate: %s", cudaGetErrorString(e));
+    L->graphs[key] = exec;
+    return 0;   // the eager pass above already produced this call's result
 }
 
 extern "C" int b200k_layer_forward(b200k_layer *L, const b200k_half *hidden_in, const int32_t *positions,
@@ -243,14 +270,7 @@ extern "C" int b200k_layer_forward(b200k_layer *L, const b200k_half *hidden_in, 
     if (rc) return rc;
     B200K_REQUIRE(hidden_in && positions && hidden_out, B200K_E_NULL, "b200k_layer_forward: NULL pointer");
     if (batch == 0) return 0;
-    if (!L->cfg.use_graph) return chain(L, hidden_in, positions, hidden_out, batch, stream);
-    cudaStream_t st = to_stream(stream);
-    const size_t hb = (size_t)batch * L->cfg.hidden * 2;
-    cudaMemcpyAsync(L->x_in, hidden_in, hb, cudaMemcpyDeviceToDevice, st);
-    cudaMemcpyAsync(L->pos, positions, (size_t)batch * 4, cudaMemcpyDeviceToDevice, st);
-    if ((rc = run_internal(L, batch, stream))) return rc;
-    cudaMemcpyAsync(hidden_out, L->y_out, hb, cudaMemcpyDeviceToDevice, st);
-    return launch_status("b200k_layer_forward");
+    return run(L, hidden_in, positions, hidden_out, batch, false, stream);
 }
 
 extern "C" int b200k_layer_forward_host(b200k_layer *L, const b200k_half *host_hidden_in,
@@ -261,13 +281,7 @@ extern "C" int b200k_layer_forward_host(b200k_layer *L, const b200k_half *host_h
     B200K_REQUIRE(host_hidden_in && host_positions && host_hidden_out, B200K_E_NULL,
                   "b200k_layer_forward_host: NULL pointer");
     if (batch == 0) return 0;
-    cudaStream_t st = to_stream(stream);
-    const size_t hb = (size_t)batch * L->cfg.hidden * 2;
-    cudaMemcpyAsync(L->x_in, host_hidden_in, hb, cudaMemcpyHostToDevice, st);
-    cudaMemcpyAsync(L->pos, host_positions, (size_t)batch * 4, cudaMemcpyHostToDevice, st);
-    if ((rc = run_internal(L, batch, stream))) return rc;
-    cudaMemcpyAsync(host_hidden_out, L->y_out, hb, cudaMemcpyDeviceToHost, st);
-    return launch_status("b200k_layer_forward_host");
+    return run(L, host_hidden_in, host_positions, host_hidden_out, batch, true, stream);
 }
 
 extern "C" int b200k_layer_forward_stage(b200k_layer *L, int stage, const b200k_half *hidden_in,
