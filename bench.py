@@ -67,8 +67,12 @@ def cpu_layer_case(rng, batch, ctx):
     ml = ctx + 1
 
     def gptq(k, n):
-        return (rng.integers(-2 ** 31, 2 ** 31, (k // 8, n), dtype=np.int64).astype(np.int32),
-                rng.uniform(0.002, 0.02, (k // G, n)).astype(np.float16),
+        # nibbles 1..15 around the zero-point 8 (stored 7, +1 in the GEMM): weights without a DC component, so the
+        # 14336-deep down projection stays inside fp16 and the result can be compared (same cost as any nibbles)
+        qw = np.zeros((k // 8, n), dtype=np.uint32)
+        for i in range(8):
+            qw |= rng.integers(1, 16, (k // 8, n), dtype=np.uint32) << np.uint32(4 * i)
+        return (qw.view(np.int32), rng.uniform(0.002, 0.02, (k // G, n)).astype(np.float16),
                 np.full((k // G, n // 8), 0x77777777, dtype=np.int32))
     cos, sin = o.rope_tables(ml, d, 500000.0)
     case = dict(H=H, hq=hq, hkv=hkv, d=d, I=I, G=G, ml=ml, cos=cos, sin=sin,
@@ -99,44 +103,45 @@ def cpu_layer_run(oc, c):
     return time.perf_counter() - t0, out
 
 
-def cpu_baseline(sample_batch=BATCH, reps=3):
+def cpu_baseline(sample_batch=BATCH, reps=3, gate=None):
+    """Times the CPU restatement on the benchmark's extents; `gate(case, cpu_out)` (optional) then checks the
+    library's result on the very same inputs against it."""
     oc = load_oracle_c()
     oc.oc_num_threads.restype = ctypes.c_int
     cores = oc.oc_num_threads()
     case = cpu_layer_case(np.random.default_rng(4), sample_batch, CTX)
-    cpu_layer_run(oc, case)                      # warm-up (page in, thread pool)
+    _, out = cpu_layer_run(oc, case)             # warm-up (page in, thread pool); every run appends the same K/V row
     ts = [cpu_layer_run(oc, case)[0] for _ in range(reps)]
     best = min(ts)
-    return {"value": sample_batch / best, "unit": "tok/s", "cores": cores, "kind": "port",
+    line = {"value": sample_batch / best, "unit": "tok/s", "cores": cores, "kind": "port",
             "sample": f"{sample_batch} of {BATCH} sequences, ctx {CTX}, full layer chain, best of {reps}"}
+    return line, (gate(case, out) if gate else None)
 
 
-def run_reference_arm(args):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
-    oc = load_oracle_c()
-    oc.oc_num_threads.restype = ctypes.c_int
-    cores = oc.oc_num_threads()
-    sample = BATCH
-    case = cpu_layer_case(np.random.default_rng(4), sample, CTX)
-    for _ in range(max(1, min(args.warmup, 2))):
-        cpu_layer_run(oc, case)
-    ts = [cpu_layer_run(oc, case)[0] for _ in range(args.steps)]
-    ms = 1e3 * sum(ts) / len(ts)
-    value = sample / (ms / 1e3)
-    line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage, f32 accumulate", "data": "synthetic",
-        "config": {"workload": "C4 decode layer chain, batch 64, ctx 4096 (each step: the whole batch)",
-                   "note": "CPU restatement of the reference kernels' arithmetic (oracle/oracle_c.c, OpenMP); "
-                           "the reference has no CPU path and its Rust/Triton toolchain is absent"},
-        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": cores, "kind": "port",
-                         "sample": f"{sample} of {BATCH} sequences per step, ctx {CTX}, full layer chain"},
-        "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }
-    print(json.dumps(line))
+def parity_gate(pkg, torch, dev, case, cpu_out):
+    """The whole config-4 layer through the C ABI on the CPU leg's inputs, against the CPU result."""
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    shape = pkg.LayerShape()
+    w = {k: tuple(t(x) for x in case[k]) for k in ("qkv", "o", "gate_up", "down")}
+    layer = pkg.DecodeLayer(shape, w, t(case["ln1"]), t(case["ln2"]), t(case["cos"]), t(case["sin"]),
+                            max_batch=case["hidden"].shape[0], max_len=case["ml"], use_graph=False,
+                            k_cache=t(case["kc"]), v_cache=t(case["vc"]))
+    got = layer.forward(t(case["hidden"]), t(case["pos"])).float().cpu().numpy()
+    layer.close()
+    # Outputs of this layer are O(30) (unit-variance input through a 14336-deep projection), so the absolute part of
+    # the tolerance (2e-2, as in the layer tests) scales with the output's RMS: |got - ref| <= 2e-2 |ref| + 2e-2 rms(ref);
+    # the relative RMS error must also stay below 5e-3 (fp16 storage between the ten kernels gives about 2e-3)
+    err = np.abs(got.astype(np.float64) - cpu_out)
+    rms_ref = float(np.sqrt(np.mean(np.square(cpu_out, dtype=np.float64))))
+    bound = 2e-2 * np.abs(cpu_out) + 2e-2 * rms_ref
+    finite = bool(np.isfinite(got).all() and np.isfinite(cpu_out).all())
+    rms_err = float(np.sqrt(np.nanmean(err * err)))
+    ok = finite and bool((err <= bound).all()) and rms_err <= 5e-3 * rms_ref
+    return {"what": "config-4 layer (batch 64, ctx 4096) through the C ABI vs the CPU restatement, same inputs",
+            "tolerance": "|got - ref| <= 2e-2 |ref| + 2e-2 rms(ref) and rms(err) <= 5e-3 rms(ref)",
+            "max_abs_err": float(np.nanmax(err)), "rms_err": rms_err, "rms_ref": rms_ref,
+            "max_abs_ref": float(np.nanmax(np.abs(cpu_out))),
+            "worst_err_over_bound": float(np.nanmax(err / bound)), "ok": ok}
 
 
 # --------------------------------------------------------------------------------------
@@ -505,7 +510,10 @@ def run_gpu_arm(args):
         if components is not None:
             line["components"] = components
         if world == 1 and not args.no_cpu:
-            line["cpu_baseline"] = cpu_baseline()
+            line["cpu_baseline"], line["parity"] = cpu_baseline(gate=lambda c, o: parity_gate(pkg, torch, dev, c, o))
+            if not line["parity"]["ok"]:          # a run that fails the gate publishes no throughput
+                line["value"] = None
+                line["e2e"]["value"] = None
         print(json.dumps(line))
     if world > 1:
         # Tearing the process group down while CUDA graphs that captured its collectives are alive

@@ -296,6 +296,22 @@ int fused_moe_gptq_f16(const b200k_half *x, const float *router_logits, const in
                        int num_experts, int top_k, int intermediate, int group_size,
                        void *workspace, size_t workspace_bytes, b200k_stream stream);
 
+/* Expert-parallel share of the same computation: this call holds the weights of experts
+ * [expert_first, expert_first + num_local_experts) only (stacks of num_local_experts matrices).  Tokens
+ * and router logits are the full, replicated ones; routing is computed over all num_experts (identically
+ * on every rank), pairs routed to other ranks' experts are dropped, and partial_out [num_tokens, hidden]
+ * receives the weighted sum over the local experts (zero rows for tokens with none).  The sum of
+ * partial_out over the ranks is the MoE output: one all-reduce (b200k_comm_allreduce_f16), no all-to-all
+ * and no size exchange.  No counterpart in the reference. */
+int fused_moe_gptq_ep_f16(const b200k_half *x, const float *router_logits,
+                          const int32_t *w13_qweight, const b200k_half *w13_scales,
+                          const int32_t *w13_qzeros, const int32_t *w2_qweight,
+                          const b200k_half *w2_scales, const int32_t *w2_qzeros,
+                          b200k_half *partial_out, int num_tokens, int hidden, int num_experts,
+                          int expert_first, int num_local_experts, int top_k, int intermediate,
+                          int group_size, void *workspace, size_t workspace_bytes,
+                          b200k_stream stream);
+
 /* ------------------------------------------------------------------------- */
 /* bandwidth-bound glue                                                        */
 /* ------------------------------------------------------------------------- */

@@ -103,6 +103,31 @@ def _rank_main(rank, world, port, q):
             dist.all_gather_object(gathered, got.tobytes())
             assert all(g == gathered[0] for g in gathered), "ranks disagree"
         assert comm.status() == 0
+
+        # ---- expert-parallel MoE: every rank computes the share of its experts, one all-reduce adds them ----
+        rng = np.random.default_rng(29)
+        T, E, k, H, I, G = 33, 8, 2, 256, 384, 128
+        x = rng.standard_normal((T, H)).astype(np.float16)
+        logits = rng.standard_normal((T, E)).astype(np.float32)
+        w13q = np.stack([o.pack_gptq_qweight(rng.integers(1, 16, (H, 2 * I), dtype=np.int32)) for _ in range(E)])
+        w13s = rng.uniform(0.002, 0.02, (E, H // G, 2 * I)).astype(np.float16)
+        w2q = np.stack([o.pack_gptq_qweight(rng.integers(1, 16, (I, H), dtype=np.int32)) for _ in range(E)])
+        w2s = rng.uniform(0.002, 0.02, (E, I // G, H)).astype(np.float16)
+        ref = o.fused_moe_gptq(x, logits, w13q, w13s, w2q, w2s, k, G)
+        per = E // world
+        lo, hi = rank * per, (rank + 1) * per
+        share = torch.empty((T, H), dtype=torch.float16, device=dev)
+        full = torch.empty_like(share)
+        st = torch.cuda.current_stream().cuda_stream
+        pkg.prelude.fused_moe_gptq_ep_f16(t(x), t(logits), t(w13q[lo:hi]), t(w13s[lo:hi]), None, t(w2q[lo:hi]), t(w2s[lo:hi]),
+                                          None, share, T, H, E, lo, per, k, I, G, None, 0, st)
+        dist.barrier()
+        comm.all_reduce(0, full, T * H, input=share)
+        comm.all_reduce(1, share, T * H, input=full)       # keeps the slots alternating for whoever comes next
+        torch.cuda.synchronize()
+        got = full.float().cpu().numpy()
+        assert np.isfinite(got).all() and np.allclose(got, ref, rtol=2e-2, atol=2e-2), f"ep moe: {np.abs(got - ref).max()}"
+        assert comm.status() == 0
         dist.barrier()
         layer.close()
         comm.close()

@@ -104,3 +104,42 @@ def test_mixtral_shape_linearity(P):
     P.fused_moe_gptq_f16(*args(x[perm].contiguous(), logits[perm].contiguous(), out2))
     assert torch.isfinite(out).all()
     assert torch.equal(out[perm], out2)
+
+
+@pytest.mark.parametrize("T,E,k,H,I,parts", [(33, 8, 2, 256, 384, 2), (64, 8, 2, 256, 384, 4), (17, 6, 3, 128, 256, 3)])
+def test_expert_parallel_shares_add_up(P, oracle, T, E, k, H, I, parts):
+    """Expert-parallel entry point on one GPU: the shares of `parts` disjoint expert ranges, added in fp32, give
+    the full MoE output (each rank of an expert-parallel group computes one share; the all-reduce adds them)."""
+    rng = np.random.default_rng(T + E)
+    G = 128
+    x = rng.standard_normal((T, H)).astype(np.float16)
+    logits = rng.standard_normal((T, E)).astype(np.float32)
+    w13q = np.stack([oracle.pack_gptq_qweight(rng.integers(1, 16, (H, 2 * I), dtype=np.int32)) for _ in range(E)])
+    w13s = rng.uniform(0.002, 0.02, (E, H // G, 2 * I)).astype(np.float16)
+    w2q = np.stack([oracle.pack_gptq_qweight(rng.integers(1, 16, (I, H), dtype=np.int32)) for _ in range(E)])
+    w2s = rng.uniform(0.002, 0.02, (E, I // G, H)).astype(np.float16)
+    ref = oracle.fused_moe_gptq(x, logits, w13q, w13s, w2q, w2s, k, G)
+    full = run_moe(P, x, logits, w13q, w13s, w2q, w2s, k, G)
+    per = E // parts
+    total = np.zeros((T, H), dtype=np.float32)
+    for r in range(parts):
+        lo, hi = r * per, (r + 1) * per
+        out = torch.full((T, H), float("nan"), dtype=torch.float16, device=DEV)     # every row must be written
+        P.fused_moe_gptq_ep_f16(t(x), t(logits), t(w13q[lo:hi]), t(w13s[lo:hi]), None, t(w2q[lo:hi]), t(w2s[lo:hi]), None,
+                                out, T, H, E, lo, per, k, I, G, None, 0)
+        share = out.float().cpu().numpy()
+        assert np.isfinite(share).all()
+        total += share
+    assert_close(total, ref, 2e-2, 2e-2, "sum of expert-parallel shares vs oracle")
+    assert_close(total, full, 4e-3, 4e-3, "sum of expert-parallel shares vs the single-GPU entry point")
+    # the whole expert range through the expert-parallel entry point is the plain computation, bit for bit
+    out = torch.empty((T, H), dtype=torch.float16, device=DEV)
+    P.fused_moe_gptq_ep_f16(t(x), t(logits), t(w13q), t(w13s), None, t(w2q), t(w2s), None, out, T, H, E, 0, E, k, I, G, None, 0)
+    assert np.array_equal(out.float().cpu().numpy(), full)
+
+
+def test_expert_parallel_rejects_bad_ranges(P):
+    z = torch.zeros(8, device=DEV)
+    for first, local in [(-1, 2), (7, 2), (0, 0), (0, 9)]:
+        with pytest.raises(Exception):
+            P.fused_moe_gptq_ep_f16(z, z, z, z, None, z, z, None, z, 4, 128, 8, first, local, 2, 128, 128, None, 0)

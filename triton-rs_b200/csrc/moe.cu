@@ -48,10 +48,19 @@ moe_route_kernel(const float *__restrict__ logits, int32_t *__restrict__ ids, fl
     }
 }
 
-// Single CTA: counts, offsets, stable segmented order and its inverse.
+// Bucket of an expert id: experts [first, first + local) map to buckets 0..local-1, every other expert to the
+// extra bucket `local` (expert-parallel ranks keep only their own experts' pairs; the rest sort to the end).
+__device__ __forceinline__ int moe_bucket(int e, int first, int local) {
+    const int b = e - first;
+    return (b >= 0 && b < local) ? b : local;
+}
+
+// Single CTA: counts, offsets, stable segmented order and its inverse, over `experts` buckets
+// (experts = local, or local + 1 when some ids fall outside [first, first + local)).
 __global__ void __launch_bounds__(1024)
-moe_permute_kernel(const int32_t *__restrict__ ids, int pairs, int experts, int32_t *__restrict__ counts,
-                   int32_t *__restrict__ offsets, int32_t *__restrict__ sorted_pairs, int32_t *__restrict__ inv) {
+moe_permute_kernel(const int32_t *__restrict__ ids, int pairs, int experts, int first, int local,
+                   int32_t *__restrict__ counts, int32_t *__restrict__ offsets, int32_t *__restrict__ sorted_pairs,
+                   int32_t *__restrict__ inv) {
     __shared__ int s_count[MOE_MAX_E];
     __shared__ int s_off[MOE_MAX_E + 1];
     __shared__ int s_run[MOE_MAX_E];          // pairs of each expert placed so far
@@ -59,7 +68,7 @@ moe_permute_kernel(const int32_t *__restrict__ ids, int pairs, int experts, int3
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     if (tid < experts) s_count[tid] = 0;
     __syncthreads();
-    for (int p = tid; p < pairs; p += blockDim.x) atomicAdd(&s_count[ids[p]], 1);   // integer counts: order-independent
+    for (int p = tid; p < pairs; p += blockDim.x) atomicAdd(&s_count[moe_bucket(ids[p], first, local)], 1);   // integer counts: order-independent
     __syncthreads();
     if (tid == 0) {
         int acc = 0;
@@ -77,7 +86,7 @@ moe_permute_kernel(const int32_t *__restrict__ ids, int pairs, int experts, int3
     // (pairs of that expert in lower warps) + (in lower lanes of its warp)
     for (int base = 0; base < pairs; base += blockDim.x) {
         const int p = base + tid;
-        const int e = p < pairs ? ids[p] : -1;
+        const int e = p < pairs ? moe_bucket(ids[p], first, local) : -1;
         int my_rank = 0;
         for (int x = 0; x < experts; ++x) {
             const unsigned mask = __ballot_sync(0xffffffffu, e == x);
@@ -103,10 +112,12 @@ moe_permute_kernel(const int32_t *__restrict__ ids, int pairs, int experts, int3
 }
 
 // x_perm[i, :] = x[sorted_pairs[i] / k, :]   (16 bytes per thread)
+// (rows at and beyond *nrows belong to experts of other ranks and are not gathered)
 __global__ void __launch_bounds__(256)
 moe_gather_kernel(const __half *__restrict__ x, const int32_t *__restrict__ sorted_pairs, __half *__restrict__ xp,
-                  int pairs, int hidden, int top_k) {
+                  const int32_t *__restrict__ nrows, int hidden, int top_k) {
     const int hv = hidden / 8;
+    const int pairs = *nrows;
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < (long)pairs * hv; i += (long)gridDim.x * blockDim.x) {
         const int row = (int)(i / hv), c = (int)(i - (long)row * hv);
         const int tok = sorted_pairs[row] / top_k;
@@ -115,16 +126,20 @@ moe_gather_kernel(const __half *__restrict__ x, const int32_t *__restrict__ sort
 }
 
 // out[t, :] = sum_j w[t, j] * y_perm[inv[t*k + j], :]   (fp32 sum in slot order, fp16 out)
+// (pairs whose row is at or beyond *nrows went to experts of other ranks: they add nothing here)
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const __half *__restrict__ yp, const int32_t *__restrict__ inv, const float *__restrict__ wts,
-                   __half *__restrict__ out, int tokens, int hidden, int top_k) {
+                   const int32_t *__restrict__ nrows, __half *__restrict__ out, int tokens, int hidden, int top_k) {
     const int hv = hidden / 8;
+    const int rows = *nrows;
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < (long)tokens * hv; i += (long)gridDim.x * blockDim.x) {
         const int t = (int)(i / hv), c = (int)(i - (long)t * hv);
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         for (int j = 0; j < top_k; ++j) {
             const float w = wts[(long)t * top_k + j];
-            const uint4 v = reinterpret_cast<const uint4 *>(yp)[(long)inv[(long)t * top_k + j] * hv + c];
+            const int r = inv[(long)t * top_k + j];
+            if (r >= rows) continue;
+            const uint4 v = reinterpret_cast<const uint4 *>(yp)[(long)r * hv + c];
             const float2 a = h2_to_f2(v.x), b = h2_to_f2(v.y), cc = h2_to_f2(v.z), d = h2_to_f2(v.w);
             acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * b.x; acc[3] += w * b.y;
             acc[4] += w * cc.x; acc[5] += w * cc.y; acc[6] += w * d.x; acc[7] += w * d.y;
@@ -133,6 +148,27 @@ moe_combine_kernel(const __half *__restrict__ yp, const int32_t *__restrict__ in
         o.x = f2_to_h2(acc[0], acc[1]); o.y = f2_to_h2(acc[2], acc[3]);
         o.z = f2_to_h2(acc[4], acc[5]); o.w = f2_to_h2(acc[6], acc[7]);
         reinterpret_cast<uint4 *>(out)[(long)t * hv + c] = o;
+    }
+}
+
+// silu(gate) * up over the first *nrows rows of gate_up [rows, 2 inter] (gate = first half of a row)
+__global__ void __launch_bounds__(256)
+moe_silu_mul_kernel(const __half *__restrict__ gu, __half *__restrict__ act, const int32_t *__restrict__ nrows, int inter) {
+    const int iv = inter / 8;
+    const long total = (long)*nrows * iv;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long row = i / iv;
+        const int c = (int)(i - row * iv);
+        const uint4 g = reinterpret_cast<const uint4 *>(gu)[row * 2 * iv + c];
+        const uint4 u = reinterpret_cast<const uint4 *>(gu)[row * 2 * iv + iv + c];
+        const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 a = h2_to_f2(gw[j]), b = h2_to_f2(uw[j]);
+            o[j] = f2_to_h2(a.x / (1.f + expf(-a.x)) * b.x, a.y / (1.f + expf(-a.y)) * b.y);
+        }
+        reinterpret_cast<uint4 *>(act)[row * iv + c] = make_uint4(o[0], o[1], o[2], o[3]);
     }
 }
 
@@ -194,8 +230,8 @@ extern "C" int moe_permute(const int32_t *topk_ids, int32_t *counts, int32_t *of
     B200K_REQUIRE(num_pairs >= 0 && num_experts >= 1 && num_experts <= MOE_MAX_E, B200K_E_SHAPE,
                   "moe_permute: pairs %d, experts %d (<= %d)", num_pairs, num_experts, MOE_MAX_E);
     B200K_REQUIRE(topk_ids && counts && offsets && sorted_pairs && inverse, B200K_E_NULL, "moe_permute: NULL pointer");
-    moe_permute_kernel<<<1, 1024, 0, to_stream(stream)>>>(topk_ids, num_pairs, num_experts, counts, offsets,
-                                                         sorted_pairs, inverse);
+    moe_permute_kernel<<<1, 1024, 0, to_stream(stream)>>>(topk_ids, num_pairs, num_experts, 0, num_experts, counts,
+                                                         offsets, sorted_pairs, inverse);
     return launch_status("moe_permute");
 }
 
@@ -204,12 +240,13 @@ extern "C" size_t fused_moe_workspace_bytes(int num_tokens, int hidden, int num_
     return moe_ws_layout(nullptr, num_tokens, hidden, num_experts, top_k, intermediate).bytes;
 }
 
-extern "C" int fused_moe_gptq_f16(const b200k_half *x, const float *router_logits, const int32_t *w13_qweight,
-                                  const b200k_half *w13_scales, const int32_t *w13_qzeros, const int32_t *w2_qweight,
-                                  const b200k_half *w2_scales, const int32_t *w2_qzeros, b200k_half *out,
-                                  int num_tokens, int hidden, int num_experts, int top_k, int intermediate,
-                                  int group_size, void *workspace, size_t workspace_bytes, b200k_stream stream) {
-    const char *name = "fused_moe_gptq_f16";
+// Shared body: experts [expert_first, expert_first + num_local) are the ones whose weights this call holds
+// (w13 / w2 stacks of num_local matrices); `out` receives their share of every token's weighted sum.
+static int moe_run(const char *name, const b200k_half *x, const float *router_logits, const int32_t *w13_qweight,
+                   const b200k_half *w13_scales, const int32_t *w13_qzeros, const int32_t *w2_qweight,
+                   const b200k_half *w2_scales, const int32_t *w2_qzeros, b200k_half *out, int num_tokens, int hidden,
+                   int num_experts, int expert_first, int num_local, int top_k, int intermediate, int group_size,
+                   void *workspace, size_t workspace_bytes, b200k_stream stream) {
     B200K_REQUIRE(x && router_logits && w13_qweight && w13_scales && w2_qweight && w2_scales && out, B200K_E_NULL,
                   "%s: NULL pointer", name);
     B200K_REQUIRE(num_tokens >= 0 && num_experts >= 1 && num_experts <= MOE_MAX_E && top_k >= 1 &&
@@ -219,6 +256,8 @@ extern "C" int fused_moe_gptq_f16(const b200k_half *x, const float *router_logit
                       intermediate % group_size == 0,
                   B200K_E_SHAPE, "%s: unsupported extents (tokens %d, hidden %d, experts %d, top_k %d, inter %d, group %d)",
                   name, num_tokens, hidden, num_experts, top_k, intermediate, group_size);
+    B200K_REQUIRE(expert_first >= 0 && num_local >= 1 && expert_first + num_local <= num_experts, B200K_E_SHAPE,
+                  "%s: local experts [%d, %d) outside 0..%d", name, expert_first, expert_first + num_local, num_experts);
     if (num_tokens == 0) return 0;
     if (!workspace) {
         int rc = default_workspace(&workspace, &workspace_bytes);
@@ -229,16 +268,20 @@ extern "C" int fused_moe_gptq_f16(const b200k_half *x, const float *router_logit
                   workspace_bytes, w.bytes);
     cudaStream_t st = to_stream(stream);
     const int pairs = num_tokens * top_k;
+    const int buckets = num_local == num_experts ? num_local : num_local + 1;
+    const int32_t *nrows = w.offsets + num_local;    // rows of the segmented list that belong to local experts
     int rc;
     if ((rc = moe_route_topk_f32(router_logits, w.ids, w.wts, num_tokens, num_experts, top_k, stream))) return rc;
-    if ((rc = moe_permute(w.ids, w.counts, w.offsets, w.sorted_pairs, w.inv, pairs, num_experts, stream))) return rc;
-    moe_gather_kernel<<<grid_for((long)pairs * hidden / 8), 256, 0, st>>>((const __half *)x, w.sorted_pairs, w.xp, pairs,
+    moe_permute_kernel<<<1, 1024, 0, st>>>(w.ids, pairs, buckets, expert_first, num_local, w.counts, w.offsets,
+                                           w.sorted_pairs, w.inv);
+    if ((rc = launch_status(name))) return rc;
+    moe_gather_kernel<<<grid_for((long)pairs * hidden / 8), 256, 0, st>>>((const __half *)x, w.sorted_pairs, w.xp, nrows,
                                                                           hidden, top_k);
     if ((rc = launch_status(name))) return rc;
 
     GemmArgs g = {};
     g.format = FMT_GPTQ; g.group = group_size; g.stream = st; g.ws = workspace; g.ws_bytes = workspace_bytes;
-    g.seg_offsets = w.offsets; g.num_segments = num_experts;
+    g.seg_offsets = w.offsets; g.num_segments = num_local;
     g.s_ak = g.s_qwn = g.s_sn = g.s_qzn = g.s_cn = 1;
     // up-projection: [pairs, H] x W13_e [H, 2I] -> [pairs, 2I]
     g.a = w.xp; g.qweight = w13_qweight; g.scales = (const __half *)w13_scales; g.qzeros = w13_qzeros; g.c = w.gu;
@@ -247,9 +290,8 @@ extern "C" int fused_moe_gptq_f16(const b200k_half *x, const float *router_logit
     g.zero_offset = w13_qzeros ? 1 : 0;
     rc = gemm_tc_launch(g);
     if (rc) return rc == 1 ? fail(B200K_E_SHAPE, "%s: expert GEMM shape not covered by the tensor-core path", name) : rc;
-    if ((rc = fused_silu_mul_interleaved_f16((const b200k_half *)w.gu, (b200k_half *)w.act, intermediate,
-                                             pairs * intermediate, stream)))
-        return rc;
+    moe_silu_mul_kernel<<<grid_for((long)pairs * intermediate / 8), 256, 0, st>>>(w.gu, w.act, nrows, intermediate);
+    if ((rc = launch_status(name))) return rc;
     // down-projection: [pairs, I] x W2_e [I, H] -> [pairs, H]
     g.a = w.act; g.qweight = w2_qweight; g.scales = (const __half *)w2_scales; g.qzeros = w2_qzeros; g.c = w.yp;
     g.n = hidden; g.k = intermediate;
@@ -257,7 +299,28 @@ extern "C" int fused_moe_gptq_f16(const b200k_half *x, const float *router_logit
     g.zero_offset = w2_qzeros ? 1 : 0;
     rc = gemm_tc_launch(g);
     if (rc) return rc == 1 ? fail(B200K_E_SHAPE, "%s: expert GEMM shape not covered by the tensor-core path", name) : rc;
-    moe_combine_kernel<<<grid_for((long)num_tokens * hidden / 8), 256, 0, st>>>(w.yp, w.inv, w.wts, (__half *)out,
+    moe_combine_kernel<<<grid_for((long)num_tokens * hidden / 8), 256, 0, st>>>(w.yp, w.inv, w.wts, nrows, (__half *)out,
                                                                                 num_tokens, hidden, top_k);
     return launch_status(name);
+}
+
+extern "C" int fused_moe_gptq_f16(const b200k_half *x, const float *router_logits, const int32_t *w13_qweight,
+                                  const b200k_half *w13_scales, const int32_t *w13_qzeros, const int32_t *w2_qweight,
+                                  const b200k_half *w2_scales, const int32_t *w2_qzeros, b200k_half *out,
+                                  int num_tokens, int hidden, int num_experts, int top_k, int intermediate,
+                                  int group_size, void *workspace, size_t workspace_bytes, b200k_stream stream) {
+    return moe_run("fused_moe_gptq_f16", x, router_logits, w13_qweight, w13_scales, w13_qzeros, w2_qweight, w2_scales,
+                   w2_qzeros, out, num_tokens, hidden, num_experts, 0, num_experts, top_k, intermediate, group_size,
+                   workspace, workspace_bytes, stream);
+}
+
+extern "C" int fused_moe_gptq_ep_f16(const b200k_half *x, const float *router_logits, const int32_t *w13_qweight,
+                                     const b200k_half *w13_scales, const int32_t *w13_qzeros, const int32_t *w2_qweight,
+                                     const b200k_half *w2_scales, const int32_t *w2_qzeros, b200k_half *partial_out,
+                                     int num_tokens, int hidden, int num_experts, int expert_first,
+                                     int num_local_experts, int top_k, int intermediate, int group_size, void *workspace,
+                                     size_t workspace_bytes, b200k_stream stream) {
+    return moe_run("fused_moe_gptq_ep_f16", x, router_logits, w13_qweight, w13_scales, w13_qzeros, w2_qweight, w2_scales,
+                   w2_qzeros, partial_out, num_tokens, hidden, num_experts, expert_first, num_local_experts, top_k,
+                   intermediate, group_size, workspace, workspace_bytes, stream);
 }
