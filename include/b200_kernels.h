@@ -268,6 +268,33 @@ int paged_decode_attention_f16(const b200k_half *q, const b200k_half *k_block_po
 /* ------------------------------------------------------------------------- */
 /* fused MoE                                                                   */
 /* ------------------------------------------------------------------------- */
+/* Projection helpers either side of attention (crates/triton-kernels/src/projection.rs), fp32 as in */
+/* the reference.  Its const generics (BLOCK, HEAD_DIM, HALF_DIM) are tile limits there and runtime    */
+/* extents here: HALF_DIM = head_dim / 2 (the tables are [positions, head_dim / 2]); the launch grid   */
+/* of the reference becomes the trailing extent argument where the signature does not already have it. */
+/* ------------------------------------------------------------------------- */
+/* Replaces split_qkv_f32 (projection.rs:18-51): qkv [batch, 3, heads, D] -> q, k, v [batch, heads, D]. */
+int split_qkv_f32(const float *qkv, float *q_out, float *k_out, float *v_out, int num_heads,
+                  int head_dim, int batch, b200k_stream stream);
+/* Replace transpose_head_to_token_f32 (:60-79): [heads, tokens, D] -> [tokens, heads, D], and
+ * transpose_token_to_head_f32 (:87-105): the inverse. */
+int transpose_head_to_token_f32(const float *input, float *output, int tokens, int heads,
+                                int head_dim, b200k_stream stream);
+int transpose_token_to_head_f32(const float *input, float *output, int tokens, int heads,
+                                int head_dim, b200k_stream stream);
+/* Replaces qk_norm_rope_transpose_f32 (:119-175): per (token, head) RMS norm with norm_w [D] (caller passes
+ * inv_n = 1 / D), RoPE on the pairs (i, i + D/2) with tables row pos_offset + token, stored head-major
+ * [heads, tokens, D]. */
+int qk_norm_rope_transpose_f32(const float *input, const float *norm_w, const float *cos_tab,
+                               const float *sin_tab, float *output, int tokens, int heads,
+                               int head_dim, int pos_offset, float inv_n, float eps,
+                               b200k_stream stream);
+/* Replaces rope_transpose_f32 (:182-215): the same without the norm. */
+int rope_transpose_f32(const float *input, const float *cos_tab, const float *sin_tab,
+                       float *output, int tokens, int heads, int head_dim, int pos_offset,
+                       b200k_stream stream);
+
+/* ------------------------------------------------------------------------- */
 /* The reference has no MoE kernel (a search of its tree finds two comment mentions,
  * crates/triton-dsl/examples/awq_gemm_int4_typed.rs:63 and
  * crates/triton-kernels/src/elementwise.rs:222); these entry points follow its conventions for

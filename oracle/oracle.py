@@ -318,6 +318,37 @@ def rope_full(x, cos_table, sin_table, positions):
     return np.concatenate([x0 * c - x1 * s, x1 * c + x0 * s], axis=-1)
 
 
+def split_qkv(qkv, num_heads, head_dim):
+    """qkv [batch, 3, heads, D] -> (q, k, v) each [batch, heads, D] (`projection.rs:18-51`)."""
+    x = np.asarray(qkv, dtype=np.float32).reshape(-1, 3, num_heads, head_dim)
+    return x[:, 0].copy(), x[:, 1].copy(), x[:, 2].copy()
+
+
+def transpose_head_to_token(x):
+    """[heads, tokens, D] -> [tokens, heads, D] (`projection.rs:60-79`)."""
+    return np.ascontiguousarray(np.asarray(x, dtype=np.float32).transpose(1, 0, 2))
+
+
+def transpose_token_to_head(x):
+    """[tokens, heads, D] -> [heads, tokens, D] (`projection.rs:87-105`)."""
+    return np.ascontiguousarray(np.asarray(x, dtype=np.float32).transpose(1, 0, 2))
+
+
+def rope_transpose(x, cos_table, sin_table, pos_offset):
+    """x [tokens, heads, D] -> RoPE with table row pos_offset + token on the pairs (i, i + D/2), stored
+    head-major [heads, tokens, D] (`projection.rs:182-215`)."""
+    x = np.asarray(x, dtype=np.float32)
+    pos = pos_offset + np.arange(x.shape[0])
+    return transpose_token_to_head(rope_full(x, cos_table, sin_table, pos))
+
+
+def qk_norm_rope_transpose(x, norm_w, cos_table, sin_table, pos_offset, eps):
+    """Per (token, head): x * rsqrt(mean(x^2) + eps) * norm_w, then RoPE, then head-major store
+    (`projection.rs:119-175`; the scaled halves feed the rotation, `:164-168`)."""
+    x = np.asarray(x, dtype=np.float32)
+    return rope_transpose(rms_norm(x, np.asarray(norm_w, dtype=np.float32), eps), cos_table, sin_table, pos_offset)
+
+
 def kv_cache_append(new_k, new_v, k_cache, v_cache, cache_idx):
     """Seq-major shared cache [max_seq, H, D]; row b goes to cache[cache_idx[b]]
     (`cache.rs:21-47`).  In place."""

@@ -211,3 +211,23 @@ def test_c_layer_matches_numpy_layer(oracle, oracle_c):
     oracle_c.oc_decode_layer(*args)
     assert_close(out, ref, 2e-3, 2e-3, "C layer")
     assert (kc2 == kc).all() and (vc2 == vc).all()
+
+
+def test_projection_helpers_compose(oracle):
+    """The fused helpers equal the composition of the plain ones; the transposes invert each other."""
+    rng = np.random.default_rng(11)
+    tokens, heads, d, off = 5, 3, 8, 2
+    x = rng.standard_normal((tokens, heads, d)).astype(np.float32)
+    w = rng.uniform(0.5, 1.5, d).astype(np.float32)
+    cos, sin = oracle.rope_tables(off + tokens, d, 10000.0)
+    assert np.array_equal(oracle.transpose_head_to_token(oracle.transpose_token_to_head(x)), x)
+    pos = off + np.arange(tokens)
+    ref = oracle.rope_full(oracle.rms_norm(x, w, 1e-6), cos, sin, pos).transpose(1, 0, 2)
+    assert np.allclose(oracle.qk_norm_rope_transpose(x, w, cos, sin, off, 1e-6), ref, rtol=0, atol=0)
+    # hand-checkable case: one token, one head, D = 2, angle with cos = 0.6, sin = 0.8
+    out = oracle.rope_transpose(np.array([[[1.0, 2.0]]], np.float32), np.array([[0.6]], np.float32),
+                                np.array([[0.8]], np.float32), 0)
+    assert np.allclose(out, [[[1.0 * 0.6 - 2.0 * 0.8, 2.0 * 0.6 + 1.0 * 0.8]]])
+    qkv = np.arange(2 * 3 * 2 * 4, dtype=np.float32).reshape(2, 3, 2, 4)
+    q, k, v = oracle.split_qkv(qkv, 2, 4)
+    assert q[1, 1, 0] == qkv[1, 0, 1, 0] and k[0, 1, 3] == qkv[0, 1, 1, 3] and v[1, 0, 2] == qkv[1, 2, 0, 2]
