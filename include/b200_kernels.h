@@ -267,6 +267,21 @@ int paged_decode_attention_f16(const b200k_half *q, const b200k_half *k_block_po
 
 /* ------------------------------------------------------------------------- */
 /* fused MoE                                                                   */
+/* Replaces unified_attention_f32 (crates/triton-kernels/src/attention.rs:988-1187): prefill and decode in one
+ * call over a paged KV pool.  q / output [total_tokens, num_q_heads, D] token-major; k/v_cache
+ * [num_blocks, block_size, num_kv_heads, D]; block_table [num_seqs, max_blocks_per_seq]; seq_lens [num_seqs];
+ * query_start_loc [num_seqs + 1] (CSR offsets of each sequence's query tokens, which are the last q_len
+ * positions of its KV stream).  Causal: query token j of a sequence sees kv positions
+ * 0 .. seq_len - q_len + j.  The reference walks the KV stream in BLOCK_KV tiles and drops a ragged tail
+ * (seq_len / BLOCK_KV tiles, :1069); here every position below seq_len is used, which is the same
+ * thing whenever the caller keeps seq_len a multiple of its tile as that kernel asks.  num_seqs (the
+ * reference's grid extent) is the trailing argument; D <= 256. */
+int unified_attention_f32(const float *q, const float *k_cache, const float *v_cache,
+                          float *output, const int32_t *block_table, const int32_t *seq_lens,
+                          const int32_t *query_start_loc, int num_q_heads, int num_kv_heads,
+                          int head_dim, int block_size, int max_blocks_per_seq, float sm_scale,
+                          int num_seqs, b200k_stream stream);
+
 /* ------------------------------------------------------------------------- */
 /* Projection helpers either side of attention (crates/triton-kernels/src/projection.rs), fp32 as in */
 /* the reference.  Its const generics (BLOCK, HEAD_DIM, HALF_DIM) are tile limits there and runtime    */

@@ -318,6 +318,32 @@ def rope_full(x, cos_table, sin_table, positions):
     return np.concatenate([x0 * c - x1 * s, x1 * c + x0 * s], axis=-1)
 
 
+def unified_attention(q, k_pool, v_pool, block_table, seq_lens, query_start_loc, num_kv_heads, block_size, scale):
+    """Prefill + decode over a paged pool (`attention.rs:988-1187`): q [tokens, Hq, D]; pools
+    [blocks, block_size, Hkv, D]; the query tokens of a sequence are the last q_len positions of its KV
+    stream, causal mask kv_pos <= context_len + q_pos (`:1137-1153`), paged address arithmetic as `:1093-1101`."""
+    q = np.asarray(q, dtype=np.float32)
+    tokens, hq, d = q.shape
+    out = np.zeros_like(q)
+    groups = hq // num_kv_heads
+    for s in range(len(seq_lens)):
+        q0, q1 = int(query_start_loc[s]), int(query_start_loc[s + 1])
+        seq_len = int(seq_lens[s])
+        ctx = seq_len - (q1 - q0)
+        pos = np.arange(seq_len)
+        phys = np.asarray(block_table[s])[pos // block_size]
+        k = np.asarray(k_pool, dtype=np.float32)[phys, pos % block_size]        # [seq_len, Hkv, D]
+        v = np.asarray(v_pool, dtype=np.float32)[phys, pos % block_size]
+        for j in range(q1 - q0):
+            vis = ctx + j + 1
+            for h in range(hq):
+                kvh = h // groups
+                sc = (k[:vis, kvh] @ q[q0 + j, h]) * np.float32(scale)
+                p = np.exp(sc - sc.max())
+                out[q0 + j, h] = (p[:, None] * v[:vis, kvh]).sum(axis=0) / p.sum()
+    return out
+
+
 def split_qkv(qkv, num_heads, head_dim):
     """qkv [batch, 3, heads, D] -> (q, k, v) each [batch, heads, D] (`projection.rs:18-51`)."""
     x = np.asarray(qkv, dtype=np.float32).reshape(-1, 3, num_heads, head_dim)

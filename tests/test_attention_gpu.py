@@ -162,3 +162,34 @@ def test_f32_batched_and_split_phases(P, oracle):
     P.flash_decode_attn_phase1_f32(t(q[0]), t(k[0]), t(v[0]), pa[0], pm[0], ps[0], hq, hkv, d, L, splits, scale, bkv)
     comb = oracle.flash_decode_phase2(pa[0].cpu().numpy(), pm[0].cpu().numpy(), ps[0].cpu().numpy())
     assert_close(comb, ref[0], 1e-4, 1e-5)
+
+
+def _unified_case(rng, q_lens, seq_lens, hq, hkv, d, bs):
+    nseq = len(q_lens)
+    qsl = np.zeros(nseq + 1, dtype=np.int32)
+    qsl[1:] = np.cumsum(q_lens)
+    blocks_per_seq = max(-(-int(s) // bs) for s in seq_lens)
+    nblocks = nseq * blocks_per_seq + 3
+    table = rng.permutation(nblocks)[:nseq * blocks_per_seq].reshape(nseq, blocks_per_seq).astype(np.int32)
+    q = rng.standard_normal((int(qsl[-1]), hq, d)).astype(np.float32)
+    kp = rng.standard_normal((nblocks, bs, hkv, d)).astype(np.float32)
+    vp = rng.standard_normal((nblocks, bs, hkv, d)).astype(np.float32)
+    return q, kp, vp, table, np.asarray(seq_lens, dtype=np.int32), qsl, blocks_per_seq
+
+
+@pytest.mark.parametrize("q_lens,seq_lens,hq,hkv,d,bs", [
+    ([1, 1, 1], [17, 64, 5], 8, 2, 128, 16),            # pure decode
+    ([7, 12], [7, 12], 4, 4, 64, 8),                    # pure prefill (context 0): the standard causal mask
+    ([1, 9, 3, 1], [40, 9, 30, 1], 8, 2, 128, 16),      # mixed batch, one sequence of a single token
+    ([5], [21], 2, 1, 96, 4),                           # head_dim not a power of two
+])
+def test_unified_attention_vs_oracle(P, oracle, q_lens, seq_lens, hq, hkv, d, bs):
+    rng = np.random.default_rng(sum(seq_lens) + d)
+    q, kp, vp, table, sl, qsl, bps = _unified_case(rng, q_lens, seq_lens, hq, hkv, d, bs)
+    scale = 1.0 / np.sqrt(d)
+    ref = oracle.unified_attention(q, kp, vp, table, sl, qsl, hkv, bs, scale)
+    out = torch.full(q.shape, float("nan"), device=DEV)
+    P.unified_attention_f32(t(q), t(kp), t(vp), out, t(table), t(sl), t(qsl), hq, hkv, d, bs, bps, scale, len(q_lens),
+                            torch.cuda.current_stream().cuda_stream)
+    assert_close(out.cpu().numpy(), ref, 1e-4, 1e-5, "unified attention")
+

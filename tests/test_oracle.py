@@ -231,3 +231,28 @@ def test_projection_helpers_compose(oracle):
     qkv = np.arange(2 * 3 * 2 * 4, dtype=np.float32).reshape(2, 3, 2, 4)
     q, k, v = oracle.split_qkv(qkv, 2, 4)
     assert q[1, 1, 0] == qkv[1, 0, 1, 0] and k[0, 1, 3] == qkv[0, 1, 1, 3] and v[1, 0, 2] == qkv[1, 2, 0, 2]
+
+
+def test_unified_attention_decode_equals_paged_decode(oracle):
+    """With one query token per sequence the unified oracle computes what the paged decode oracle computes; with
+    context 0 it is plain causal attention."""
+    rng = np.random.default_rng(5)
+    hq, hkv, d, bs, n = 8, 2, 16, 4, 13
+    nblocks = 6
+    table = rng.permutation(nblocks)[:4].reshape(1, 4).astype(np.int32)
+    q = rng.standard_normal((1, hq, d)).astype(np.float32)
+    kp = rng.standard_normal((nblocks, bs, hkv, d)).astype(np.float32)
+    vp = rng.standard_normal((nblocks, bs, hkv, d)).astype(np.float32)
+    scale = 1.0 / np.sqrt(d)
+    got = oracle.unified_attention(q, kp, vp, table, np.array([n], np.int32), np.array([0, 1], np.int32), hkv, bs, scale)[0]
+    ref = oracle.paged_decode_attention(q[0], kp, vp, table[0], n, bs, scale)
+    assert np.allclose(got, ref, rtol=1e-5, atol=1e-6)
+    # prefill of 3 tokens, one head: token j attends to positions 0..j
+    q3 = rng.standard_normal((3, 1, d)).astype(np.float32)
+    out = oracle.unified_attention(q3, kp[:, :, :1], vp[:, :, :1], table, np.array([3], np.int32), np.array([0, 3], np.int32), 1, bs, scale)
+    k = kp[table[0][0], :3, 0]
+    v = vp[table[0][0], :3, 0]
+    for j in range(3):
+        sc = (k[:j + 1] @ q3[j, 0]) * scale
+        p = np.exp(sc - sc.max())
+        assert np.allclose(out[j, 0], (p[:, None] * v[:j + 1]).sum(0) / p.sum(), rtol=1e-5, atol=1e-6)

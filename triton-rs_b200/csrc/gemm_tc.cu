@@ -192,7 +192,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     // TMEM columns: NMMA fp32 accumulators [128 lanes][TT]; with TS, SD operand tiles of 32 columns behind them
     const uint32_t a_col0 = NMMA * TT < 32 ? 32 : NMMA * TT;
     uint32_t tmem_cols = 32;
-    while (tmem_cols < (TS ? a_col0 + 32u * SD : (uint32_t)TT)) tmem_cols <<= 1;
+    while (tmem_cols < (TS ? a_col0 + 32u * SD : (uint32_t)(NMMA * TT))) tmem_cols <<= 1;
 
     if (tid == 0) {
         for (int s = 0; s < SA; ++s) {
@@ -497,7 +497,7 @@ int gemm_tc_launch(const GemmArgs &g) {
     if (const char *e = getenv("B200K_TC_OPERAND")) ts = ts && e[0] != 's';
     const int a_bytes = ts ? 0 : TC_A_BYTES;
     int dq_stages, act_stages;
-    const int nmma = (ts && tt <= 64) ? 2 : 1;   // issuing warps (each with its own accumulator)
+    const int nmma = tt <= 64 ? 2 : 1;           // issuing warps (each with its own accumulator)
     if (ts) {   // operand tiles cost 32 TMEM columns each: 256 columns per CTA with two CTAs per SM, 512 with one
         dq_stages = 4;                                   // shallow: an activation tile is requested act - dq blocks ahead
         act_stages = tt <= 64 ? 8 : (tt == 128 ? 6 : 4);
@@ -597,9 +597,9 @@ int gemm_tc_launch(const GemmArgs &g) {
     P.status = (int *)g.ws;   // status word at the start of the scratch buffer
     if (!P.status) return fail(B200K_E_WORKSPACE, "w4a16 gemm (tensor core): workspace is NULL");
 
-    auto kern = g.format == FMT_AWQ ? (ng == 2 ? gemm_tc_kernel<FMT_AWQ, 2, false, 1> : gemm_tc_kernel<FMT_AWQ, 4, false, 1>)
+    auto kern = g.format == FMT_AWQ ? (ng == 2 ? gemm_tc_kernel<FMT_AWQ, 2, false, 2> : gemm_tc_kernel<FMT_AWQ, 4, false, 1>)
                 : ts ? (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1>)
-                     : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, false, 1> : gemm_tc_kernel<FMT_GPTQ, 4, false, 1>);
+                     : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, false, 2> : gemm_tc_kernel<FMT_GPTQ, 4, false, 1>);
     static bool attr_set[3][2][16] = {};
     const int variant = g.format == FMT_AWQ ? 1 : (ts ? 2 : 0);
     int dev = 0;
