@@ -127,6 +127,20 @@ int awq_gemm_int4_f16_ws(const b200k_half *a, const int32_t *qweight, const b200
                          int stride_qzk, int stride_qzn, int stride_cm, int stride_cn,
                          void *workspace, size_t workspace_bytes, b200k_stream stream);
 
+/* GPTQ GEMM on activations whose every 8 consecutive k are stored as (k0,k4,k1,k5,k2,k6,k3,k7) -- the order in
+ * which the nibble arithmetic yields a packed word's values, so the kernel skips the byte-permutes that would
+ * restore k order (a contraction may visit k in any order when both operands agree).  Contiguous tensors only
+ * (a [M, K], qweight [K/8, N], scales [K/G, N], qzeros [K/G, N/8] or NULL for the symmetric zero-point 8,
+ * c [M, N]); same result, bit for bit, as w4a16_gptq_gemm_f16 / _sym_f16 on the unpermuted activations.
+ * permute_k8_f16 produces that order from a plain [rows, K] tensor (a producer kernel that writes it directly
+ * pays nothing: b200k_layer does so internally).  No counterpart in the reference. */
+int permute_k8_f16(const b200k_half *input, b200k_half *output, int rows, int k_size,
+                   b200k_stream stream);
+int w4a16_gptq_gemm_kperm_f16(const b200k_half *a_permuted, const int32_t *qweight,
+                              const b200k_half *scales, const int32_t *qzeros, b200k_half *c,
+                              int m_size, int n_size, int k_size, int group_size,
+                              b200k_stream stream);
+
 /* Launch plan of the tensor-core GEMM family for a shape, without launching anything (usable without a
  * GPU): host_plan_out[10] = {token tile, dequant groups, operand-ring depth, activation-ring depth,
  * weight-ring depth, K split, K blocks per split, output tiles, MMA-issuing warps, 1 if the dequantised

@@ -138,3 +138,24 @@ def test_golden_gemm(P):
     w = golden("awq_gemm")
     c = P.awq_gemm(t(w["a"]), t(w["qweight"]), t(w["scales"]), t(w["qzeros"]), 128)
     assert_close(c.float().cpu().numpy(), w["c"])
+
+
+@pytest.mark.parametrize("M,K,N,G,sym", [(64, 4096, 6144, 128, True), (16, 512, 256, 128, False), (1, 1024, 512, 128, False),
+                                         (300, 1024, 256, 64, False), (7, 256, 128, 128, True)])
+def test_prepermuted_activations_give_identical_bits(P, M, K, N, G, sym):
+    """w4a16_gptq_gemm_kperm_f16 on permute_k8_f16(a) == the plain entry point on a, bit for bit."""
+    gen = torch.Generator(device=DEV).manual_seed(M + K)
+    a = torch.randn((M, K), device=DEV, generator=gen).half()
+    qw = torch.randint(-2 ** 31, 2 ** 31 - 1, (K // 8, N), device=DEV, dtype=torch.int32, generator=gen)
+    sc = (torch.rand((K // G, N), device=DEV, generator=gen) * 0.018 + 0.002).half()
+    qz = None if sym else torch.randint(-2 ** 31, 2 ** 31 - 1, (K // G, N // 8), device=DEV, dtype=torch.int32, generator=gen)
+    ref = P.gptq_gemm(a, qw, sc, qz, G)
+    ap = torch.empty_like(a)
+    st = torch.cuda.current_stream().cuda_stream
+    P.permute_k8_f16(a, ap, M, K, st)
+    chunk = a.view(M, K // 8, 8)[:, :, [0, 4, 1, 5, 2, 6, 3, 7]].reshape(M, K)
+    assert torch.equal(ap, chunk)
+    out = torch.empty_like(ref)
+    P.w4a16_gptq_gemm_kperm_f16(ap, qw, sc, qz, out, M, N, K, G, st)
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int16), ref.view(torch.int16))

@@ -65,7 +65,15 @@ struct AttnSplitArgs {
     float *ws_ml;           // [B*Hkv*max_chunks, G, 2]  (max, sum)
     int *counters;          // [B*Hkv], zero between launches
     int *status;            // device status word (0 = ok)
+    int out_kperm;          // store every 8 output values of a head as (d0,d4,d1,d5,d2,d6,d3,d7), the order the int4 GEMM that
+                            // consumes them wants (see gemm_tc.cu)
 };
+
+// index of element i of a row when every 8-chunk is stored as (0,4,1,5,2,6,3,7)
+__device__ __forceinline__ long kperm_index(long i, int on) {
+    const int e = (int)(i & 7);
+    return on ? (i & ~7L) | (e < 4 ? 2 * e : 2 * (e - 4) + 1) : i;
+}
 
 struct AttnSmem {
     __align__(1024) unsigned char kv[AT_STAGES][2][2][AT_HALF_BYTES];   // [stage][K|V][dims 0-63 | 64-127][swizzled rows]
@@ -295,7 +303,7 @@ attn_split_f16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
 #pragma unroll
         for (int w = 0; w < AT_THREADS / 32; ++w) o += So[w][d][g] * S.wgt[w][g];
         if (nchunks == 1)
-            A.out[out_row0 + i] = __float2half_rn(o / S.lsum[g]);
+            A.out[out_row0 + kperm_index(i, A.out_kperm)] = __float2half_rn(o / S.lsum[g]);
         else
             A.ws_acc[item * G * AT_D + i] = o;
     }
@@ -325,7 +333,7 @@ attn_split_f16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
             Lt += __ldcg(&A.ws_ml[((item0 + c) * G + g) * 2 + 1]) * w;
             o += __ldcg(&A.ws_acc[(item0 + c) * G * AT_D + i]) * w;
         }
-        A.out[out_row0 + i] = __float2half_rn(o / Lt);
+        A.out[out_row0 + kperm_index(i, A.out_kperm)] = __float2half_rn(o / Lt);
     }
     if (tid == 0) A.counters[b * A.hkv + kvh] = 0;  // ready for the next launch
 }
@@ -387,6 +395,7 @@ struct AttnCall {
     size_t ws_bytes;
     bool own_ws;
     cudaStream_t stream;
+    bool out_kperm = false;
 };
 
 static int attn_split_launch(const char *name, AttnCall c) {
@@ -404,6 +413,7 @@ static int attn_split_launch(const char *name, AttnCall c) {
     B200K_REQUIRE(w.bytes <= c.ws_bytes, B200K_E_WORKSPACE, "%s: workspace %zu bytes, need %zu", name, c.ws_bytes, w.bytes);
     AttnSplitArgs A;
     A.q = c.q; A.k = c.k; A.v = c.v; A.out = c.out; A.lens = c.lens; A.len_scalar = c.len_scalar;
+    A.out_kperm = c.out_kperm ? 1 : 0;
     A.hq = c.hq; A.hkv = c.hkv; A.g = g; A.chunk = chunk;
     A.scale_log2e = c.scale * 1.4426950408889634f;
     A.seq_major = c.mode != KV_HEAD_MAJOR;
@@ -672,6 +682,28 @@ extern "C" int batched_decode_attention_hm_f16_ws(const b200k_half *q, const b20
     c.stream = to_stream(stream);
     return attn_split_launch(name, c);
 }
+// The same call with the output written in the pre-permuted order the int4 GEMM wants (used by the decode layer)
+namespace b200k {
+int batched_decode_attention_hm_f16_kperm(const __half *q, const __half *k_cache, const __half *v_cache,
+                                          const int32_t *context_lens, __half *output, int batch_size, int num_q_heads,
+                                          int num_kv_heads, int head_dim, int max_len, float scale, cudaStream_t st) {
+    const char *name = "batched_decode_attention_hm_f16";
+    B200K_REQUIRE(q && k_cache && v_cache && context_lens && output, B200K_E_NULL, "%s: NULL pointer", name);
+    if (batch_size == 0) return 0;
+    B200K_REQUIRE(split_ok(num_q_heads, num_kv_heads, head_dim, q, k_cache, v_cache, output), B200K_E_SHAPE,
+                  "%s: needs head_dim 128, GQA group size <= 8 and 16-byte aligned tensors", name);
+    AttnCall c = {};
+    c.q = q; c.k = k_cache; c.v = v_cache; c.out = output;
+    c.lens = context_lens; c.len_scalar = 0; c.batch = batch_size; c.hq = num_q_heads; c.hkv = num_kv_heads;
+    c.d = head_dim; c.max_len = max_len; c.mode = KV_HEAD_MAJOR; c.pos_extent = max_len; c.row_pitch = max_len;
+    c.scale = scale;
+    c.ws = nullptr; c.ws_bytes = 0; c.own_ws = true;
+    c.stream = st;
+    c.out_kperm = true;
+    return attn_split_launch(name, c);
+}
+}  // namespace b200k
+
 extern "C" int batched_decode_attention_hm_f16(const b200k_half *q, const b200k_half *k_cache,
                                                const b200k_half *v_cache, const int32_t *context_lens,
                                                b200k_half *output, int batch_size, int num_q_heads, int num_kv_heads,

@@ -89,9 +89,13 @@ constexpr int GEMV_THREADS = 256;
 constexpr int GEMV_WARPS = GEMV_THREADS / 32;
 
 // x permuted per 8-group to (x0,x4,x1,x5,x2,x6,x3,x7): the order nib_lo/nib_hi pair up.
-__device__ __forceinline__ void stage_x_gptq(const __half *x, __half *xs, int k) {
+__device__ __forceinline__ void stage_x_gptq(const __half *x, __half *xs, int k, bool already_permuted) {
     for (int i = threadIdx.x; i < k / 8; i += blockDim.x) {
         const uint4 u = *reinterpret_cast<const uint4 *>(x + i * 8);
+        if (already_permuted) {
+            *reinterpret_cast<uint4 *>(xs + i * 8) = u;
+            continue;
+        }
         uint4 p;
         p.x = __byte_perm(u.x, u.z, 0x5410);  // (x0, x4)
         p.y = __byte_perm(u.x, u.z, 0x7632);  // (x1, x5)
@@ -153,7 +157,7 @@ gemv_gptq_kernel(GemmArgs g, int ksplit) {
     };
     if (live && kslot < groups) request(kslot);
 
-    stage_x_gptq(g.a, xs, g.k);
+    stage_x_gptq(g.a, xs, g.k, g.a_kperm);
     __syncthreads();
 
     float tot[4] = {0.f, 0.f, 0.f, 0.f};
@@ -454,6 +458,17 @@ static int gemm_dispatch(const char *name, GemmArgs g, bool own_ws) {
                   g.k, g.n, g.group);
     if (g.m == 0) return 0;
     const bool canon = gemm_layout_is_canonical(g);
+    if (g.a_kperm) {
+        // pre-permuted activations: only the families that consume that order (GPTQ GEMV and tensor-core path)
+        B200K_REQUIRE(canon && g.format == FMT_GPTQ, B200K_E_SHAPE, "%s: needs the canonical GPTQ layout (contiguous, 16-byte aligned rows)", name);
+        if (g.m == 1 && g.k <= 65536) return gemv_launch(g);
+        if (!g.ws && own_ws) {
+            int rc = default_workspace(&g.ws, &g.ws_bytes);
+            if (rc) return rc;
+        }
+        const int rc = gemm_tc_launch(g);
+        return rc == 1 ? fail(B200K_E_SHAPE, "%s: shape not covered by the tensor-core family (K %% 64, group a power of two >= 64, N %% 32 with qzeros)", name) : rc;
+    }
     const char *force = getenv("B200K_GEMM_PATH");  // tuning/testing override: strided | gemv | tc
     if (force && !strcmp(force, "strided")) return gemm_strided_launch(g);
     if (canon && g.m == 1 && g.k <= 65536 && !(force && !strcmp(force, "tc"))) return gemv_launch(g);
@@ -479,7 +494,7 @@ using namespace b200k;
     g.s_am = stride_am; g.s_ak = stride_ak; g.s_qwk = stride_qwk; g.s_qwn = stride_qwn;               \
     g.s_sk = stride_sk; g.s_sn = stride_sn; g.s_cm = stride_cm; g.s_cn = stride_cn;                   \
     g.format = FMT; g.zero_offset = ZO; g.stream = to_stream(stream);                                 \
-    g.seg_offsets = nullptr; g.num_segments = 0; g.plan_out = nullptr;
+    g.seg_offsets = nullptr; g.num_segments = 0; g.plan_out = nullptr; g.a_kperm = false;
 
 extern "C" int w4a16_gptq_gemm_f16_ws(const b200k_half *a, const int32_t *qweight, const b200k_half *scales,
                                       const int32_t *qzeros, b200k_half *c, int m_size, int n_size, int k_size,
@@ -560,6 +575,43 @@ extern "C" int b200k_unpack_gptq_qzeros(const int32_t *qzeros, int8_t *out, int 
 }
 extern "C" int b200k_unpack_awq(const int32_t *packed, int8_t *out, int rows, int n_dim, b200k_stream s) {
     return unpack_launch("b200k_unpack_awq", packed, out, rows, n_dim, 2, 0, to_stream(s));
+}
+
+// ---- pre-permuted activations ---------------------------------------------------------------
+__global__ void __launch_bounds__(256) permute_k8_kernel(const uint4 *__restrict__ in, uint4 *__restrict__ out, long chunks) {
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < chunks; i += (long)gridDim.x * blockDim.x) {
+        const uint4 u = in[i];
+        uint4 p;
+        p.x = __byte_perm(u.x, u.z, 0x5410);  // (x0, x4)
+        p.y = __byte_perm(u.x, u.z, 0x7632);  // (x1, x5)
+        p.z = __byte_perm(u.y, u.w, 0x5410);  // (x2, x6)
+        p.w = __byte_perm(u.y, u.w, 0x7632);  // (x3, x7)
+        out[i] = p;
+    }
+}
+
+extern "C" int permute_k8_f16(const b200k_half *input, b200k_half *output, int rows, int k_size, b200k_stream stream) {
+    B200K_REQUIRE(rows >= 0 && k_size >= 0 && k_size % 8 == 0, B200K_E_SHAPE, "permute_k8_f16: rows %d, K %d (multiple of 8)", rows, k_size);
+    const long chunks = (long)rows * k_size / 8;
+    if (chunks == 0) return 0;
+    B200K_REQUIRE(input && output && aligned16(input) && aligned16(output), B200K_E_NULL, "permute_k8_f16: NULL or unaligned pointer");
+    long blocks = (chunks + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    permute_k8_kernel<<<(int)blocks, 256, 0, to_stream(stream)>>>((const uint4 *)input, (uint4 *)output, chunks);
+    return launch_status("permute_k8_f16");
+}
+
+extern "C" int w4a16_gptq_gemm_kperm_f16(const b200k_half *a_permuted, const int32_t *qweight, const b200k_half *scales,
+                                         const int32_t *qzeros, b200k_half *c, int m_size, int n_size, int k_size,
+                                         int group_size, b200k_stream stream) {
+    const int stride_am = k_size, stride_ak = 1, stride_qwk = n_size, stride_qwn = 1, stride_sk = n_size, stride_sn = 1,
+              stride_cm = n_size, stride_cn = 1;
+    const b200k_half *a = a_permuted;
+    GEMM_ARGS_FILL(FMT_GPTQ, qzeros ? 1 : 0)
+    g.qzeros = qzeros; g.s_qzk = n_size / 8; g.s_qzn = 1;
+    g.ws = nullptr; g.ws_bytes = 0;
+    g.a_kperm = true;
+    return gemm_dispatch("w4a16_gptq_gemm_kperm_f16", g, true);
 }
 
 extern "C" int b200k_gemm_tc_plan(int m_size, int n_size, int k_size, int group_size, int awq, int *host_plan_out) {

@@ -22,6 +22,7 @@ struct GemmArgs {
     // [num_segments, K/8 (or K), ...] laid out contiguously; m = total rows.  nullptr: ordinary GEMM.
     const int *seg_offsets;
     int num_segments;
+    bool a_kperm;     // activations pre-permuted per 8 consecutive k to (k0,k4,k1,k5,k2,k6,k3,k7) (tensor-core GPTQ path, GEMV)
     int *plan_out;    // host pointer: when set, the tensor-core family writes its launch plan there and launches nothing
     void *ws;         // scratch (may be nullptr when the chosen path needs none)
     size_t ws_bytes;

@@ -52,9 +52,9 @@ struct TcArgs {
     int s_sk, s_qzk, s_cm;
     int zero_offset;
     int tt;            // token tile = MMA N (16, 32, 64, 128, 256)
-    int dq_stages;     // SD: ring of dequantised operand tiles (on-chip producer and consumer: shallow)
-    int act_stages;    // SA: ring of activation tiles (TMA from L2: deep enough to cover its latency)
-    int raw_stages;    // R: ring of packed-weight tiles; deepest, because 4 KiB per K block is all
+    int dq_log2;       // log2 of SD: ring of dequantised operand tiles (on-chip producer and consumer: shallow)
+    int act_log2;      // log2 of SA: ring of activation tiles (TMA from L2: deep enough to cover its latency)
+    int raw_log2;      // log2 of R: ring of packed-weight tiles; deepest, because 4 KiB per K block is all
                        //    the HBM traffic there is and enough of it must be in flight
     int ksplit;        // cluster size along K
     int kb_per_split;  // K blocks per split
@@ -129,18 +129,11 @@ __host__ __device__ __forceinline__ uint32_t umma_idesc(int m, int n, int a_mn_m
     return (1u << 4) | ((uint32_t)a_mn_major << 15) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-// Position in a ring of `n` slots: slot index and the parity of the phase in flight.
-struct Ring {
-    int n, slot;
-    uint32_t phase;
-    __device__ __forceinline__ Ring(int n_) : n(n_), slot(0), phase(0) {}
-    __device__ __forceinline__ void next() {
-        if (++slot == n) {
-            slot = 0;
-            phase ^= 1u;
-        }
-    }
-};
+// The depths of the three rings are powers of two, so the slot of block i and the parity of the phase it
+// belongs to are bit fields of i: nothing but i is carried from block to block (ring cursors kept in
+// registers and advanced block by block cost a tenth of the dequant warps' instruction stream).
+__device__ __forceinline__ int ring_slot(int i, int lg) { return i & ((1 << lg) - 1); }
+__device__ __forceinline__ uint32_t ring_phase(int i, int lg) { return (uint32_t)(i >> lg) & 1u; }
 
 // TS: the dequantised operand tile goes to tensor memory (tcgen05.st) instead of shared memory and the
 // MMA reads it from there.  GPTQ only: a thread that owns weight column n holds, word by word, 8
@@ -150,13 +143,18 @@ struct Ring {
 // to issuer i % 2, which is also dequant group i % 2 when there are two groups); the epilogue adds the two
 // accumulators.  At token tiles of 16..64 one thread cannot issue 4 MMAs, wait and commit fast enough to
 // keep up with the operand stream; at 128 and above the MMAs themselves take longer than their issue.
-template <int FMT, int NG, bool TS, int NMMA>
+// KPERM: the activations arrive with every 8 consecutive k stored as (k0,k4,k1,k5,k2,k6,k3,k7), the order in which the
+// nibble trick yields a word's values; the 4 byte-permutes per word that would restore k order then disappear (they
+// run on the half-rate integer pipe, the busiest unit of this kernel).  A contraction may visit k in any order as
+// long as both operands agree.
+template <int FMT, int NG, bool TS, int NMMA, bool KPERM>
 __global__ void __launch_bounds__(tc_threads(NG), NG == 2 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap amap,
                const __grid_constant__ CUtensorMap smap, const __grid_constant__ CUtensorMap zmap, TcArgs P) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    const int SD = P.dq_stages, SA = P.act_stages, R = P.raw_stages, TT = P.tt;
+    const int LSD = P.dq_log2, LSA = P.act_log2, LR = P.raw_log2, TT = P.tt;
+    const int SD = 1 << LSD, SA = 1 << LSA, R = 1 << LR;
     const int b_bytes = TT * TC_BK * 2;
     unsigned char *a_tile = smem;                               // [SD][16 KiB] (absent when the operand tile lives in TMEM)
     unsigned char *b_tile = a_tile + (TS ? 0 : (size_t)SD * TC_A_BYTES);   // [SA][TT * 128]
@@ -230,6 +228,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         }
     };
 
+    // For a barrier already tested once (result `ok`): nothing to do when that test succeeded.
+    auto wait_after_test = [&](bool ok, int bar_idx, uint32_t parity) {
+        if (!ok) wait(bar_idx, parity);
+    };
+
     if (warp == 0) {
         // ---------------- TMA producer, packed weights: R blocks ahead ----------------
         if (lane == 0) {
@@ -237,10 +240,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             tma_prefetch_desc(&wmap);
             tma_prefetch_desc(&smap);
             if (P.qzeros) tma_prefetch_desc(&zmap);
-            Ring rr(R);
-            for (int i = 0; i < nkb; ++i, rr.next()) {
-                const int r = rr.slot, kb = kb_begin + i;
-                if (i >= R) wait(B_RAWE + r, rr.phase ^ 1u);
+            for (int i = 0; i < nkb; ++i) {
+                const int r = ring_slot(i, LR), kb = kb_begin + i;
+                if (i >= R) wait(B_RAWE + r, ring_phase(i, LR) ^ 1u);
                 const uint32_t bar = smem_u32(&bars[B_RAWF + r]);
                 const uint32_t dst = smem_u32(raw + (size_t)r * TC_RAW_BYTES);
                 mbar_expect_tx(bar, TC_W_BYTES + TC_SC_BYTES + (P.qzeros ? TC_ZP_BYTES : 0));
@@ -258,10 +260,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         // ---------------- TMA producer, activation tiles: SA blocks ahead ----------------
         if (lane == 0) {
             tma_prefetch_desc(&amap);
-            Ring ra(SA);
-            for (int i = 0; i < nkb; ++i, ra.next()) {
-                const int s = ra.slot;
-                if (i >= SA) wait(B_ACTE + s, ra.phase ^ 1u);
+            for (int i = 0; i < nkb; ++i) {
+                const int s = ring_slot(i, LSA);
+                if (i >= SA) wait(B_ACTE + s, ring_phase(i, LSA) ^ 1u);
                 const uint32_t bar = smem_u32(&bars[B_ACTF + s]);
                 mbar_expect_tx(bar, b_bytes);
                 tma_load_2d(smem_u32(b_tile + (size_t)s * b_bytes), &amap, (kb_begin + i) * TC_BK, m0, bar);
@@ -280,11 +281,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             const uint64_t db0 = umma_desc(smem_u32(b_tile), 16, 1024);
             const uint32_t a_step = (FMT == FMT_GPTQ ? 32 : 2048) >> 4;     // descriptor address units of 16 bytes
             const uint32_t acc = tmem_acc + mw * TT;
-            Ring ra(SA), rd(SD);
-            for (int j = 0; j < mw; ++j) { ra.next(); rd.next(); }
             for (int i = mw; i < nkb; i += NMMA) {
-                const int sd = rd.slot, sa = ra.slot;
-                wait(B_DQF + sd, rd.phase);
+                const int sd = ring_slot(i, LSD), sa = ring_slot(i, LSA);
+                wait(B_DQF + sd, ring_phase(i, LSD));
                 tc_fence_after();
                 const uint64_t da = da0 + (uint64_t)((sd * TC_A_BYTES) >> 4);
                 const uint64_t db = db0 + (uint64_t)((sa * b_bytes) >> 4);
@@ -297,8 +296,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                         tc_mma_f16(acc, da + (uint64_t)(j * a_step), db + (uint64_t)(j * 2), idesc, (i >= NMMA || j > 0) ? 1u : 0u);
                 }
                 tc_commit(smem_u32(&bars[B_DQE + sd]));   // operand tile (and, through it, the activation tile) reusable once these retire
-#pragma unroll
-                for (int j = 0; j < NMMA; ++j) { ra.next(); rd.next(); }
             }
             tc_commit(smem_u32(&bars[B_ACC]));            // this issuer's accumulator complete (immediately, if it had no block)
         }
@@ -308,13 +305,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         const int tg = tid - 32 * TC_DQ_WARP0;
         // t = operand row; the hardware warp's TMEM lane quadrant is warp % 4, and a group is 4 consecutive warps
         const int grp_id = tg >> 7, t = ((warp & 3) << 5) | lane, warp_in_group = (tg & 127) >> 5;
-        Ring rr(R), rd(SD), ra(SA), ra_old(SA);   // ra: this block's activation slot; ra_old: that of block i - SD
-        for (int j = 0; j < grp_id; ++j) { rr.next(); rd.next(); ra.next(); }
-        // the first block this group sees retire is block (grp_id - SD) mod NG
-        for (int j = 0, first_old = ((grp_id - SD) % NG + NG) % NG; j < first_old; ++j) ra_old.next();
         for (int i = grp_id; i < nkb; i += NG) {
-            const int s = rd.slot, r = rr.slot;
-            wait(B_RAWF + r, rr.phase);                               // packed words, scales, zero-points landed
+            const int s = ring_slot(i, LSD), r = ring_slot(i, LR);
+            // The three barriers of this block are tested back to back: a test costs well over a hundred cycles even
+            // when the phase is long complete, and the tests are independent, so their latencies overlap.
+            const bool ok_raw = mbar_try_wait(smem_u32(&bars[B_RAWF + r]), ring_phase(i, LR));
+            const bool ok_dqe = i < SD || mbar_try_wait(smem_u32(&bars[B_DQE + s]), ring_phase(i, LSD) ^ 1u);
+            const bool ok_act = mbar_try_wait(smem_u32(&bars[B_ACTF + ring_slot(i, LSA)]), ring_phase(i, LSA));
+            wait_after_test(ok_raw, B_RAWF + r, ring_phase(i, LR));                               // packed words, scales, zero-points landed
             const unsigned char *slot = raw + (size_t)r * TC_RAW_BYTES;
             const uint32_t *rw = reinterpret_cast<const uint32_t *>(slot);
             uint32_t w[8];
@@ -332,11 +330,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bars[B_RAWE + r]));  // this warp is done with the packed tile
                 if (i >= SD) {
-                    wait(B_DQE + s, rd.phase ^ 1u);   // block i - SD retired: its operand tile is free, and so is its activation tile
+                    wait_after_test(ok_dqe, B_DQE + s, ring_phase(i, LSD) ^ 1u);   // block i - SD retired: its operand tile is free, and so is its activation tile
                     if (TS) tc_fence_after();         // the tensor-memory store below is ordered after the MMAs that read the tile
-                    if (warp_in_group == 0 && lane == 0) mbar_arrive(smem_u32(&bars[B_ACTE + ra_old.slot]));
-#pragma unroll
-                    for (int j = 0; j < NG; ++j) ra_old.next();
+                    if (warp_in_group == 0 && lane == 0) mbar_arrive(smem_u32(&bars[B_ACTE + ring_slot(i - SD, LSA)]));
                 }
                 unsigned char *arow = a_tile + (size_t)s * TC_A_BYTES + t * 128;
                 uint32_t v[32];
@@ -348,10 +344,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                     const uint32_t v26 = h22u(__hmul2(__hsub2(u2h2(nib_lo(w8)), zlo), s2));
                     const uint32_t v37 = h22u(__hmul2(__hsub2(u2h2(nib_hi(w8)), zhi), s2));
                     uint4 o;
-                    o.x = __byte_perm(v04, v15, 0x5410);   // k0 k1
-                    o.y = __byte_perm(v26, v37, 0x5410);   // k2 k3
-                    o.z = __byte_perm(v04, v15, 0x7632);   // k4 k5
-                    o.w = __byte_perm(v26, v37, 0x7632);   // k6 k7
+                    if (KPERM) {
+                        o = make_uint4(v04, v15, v26, v37);    // (k0 k4) (k1 k5) (k2 k6) (k3 k7): the activations' order
+                    } else {
+                        o.x = __byte_perm(v04, v15, 0x5410);   // k0 k1
+                        o.y = __byte_perm(v26, v37, 0x5410);   // k2 k3
+                        o.z = __byte_perm(v04, v15, 0x7632);   // k4 k5
+                        o.w = __byte_perm(v26, v37, 0x7632);   // k6 k7
+                    }
                     if (TS) {
                         v[4 * j] = o.x; v[4 * j + 1] = o.y; v[4 * j + 2] = o.z; v[4 * j + 3] = o.w;
                     } else {
@@ -376,10 +376,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bars[B_RAWE + r]));
                 if (i >= SD) {
-                    wait(B_DQE + s, rd.phase ^ 1u);   // block i - SD retired: its operand tile is free, and so is its activation tile
-                    if (warp_in_group == 0 && lane == 0) mbar_arrive(smem_u32(&bars[B_ACTE + ra_old.slot]));
-#pragma unroll
-                    for (int j = 0; j < NG; ++j) ra_old.next();
+                    wait_after_test(ok_dqe, B_DQE + s, ring_phase(i, LSD) ^ 1u);   // block i - SD retired: its operand tile is free, and so is its activation tile
+                    if (warp_in_group == 0 && lane == 0) mbar_arrive(smem_u32(&bars[B_ACTE + ring_slot(i - SD, LSA)]));
                 }
                 unsigned char *ahalf = a_tile + (size_t)s * TC_A_BYTES + (n8 >> 3) * 8192;
 #pragma unroll
@@ -397,11 +395,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             if (!TS) fence_proxy_async();
             __syncwarp();
             if (lane == 0) {
-                wait(B_ACTF + ra.slot, ra.phase);     // the MMA issuer waits on B_DQF alone
+                wait_after_test(ok_act, B_ACTF + ring_slot(i, LSA), ring_phase(i, LSA));     // the MMA issuer waits on B_DQF alone
                 mbar_arrive(smem_u32(&bars[B_DQF + s]));
             }
-#pragma unroll
-            for (int j = 0; j < NG; ++j) { rr.next(); rd.next(); ra.next(); }
         }
         // ---------------- epilogue: TMEM -> registers -> C (or the split-K exchange) ----------------
         if (nkb > 0) {
@@ -496,33 +492,33 @@ int gemm_tc_launch(const GemmArgs &g) {
     bool ts = g.format == FMT_GPTQ;
     if (const char *e = getenv("B200K_TC_OPERAND")) ts = ts && e[0] != 's';
     const int a_bytes = ts ? 0 : TC_A_BYTES;
-    int dq_stages, act_stages;
+    // Ring depths, powers of two (slot and phase of a block are then bit fields of its index).  The operand ring
+    // is shallow (producer and consumer are on chip) and at least as deep as there are dequant groups; an
+    // activation slot is handed back when the operand tile SD blocks later is recycled, so the activation ring
+    // is at least as deep as the operand ring (the last SD blocks never hand theirs back) and an activation
+    // tile is requested SA - SD blocks ahead; the ring of packed words takes what is left, 16 at most.
     const int nmma = tt <= 64 ? 2 : 1;           // issuing warps (each with its own accumulator)
+    auto pow2_floor = [](int v) { int p = 1; while (p * 2 <= v) p *= 2; return p; };
+    auto log2i = [](int v) { int l = 0; while ((1 << l) < v) ++l; return l; };
+    int dq_stages, act_stages;
     if (ts) {   // operand tiles cost 32 TMEM columns each: 256 columns per CTA with two CTAs per SM, 512 with one
-        dq_stages = 4;                                   // shallow: an activation tile is requested act - dq blocks ahead
-        act_stages = tt <= 64 ? 8 : (tt == 128 ? 6 : 4);
+        dq_stages = 4;
+        act_stages = tt <= 128 ? 8 : 4;
     } else {
-        dq_stages = tt <= 32 ? 3 : (tt == 64 ? 2 : (tt == 128 ? 5 : 4));
-        act_stages = tt <= 32 ? 8 : (tt == 64 ? 6 : (tt == 128 ? 5 : 4));
+        dq_stages = tt <= 64 ? 2 : 4;
+        act_stages = tt <= 32 ? 8 : 4;
     }
-    if (const char *e = getenv("B200K_TC_DQ_STAGES")) dq_stages = atoi(e);     // tuning overrides
-    if (const char *e = getenv("B200K_TC_ACT_STAGES")) act_stages = atoi(e);
-    // An activation slot is handed back when the operand tile SD blocks later is recycled, so the last SD
-    // blocks never hand theirs back: the activation ring must be at least as deep as the operand ring, and
-    // the operand ring as deep as there are dequant groups.
+    if (const char *e = getenv("B200K_TC_DQ_STAGES")) dq_stages = pow2_floor(atoi(e) < 1 ? 1 : atoi(e));     // tuning overrides
+    if (const char *e = getenv("B200K_TC_ACT_STAGES")) act_stages = pow2_floor(atoi(e) < 1 ? 1 : atoi(e));
     if (dq_stages < ng) dq_stages = ng;
-    if (ts) {
-        const int cols = (ctas_per_sm == 2 ? 256 : 512) - (nmma * tt < 32 ? 32 : nmma * tt);
-        if (dq_stages > cols / 32) dq_stages = cols / 32;
-        if (dq_stages < ng) return 1;
-    }
+    if (ts && (nmma * tt < 32 ? 32 : nmma * tt) + 32 * dq_stages > (ctas_per_sm == 2 ? 256 : 512)) return 1;
     if (act_stages < dq_stages) act_stages = dq_stages;
     int raw_stages = (budget - dq_stages * a_bytes - act_stages * act_bytes - 1024) / TC_RAW_BYTES;
-    if (raw_stages > 16) raw_stages = 16;
     if (raw_stages < 2) return 1;
+    raw_stages = pow2_floor(raw_stages > 16 ? 16 : raw_stages);
     if (const char *e = getenv("B200K_TC_RAW_STAGES")) {
         const int v = atoi(e);
-        if (v >= 2 && v <= raw_stages) raw_stages = v;
+        if (v >= 2 && v <= raw_stages) raw_stages = pow2_floor(v);
     }
     // K split (cluster of 1, 2, 4 or 8 CTAs along K).  A CTA costs ~6 us of fill, drain and exchange
     // whatever its length, so: the fewest CTAs that still occupy most SMs; one more doubling only when
@@ -589,7 +585,7 @@ int gemm_tc_launch(const GemmArgs &g) {
     P.m = g.m; P.n = g.n; P.k = g.k; P.group = g.group;
     P.s_sk = g.s_sk; P.s_qzk = g.s_qzk; P.s_cm = g.s_cm;
     P.zero_offset = g.zero_offset;
-    P.tt = tt; P.dq_stages = dq_stages; P.act_stages = act_stages; P.raw_stages = raw_stages; P.ksplit = ksplit;
+    P.tt = tt; P.dq_log2 = log2i(dq_stages); P.act_log2 = log2i(act_stages); P.raw_log2 = log2i(raw_stages); P.ksplit = ksplit;
     P.kb_per_split = ceil_div(kb_total, ksplit);
     P.seg_offsets = g.seg_offsets;
     P.w_rows_per_seg = g.format == FMT_GPTQ ? g.k / 8 : g.k;
@@ -597,11 +593,13 @@ int gemm_tc_launch(const GemmArgs &g) {
     P.status = (int *)g.ws;   // status word at the start of the scratch buffer
     if (!P.status) return fail(B200K_E_WORKSPACE, "w4a16 gemm (tensor core): workspace is NULL");
 
-    auto kern = g.format == FMT_AWQ ? (ng == 2 ? gemm_tc_kernel<FMT_AWQ, 2, false, 2> : gemm_tc_kernel<FMT_AWQ, 4, false, 1>)
-                : ts ? (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1>)
-                     : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, false, 2> : gemm_tc_kernel<FMT_GPTQ, 4, false, 1>);
-    static bool attr_set[3][2][16] = {};
-    const int variant = g.format == FMT_AWQ ? 1 : (ts ? 2 : 0);
+    if (g.a_kperm && !ts) return 1;   // pre-permuted activations: only the tensor-memory operand variants take them
+    auto kern = g.format == FMT_AWQ ? (ng == 2 ? gemm_tc_kernel<FMT_AWQ, 2, false, 2, false> : gemm_tc_kernel<FMT_AWQ, 4, false, 1, false>)
+                : ts ? (g.a_kperm ? (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, true>)
+                                  : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, false>))
+                     : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, false, 2, false> : gemm_tc_kernel<FMT_GPTQ, 4, false, 1, false>);
+    static bool attr_set[4][2][16] = {};
+    const int variant = g.format == FMT_AWQ ? 1 : (ts ? (g.a_kperm ? 3 : 2) : 0);
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 16 && !attr_set[variant][ng == 4][dev]) {

@@ -23,6 +23,14 @@ template <> struct Elem<__half> {
         u.z = f2_to_h2(f[4], f[5]); u.w = f2_to_h2(f[6], f[7]);
         *reinterpret_cast<uint4 *>(p) = u;
     }
+    // the same 8 values stored as (f0,f4,f1,f5,f2,f6,f3,f7): the order the int4 GEMM's nibble arithmetic yields a
+    // packed word's values in, so a GEMM fed with such activations skips its byte-permutes
+    __device__ static void store_kperm(__half *p, const float (&f)[8]) {
+        uint4 u;
+        u.x = f2_to_h2(f[0], f[4]); u.y = f2_to_h2(f[1], f[5]);
+        u.z = f2_to_h2(f[2], f[6]); u.w = f2_to_h2(f[3], f[7]);
+        *reinterpret_cast<uint4 *>(p) = u;
+    }
     __device__ static float ld1(const __half *p) { return __half2float(*p); }
     __device__ static void st1(__half *p, float v) { *p = __float2half_rn(v); }
 };
@@ -35,6 +43,7 @@ template <> struct Elem<float> {
     __device__ static void store(float *p, const float (&f)[4]) {
         *reinterpret_cast<float4 *>(p) = make_float4(f[0], f[1], f[2], f[3]);
     }
+    __device__ static void store_kperm(float *p, const float (&f)[4]) { store(p, f); }   // fp16 only; never selected
     __device__ static float ld1(const float *p) { return *p; }
     __device__ static void st1(float *p, float v) { *p = v; }
 };
@@ -46,7 +55,7 @@ template <> struct Elem<float> {
 template <typename T, bool FUSED_ADD, bool VECTOR, int ITERS>
 __global__ void __launch_bounds__(1024)
 rms_norm_kernel(const T *__restrict__ x, const T *__restrict__ res, const T *__restrict__ w,
-                T *__restrict__ y, T *__restrict__ res_out, int n, float inv_n, float eps) {
+                T *__restrict__ y, T *__restrict__ res_out, int n, float inv_n, float eps, bool kperm) {
     constexpr int VEC = Elem<T>::VEC;
     __shared__ float red[32];
     const size_t row_off = (size_t)blockIdx.x * n;
@@ -80,7 +89,8 @@ rms_norm_kernel(const T *__restrict__ x, const T *__restrict__ res, const T *__r
                 Elem<T>::load(w + i * VEC, wv);
 #pragma unroll
                 for (int j = 0; j < VEC; ++j) o[j] = v[it][j] * inv * wv[j];
-                Elem<T>::store(y + row_off + i * VEC, o);
+                if (kperm) Elem<T>::store_kperm(y + row_off + i * VEC, o);
+                else Elem<T>::store(y + row_off + i * VEC, o);
             }
         }
     } else {
@@ -104,7 +114,7 @@ rms_norm_kernel(const T *__restrict__ x, const T *__restrict__ res, const T *__r
 
 template <typename T, bool FUSED_ADD>
 static int rms_norm_launch(const char *name, const T *x, const T *res, const T *w, T *y, T *res_out,
-                           int n, float inv_n, float eps, int rows, cudaStream_t st) {
+                           int n, float inv_n, float eps, int rows, cudaStream_t st, bool kperm = false) {
     B200K_REQUIRE(x && w && y && (!FUSED_ADD || (res && res_out)), B200K_E_NULL, "%s: NULL pointer", name);
     B200K_REQUIRE(n > 0 && rows >= 0, B200K_E_SHAPE, "%s: row_size %d, rows %d", name, n, rows);
     if (rows == 0) return 0;
@@ -114,18 +124,19 @@ static int rms_norm_launch(const char *name, const T *x, const T *res, const T *
     const int nv = n / VEC;
     // In the fused kernel the in-place form (residual_out == residual) is allowed: each
     // element is read and written by the same thread.
+    B200K_REQUIRE(!kperm || (vec && nv <= 4 * 1024 && VEC == 8), B200K_E_SHAPE, "%s: the permuted output needs fp16 rows of a multiple of 8, 16-byte aligned", name);
     if (vec && nv <= 4 * 1024) {
         int threads = nv <= 128 ? 128 : (nv <= 256 ? 256 : (nv <= 512 ? 512 : 1024));
         int iters = ceil_div(nv, threads);
         if (iters == 1)
-            rms_norm_kernel<T, FUSED_ADD, true, 1><<<rows, threads, 0, st>>>(x, res, w, y, res_out, n, inv_n, eps);
+            rms_norm_kernel<T, FUSED_ADD, true, 1><<<rows, threads, 0, st>>>(x, res, w, y, res_out, n, inv_n, eps, kperm);
         else if (iters == 2)
-            rms_norm_kernel<T, FUSED_ADD, true, 2><<<rows, threads, 0, st>>>(x, res, w, y, res_out, n, inv_n, eps);
+            rms_norm_kernel<T, FUSED_ADD, true, 2><<<rows, threads, 0, st>>>(x, res, w, y, res_out, n, inv_n, eps, kperm);
         else
-            rms_norm_kernel<T, FUSED_ADD, true, 4><<<rows, threads, 0, st>>>(x, res, w, y, res_out, n, inv_n, eps);
+            rms_norm_kernel<T, FUSED_ADD, true, 4><<<rows, threads, 0, st>>>(x, res, w, y, res_out, n, inv_n, eps, kperm);
     } else {
         int threads = n >= 1024 ? 1024 : ((n + 31) / 32) * 32;
-        rms_norm_kernel<T, FUSED_ADD, false, 1><<<rows, threads, 0, st>>>(x, res, w, y, res_out, n, inv_n, eps);
+        rms_norm_kernel<T, FUSED_ADD, false, 1><<<rows, threads, 0, st>>>(x, res, w, y, res_out, n, inv_n, eps, kperm);
     }
     return launch_status(name);
 }
@@ -178,7 +189,7 @@ static int binary_launch(const char *name, const T *a, const T *b, T *out, int n
 // gate_up [B, 2*inter]: gate = row[0:inter], up = row[inter:2*inter]  (elementwise.rs:199-206)
 template <typename T>
 __global__ void __launch_bounds__(256)
-silu_mul_interleaved_kernel(const T *__restrict__ gu, T *__restrict__ out, int inter, int total, bool vector) {
+silu_mul_interleaved_kernel(const T *__restrict__ gu, T *__restrict__ out, int inter, int total, bool vector, bool kperm) {
     constexpr int VEC = Elem<T>::VEC;
     const int stride = gridDim.x * blockDim.x;
     const int tid = blockIdx.x * blockDim.x + threadIdx.x;
@@ -192,7 +203,8 @@ silu_mul_interleaved_kernel(const T *__restrict__ gu, T *__restrict__ out, int i
             Elem<T>::load(row + inter + c, u);
 #pragma unroll
             for (int j = 0; j < VEC; ++j) o[j] = silu_mul(g[j], u[j]);
-            Elem<T>::store(out + (size_t)i * VEC, o);
+            if (kperm) Elem<T>::store_kperm(out + (size_t)i * VEC, o);
+            else Elem<T>::store(out + (size_t)i * VEC, o);
         }
     } else {
         for (int i = tid; i < total; i += stride) {
@@ -204,7 +216,7 @@ silu_mul_interleaved_kernel(const T *__restrict__ gu, T *__restrict__ out, int i
 }
 
 template <typename T>
-static int silu_interleaved_launch(const char *name, const T *gu, T *out, int inter, int total, cudaStream_t st) {
+static int silu_interleaved_launch(const char *name, const T *gu, T *out, int inter, int total, cudaStream_t st, bool kperm = false) {
     B200K_REQUIRE(gu && out, B200K_E_NULL, "%s: NULL pointer", name);
     B200K_REQUIRE(inter > 0 && total >= 0 && total % inter == 0, B200K_E_SHAPE,
                   "%s: inter %d, total %d (total must be a multiple of inter)", name, inter, total);
@@ -213,7 +225,8 @@ static int silu_interleaved_launch(const char *name, const T *gu, T *out, int in
     int blocks = ceil_div(ceil_div(total, Elem<T>::VEC), 256);
     const int cap = sm_count() * 16;
     if (blocks > cap) blocks = cap;
-    silu_mul_interleaved_kernel<T><<<blocks, 256, 0, st>>>(gu, out, inter, total, vec);
+    B200K_REQUIRE(!kperm || (vec && Elem<T>::VEC == 8), B200K_E_SHAPE, "%s: the permuted output needs fp16 rows of a multiple of 8, 16-byte aligned", name);
+    silu_mul_interleaved_kernel<T><<<blocks, 256, 0, st>>>(gu, out, inter, total, vec, kperm);
     return launch_status(name);
 }
 
@@ -332,6 +345,21 @@ using namespace b200k;
 // ---------------------------------------------------------------------------
 // C ABI
 // ---------------------------------------------------------------------------
+// fp16 variants whose output is written in the pre-permuted order (see Elem<__half>::store_kperm); used by the
+// decode layer to feed its int4 GEMMs
+namespace b200k {
+int rms_norm_f16_kperm(const __half *x, const __half *w, __half *y, int n, float inv_n, float eps, int rows, cudaStream_t st) {
+    return rms_norm_launch<__half, false>("rms_norm_f16", x, nullptr, w, y, nullptr, n, inv_n, eps, rows, st, true);
+}
+int fused_add_rms_norm_f16_kperm(const __half *x, const __half *res, const __half *w, __half *y, __half *res_out, int n,
+                                 float inv_n, float eps, int rows, cudaStream_t st) {
+    return rms_norm_launch<__half, true>("fused_add_rms_norm_f16", x, res, w, y, res_out, n, inv_n, eps, rows, st, true);
+}
+int silu_mul_interleaved_f16_kperm(const __half *gu, __half *out, int inter, int total, cudaStream_t st) {
+    return silu_interleaved_launch<__half>("fused_silu_mul_interleaved_f16", gu, out, inter, total, st, true);
+}
+}  // namespace b200k
+
 extern "C" int rms_norm_f16(const b200k_half *input, const b200k_half *weight, b200k_half *output, int row_size,
                             float inv_n, float eps, int num_rows, b200k_stream stream) {
     return rms_norm_launch<__half, false>("rms_norm_f16", (const __half *)input, nullptr, (const __half *)weight,

@@ -1,6 +1,8 @@
 // One Llama-shape W4A16 decode layer as a fixed call sequence over the library's own
 // entry points, optionally captured in a CUDA graph.  Host-side C++ only; every
 // arithmetic step is one of the kernels declared in b200_kernels.h.
+#include <stdlib.h>
+
 #include <array>
 #include <map>
 #include <vector>
@@ -15,6 +17,15 @@ int rope_kv_append_lens_launch(const __half *qkv, const float *cos_t, const floa
 int comm_allreduce_f16(struct ::b200k_comm *comm, int slot, __half *out, size_t count, cudaStream_t st);
 __half *comm_slot(struct ::b200k_comm *comm, int slot);
 size_t comm_slot_capacity(struct ::b200k_comm *comm);
+// producers that write their fp16 output with every 8 values stored as (0,4,1,5,2,6,3,7): the order the GPTQ
+// tensor-core GEMM consumes without its byte-permutes (w4a16_gptq_gemm_kperm_f16)
+int rms_norm_f16_kperm(const __half *x, const __half *w, __half *y, int n, float inv_n, float eps, int rows, cudaStream_t st);
+int fused_add_rms_norm_f16_kperm(const __half *x, const __half *res, const __half *w, __half *y, __half *res_out, int n,
+                                 float inv_n, float eps, int rows, cudaStream_t st);
+int silu_mul_interleaved_f16_kperm(const __half *gu, __half *out, int inter, int total, cudaStream_t st);
+int batched_decode_attention_hm_f16_kperm(const __half *q, const __half *k_cache, const __half *v_cache,
+                                          const int32_t *context_lens, __half *output, int batch_size, int num_q_heads,
+                                          int num_kv_heads, int head_dim, int max_len, float scale, cudaStream_t st);
 }  // namespace b200k
 
 struct b200k_layer {
@@ -34,6 +45,7 @@ struct b200k_layer {
     std::map<std::array<uintptr_t, 5>, cudaGraphExec_t> graphs;
     cudaStream_t cap_stream;                 // capture happens here: the caller's stream may be the legacy default stream
     int launches;
+    bool kperm;   // GEMM inputs travel in the pre-permuted order (GPTQ weights, shapes the tensor-core path covers)
 };
 
 using namespace b200k;
@@ -41,6 +53,7 @@ using namespace b200k;
 static int gemm(b200k_layer *L, int which, const b200k_half *a, b200k_half *c, int m, int n, int k,
                 b200k_stream st) {
     const int g = L->cfg.group_size;
+    if (L->kperm) return w4a16_gptq_gemm_kperm_f16(a, L->qw[which], L->sc[which], L->qz[which], c, m, n, k, g, st);
     if (L->cfg.weight_format == 1)
         return awq_gemm_int4_f16(a, L->qw[which], L->sc[which], L->qz[which], c, m, n, k, g, k, 1, n / 8, 1, n, 1, n / 8,
                                  1, n, 1, st);
@@ -56,15 +69,21 @@ static int stage0(b200k_layer *L, const b200k_half *hidden, const int32_t *posit
     const b200k_layer_config &c = L->cfg;
     const int H = c.hidden, hq = c.num_q_heads, hkv = c.num_kv_heads, d = c.head_dim;
     int rc;
-    if ((rc = rms_norm_f16(hidden, L->ln1, L->n1, H, 1.0f / H, c.rms_eps, b, st))) return rc;
+    if (L->kperm) rc = rms_norm_f16_kperm((const __half *)hidden, (const __half *)L->ln1, (__half *)L->n1, H, 1.0f / H, c.rms_eps, b, to_stream(st));
+    else rc = rms_norm_f16(hidden, L->ln1, L->n1, H, 1.0f / H, c.rms_eps, b, st);
+    if (rc) return rc;
     if ((rc = gemm(L, 0, L->n1, L->qkv, b, (hq + 2 * hkv) * d, H, st))) return rc;
     if ((rc = rope_kv_append_lens_launch((const __half *)L->qkv, L->cos_t, L->sin_t, positions, (__half *)L->qrot,
                                          (__half *)L->kc, (__half *)L->vc, L->lens, hq, hkv, d, c.max_len, b,
                                          to_stream(st))))
         return rc;
-    if ((rc = batched_decode_attention_hm_f16(L->qrot, L->kc, L->vc, L->lens, L->att, b, hq, hkv, d, c.max_len,
-                                              1.0f / sqrtf((float)d), st)))
-        return rc;
+    if (L->kperm)
+        rc = batched_decode_attention_hm_f16_kperm((const __half *)L->qrot, (const __half *)L->kc, (const __half *)L->vc, L->lens,
+                                                   (__half *)L->att, b, hq, hkv, d, c.max_len, 1.0f / sqrtf((float)d), to_stream(st));
+    else
+        rc = batched_decode_attention_hm_f16(L->qrot, L->kc, L->vc, L->lens, L->att, b, hq, hkv, d, c.max_len,
+                                             1.0f / sqrtf((float)d), st);
+    if (rc) return rc;
     return gemm(L, 1, L->att, o_out, b, H, hq * d, st);
 }
 // stage 1: reduced o + hidden -> h1, then the MLP up to the partial down output
@@ -73,9 +92,16 @@ static int stage1(b200k_layer *L, const b200k_half *hidden, const b200k_half *o_
     const b200k_layer_config &c = L->cfg;
     const int H = c.hidden, I = c.intermediate;
     int rc;
-    if ((rc = fused_add_rms_norm_f16(o_red, hidden, L->ln2, L->n2, L->h1, H, 1.0f / H, c.rms_eps, b, st))) return rc;
+    if (L->kperm)
+        rc = fused_add_rms_norm_f16_kperm((const __half *)o_red, (const __half *)hidden, (const __half *)L->ln2, (__half *)L->n2,
+                                          (__half *)L->h1, H, 1.0f / H, c.rms_eps, b, to_stream(st));
+    else
+        rc = fused_add_rms_norm_f16(o_red, hidden, L->ln2, L->n2, L->h1, H, 1.0f / H, c.rms_eps, b, st);
+    if (rc) return rc;
     if ((rc = gemm(L, 2, L->n2, L->gu, b, 2 * I, H, st))) return rc;
-    if ((rc = fused_silu_mul_interleaved_f16(L->gu, L->act, I, b * I, st))) return rc;
+    if (L->kperm) rc = silu_mul_interleaved_f16_kperm((const __half *)L->gu, (__half *)L->act, I, b * I, to_stream(st));
+    else rc = fused_silu_mul_interleaved_f16(L->gu, L->act, I, b * I, st);
+    if (rc) return rc;
     return gemm(L, 3, L->act, dn_out, b, H, I, st);
 }
 static int stage2(b200k_layer *L, const b200k_half *dn_red, b200k_half *out, int b, b200k_stream st) {
@@ -150,6 +176,14 @@ extern "C" int b200k_layer_create(const b200k_layer_config *config, b200k_layer 
     L->lens = (int32_t *)(base + off);
     // rms_norm, gemm, rope+append, attention, gemm, add+norm, gemm, silu, gemm, add
     L->launches = 10;
+    {
+        // Pre-permuted GEMM inputs: GPTQ weights and extents the tensor-core GEMM family covers for all four projections
+        // (K a multiple of 64, group a power of two >= 64, N a multiple of 32).  B200K_LAYER_KPERM=0 turns it off.
+        const int g = c.group_size, qd = c.num_q_heads * c.head_dim, nq = (c.num_q_heads + 2 * c.num_kv_heads) * c.head_dim;
+        const char *e = getenv("B200K_LAYER_KPERM");
+        L->kperm = c.weight_format == 0 && !(e && e[0] == '0') && g >= 64 && (g & (g - 1)) == 0 && c.hidden % 64 == 0 &&
+                   qd % 64 == 0 && c.intermediate % 64 == 0 && c.hidden % 32 == 0 && nq % 32 == 0 && (2 * c.intermediate) % 32 == 0;
+    }
     *out_layer = L;
     return 0;
 }

@@ -39,6 +39,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// The same with a suspend-time hint (nanoseconds): a thread whose phase is not complete yet may be parked by
+// the hardware until the phase completes or the time is up, instead of coming straight back to poll again.
+// Polling warps otherwise take issue slots from the warps that do the work.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: gives up after ~1 s of SM clock and returns false; the caller records
 // the failure in a status word and carries on without waiting again.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
@@ -46,7 +60,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
     const long long t0 = clock64();
     for (;;) {
         for (int i = 0; i < 64; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
+            if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
         if (clock64() - t0 > 2000000000LL) return false;
     }
 }
