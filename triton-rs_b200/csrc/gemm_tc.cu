@@ -309,9 +309,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             const int s = ring_slot(i, LSD), r = ring_slot(i, LR);
             // The three barriers of this block are tested back to back: a test costs well over a hundred cycles even
             // when the phase is long complete, and the tests are independent, so their latencies overlap.
-            const bool ok_raw = mbar_try_wait(smem_u32(&bars[B_RAWF + r]), ring_phase(i, LR));
-            const bool ok_dqe = i < SD || mbar_try_wait(smem_u32(&bars[B_DQE + s]), ring_phase(i, LSD) ^ 1u);
-            const bool ok_act = mbar_try_wait(smem_u32(&bars[B_ACTF + ring_slot(i, LSA)]), ring_phase(i, LSA));
+            // (test_wait: a test that does not park the thread when the phase is still open)
+            const bool ok_raw = mbar_test_wait(smem_u32(&bars[B_RAWF + r]), ring_phase(i, LR));
+            const bool ok_dqe = i < SD || mbar_test_wait(smem_u32(&bars[B_DQE + s]), ring_phase(i, LSD) ^ 1u);
+            const bool ok_act = mbar_test_wait(smem_u32(&bars[B_ACTF + ring_slot(i, LSA)]), ring_phase(i, LSA));
             wait_after_test(ok_raw, B_RAWF + r, ring_phase(i, LR));                               // packed words, scales, zero-points landed
             const unsigned char *slot = raw + (size_t)r * TC_RAW_BYTES;
             const uint32_t *rw = reinterpret_cast<const uint32_t *>(slot);

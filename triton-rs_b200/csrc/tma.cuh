@@ -39,17 +39,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// The same with a suspend-time hint (nanoseconds): a thread whose phase is not complete yet may be parked by
-// the hardware until the phase completes or the time is up, instead of coming straight back to poll again.
-// Polling warps otherwise take issue slots from the warps that do the work.
-__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t ns) {
+// Non-blocking test of a phase (try_wait may park the thread for a while when the phase is not complete yet).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(ns)
+        : "r"(bar), "r"(parity)
         : "memory");
     return ok != 0;
 }
@@ -60,7 +58,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
     const long long t0 = clock64();
     for (;;) {
         for (int i = 0; i < 64; ++i)
-            if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
+            if (mbar_try_wait(bar, parity)) return true;
         if (clock64() - t0 > 2000000000LL) return false;
     }
 }
