@@ -117,6 +117,8 @@ attn_split_f16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int chunk_id = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int G = A.g;
+    pdl_wait();                 // the lengths, q and the appended K/V rows come from the kernel before
+    pdl_launch_dependents();
     const int len = A.lens ? A.lens[b] : A.len_scalar;
     const int nchunks = (len + A.chunk - 1) / A.chunk;
     const long out_row0 = ((long)b * A.hq + (long)kvh * G) * AT_D;
@@ -457,7 +459,7 @@ static int attn_split_launch(const char *name, AttnCall c) {
         attr_set[dev] = true;
     }
     dim3 grid(max_chunks, c.hkv, c.batch);
-    attn_split_f16_kernel<<<grid, AT_THREADS, smem, c.stream>>>(kmap, vmap, A);
+    launch_kernel(attn_split_f16_kernel, grid, dim3(AT_THREADS), smem, c.stream, kmap, vmap, A);
     return launch_status("decode attention (split-KV)");
 }
 

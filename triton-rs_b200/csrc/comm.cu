@@ -43,6 +43,8 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
 __global__ void __launch_bounds__(512)
 allreduce_oneshot_kernel(unsigned char *const *__restrict__ peers, int rank, int world, int slot, size_t slot_bytes,
                          __half *__restrict__ out, size_t count) {
+    pdl_wait();                 // the partial sums in my slot come from the kernel before
+    pdl_launch_dependents();
     unsigned char *mine = peers[rank];
     unsigned *my_flags = reinterpret_cast<unsigned *>(mine);
     unsigned *seq_p = my_flags + 16, *done_p = my_flags + 17, *status_p = my_flags + 18;
@@ -103,7 +105,7 @@ int comm_allreduce_f16(struct ::b200k_comm *c, int slot, __half *out, size_t cou
     if (count == 0) return 0;
     int blocks = (int)((count / 8 + 511) / 512);
     if (blocks > 32) blocks = 32;
-    allreduce_oneshot_kernel<<<blocks, 512, 0, st>>>(c->d_peers, c->rank, c->world, slot, c->slot_bytes, out, count);
+    launch_kernel(allreduce_oneshot_kernel, dim3(blocks), dim3(512), 0, st, c->d_peers, c->rank, c->world, slot, c->slot_bytes, out, count);
     return launch_status("all-reduce (peer to peer)");
 }
 

@@ -25,6 +25,32 @@ static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t
 static inline cudaStream_t to_stream(b200k_stream s) { return reinterpret_cast<cudaStream_t>(s); }
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// ---- programmatic dependent launch ------------------------------------------------------------
+// Kernels of a decode step follow one another on one stream, each a few microseconds long.  Launched with the
+// programmatic-serialization attribute, a kernel may start (be scheduled, run its set-up) while its predecessor
+// is still draining; it must execute pdl_wait() before it touches anything the predecessor wrote or still reads,
+// and pdl_wait() returns only when the predecessor has completed and its writes are visible.
+// pdl_launch_dependents() tells the scheduler that the successor may be brought in as soon as there is room.
+// Both are no-ops in a kernel launched without the attribute.  B200K_PDL=0 turns the attribute off.
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- device: reductions ----------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

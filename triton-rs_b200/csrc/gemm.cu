@@ -157,6 +157,8 @@ gemv_gptq_kernel(GemmArgs g, int ksplit) {
     };
     if (live && kslot < groups) request(kslot);
 
+    pdl_wait();                 // the activation vector comes from the kernel before; the weights do not
+    pdl_launch_dependents();
     stage_x_gptq(g.a, xs, g.k, g.a_kperm);
     __syncthreads();
 
@@ -261,6 +263,8 @@ gemv_awq_kernel(GemmArgs g, int ksplit) {
         if (batched) request_rows(kslot * g.group);
     }
 
+    pdl_wait();                 // the activation vector comes from the kernel before; the weights do not
+    pdl_launch_dependents();
     for (int i = threadIdx.x; i < g.k / 8; i += blockDim.x)
         *reinterpret_cast<uint4 *>(xs + i * 8) = *reinterpret_cast<const uint4 *>(g.a + i * 8);
     __syncthreads();
@@ -371,13 +375,15 @@ int gemv_launch(const GemmArgs &g) {
     cfg.blockDim = dim3(GEMV_THREADS, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = g.stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = ksplit;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, g, ksplit);
     if (e != cudaSuccess) {
         cudaGetLastError();

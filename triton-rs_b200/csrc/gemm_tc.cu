@@ -175,6 +175,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     const int n0 = blockIdx.x * TC_BN;
     int m0 = blockIdx.y * TT, m_end = P.m, w_row0 = 0, g_row0 = 0;
     if (P.seg_offsets) {
+        pdl_wait();   // the segment offsets are written by the kernel before
         // grouped mode: this CTA works on segment blockIdx.z with that segment's weights; no K split
         const int e = blockIdx.z;
         m0 += P.seg_offsets[e];
@@ -217,6 +218,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_acc = *tmem_slot;
+    // barriers, tensor memory and descriptors are set up: only now wait for the kernel that produces the activations
+    pdl_wait();
+    pdl_launch_dependents();
 
     auto wait = [&](int bar_idx, uint32_t parity) {
         const uint32_t bar = smem_u32(&bars[bar_idx]);
@@ -613,13 +617,15 @@ int gemm_tc_launch(const GemmArgs &g) {
     cfg.blockDim = dim3(tc_threads(ng), 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = g.stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = grouped ? 1 : ksplit;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, wmap, amap, smap, zmap, P);
     if (e != cudaSuccess) {
         cudaGetLastError();

@@ -58,6 +58,8 @@ rms_norm_kernel(const T *__restrict__ x, const T *__restrict__ res, const T *__r
                 T *__restrict__ y, T *__restrict__ res_out, int n, float inv_n, float eps, bool kperm) {
     constexpr int VEC = Elem<T>::VEC;
     __shared__ float red[32];
+    pdl_wait();
+    pdl_launch_dependents();
     const size_t row_off = (size_t)blockIdx.x * n;
     const T *xr = x + row_off;
     float ss = 0.f;
@@ -129,14 +131,14 @@ static int rms_norm_launch(const char *name, const T *x, const T *res, const T *
         int threads = nv <= 128 ? 128 : (nv <= 256 ? 256 : (nv <= 512 ? 512 : 1024));
         int iters = ceil_div(nv, threads);
         if (iters == 1)
-            rms_norm_kernel<T, FUSED_ADD, true, 1><<<rows, threads, 0, st>>>(x, res, w, y, res_out, n, inv_n, eps, kperm);
+            launch_kernel(rms_norm_kernel<T, FUSED_ADD, true, 1>, dim3(rows), dim3(threads), 0, st, x, res, w, y, res_out, n, inv_n, eps, kperm);
         else if (iters == 2)
-            rms_norm_kernel<T, FUSED_ADD, true, 2><<<rows, threads, 0, st>>>(x, res, w, y, res_out, n, inv_n, eps, kperm);
+            launch_kernel(rms_norm_kernel<T, FUSED_ADD, true, 2>, dim3(rows), dim3(threads), 0, st, x, res, w, y, res_out, n, inv_n, eps, kperm);
         else
-            rms_norm_kernel<T, FUSED_ADD, true, 4><<<rows, threads, 0, st>>>(x, res, w, y, res_out, n, inv_n, eps, kperm);
+            launch_kernel(rms_norm_kernel<T, FUSED_ADD, true, 4>, dim3(rows), dim3(threads), 0, st, x, res, w, y, res_out, n, inv_n, eps, kperm);
     } else {
         int threads = n >= 1024 ? 1024 : ((n + 31) / 32) * 32;
-        rms_norm_kernel<T, FUSED_ADD, false, 1><<<rows, threads, 0, st>>>(x, res, w, y, res_out, n, inv_n, eps, kperm);
+        launch_kernel(rms_norm_kernel<T, FUSED_ADD, false, 1>, dim3(rows), dim3(threads), 0, st, x, res, w, y, res_out, n, inv_n, eps, kperm);
     }
     return launch_status(name);
 }
@@ -155,6 +157,8 @@ template <typename T, int OP>
 __global__ void __launch_bounds__(256)
 binary_kernel(const T *__restrict__ a, const T *__restrict__ b, T *__restrict__ out, int n, bool vector) {
     constexpr int VEC = Elem<T>::VEC;
+    pdl_wait();
+    pdl_launch_dependents();
     const int stride = gridDim.x * blockDim.x;
     const int tid = blockIdx.x * blockDim.x + threadIdx.x;
     const int nv = vector ? n / VEC : 0;
@@ -182,7 +186,7 @@ static int binary_launch(const char *name, const T *a, const T *b, T *out, int n
     int blocks = ceil_div(work, 256);
     const int cap = sm_count() * 16;
     if (blocks > cap) blocks = cap;
-    binary_kernel<T, OP><<<blocks, 256, 0, st>>>(a, b, out, n, vec);
+    launch_kernel(binary_kernel<T, OP>, dim3(blocks), dim3(256), 0, st, a, b, out, n, vec);
     return launch_status(name);
 }
 
@@ -191,6 +195,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 silu_mul_interleaved_kernel(const T *__restrict__ gu, T *__restrict__ out, int inter, int total, bool vector, bool kperm) {
     constexpr int VEC = Elem<T>::VEC;
+    pdl_wait();
+    pdl_launch_dependents();
     const int stride = gridDim.x * blockDim.x;
     const int tid = blockIdx.x * blockDim.x + threadIdx.x;
     if (vector) {
@@ -226,7 +232,7 @@ static int silu_interleaved_launch(const char *name, const T *gu, T *out, int in
     const int cap = sm_count() * 16;
     if (blocks > cap) blocks = cap;
     B200K_REQUIRE(!kperm || (vec && Elem<T>::VEC == 8), B200K_E_SHAPE, "%s: the permuted output needs fp16 rows of a multiple of 8, 16-byte aligned", name);
-    silu_mul_interleaved_kernel<T><<<blocks, 256, 0, st>>>(gu, out, inter, total, vec, kperm);
+    launch_kernel(silu_mul_interleaved_kernel<T>, dim3(blocks), dim3(256), 0, st, gu, out, inter, total, vec, kperm);
     return launch_status(name);
 }
 
@@ -293,6 +299,8 @@ rope_kv_append_kernel(const __half *__restrict__ qkv, const float *__restrict__ 
                       const float *__restrict__ sin_t, const int32_t *__restrict__ positions,
                       __half *__restrict__ q_out, __half *__restrict__ kc, __half *__restrict__ vc,
                       int32_t *__restrict__ lens_out, int hq, int hkv, int d, int max_len) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int b = blockIdx.y;
     const int half = d / 2;
     const int pos = positions[b];
@@ -333,8 +341,8 @@ int rope_kv_append_lens_launch(const __half *qkv, const float *cos_t, const floa
                   "rope_kv_append_hm_f16: Hq %d, Hkv %d, D %d, max_len %d, batch %d", hq, hkv, d, max_len, batch);
     if (batch == 0) return 0;
     const int items = (hq + 2 * hkv) * (d / 2);
-    rope_kv_append_kernel<<<dim3(ceil_div(items, 256), batch), 256, 0, st>>>(qkv, cos_t, sin_t, positions, q_out, kc, vc,
-                                                                             lens_out, hq, hkv, d, max_len);
+    launch_kernel(rope_kv_append_kernel, dim3(ceil_div(items, 256), batch), dim3(256), 0, st, qkv, cos_t, sin_t, positions, q_out, kc, vc,
+                  lens_out, hq, hkv, d, max_len);
     return launch_status("rope_kv_append_hm_f16");
 }
 

@@ -3,6 +3,8 @@
 
 #include <mutex>
 
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "tma.cuh"
 
@@ -31,6 +33,15 @@ static void *g_ws[kMaxDev];
 static size_t g_ws_bytes[kMaxDev];
 static bool g_ws_owned[kMaxDev];
 static int g_sms[kMaxDev];
+
+bool pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char *e = getenv("B200K_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
 
 int sm_count() {
     int dev = 0;
