@@ -218,8 +218,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_acc = *tmem_slot;
-    // barriers, tensor memory and descriptors are set up: only now wait for the kernel that produces the activations
-    pdl_wait();
+    // Barriers, tensor memory and descriptors are set up.  The packed weights, scales and zero-points do not depend on
+    // the kernel before this one, so their stream and the dequantisation start at once; only the activation producer
+    // waits for the predecessor, and every global write of this kernel comes after the MMAs that consume its tiles
+    // (the epilogue waits once more, formally, before it stores).
     pdl_launch_dependents();
 
     auto wait = [&](int bar_idx, uint32_t parity) {
@@ -264,6 +266,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         // ---------------- TMA producer, activation tiles: SA blocks ahead ----------------
         if (lane == 0) {
             tma_prefetch_desc(&amap);
+            pdl_wait();   // the activations come from the kernel before
             for (int i = 0; i < nkb; ++i) {
                 const int s = ring_slot(i, LSA);
                 if (i >= SA) wait(B_ACTE + s, ring_phase(i, LSA) ^ 1u);
@@ -409,6 +412,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             wait(B_ACC, 0);
             tc_fence_after();
         }
+        pdl_wait();   // nothing of this kernel is stored before the predecessor has completed
         const int q = warp & 3;                       // TMEM lane quadrant this warp may read
         const int chunk0 = (warp - TC_DQ_WARP0) >> 2; // the NG warps of a quadrant take 16-column chunks round-robin
         const int row = q * 32 + lane;                // accumulator row = weight column n0 + row
