@@ -372,11 +372,27 @@ static AttnWs attn_ws_layout(void *base, int batch, int hkv, int g, int max_chun
 }
 
 static int pick_chunk(int batch, int hkv, int max_len) {
-    // Largest chunk that still gives every SM ~4 CTAs when all sequences are full length.
-    const long want = 4L * sm_count();
-    int chunk = AT_MAX_CH;
-    while (chunk > 256 && (long)batch * hkv * ceil_div(max_len, chunk) < want) chunk /= 2;
-    return chunk;
+    // The KV range of a sequence is cut into n equal chunks of whole tiles, one CTA each.  n is chosen for the
+    // wave balance of the grid when all sequences are full length: CTAs / (2 per SM) should sit just below a
+    // whole number of waves.  A finer cut is taken only when it is clearly better balanced (every chunk adds a
+    // partial result to merge), and never below 256 positions per chunk.
+    const double slots = 2.0 * sm_count();
+    const long rows = (long)batch * hkv;
+    int best_chunk = AT_MAX_CH;
+    double best = -1.0;
+    for (int n = ceil_div(max_len, AT_MAX_CH); n <= 64; ++n) {
+        const int chunk = ceil_div(ceil_div(max_len, n), AT_TILE) * AT_TILE;
+        if (chunk < 256 && best >= 0.0) break;
+        const long ctas = rows * ceil_div(max_len, chunk);
+        const double waves = (double)ctas / slots;
+        const double eff = waves / (double)(long)(waves + 0.999999);
+        if (eff > best + 0.02) {
+            best = eff;
+            best_chunk = chunk;
+        }
+        if (best > 0.97 || waves > 16.0) break;
+    }
+    return best_chunk;
 }
 
 enum KvMode { KV_HEAD_MAJOR = 0, KV_SEQ_MAJOR = 1, KV_PAGED = 2 };
