@@ -443,22 +443,24 @@ def moe_permute(topk_ids, num_experts):
     return counts, offsets, sorted_pairs, inv
 
 
-def fused_moe_gptq(x, logits, w13_q, w13_s, w2_q, w2_s, top_k, group_size, round_intermediate=True):
+def fused_moe_gptq(x, logits, w13_q, w13_s, w2_q, w2_s, top_k, group_size, round_intermediate=True, expert_first=0):
     """x [T, H] fp16; per-expert symmetric GPTQ w13 [E, H/8, 2I] (gate | up halves),
     w2 [E, I/8, H]; out[t] = sum_j w[t,j] * (silu(g)*u) @ W2_e.  The intermediate
     activation is rounded to fp16 between the GEMMs when `round_intermediate`
-    (the CUDA path stores it as fp16).  Returns fp32 [T, H]."""
+    (the CUDA path stores it as fp16).  Returns fp32 [T, H].
+    Expert-parallel share: pass the weight stacks of experts [expert_first, expert_first + len(w13_q)) only;
+    routing still runs over all of `logits`' experts and pairs routed elsewhere contribute nothing."""
     t, h = x.shape
     e = logits.shape[1]
     ids, wts = moe_route(logits, top_k)
     out = np.zeros((t, h), np.float32)
     xf = x.astype(np.float32)
-    for ex in range(e):
+    for ex in range(expert_first, min(e, expert_first + len(w13_q))):
         tok, slot = np.nonzero(ids == ex)
         if tok.size == 0:
             continue
-        w13 = gptq_dequant(w13_q[ex], w13_s[ex], None, group_size)
-        w2 = gptq_dequant(w2_q[ex], w2_s[ex], None, group_size)
+        w13 = gptq_dequant(w13_q[ex - expert_first], w13_s[ex - expert_first], None, group_size)
+        w2 = gptq_dequant(w2_q[ex - expert_first], w2_s[ex - expert_first], None, group_size)
         gu = xf[tok] @ w13
         inter = w13.shape[1] // 2
         act = fused_silu_mul(gu[:, :inter], gu[:, inter:])

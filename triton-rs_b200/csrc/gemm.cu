@@ -364,6 +364,10 @@ int gemv_launch(const GemmArgs &g) {
     // enough CTAs for ~2 per SM, cluster size a power of two <= 8, no warp without a group
     int ksplit = 1;
     while (ksplit < 8 && colblocks * ksplit < 2 * sm_count() && ksplit * 2 * kwarps <= groups) ksplit *= 2;
+    if (const char *e = getenv("B200K_GEMV_KSPLIT")) {   // tuning override
+        const int v = atoi(e);
+        if ((v == 1 || v == 2 || v == 4 || v == 8) && v * kwarps <= groups) ksplit = v;
+    }
     const size_t smem = (size_t)g.k * 2 + (size_t)GEMV_WARPS * 256 * sizeof(float);
     auto kern = g.format == FMT_GPTQ ? (g.group == 128 ? gemv_gptq_kernel<16> : gemv_gptq_kernel<0>) : gemv_awq_kernel;
     if (smem > 48 * 1024) {
