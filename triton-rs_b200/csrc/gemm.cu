@@ -126,7 +126,9 @@ __device__ __forceinline__ float gptq_word_dot(uint32_t w, __half2 zlo, __half2 
 
 // RPG = packed rows per quantisation group when known at compile time (16 for group 128):
 // the whole group's weights are then requested before anything waits on them.
-template <int RPG>
+// CW = column-warps per CTA (each covers 128 columns); the other 8 / CW warp groups split K.  Narrow matrices take
+// CW = 1 (twice as many CTAs and k-warps), so that the launch still fills the machine.
+template <int RPG, int CW>
 __global__ void __launch_bounds__(GEMV_THREADS)
 gemv_gptq_kernel(GemmArgs g, int ksplit) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -134,9 +136,9 @@ gemv_gptq_kernel(GemmArgs g, int ksplit) {
     float *red = reinterpret_cast<float *>(smem_raw + (size_t)g.k * 2);      // [GEMV_WARPS/2][256]
     cg::cluster_group cluster = cg::this_cluster();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int cw = warp & 1, kw = warp >> 1;         // 2 column-warps x 4 k-warps
-    constexpr int KW = GEMV_WARPS / 2;
-    const int col = blockIdx.x * 256 + cw * 128 + lane * 4;
+    const int cw = warp % CW, kw = warp / CW;        // CW column-warps x KW k-warps
+    constexpr int KW = GEMV_WARPS / CW;
+    const int col = blockIdx.x * (128 * CW) + cw * 128 + lane * 4;
     const int kslot = blockIdx.y * KW + kw, kslots = ksplit * KW;
     const int groups = g.k / g.group, rows_per_group = RPG > 0 ? RPG : g.group / 8;
     const bool live = col < g.n;
@@ -205,12 +207,12 @@ gemv_gptq_kernel(GemmArgs g, int ksplit) {
     }
     // reduce the KW k-warps of this CTA (fixed order), then the cluster's CTAs
     float4 *red4 = reinterpret_cast<float4 *>(red);
-    if (kw > 0) red4[(kw - 1) * 64 + cw * 32 + lane] = make_float4(tot[0], tot[1], tot[2], tot[3]);
+    if (kw > 0) red4[(kw - 1) * (32 * CW) + cw * 32 + lane] = make_float4(tot[0], tot[1], tot[2], tot[3]);
     __syncthreads();
     if (kw == 0) {
 #pragma unroll
         for (int j = 0; j < KW - 1; ++j) {
-            const float4 o = red4[j * 64 + cw * 32 + lane];
+            const float4 o = red4[j * (32 * CW) + cw * 32 + lane];
             tot[0] += o.x; tot[1] += o.y; tot[2] += o.z; tot[3] += o.w;
         }
     }
@@ -359,8 +361,12 @@ gemv_awq_kernel(GemmArgs g, int ksplit) {
 
 int gemv_launch(const GemmArgs &g) {
     const int groups = g.k / g.group;
-    const int colblocks = ceil_div(g.n, 256);
-    const int kwarps = g.format == FMT_GPTQ ? GEMV_WARPS / 2 : GEMV_WARPS;
+    // GPTQ: 256 columns per CTA (2 column-warps x 4 k-warps), or 128 (1 x 8) when 256-column blocks with the largest
+    // cluster would leave SMs without a CTA.  AWQ: 256 columns per CTA, all 8 warps split K.
+    int cw = 2;
+    if (g.format == FMT_GPTQ && ceil_div(g.n, 256) * 8 < 2 * sm_count()) cw = 1;
+    const int colblocks = g.format == FMT_GPTQ ? ceil_div(g.n, 128 * cw) : ceil_div(g.n, 256);
+    const int kwarps = g.format == FMT_GPTQ ? GEMV_WARPS / cw : GEMV_WARPS;
     // enough CTAs for ~2 per SM, cluster size a power of two <= 8, no warp without a group
     int ksplit = 1;
     while (ksplit < 8 && colblocks * ksplit < 2 * sm_count() && ksplit * 2 * kwarps <= groups) ksplit *= 2;
@@ -369,7 +375,9 @@ int gemv_launch(const GemmArgs &g) {
         if ((v == 1 || v == 2 || v == 4 || v == 8) && v * kwarps <= groups) ksplit = v;
     }
     const size_t smem = (size_t)g.k * 2 + (size_t)GEMV_WARPS * 256 * sizeof(float);
-    auto kern = g.format == FMT_GPTQ ? (g.group == 128 ? gemv_gptq_kernel<16> : gemv_gptq_kernel<0>) : gemv_awq_kernel;
+    auto kern = g.format != FMT_GPTQ ? gemv_awq_kernel
+                : cw == 2 ? (g.group == 128 ? gemv_gptq_kernel<16, 2> : gemv_gptq_kernel<0, 2>)
+                          : (g.group == 128 ? gemv_gptq_kernel<16, 1> : gemv_gptq_kernel<0, 1>);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail((int)e, "gemv: shared memory %zu: %s", smem, cudaGetErrorString(e));
