@@ -253,7 +253,7 @@ def component_metrics(pkg, torch, dev, gen):
         out[f"{fmt}_gemm_m{m}_k{k}_n{n}"] = {
             "us": ms * 1e3, "GB/s": byts / ms / 1e6, "TFLOP/s": 2 * m * k * n / ms / 1e9,
             "frac_hbm": byts / ms / 1e6 / hbm_peak, "frac_tensor": 2 * m * k * n / ms / 1e9 / tf_peak,
-            "timing": "cold (rotating weight buffers), CUDA-graph replay"}
+            "timing": "cold (rotating weight buffers), CUDA-graph replay of back-to-back launches (the set-up of a launch overlaps the tail of the one before: programmatic dependent launch)"}
         del qws
     # config 1: decode attention, batch 32, lengths U[512, 8192]
     b, hq, hkv, d, ml = 32, 32, 8, 128, 8192
