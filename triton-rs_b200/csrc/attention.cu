@@ -15,6 +15,8 @@
 //    arrive.  Every mbarrier wait is bounded and reports through a status word.
 //  * attn_generic (any head_dim <= 256, fp16 or fp32): one CTA per (sequence, q head,
 //    split); backs the f32 entry points and the explicit phase-1 / phase-2 API.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "tma.cuh"
 
@@ -376,6 +378,10 @@ static int pick_chunk(int batch, int hkv, int max_len) {
     // wave balance of the grid when all sequences are full length: CTAs / (2 per SM) should sit just below a
     // whole number of waves.  A finer cut is taken only when it is clearly better balanced (every chunk adds a
     // partial result to merge), and never below 256 positions per chunk.
+    if (const char *e = getenv("B200K_ATTN_CHUNK")) {   // tuning override: positions per chunk (multiple of 64)
+        const int v = atoi(e);
+        if (v >= AT_TILE && v <= AT_MAX_CH && v % AT_TILE == 0) return v;
+    }
     const double slots = 2.0 * sm_count();
     const long rows = (long)batch * hkv;
     int best_chunk = AT_MAX_CH;
