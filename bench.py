@@ -525,6 +525,37 @@ def run_gpu_arm(args):
         os._exit(0)
 
 
+def run_reference_arm(args):
+    """The reference has no CPU implementation of these kernels and its Rust / Triton toolchain is absent, so the
+    reference arm is the CPU restatement of the same layer chain (oracle/oracle_c.c, OpenMP on all host cores) on
+    the benchmark's own extents: each step = the whole batch of 64 sequences at context 4096.  Rank 0 alone runs
+    and prints; other ranks return at once."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    oc = load_oracle_c()
+    oc.oc_num_threads.restype = ctypes.c_int
+    cores = oc.oc_num_threads()
+    sample = BATCH
+    case = cpu_layer_case(np.random.default_rng(4), sample, CTX)
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_layer_run(oc, case)
+    ts = [cpu_layer_run(oc, case)[0] for _ in range(max(1, args.steps))]
+    ms = 1e3 * sum(ts) / len(ts)
+    value = sample / (ms / 1e3)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage, int4 weights, f32 accumulate", "data": "synthetic",
+        "config": {"workload": "C4: Llama-3-8B-shape W4A16 (GPTQ) decode layer chain, batch 64, ctx 4096",
+                   "note": "CPU restatement of the reference kernels' arithmetic (oracle/oracle_c.c, OpenMP); "
+                           "the reference has no CPU path and its Rust/Triton toolchain is absent"},
+        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": cores, "kind": "port",
+                         "sample": f"{sample} of {BATCH} sequences per step, ctx {CTX}, full layer chain"},
+        "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
