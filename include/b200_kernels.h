@@ -296,6 +296,19 @@ int unified_attention_f32(const float *q, const float *k_cache, const float *v_c
                           int head_dim, int block_size, int max_blocks_per_seq, float sm_scale,
                           int num_seqs, b200k_stream stream);
 
+/* Replaces flash_attn_full<T, HEAD_DIM, BLOCK_Q, BLOCK_KV> (crates/triton-kernels/src/attention.rs:780-909): causal
+ * prefill attention.  q / output [batch, num_heads, q_len, D]; k / v [batch, num_kv_heads, kv_len, D] (all
+ * contiguous); query row i sees kv positions 0 .. pos_offset + i.  Arguments in the reference's order, with the
+ * grid's batch extent made an explicit argument after `output`.  All arithmetic in fp32 for either element type
+ * (:773-779).  The reference asks for q_len and kv_len to be multiples of its tiles; any length is accepted
+ * here, and masked positions contribute exactly 0 (its -1e30 additive mask underflows to the same).  D <= 256. */
+int flash_attn_full_f32(const float *q, const float *k, const float *v, float *output, int batch,
+                        int num_heads, int num_kv_heads, int q_len, int kv_len, int head_dim,
+                        int pos_offset, float scale, b200k_stream stream);
+int flash_attn_full_f16(const b200k_half *q, const b200k_half *k, const b200k_half *v,
+                        b200k_half *output, int batch, int num_heads, int num_kv_heads, int q_len,
+                        int kv_len, int head_dim, int pos_offset, float scale, b200k_stream stream);
+
 /* ------------------------------------------------------------------------- */
 /* Projection helpers either side of attention (crates/triton-kernels/src/projection.rs), fp32 as in */
 /* the reference.  Its const generics (BLOCK, HEAD_DIM, HALF_DIM) are tile limits there and runtime    */

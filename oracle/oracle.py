@@ -344,6 +344,29 @@ def unified_attention(q, k_pool, v_pool, block_table, seq_lens, query_start_loc,
     return out
 
 
+def flash_attn_full(q, k, v, pos_offset, scale):
+    """Causal prefill attention (`attention.rs:780-909`): q [B, Hq, q_len, D], k / v [B, Hkv, kv_len, D];
+    query row i sees kv positions <= pos_offset + i (`:864-870`); fp32 throughout (`:773-779`)."""
+    q = np.asarray(q, dtype=np.float32)
+    k = np.asarray(k, dtype=np.float32)
+    v = np.asarray(v, dtype=np.float32)
+    b, hq, q_len, d = q.shape
+    hkv, kv_len = k.shape[1], k.shape[2]
+    groups = hq // hkv
+    out = np.zeros_like(q)
+    for bi in range(b):
+        for h in range(hq):
+            kvh = h // groups
+            sc = (q[bi, h] @ k[bi, kvh].T) * np.float32(scale)                       # [q_len, kv_len]
+            allowed = np.arange(kv_len)[None, :] <= (np.arange(q_len)[:, None] + pos_offset)
+            sc = np.where(allowed, sc, -np.inf)
+            mx = sc.max(axis=1, keepdims=True)
+            p = np.exp(sc - np.where(np.isfinite(mx), mx, 0.0))
+            den = p.sum(axis=1, keepdims=True)
+            out[bi, h] = np.where(den > 0, (p @ v[bi, kvh]) / np.where(den > 0, den, 1.0), 0.0)
+    return out
+
+
 def split_qkv(qkv, num_heads, head_dim):
     """qkv [batch, 3, heads, D] -> (q, k, v) each [batch, heads, D] (`projection.rs:18-51`)."""
     x = np.asarray(qkv, dtype=np.float32).reshape(-1, 3, num_heads, head_dim)

@@ -193,3 +193,37 @@ def test_unified_attention_vs_oracle(P, oracle, q_lens, seq_lens, hq, hkv, d, bs
                             torch.cuda.current_stream().cuda_stream)
     assert_close(out.cpu().numpy(), ref, 1e-4, 1e-5, "unified attention")
 
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f16"])
+@pytest.mark.parametrize("b,hq,hkv,q_len,kv_len,d,off", [
+    (2, 8, 2, 64, 64, 128, 0),        # plain causal prefill, the reference's tile-aligned case
+    (1, 4, 4, 37, 100, 64, 63),       # chunked prefill: 63 cached positions, ragged lengths
+    (1, 2, 1, 5, 3, 96, 0),           # queries past the end of the KV stream see all of it; head_dim not a power of two
+    (3, 4, 2, 1, 9, 128, 8),          # a single query row per sequence (decode through the prefill entry point)
+])
+def test_flash_attn_full_vs_oracle(P, oracle, dtype, b, hq, hkv, q_len, kv_len, d, off):
+    rng = np.random.default_rng(q_len * 7 + kv_len)
+    np_t, th_t = (np.float32, torch.float32) if dtype == "f32" else (np.float16, torch.float16)
+    q = rng.standard_normal((b, hq, q_len, d)).astype(np_t)
+    k = rng.standard_normal((b, hkv, kv_len, d)).astype(np_t)
+    v = rng.standard_normal((b, hkv, kv_len, d)).astype(np_t)
+    scale = 1.0 / np.sqrt(d)
+    ref = oracle.flash_attn_full(q, k, v, off, scale)
+    out = torch.full(q.shape, float("nan"), device=DEV, dtype=th_t)
+    fn = P.flash_attn_full_f32 if dtype == "f32" else P.flash_attn_full_f16
+    fn(t(q), t(k), t(v), out, b, hq, hkv, q_len, kv_len, d, off, scale, torch.cuda.current_stream().cuda_stream)
+    if dtype == "f32":
+        assert_close(out.cpu().numpy(), ref, 1e-4, 1e-5, "prefill attention f32")
+    else:
+        assert_close(out.float().cpu().numpy(), ref, 1e-2, 1e-2, "prefill attention f16")
+
+
+def test_flash_attn_full_rejects_bad_shapes(P, pkg):
+    z = torch.zeros(16, device=DEV)
+    st = torch.cuda.current_stream().cuda_stream
+    with pytest.raises(pkg.B200KError):
+        P.flash_attn_full_f32(z, z, z, z, 1, 3, 2, 1, 1, 16, 0, 1.0, st)       # q heads not a multiple of kv heads
+    with pytest.raises(pkg.B200KError):
+        P.flash_attn_full_f32(z, z, z, z, 1, 2, 2, 1, 1, 512, 0, 1.0, st)      # head_dim too large
+    P.flash_attn_full_f32(z, z, z, z, 0, 2, 2, 1, 1, 16, 0, 1.0, st)           # empty batch: nothing to do

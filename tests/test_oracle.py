@@ -256,3 +256,40 @@ def test_unified_attention_decode_equals_paged_decode(oracle):
         sc = (k[:j + 1] @ q3[j, 0]) * scale
         p = np.exp(sc - sc.max())
         assert np.allclose(out[j, 0], (p[:, None] * v[:j + 1]).sum(0) / p.sum(), rtol=1e-5, atol=1e-6)
+
+
+def test_flash_attn_full_matches_the_reference_mask_formulation(oracle):
+    """The prefill oracle against a literal restatement of the reference's tile loop: additive -1e30 mask on every
+    KV tile, online softmax with running max (`attention.rs:836-890`); and, with context = pos_offset, against the
+    unified oracle on the same tokens."""
+    rng = np.random.default_rng(11)
+    b, hq, hkv, ql, kl, d, off = 2, 4, 2, 8, 16, 16, 8
+    q = rng.standard_normal((b, hq, ql, d)).astype(np.float32)
+    k = rng.standard_normal((b, hkv, kl, d)).astype(np.float32)
+    v = rng.standard_normal((b, hkv, kl, d)).astype(np.float32)
+    scale = np.float32(1.0 / np.sqrt(d))
+    got = oracle.flash_attn_full(q, k, v, off, scale)
+    bkv = 4
+    for bi in range(b):
+        for h in range(hq):
+            kvh = h // (hq // hkv)
+            m = np.full(ql, -1e30, np.float32); l = np.zeros(ql, np.float32); acc = np.zeros((ql, d), np.float32)
+            for kb in range(kl // bkv):
+                kt, vt = k[bi, kvh, kb * bkv:(kb + 1) * bkv], v[bi, kvh, kb * bkv:(kb + 1) * bkv]
+                sc = (q[bi, h] @ kt.T) * scale
+                mask = (np.arange(kb * bkv, (kb + 1) * bkv)[None, :] <= (np.arange(ql)[:, None] + off)).astype(np.float32)
+                sc = sc + (mask - 1.0) * np.float32(1e30)
+                m_new = np.maximum(m, sc.max(axis=1))
+                alpha = np.exp(m - m_new)
+                p = np.exp(sc - m_new[:, None])
+                acc = acc * alpha[:, None] + p @ vt
+                l = l * alpha + p.sum(axis=1)
+                m = m_new
+            assert np.allclose(got[bi, h], acc / l[:, None], rtol=1e-5, atol=1e-6)
+    # the same tokens through the unified (paged) oracle: one block per sequence, query = the last q_len positions
+    kp = np.ascontiguousarray(k.transpose(0, 2, 1, 3))          # [b, kl, hkv, d] = pool of b blocks of size kl
+    vp = np.ascontiguousarray(v.transpose(0, 2, 1, 3))
+    qt = np.ascontiguousarray(q.transpose(0, 2, 1, 3)).reshape(b * ql, hq, d)
+    uni = oracle.unified_attention(qt, kp, vp, np.arange(b, dtype=np.int32).reshape(b, 1), np.full(b, off + ql, np.int32),
+                                   np.arange(0, (b + 1) * ql, ql, dtype=np.int32), hkv, kl, scale)
+    assert np.allclose(uni.reshape(b, ql, hq, d).transpose(0, 2, 1, 3), got, rtol=1e-5, atol=1e-6)
