@@ -71,6 +71,15 @@ int b200k_set_workspace(void *workspace, size_t bytes);
 size_t b200k_gemm_workspace_bytes(int m, int n, int k);
 size_t b200k_attention_workspace_bytes(int batch, int num_q_heads, int num_kv_heads,
                                        int head_dim, int max_len);
+/* The first word of every workspace is a status word that kernels OR bits into and never clear:
+ *   bit 0 (1)  a bounded device-side wait gave up (attention pipeline);
+ *   bit 1 (2)  a bounded wait of the tensor-core GEMM pipeline gave up;
+ *   bit 2 (4)  a sequence length or cache position outside [0, max_len) was clamped / its row skipped.
+ * b200k_workspace_status copies it to the host for a caller-owned workspace (the `_ws` entry points;
+ * synchronises the stream; allocates nothing); b200k_device_status (below) does the same for the
+ * default workspace; b200k_workspace_clear_status sets it back to 0. */
+int b200k_workspace_status(const void *workspace, int *host_status_out, b200k_stream stream);
+int b200k_workspace_clear_status(void *workspace, b200k_stream stream);
 
 /* ------------------------------------------------------------------------- */
 /* int4 W4A16 GEMM                                                             */
@@ -230,21 +239,29 @@ int batched_decode_attention_hm_f16_ws(const b200k_half *q, const b200k_half *k_
  * that has handed the whole GPU to its own arena, a plugin running inside someone else's
  * allocator, or a host that may not call cudaMalloc once serving has started.  It has no
  * counterpart in the reference.  The split-KV partials go to a fixed array that is part of the
- * library image (B200K_NOALLOC_SCRATCH_BYTES per GPU, resident from library load to process exit)
- * instead of the workspace; the call performs no cudaMalloc, cudaFree or other allocating call.
+ * library image (B200K_NOALLOC_SCRATCH_BYTES per GPU) instead of the workspace; the call performs
+ * no cudaMalloc, cudaFree or other allocating call.  The array becomes resident when the CUDA
+ * runtime loads the module that holds it, which with lazy module loading (the default) is the
+ * first use of this part of the library on that GPU, and stays until the process exits: an engine
+ * that is about to claim the rest of the GPU for its own arena should make one call first (a call
+ * with batch_size 0 is enough: it looks the array up and launches nothing).
  *   - Shapes whose scratch need (b200k_attention_workspace_bytes) exceeds the array are rejected
  *     with B200K_E_WORKSPACE and a message naming both sizes; nothing is launched.
  *   - The first call on each device looks the array's address up (that device must be current):
  *     make that call before any stream capture begins.
  *   - All calls on a device share the one array.  Its arrival counters are left at zero by every
  *     call, so back-to-back calls on one stream are fine; calls that may run at the same time
- *     on the same GPU (different streams) race on it and must not be made. */
+ *     on the same GPU (different streams) race on it and must not be made.
+ *   - b200k_noalloc_status reads the array's status word (same bits as b200k_workspace_status; a
+ *     bounded wait that gave up on this path reports there); it allocates nothing either. */
 #define B200K_NOALLOC_SCRATCH_BYTES (8u << 20)
 int batched_decode_attention_hm_f16_noalloc(const b200k_half *q, const b200k_half *k_cache,
                                             const b200k_half *v_cache, const int32_t *context_lens,
                                             b200k_half *output, int batch_size, int num_q_heads,
                                             int num_kv_heads, int head_dim, int max_len, float scale,
                                             b200k_stream stream);
+
+int b200k_noalloc_status(int *host_status_out, b200k_stream stream);
 
 /* Replaces flash_decode_attn_phase1_f32<HEAD_DIM,BLOCK_KV> (attention.rs:508-585):
  * split s of q head h covers chunk_blocks*block_kv positions from
@@ -279,8 +296,6 @@ int paged_decode_attention_f16(const b200k_half *q, const b200k_half *k_block_po
                                int head_dim, int valid_kv_len, int block_size, float scale,
                                b200k_stream stream);
 
-/* ------------------------------------------------------------------------- */
-/* fused MoE                                                                   */
 /* Replaces unified_attention_f32 (crates/triton-kernels/src/attention.rs:988-1187): prefill and decode in one
  * call over a paged KV pool.  q / output [total_tokens, num_q_heads, D] token-major; k/v_cache
  * [num_blocks, block_size, num_kv_heads, D]; block_table [num_seqs, max_blocks_per_seq]; seq_lens [num_seqs];
@@ -336,6 +351,8 @@ int rope_transpose_f32(const float *input, const float *cos_tab, const float *si
                        float *output, int tokens, int heads, int head_dim, int pos_offset,
                        b200k_stream stream);
 
+/* ------------------------------------------------------------------------- */
+/* fused MoE                                                                   */
 /* ------------------------------------------------------------------------- */
 /* The reference has no MoE kernel (a search of its tree finds two comment mentions,
  * crates/triton-dsl/examples/awq_gemm_int4_typed.rs:63 and
@@ -465,6 +482,27 @@ int rope_kv_append_hm_f16(const b200k_half *qkv, const float *cos_table,
                           int batch, b200k_stream stream);
 
 /* ------------------------------------------------------------------------- */
+/* the two ends of a decode step                                               */
+/* ------------------------------------------------------------------------- */
+/* Replace embedding_lookup_f32 / _f16 (crates/triton-kernels/src/embedding.rs:17-55):
+ * output[tok, :] = embeddings[indices[tok], :], rows of hidden_size elements.  num_tokens is the
+ * reference's launch grid; its BLOCK >= hidden_size limit is gone.  The table's row count is not an
+ * argument (it is not one in the reference either), so indices are the caller's responsibility. */
+int embedding_lookup_f32(const float *embeddings, const int32_t *indices, float *output,
+                         int hidden_size, int num_tokens, b200k_stream stream);
+int embedding_lookup_f16(const b200k_half *embeddings, const int32_t *indices, b200k_half *output,
+                         int hidden_size, int num_tokens, b200k_stream stream);
+/* Replace softmax_f32 / _f16 (crates/triton-kernels/src/reduction.rs:11-68): row softmax,
+ * out[r,c] = exp(x[r,c] - max_r) / sum_c exp(x[r,c] - max_r), fp32 arithmetic for either element
+ * type, any cols (the reference needs cols <= BLOCK and, through its zero-filled masked loads, counts
+ * the BLOCK - cols padding lanes in the sum when cols < BLOCK; this entry sums over cols only, which is
+ * the documented formula and what the reference computes whenever cols == BLOCK, as in its own check,
+ * crates/triton-runtime/examples/run_softmax.rs:20-21). */
+int softmax_f32(const float *input, float *output, int rows, int cols, b200k_stream stream);
+int softmax_f16(const b200k_half *input, b200k_half *output, int rows, int cols,
+                b200k_stream stream);
+
+/* ------------------------------------------------------------------------- */
 /* decode layer chain                                                          */
 /* ------------------------------------------------------------------------- */
 /* The reference holds the kernels but not the loop that strings them together: its
@@ -528,6 +566,14 @@ int b200k_comm_slot(struct b200k_comm *comm, int slot, b200k_half **host_out_ptr
 int b200k_comm_allreduce_f16(struct b200k_comm *comm, int slot, const b200k_half *input, b200k_half *output,
                              size_t count, b200k_stream stream);
 int b200k_comm_status(struct b200k_comm *comm, int *host_status_out, b200k_stream stream);
+int b200k_comm_clear_status(struct b200k_comm *comm, b200k_stream stream);
+/* How long a kernel waits for its peers, in SM clock cycles (default 2e9, about a second; <= 0 restores it). */
+int b200k_comm_set_timeout_cycles(struct b200k_comm *comm, int64_t cycles);
+/* For ranks that live in ONE process (several GPUs with peer access enabled by the caller, or a test that
+ * stands a second buffer in for a peer): b200k_comm_buffer yields this rank's exchange buffer,
+ * b200k_comm_set_peer_pointer installs a peer's buffer directly instead of an IPC mapping. */
+int b200k_comm_buffer(struct b200k_comm *comm, void **host_out_ptr);
+int b200k_comm_set_peer_pointer(struct b200k_comm *comm, int peer_rank, void *peer_buffer);
 void b200k_comm_destroy(struct b200k_comm *comm);
 /* Attach to a layer: the o and down GEMMs then write into slots 0 and 1 and the layer chain runs the
  * two all-reduces itself (12 launches).  NULL detaches (single GPU). */
@@ -553,9 +599,11 @@ int b200k_layer_forward_stage(b200k_layer *layer, int stage, const b200k_half *h
                               b200k_stream stream);
 /* Number of kernel launches one forward call issues (for launch accounting). */
 int b200k_layer_launches_per_forward(const b200k_layer *layer);
-/* Reads the device status word of the default workspace (0 = no bounded wait ever gave up).
- * Synchronises the stream. */
+/* Reads the device status word of the default workspace (0 = nothing to report; bits as listed at
+ * b200k_workspace_status).  Synchronises the stream. */
 int b200k_device_status(int *host_status_out, b200k_stream stream);
+/* Sets that word back to 0 (stream-ordered). */
+int b200k_device_clear_status(b200k_stream stream);
 
 #ifdef __cplusplus
 }

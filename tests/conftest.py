@@ -56,5 +56,30 @@ def assert_close(got, ref, rtol=TOL_RTOL, atol=TOL_ATOL, what=""):
                            f"at ref {ref.flat[err.argmax()]:.4g}")
 
 
+def assert_close_sum(got, ref, parts, rtol=TOL_RTOL, atol=TOL_ATOL, what=""):
+    """For an output that is the SUM of fp16 tensors `parts` (e.g. the closing residual add of a layer:
+    h1 + down): each summand is good to atol + rtol * |summand|, so the sum is good to the sum of those
+    bounds.  The plain bound atol + rtol * |ref| is not attainable where large summands cancel: one fp16
+    ulp of a summand of magnitude 40 is 0.03, whatever the sum comes to."""
+    got = np.asarray(got, dtype=np.float32)
+    ref = np.asarray(ref, dtype=np.float32)
+    assert got.shape == ref.shape and np.isfinite(got).all(), f"{what}: shape or non-finite output"
+    bound = sum(atol + rtol * np.abs(np.asarray(p, dtype=np.float32)) for p in parts)
+    err = np.abs(got - ref)
+    bad = err > bound
+    assert not bad.any(), f"{what}: {bad.sum()} of {bad.size} outside the propagated tolerance; worst |err| {err.max():.4g}"
+
+
+def assert_close_terms(got, ref, mag, terms, rtol=TOL_RTOL, atol=TOL_ATOL, what=""):
+    """For an output that is a weighted sum of `terms` fp16 tensors whose absolute values add up to `mag` (the
+    fused-MoE combine): bound = terms * atol + rtol * mag, i.e. the per-term tolerance summed."""
+    got = np.asarray(got, dtype=np.float32)
+    ref = np.asarray(ref, dtype=np.float32)
+    assert got.shape == ref.shape and np.isfinite(got).all(), f"{what}: shape or non-finite output"
+    err = np.abs(got - ref)
+    bad = err > terms * atol + rtol * np.asarray(mag, dtype=np.float32)
+    assert not bad.any(), f"{what}: {bad.sum()} of {bad.size} outside the propagated tolerance; worst |err| {err.max():.4g}"
+
+
 def golden(name):
     return np.load(ROOT / "tests" / "golden" / f"{name}.npz")

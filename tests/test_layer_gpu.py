@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import assert_close
+from conftest import assert_close, assert_close_sum
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -53,21 +53,24 @@ def test_layer_small_vs_numpy_oracle(pkg, oracle, use_graph, sym):
     for step, pos in enumerate([[5, 0, 38], [6, 1, 39]]):       # second step replays the captured graph
         pos = np.array(pos, dtype=np.int32)
         hidden = rng.standard_normal((B, H)).astype(np.float16)
-        ref = oracle.decode_layer(hidden, p, kc, vc, pos)       # appends into kc, vc
+        st = {}
+        ref = oracle.decode_layer(hidden, p, kc, vc, pos, stages=st)       # appends into kc, vc
         out = layer.forward(t(hidden), t(pos))
-        assert_close(out.float().cpu().numpy(), ref, 2e-2, 2e-2, f"layer step {step}")
+        # the output is the sum of two fp16 tensors (h1 + down): its tolerance is the sum of theirs
+        assert_close_sum(out.float().cpu().numpy(), ref, (st["h1"], st["down"]), what=f"layer step {step}")
         assert_close(layer.k_cache.float().cpu().numpy(), kc.astype(np.float32), 2e-3, 2e-3, "k cache")
         assert_close(layer.v_cache.float().cpu().numpy(), vc.astype(np.float32), 2e-3, 2e-3, "v cache")
     # host-buffer entry point
     hidden = rng.standard_normal((B, H)).astype(np.float16)
     pos = np.array([7, 2, 3], dtype=np.int32)
-    ref = oracle.decode_layer(hidden, p, kc, vc, pos)
+    st = {}
+    ref = oracle.decode_layer(hidden, p, kc, vc, pos, stages=st)
     hh = torch.from_numpy(hidden).pin_memory()
     hp = torch.from_numpy(pos).pin_memory()
     ho = torch.empty((B, H), dtype=torch.float16).pin_memory()
     layer.forward_host(hh, hp, ho)
     torch.cuda.synchronize()
-    assert_close(ho.float().numpy(), ref, 2e-2, 2e-2, "layer via host buffers")
+    assert_close_sum(ho.float().numpy(), ref, (st["h1"], st["down"]), what="layer via host buffers")
     # staged form == fused form
     part = torch.empty((B, H), dtype=torch.float16, device=DEV)
     part2 = torch.empty_like(part)
@@ -83,29 +86,20 @@ def test_layer_small_vs_numpy_oracle(pkg, oracle, use_graph, sym):
     layer.close()
 
 
-def test_layer_llama_shape_vs_c_oracle(pkg, oracle, oracle_c):
-    """BASELINE config 4 extents with a short context (the C oracle handles it in seconds)."""
-    import ctypes
+@pytest.mark.parametrize("zero_mean", [True, False])
+def test_layer_llama_shape_vs_c_oracle(pkg, oracle, zero_mean):
+    """BASELINE config 4 extents with a short context (the C oracle handles it in seconds): every kernel of the
+    chain on the oracle's own input at 1e-2 / 1e-2, and the whole chain end to end.  zero_mean=False is the
+    benchmark's own weight distribution (nibbles uniform 0..15 around the zero-point 8)."""
+    import layer_check
     rng = np.random.default_rng(4)
     B, H, hq, hkv, d, I, G, ml = 8, 4096, 32, 8, 128, 14336, 128, 300
-    p = make_layer(oracle, rng, H, hq, hkv, d, I, G, ml, zero_mean=True)
-    w, ln1, ln2, cos, sin = to_dev(p)
-    kc = rng.standard_normal((B, hkv, ml, d)).astype(np.float16)
-    vc = rng.standard_normal((B, hkv, ml, d)).astype(np.float16)
-    layer = pkg.DecodeLayer(pkg.LayerShape(), w, ln1, ln2, cos, sin, max_batch=B, max_len=ml, k_cache=t(kc), v_cache=t(vc))
-    hidden = rng.standard_normal((B, H)).astype(np.float16)
-    pos = rng.integers(100, ml - 1, B).astype(np.int32)
-    out = layer.forward(t(hidden), t(pos))
-    ref = np.zeros((B, H), np.float32)
-    ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)
-    args = [ptr(hidden), ptr(ref), B, H, hq, hkv, d, I, G, 1, ctypes.c_float(1e-5), ptr(p["ln1"]), ptr(p["ln2"])]
-    for name in ("qkv", "o", "gate_up", "down"):
-        args += [ptr(x) for x in p[name]]
-    args += [ptr(p["cos"]), ptr(p["sin"]), ptr(pos), ptr(kc), ptr(vc), ml]
-    oracle_c.oc_decode_layer(*args)
+    p = make_layer(oracle, rng, H, hq, hkv, d, I, G, ml, zero_mean=zero_mean)
+    case = dict(H=H, hq=hq, hkv=hkv, d=d, I=I, G=G, ml=ml, eps=1e-5, cos=p["cos"], sin=p["sin"], ln1=p["ln1"], ln2=p["ln2"],
+                qkv=p["qkv"], o=p["o"], gate_up=p["gate_up"], down=p["down"],
+                kc=rng.standard_normal((B, hkv, ml, d)).astype(np.float16), vc=rng.standard_normal((B, hkv, ml, d)).astype(np.float16),
+                hidden=rng.standard_normal((B, H)).astype(np.float16), pos=rng.integers(100, ml - 1, B).astype(np.int32))
+    ref, st, _ = layer_check.oracle_layer(layer_check.load_oracle_c(), case)
     assert np.isfinite(ref).all()
-    # ten fp16 roundings deep, values up to a few hundred: tolerance relative to the row scale
-    scale = np.abs(ref).max(axis=1, keepdims=True)
-    err = np.abs(out.float().cpu().numpy() - ref)
-    assert (err <= 2e-2 * scale + 2e-2).all(), float((err / scale).max())
-    layer.close()
+    rep = layer_check.check_layer(pkg, torch, DEV, case, ref, st)
+    assert rep["ok"], rep

@@ -3,9 +3,9 @@
 // Two kernel families:
 //  * attn_split_f16 (head_dim 128, fp16, GQA group size <= 8): split-KV flash-decode.
 //    One CTA per (sequence, kv head, chunk of positions) serves ALL q heads of the
-//    GQA group, so every K/V element is read from HBM once.  K/V rows are staged into
-//    shared memory by bulk asynchronous copies (cp.async.bulk, one 256-byte row per
-//    copy, mbarrier transaction counts) in a 3-deep ring of 64-position K+V tiles.
+//    GQA group, so every K/V element is read from HBM once.  K/V tiles are staged into
+//    shared memory by TMA tensor loads (4-D tensor map, 64 positions x 64 dims per box,
+//    128-byte swizzle, mbarrier transaction counts) in a 3-deep ring of K+V tiles.
 //    The products run on mma.sync m16n8k16 in transposed form (positions fill the 16
 //    MMA rows, the group's q heads the 8 columns): one query token per sequence gives
 //    at most 8 useful rows, far below the 64/128-row tcgen05 tile, and the kernel is
@@ -16,6 +16,8 @@
 //  * attn_generic (any head_dim <= 256, fp16 or fp32): one CTA per (sequence, q head,
 //    split); backs the f32 entry points and the explicit phase-1 / phase-2 API.
 #include <stdlib.h>
+
+#include <atomic>
 
 #include "common.cuh"
 #include "tma.cuh"
@@ -66,7 +68,8 @@ struct AttnSplitArgs {
     float *ws_acc;          // [B*Hkv*max_chunks, G, D]
     float *ws_ml;           // [B*Hkv*max_chunks, G, 2]  (max, sum)
     int *counters;          // [B*Hkv], zero between launches
-    int *status;            // device status word (0 = ok)
+    int *status;            // device status word (0 = ok; bit 0: a bounded wait gave up, bit 2: a length beyond max_len was clamped)
+    int max_len;            // rows per (sequence, kv head) the cache holds: lengths are clamped to it
     int out_kperm;          // store every 8 output values of a head as (d0,d4,d1,d5,d2,d6,d3,d7), the order the int4 GEMM that
                             // consumes them wants (see gemm_tc.cu)
 };
@@ -121,7 +124,13 @@ attn_split_f16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
     const int G = A.g;
     pdl_wait();                 // the lengths, q and the appended K/V rows come from the kernel before
     pdl_launch_dependents();
-    const int len = A.lens ? A.lens[b] : A.len_scalar;
+    int len = A.lens ? A.lens[b] : A.len_scalar;
+    if (len > A.max_len) {
+        // a length beyond the cache: attend to the rows that exist and say so (with more chunks than the grid has,
+        // the arrival counter of this (sequence, kv head) would never reach its target)
+        len = A.max_len;
+        if (tid == 0 && chunk_id == 0) atomicOr(A.status, 4);
+    }
     const int nchunks = (len + A.chunk - 1) / A.chunk;
     const long out_row0 = ((long)b * A.hq + (long)kvh * G) * AT_D;
     if (len <= 0) {
@@ -204,7 +213,7 @@ attn_split_f16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_con
         const int st = t % AT_STAGES;
         if (!S.abort_flag && !mbar_wait_bounded(smem_u32(&S.full[st]), (t / AT_STAGES) & 1)) {
             S.abort_flag = 1;
-            atomicExch(A.status, 1);
+            atomicOr(A.status, 1);
         }
         const int rows_valid = npos - t * AT_TILE;     // < 64 only in the last tile of the sequence
         if (rows_valid < AT_TILE) {
@@ -378,8 +387,8 @@ static int pick_chunk(int batch, int hkv, int max_len) {
     // wave balance of the grid when all sequences are full length: CTAs / (2 per SM) should sit just below a
     // whole number of waves.  A finer cut is taken only when it is clearly better balanced (every chunk adds a
     // partial result to merge), and never below 256 positions per chunk.
-    if (const char *e = getenv("B200K_ATTN_CHUNK")) {   // tuning override: positions per chunk (multiple of 64)
-        const int v = atoi(e);
+    {   // tuning override: positions per chunk (multiple of 64)
+        const int v = env_int("B200K_ATTN_CHUNK", 0);
         if (v >= AT_TILE && v <= AT_MAX_CH && v % AT_TILE == 0) return v;
     }
     const double slots = 2.0 * sm_count();
@@ -444,7 +453,7 @@ static int attn_split_launch(const char *name, AttnCall c) {
     A.block_table = c.mode == KV_PAGED ? c.block_table : nullptr;
     A.block_size = c.block_size;
     A.box_rows = c.mode == KV_PAGED && c.block_size < AT_TILE ? c.block_size : AT_TILE;
-    A.ws_acc = w.acc; A.ws_ml = w.ml; A.counters = w.counters; A.status = w.status;
+    A.ws_acc = w.acc; A.ws_ml = w.ml; A.counters = w.counters; A.status = w.status; A.max_len = c.max_len;
 
     // tensor maps: innermost dimension = head_dim, then by ascending stride
     const uint64_t row = AT_D * 2;
@@ -472,13 +481,10 @@ static int attn_split_launch(const char *name, AttnCall c) {
     if (rc) return rc;
 
     const size_t smem = sizeof(AttnSmem) + 1024;
-    static bool attr_set[16] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 16 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_split_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    {
+        static OncePerDevice once;
+        cudaError_t e = once.run([&] { return cudaFuncSetAttribute(attn_split_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); });
         if (e != cudaSuccess) return fail((int)e, "attention: shared memory %zu: %s", smem, cudaGetErrorString(e));
-        attr_set[dev] = true;
     }
     dim3 grid(max_chunks, c.hkv, c.batch);
     launch_kernel(attn_split_f16_kernel, grid, dim3(AT_THREADS), smem, c.stream, kmap, vmap, A);
@@ -742,38 +748,63 @@ extern "C" int batched_decode_attention_hm_f16(const b200k_half *q, const b200k_
 // device with cudaGetSymbolAddress and handed to the kernel like any other workspace.
 static __device__ __align__(256) unsigned char g_attn_static_scratch[B200K_NOALLOC_SCRATCH_BYTES];
 
+// Device address of the array on device `dev` (which must be current), looked up on first use and cached; the
+// cache is an atomic pointer per device because first calls may come from several host threads (they all
+// store the same value).  No allocation happens here.
+static int noalloc_scratch(const char *name, int dev, void **out) {
+    static std::atomic<void *> cache[16];
+    void *p = cache[dev].load(std::memory_order_acquire);
+    if (!p) {
+        cudaError_t e = cudaGetSymbolAddress(&p, g_attn_static_scratch);
+        if (e != cudaSuccess || !p) {
+            cudaGetLastError();
+            return fail((int)(e != cudaSuccess ? e : cudaErrorInvalidSymbol), "%s: cudaGetSymbolAddress: %s", name,
+                        cudaGetErrorString(e));
+        }
+        cache[dev].store(p, std::memory_order_release);
+    }
+    *out = p;
+    return 0;
+}
+
 extern "C" int batched_decode_attention_hm_f16_noalloc(const b200k_half *q, const b200k_half *k_cache,
                                                        const b200k_half *v_cache, const int32_t *context_lens,
                                                        b200k_half *output, int batch_size, int num_q_heads,
                                                        int num_kv_heads, int head_dim, int max_len, float scale,
                                                        b200k_stream stream) {
     const char *name = "batched_decode_attention_hm_f16_noalloc";
-    static void *scratch_of_device[16] = {};
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= 16) {
         cudaGetLastError();
         return fail(B200K_E_DEVICE, "%s: no usable current device", name);
     }
-    if (!scratch_of_device[dev]) {
-        // first call on this device: resolve the array's device address (no allocation happens)
-        void *p = nullptr;
-        e = cudaGetSymbolAddress(&p, g_attn_static_scratch);
-        if (e != cudaSuccess || !p) {
-            cudaGetLastError();
-            return fail((int)(e != cudaSuccess ? e : cudaErrorInvalidSymbol), "%s: cudaGetSymbolAddress: %s", name,
-                        cudaGetErrorString(e));
-        }
-        scratch_of_device[dev] = p;
-    }
+    void *scratch = nullptr;
+    int rc = noalloc_scratch(name, dev, &scratch);
+    if (rc) return rc;
     const size_t need = b200k_attention_workspace_bytes(batch_size, num_q_heads, num_kv_heads, head_dim, max_len);
     B200K_REQUIRE(need <= (size_t)B200K_NOALLOC_SCRATCH_BYTES, B200K_E_WORKSPACE,
                   "%s: this call needs %zu bytes of scratch, the built-in array holds %zu (batch %d, kv heads %d, "
                   "max_len %d): use batched_decode_attention_hm_f16_ws with a caller-owned workspace",
                   name, need, (size_t)B200K_NOALLOC_SCRATCH_BYTES, batch_size, num_kv_heads, max_len);
     return batched_decode_attention_hm_f16_ws(q, k_cache, v_cache, context_lens, output, batch_size, num_q_heads,
-                                              num_kv_heads, head_dim, max_len, scale, scratch_of_device[dev],
+                                              num_kv_heads, head_dim, max_len, scale, scratch,
                                               (size_t)B200K_NOALLOC_SCRATCH_BYTES, stream);
+}
+
+extern "C" int b200k_noalloc_status(int *host_status_out, b200k_stream stream) {
+    const char *name = "b200k_noalloc_status";
+    B200K_REQUIRE(host_status_out, B200K_E_NULL, "%s: NULL pointer", name);
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 16) {
+        cudaGetLastError();
+        return fail(B200K_E_DEVICE, "%s: no usable current device", name);
+    }
+    void *scratch = nullptr;
+    int rc = noalloc_scratch(name, dev, &scratch);
+    if (rc) return rc;
+    return b200k_workspace_status(scratch, host_status_out, stream);
 }
 
 extern "C" size_t b200k_attention_workspace_bytes(int batch, int num_q_heads, int num_kv_heads, int head_dim,

@@ -24,12 +24,14 @@ struct b200k_comm {
     unsigned char *peer[8];        // mapped buffers, peer[rank] == local
     bool opened[8];
     unsigned char **d_peers;       // device copy of peer[]
+    long long wait_cycles;         // SM clock cycles a kernel waits for its peers before it gives up
 };
 
 namespace b200k {
 
 constexpr size_t COMM_FLAGS_BYTES = 4096;   // [0,32): flags (one per peer, written by that peer); [64]: sequence; [68]: done counter; [72]: status
 constexpr int COMM_MAX_WORLD = 8;
+constexpr long long COMM_DEFAULT_WAIT_CYCLES = 2000000000LL;   // about a second of SM clock
 
 __device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -42,7 +44,7 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
 
 __global__ void __launch_bounds__(512)
 allreduce_oneshot_kernel(unsigned char *const *__restrict__ peers, int rank, int world, int slot, size_t slot_bytes,
-                         __half *__restrict__ out, size_t count) {
+                         __half *__restrict__ out, size_t count, long long wait_cycles) {
     pdl_wait();                 // the partial sums in my slot come from the kernel before
     pdl_launch_dependents();
     unsigned char *mine = peers[rank];
@@ -59,7 +61,7 @@ allreduce_oneshot_kernel(unsigned char *const *__restrict__ peers, int rank, int
     if (threadIdx.x < world) {
         const long long t0 = clock64();
         while ((int)(ld_acquire_sys(my_flags + threadIdx.x) - seq) < 0) {
-            if (clock64() - t0 > 2000000000LL) {   // a peer never arrived: report, do not spin for ever
+            if (clock64() - t0 > wait_cycles) {   // a peer never arrived: report, do not spin for ever
                 s_fail = 1;
                 atomicExch(status_p, 1u);
                 break;
@@ -105,7 +107,7 @@ int comm_allreduce_f16(struct ::b200k_comm *c, int slot, __half *out, size_t cou
     if (count == 0) return 0;
     int blocks = (int)((count / 8 + 511) / 512);
     if (blocks > 32) blocks = 32;
-    launch_kernel(allreduce_oneshot_kernel, dim3(blocks), dim3(512), 0, st, c->d_peers, c->rank, c->world, slot, c->slot_bytes, out, count);
+    launch_kernel(allreduce_oneshot_kernel, dim3(blocks), dim3(512), 0, st, c->d_peers, c->rank, c->world, slot, c->slot_bytes, out, count, c->wait_cycles);
     return launch_status("all-reduce (peer to peer)");
 }
 
@@ -119,12 +121,15 @@ size_t comm_slot_capacity(struct ::b200k_comm *c) { return c ? c->slot_bytes : 0
 
 using namespace b200k;
 
+static int upload_peers(struct b200k_comm *comm, const char *name);
+
 extern "C" int b200k_comm_create(int rank, int world, size_t slot_bytes, struct b200k_comm **out_comm) {
     B200K_REQUIRE(out_comm, B200K_E_NULL, "b200k_comm_create: NULL pointer");
     B200K_REQUIRE(world >= 1 && world <= COMM_MAX_WORLD && rank >= 0 && rank < world && slot_bytes > 0, B200K_E_SHAPE,
                   "b200k_comm_create: rank %d, world %d (<= %d), slot_bytes %zu", rank, world, COMM_MAX_WORLD, slot_bytes);
     b200k_comm *c = new b200k_comm();
     c->rank = rank; c->world = world;
+    c->wait_cycles = COMM_DEFAULT_WAIT_CYCLES;
     c->slot_bytes = (slot_bytes + 255) / 256 * 256;
     const size_t total = COMM_FLAGS_BYTES + 2 * c->slot_bytes;
     cudaError_t e = cudaMalloc(&c->local, total);
@@ -166,8 +171,43 @@ extern "C" int b200k_comm_open_peers(struct b200k_comm *comm, const void *host_a
         comm->peer[r] = (unsigned char *)p;
         comm->opened[r] = true;
     }
+    return upload_peers(comm, "b200k_comm_open_peers");
+}
+
+static int upload_peers(struct b200k_comm *comm, const char *name) {
     cudaError_t e = cudaMemcpy(comm->d_peers, comm->peer, sizeof(unsigned char *) * COMM_MAX_WORLD, cudaMemcpyHostToDevice);
-    if (e != cudaSuccess) return fail((int)e, "b200k_comm_open_peers: %s", cudaGetErrorString(e));
+    if (e != cudaSuccess) return fail((int)e, "%s: %s", name, cudaGetErrorString(e));
+    return 0;
+}
+
+extern "C" int b200k_comm_buffer(struct b200k_comm *comm, void **host_out_ptr) {
+    B200K_REQUIRE(comm && host_out_ptr, B200K_E_NULL, "b200k_comm_buffer: NULL pointer");
+    *host_out_ptr = comm->local;
+    return 0;
+}
+
+extern "C" int b200k_comm_set_peer_pointer(struct b200k_comm *comm, int peer_rank, void *peer_buffer) {
+    B200K_REQUIRE(comm && peer_buffer, B200K_E_NULL, "b200k_comm_set_peer_pointer: NULL pointer");
+    B200K_REQUIRE(peer_rank >= 0 && peer_rank < comm->world && peer_rank != comm->rank, B200K_E_SHAPE,
+                  "b200k_comm_set_peer_pointer: peer rank %d (world %d, own rank %d)", peer_rank, comm->world, comm->rank);
+    if (comm->opened[peer_rank]) {
+        cudaIpcCloseMemHandle(comm->peer[peer_rank]);
+        comm->opened[peer_rank] = false;
+    }
+    comm->peer[peer_rank] = (unsigned char *)peer_buffer;
+    return upload_peers(comm, "b200k_comm_set_peer_pointer");
+}
+
+extern "C" int b200k_comm_set_timeout_cycles(struct b200k_comm *comm, int64_t cycles) {
+    B200K_REQUIRE(comm, B200K_E_NULL, "b200k_comm_set_timeout_cycles: NULL pointer");
+    comm->wait_cycles = cycles > 0 ? (long long)cycles : COMM_DEFAULT_WAIT_CYCLES;
+    return 0;
+}
+
+extern "C" int b200k_comm_clear_status(struct b200k_comm *comm, b200k_stream stream) {
+    B200K_REQUIRE(comm, B200K_E_NULL, "b200k_comm_clear_status: NULL pointer");
+    cudaError_t e = cudaMemsetAsync(comm->local + 72, 0, sizeof(int), to_stream(stream));
+    if (e != cudaSuccess) return fail((int)e, "b200k_comm_clear_status: %s", cudaGetErrorString(e));
     return 0;
 }
 

@@ -5,6 +5,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <mutex>
+
 #include "../../include/b200_kernels.h"
 
 namespace b200k {
@@ -15,11 +17,37 @@ int launch_status(const char *what);
 // Per-device default workspace (allocated on first use unless installed by the caller).
 int default_workspace(void **ptr, size_t *bytes);
 int sm_count();
+// The device status word kernels report through (first word of the default workspace); nullptr when the
+// workspace cannot be had, in which case kernels skip the report.
+int *status_word();
 
 #define B200K_REQUIRE(cond, code, ...)                 \
     do {                                               \
         if (!(cond)) return b200k::fail(code, __VA_ARGS__); \
     } while (0)
+
+// Integer value of an environment variable, read once per process and variable (tuning overrides are not meant
+// to change while the process runs); `dflt` when unset or empty.
+int env_int(const char *name, int dflt);
+// First character of an environment variable (0 when unset), read once.
+int env_char(const char *name);
+
+// Runs a set-up call (e.g. cudaFuncSetAttribute, which is per device) at most once per device, thread-safely.
+// A failed call is not remembered: the next caller tries again.
+struct OncePerDevice {
+    std::mutex mu;
+    bool done[16] = {};
+    template <typename F> cudaError_t run(F f) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev < 0 || dev >= 16) return f();
+        std::lock_guard<std::mutex> lk(mu);
+        if (done[dev]) return cudaSuccess;
+        cudaError_t e = f();
+        if (e == cudaSuccess) done[dev] = true;
+        return e;
+    }
+};
 
 static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 static inline cudaStream_t to_stream(b200k_stream s) { return reinterpret_cast<cudaStream_t>(s); }

@@ -370,8 +370,8 @@ int gemv_launch(const GemmArgs &g) {
     // enough CTAs for ~2 per SM, cluster size a power of two <= 8, no warp without a group
     int ksplit = 1;
     while (ksplit < 8 && colblocks * ksplit < 2 * sm_count() && ksplit * 2 * kwarps <= groups) ksplit *= 2;
-    if (const char *e = getenv("B200K_GEMV_KSPLIT")) {   // tuning override
-        const int v = atoi(e);
+    {   // tuning override
+        const int v = env_int("B200K_GEMV_KSPLIT", 0);
         if ((v == 1 || v == 2 || v == 4 || v == 8) && v * kwarps <= groups) ksplit = v;
     }
     const size_t smem = (size_t)g.k * 2 + (size_t)GEMV_WARPS * 256 * sizeof(float);
@@ -379,7 +379,13 @@ int gemv_launch(const GemmArgs &g) {
                 : cw == 2 ? (g.group == 128 ? gemv_gptq_kernel<16, 2> : gemv_gptq_kernel<0, 2>)
                           : (g.group == 128 ? gemv_gptq_kernel<16, 1> : gemv_gptq_kernel<0, 1>);
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        // raised once per kernel variant and device to the most any K this family accepts can need
+        static OncePerDevice once[5];
+        const int variant = g.format != FMT_GPTQ ? 4 : (cw == 2 ? 0 : 2) + (g.group == 128 ? 0 : 1);
+        cudaError_t e = once[variant].run([&] {
+            return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        65536 * 2 + GEMV_WARPS * 256 * (int)sizeof(float));
+        });
         if (e != cudaSuccess) return fail((int)e, "gemv: shared memory %zu: %s", smem, cudaGetErrorString(e));
     }
     cudaLaunchConfig_t cfg = {};
@@ -485,18 +491,18 @@ static int gemm_dispatch(const char *name, GemmArgs g, bool own_ws) {
             if (rc) return rc;
         }
         const int rc = gemm_tc_launch(g);
-        return rc == 1 ? fail(B200K_E_SHAPE, "%s: shape not covered by the tensor-core family (K %% 64, group a power of two >= 64, N %% 32 with qzeros)", name) : rc;
+        return rc == TC_NOT_COVERED ? fail(B200K_E_SHAPE, "%s: shape not covered by the tensor-core family (K %% 64, group a power of two >= 64, N %% 32 with qzeros)", name) : rc;
     }
-    const char *force = getenv("B200K_GEMM_PATH");  // tuning/testing override: strided | gemv | tc
-    if (force && !strcmp(force, "strided")) return gemm_strided_launch(g);
-    if (canon && g.m == 1 && g.k <= 65536 && !(force && !strcmp(force, "tc"))) return gemv_launch(g);
+    const int force = env_char("B200K_GEMM_PATH");  // tuning/testing override: s(trided) | g(emv) | t(c)
+    if (force == 's') return gemm_strided_launch(g);
+    if (canon && g.m == 1 && g.k <= 65536 && force != 't') return gemv_launch(g);
     if (canon) {
         if (!g.ws && own_ws) {
             int rc = default_workspace(&g.ws, &g.ws_bytes);
             if (rc) return rc;
         }
         int rc = gemm_tc_launch(g);
-        if (rc != 1) return rc;
+        if (rc != TC_NOT_COVERED) return rc;
     }
     return gemm_strided_launch(g);
 }
@@ -646,7 +652,7 @@ extern "C" int b200k_gemm_tc_plan(int m_size, int n_size, int k_size, int group_
     g.plan_out = host_plan_out;
     for (int i = 0; i < 10; ++i) host_plan_out[i] = 0;
     const int rc = gemm_tc_launch(g);
-    return rc == 1 ? fail(B200K_E_SHAPE, "b200k_gemm_tc_plan: shape not covered by the tensor-core family") : rc;
+    return rc == TC_NOT_COVERED ? fail(B200K_E_SHAPE, "b200k_gemm_tc_plan: shape not covered by the tensor-core family") : rc;
 }
 
 extern "C" size_t b200k_gemm_workspace_bytes(int m, int n, int k) {

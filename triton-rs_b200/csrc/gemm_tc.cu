@@ -482,9 +482,9 @@ static int pick_tt(int m) {
 }
 
 int gemm_tc_launch(const GemmArgs &g) {
-    if (g.k % TC_BK || g.group % TC_BK || (g.group & (g.group - 1)) || g.n % 8) return 1;
-    if (g.format == FMT_AWQ && !g.qzeros) return 1;
-    if (g.qzeros && (g.s_qzk % 4 || !aligned16(g.qzeros))) return 1;   // zero-point rows travel by TMA: 16-byte pitch
+    if (g.k % TC_BK || g.group % TC_BK || (g.group & (g.group - 1)) || g.n % 8) return TC_NOT_COVERED;
+    if (g.format == FMT_AWQ && !g.qzeros) return TC_NOT_COVERED;
+    if (g.qzeros && (g.s_qzk % 4 || !aligned16(g.qzeros))) return TC_NOT_COVERED;   // zero-point rows travel by TMA: 16-byte pitch
     const bool grouped = g.seg_offsets != nullptr;
     // grouped: the token tile follows the average segment; the grid covers the worst case (every row in
     // one segment) and CTAs past their segment's end return at once
@@ -499,7 +499,7 @@ int gemm_tc_launch(const GemmArgs &g) {
     const int ng = tt <= 64 ? 2 : 4;                 // dequant groups
     // operand tile in tensor memory (GPTQ) or in shared memory (AWQ; B200K_TC_OPERAND=smem forces it)
     bool ts = g.format == FMT_GPTQ;
-    if (const char *e = getenv("B200K_TC_OPERAND")) ts = ts && e[0] != 's';
+    if (env_char("B200K_TC_OPERAND") == 's') ts = false;
     const int a_bytes = ts ? 0 : TC_A_BYTES;
     // Ring depths, powers of two (slot and phase of a block are then bit fields of its index).  The operand ring
     // is shallow (producer and consumer are on chip) and at least as deep as there are dequant groups; an
@@ -517,16 +517,16 @@ int gemm_tc_launch(const GemmArgs &g) {
         dq_stages = tt <= 64 ? 2 : 4;
         act_stages = tt <= 32 ? 8 : 4;
     }
-    if (const char *e = getenv("B200K_TC_DQ_STAGES")) dq_stages = pow2_floor(atoi(e) < 1 ? 1 : atoi(e));     // tuning overrides
-    if (const char *e = getenv("B200K_TC_ACT_STAGES")) act_stages = pow2_floor(atoi(e) < 1 ? 1 : atoi(e));
+    if (const int v = env_int("B200K_TC_DQ_STAGES", 0)) dq_stages = pow2_floor(v < 1 ? 1 : v);     // tuning overrides
+    if (const int v = env_int("B200K_TC_ACT_STAGES", 0)) act_stages = pow2_floor(v < 1 ? 1 : v);
     if (dq_stages < ng) dq_stages = ng;
-    if (ts && (nmma * tt < 32 ? 32 : nmma * tt) + 32 * dq_stages > (ctas_per_sm == 2 ? 256 : 512)) return 1;
+    if (ts && (nmma * tt < 32 ? 32 : nmma * tt) + 32 * dq_stages > (ctas_per_sm == 2 ? 256 : 512)) return TC_NOT_COVERED;
     if (act_stages < dq_stages) act_stages = dq_stages;
     int raw_stages = (budget - dq_stages * a_bytes - act_stages * act_bytes - 1024) / TC_RAW_BYTES;
-    if (raw_stages < 2) return 1;
+    if (raw_stages < 2) return TC_NOT_COVERED;
     raw_stages = pow2_floor(raw_stages > 16 ? 16 : raw_stages);
-    if (const char *e = getenv("B200K_TC_RAW_STAGES")) {
-        const int v = atoi(e);
+    {
+        const int v = env_int("B200K_TC_RAW_STAGES", 0);
         if (v >= 2 && v <= raw_stages) raw_stages = pow2_floor(v);
     }
     // K split (cluster of 1, 2, 4 or 8 CTAs along K).  A CTA costs ~6 us of fill, drain and exchange
@@ -541,8 +541,8 @@ int gemm_tc_launch(const GemmArgs &g) {
         while (ksplit < 8 && tiles * ksplit < (sms * 7) / 8 && kb_total / (ksplit * 2) >= 4) ksplit *= 2;
         if (ksplit < 8 && ksplit > 1 && tiles * ksplit <= sms && kb_total / (ksplit * 2) >= 24) ksplit *= 2;
     }
-    if (const char *e = getenv("B200K_TC_KSPLIT")) {   // tuning override
-        const int v = atoi(e);
+    {   // tuning override
+        const int v = env_int("B200K_TC_KSPLIT", 0);
         if (v >= 1 && v <= 8 && (v == 1 || can_split)) ksplit = v;
     }
     if (g.plan_out) {
@@ -568,25 +568,25 @@ int gemm_tc_launch(const GemmArgs &g) {
         const uint32_t box[2] = {TC_BN / 8, TC_BK};
         rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, g.qweight, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
     }
-    if (rc) return 1;
+    if (rc) return TC_NOT_COVERED;
     {
         const uint64_t dims[2] = {(uint64_t)g.k, (uint64_t)g.m}, str[1] = {(uint64_t)g.s_am * 2};
         const uint32_t box[2] = {TC_BK, (uint32_t)tt};
         rc = make_tensor_map(&amap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
     }
-    if (rc) return 1;   // layout the TMA cannot describe: the strided family takes it
+    if (rc) return TC_NOT_COVERED;   // layout the TMA cannot describe: the strided family takes it
     {
         const uint64_t dims[2] = {(uint64_t)g.n, (uint64_t)(g.k / g.group) * nseg}, str[1] = {(uint64_t)g.s_sk * 2};
         const uint32_t box[2] = {TC_BN, 1};
         rc = make_tensor_map(&smap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.scales, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
     }
-    if (rc) return 1;
+    if (rc) return TC_NOT_COVERED;
     zmap = smap;
     if (g.qzeros) {
         const uint64_t dims[2] = {(uint64_t)(g.n / 8), (uint64_t)(g.k / g.group) * nseg}, str[1] = {(uint64_t)g.s_qzk * 4};
         const uint32_t box[2] = {TC_BN / 8, 1};
         rc = make_tensor_map(&zmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, g.qzeros, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
-        if (rc) return 1;
+        if (rc) return TC_NOT_COVERED;
     }
 
     TcArgs P;
@@ -602,19 +602,16 @@ int gemm_tc_launch(const GemmArgs &g) {
     P.status = (int *)g.ws;   // status word at the start of the scratch buffer
     if (!P.status) return fail(B200K_E_WORKSPACE, "w4a16 gemm (tensor core): workspace is NULL");
 
-    if (g.a_kperm && !ts) return 1;   // pre-permuted activations: only the tensor-memory operand variants take them
+    if (g.a_kperm && !ts) return TC_NOT_COVERED;   // pre-permuted activations: only the tensor-memory operand variants take them
     auto kern = g.format == FMT_AWQ ? (ng == 2 ? gemm_tc_kernel<FMT_AWQ, 2, false, 2, false> : gemm_tc_kernel<FMT_AWQ, 4, false, 1, false>)
                 : ts ? (g.a_kperm ? (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, true>)
                                   : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, false>))
                      : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, false, 2, false> : gemm_tc_kernel<FMT_GPTQ, 4, false, 1, false>);
-    static bool attr_set[4][2][16] = {};
-    const int variant = g.format == FMT_AWQ ? 1 : (ts ? (g.a_kperm ? 3 : 2) : 0);
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 16 && !attr_set[variant][ng == 4][dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    {
+        static OncePerDevice once[4][2];
+        const int variant = g.format == FMT_AWQ ? 1 : (ts ? (g.a_kperm ? 3 : 2) : 0);
+        cudaError_t e = once[variant][ng == 4].run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); });
         if (e != cudaSuccess) return fail((int)e, "w4a16 gemm (tensor core): shared memory: %s", cudaGetErrorString(e));
-        attr_set[variant][ng == 4][dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(col_tiles, tok_tiles, grouped ? g.num_segments : ksplit);

@@ -280,12 +280,17 @@ static int rope_launch(const char *name, const T *x, const float *c, const float
 template <typename T, bool HEAD_MAJOR>
 __global__ void __launch_bounds__(256)
 kv_append_kernel(const T *__restrict__ nk, const T *__restrict__ nv, T *__restrict__ kc, T *__restrict__ vc,
-                 const int32_t *__restrict__ idx, int heads, int d, int max_len, long total) {
+                 const int32_t *__restrict__ idx, int heads, int d, int max_len, long total, int *status) {
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
         const long bh = i / d;
         const int c = (int)(i - bh * d);
         const int b = (int)(bh / heads), h = (int)(bh - (long)b * heads);
         const long pos = idx[b];
+        if (HEAD_MAJOR && (unsigned long)pos >= (unsigned long)max_len) {
+            // a row index outside the cache: nothing is stored for this sequence, the status word says so
+            if (c == 0 && h == 0 && status) atomicOr(status, 4);
+            continue;
+        }
         const long dst = HEAD_MAJOR ? (((long)b * heads + h) * max_len + pos) * d + c : (pos * heads + h) * d + c;
         kc[dst] = nk[i];
         vc[dst] = nv[i];
@@ -298,12 +303,20 @@ __global__ void __launch_bounds__(256)
 rope_kv_append_kernel(const __half *__restrict__ qkv, const float *__restrict__ cos_t,
                       const float *__restrict__ sin_t, const int32_t *__restrict__ positions,
                       __half *__restrict__ q_out, __half *__restrict__ kc, __half *__restrict__ vc,
-                      int32_t *__restrict__ lens_out, int hq, int hkv, int d, int max_len) {
+                      int32_t *__restrict__ lens_out, int hq, int hkv, int d, int max_len, int *status) {
     pdl_wait();
     pdl_launch_dependents();
     const int b = blockIdx.y;
     const int half = d / 2;
-    const int pos = positions[b];
+    int pos = positions[b];
+    // A position outside the cache (a decode loop that ran past max_len, or a negative index): the K/V rows are not
+    // stored, q is rotated with the nearest valid table row so that every read stays in range, the length handed to
+    // attention stays within the cache, and bit 2 of the status word reports it.
+    const bool in_range = (unsigned)pos < (unsigned)max_len;
+    if (!in_range) {
+        pos = pos < 0 ? 0 : max_len - 1;
+        if (status && threadIdx.x == 0 && blockIdx.x == 0) atomicOr(status, 4);
+    }
     if (lens_out && threadIdx.x == 0 && blockIdx.x == 0) lens_out[b] = pos + 1;   // rows attention covers after this append
     const __half *row = qkv + (size_t)b * (hq + 2 * hkv) * d;
     const float *cr = cos_t + (size_t)pos * half, *sr = sin_t + (size_t)pos * half;
@@ -318,12 +331,12 @@ rope_kv_append_kernel(const __half *__restrict__ qkv, const float *__restrict__ 
                 __half *o = q_out + ((size_t)b * hq + h) * d;
                 o[p] = lo;
                 o[p + half] = hi;
-            } else {
+            } else if (in_range) {
                 __half *o = kc + (((size_t)b * hkv + (h - hq)) * max_len + pos) * d;
                 o[p] = lo;
                 o[p + half] = hi;
             }
-        } else {
+        } else if (in_range) {
             const int j = i - rot_pairs;            // pair index inside the v block
             const int h = j / half, p = (j - h * half) * 2;
             const __half2 v = *reinterpret_cast<const __half2 *>(row + (hq + hkv + h) * d + p);
@@ -342,7 +355,7 @@ int rope_kv_append_lens_launch(const __half *qkv, const float *cos_t, const floa
     if (batch == 0) return 0;
     const int items = (hq + 2 * hkv) * (d / 2);
     launch_kernel(rope_kv_append_kernel, dim3(ceil_div(items, 256), batch), dim3(256), 0, st, qkv, cos_t, sin_t, positions, q_out, kc, vc,
-                  lens_out, hq, hkv, d, max_len);
+                  lens_out, hq, hkv, d, max_len, status_word());
     return launch_status("rope_kv_append_hm_f16");
 }
 
@@ -458,7 +471,7 @@ static int kv_append_launch(const char *name, const T *nk, const T *nv, T *kc, T
     long blocks = (total + 255) / 256;
     const long cap = (long)sm_count() * 16;
     if (blocks > cap) blocks = cap;
-    kv_append_kernel<T, HM><<<(int)blocks, 256, 0, st>>>(nk, nv, kc, vc, idx, heads, d, max_len, total);
+    kv_append_kernel<T, HM><<<(int)blocks, 256, 0, st>>>(nk, nv, kc, vc, idx, heads, d, max_len, total, HM ? status_word() : nullptr);
     return launch_status(name);
 }
 extern "C" int kv_cache_append_f32(const float *new_keys, const float *new_values, float *k_cache, float *v_cache,

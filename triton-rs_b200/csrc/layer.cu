@@ -180,8 +180,7 @@ extern "C" int b200k_layer_create(const b200k_layer_config *config, b200k_layer 
         // Pre-permuted GEMM inputs: GPTQ weights and extents the tensor-core GEMM family covers for all four projections
         // (K a multiple of 64, group a power of two >= 64, N a multiple of 32).  B200K_LAYER_KPERM=0 turns it off.
         const int g = c.group_size, qd = c.num_q_heads * c.head_dim, nq = (c.num_q_heads + 2 * c.num_kv_heads) * c.head_dim;
-        const char *e = getenv("B200K_LAYER_KPERM");
-        L->kperm = c.weight_format == 0 && !(e && e[0] == '0') && g >= 64 && (g & (g - 1)) == 0 && c.hidden % 64 == 0 &&
+        L->kperm = c.weight_format == 0 && env_char("B200K_LAYER_KPERM") != '0' && g >= 64 && (g & (g - 1)) == 0 && c.hidden % 64 == 0 &&
                    qd % 64 == 0 && c.intermediate % 64 == 0 && c.hidden % 32 == 0 && nq % 32 == 0 && (2 * c.intermediate) % 32 == 0;
     }
     *out_layer = L;
@@ -349,4 +348,12 @@ extern "C" int b200k_device_status(int *host_status_out, b200k_stream stream) {
     if (e == cudaSuccess) e = cudaStreamSynchronize(to_stream(stream));
     if (e != cudaSuccess) return fail((int)e, "b200k_device_status: %s", cudaGetErrorString(e));
     return 0;
+}
+
+extern "C" int b200k_device_clear_status(b200k_stream stream) {
+    void *ws = nullptr;
+    size_t bytes = 0;
+    int rc = default_workspace(&ws, &bytes);
+    if (rc) return rc;
+    return b200k_workspace_clear_status(ws, stream);
 }

@@ -289,7 +289,7 @@ static int moe_run(const char *name, const b200k_half *x, const float *router_lo
     g.s_am = hidden; g.s_qwk = g.n; g.s_sk = g.n; g.s_qzk = g.n / 8; g.s_cm = g.n;
     g.zero_offset = w13_qzeros ? 1 : 0;
     rc = gemm_tc_launch(g);
-    if (rc) return rc == 1 ? fail(B200K_E_SHAPE, "%s: expert GEMM shape not covered by the tensor-core path", name) : rc;
+    if (rc) return rc == TC_NOT_COVERED ? fail(B200K_E_SHAPE, "%s: expert GEMM shape not covered by the tensor-core path", name) : rc;
     moe_silu_mul_kernel<<<grid_for((long)pairs * intermediate / 8), 256, 0, st>>>(w.gu, w.act, nrows, intermediate);
     if ((rc = launch_status(name))) return rc;
     // down-projection: [pairs, I] x W2_e [I, H] -> [pairs, H]
@@ -298,7 +298,7 @@ static int moe_run(const char *name, const b200k_half *x, const float *router_lo
     g.s_am = intermediate; g.s_qwk = g.n; g.s_sk = g.n; g.s_qzk = g.n / 8; g.s_cm = g.n;
     g.zero_offset = w2_qzeros ? 1 : 0;
     rc = gemm_tc_launch(g);
-    if (rc) return rc == 1 ? fail(B200K_E_SHAPE, "%s: expert GEMM shape not covered by the tensor-core path", name) : rc;
+    if (rc) return rc == TC_NOT_COVERED ? fail(B200K_E_SHAPE, "%s: expert GEMM shape not covered by the tensor-core path", name) : rc;
     moe_combine_kernel<<<grid_for((long)num_tokens * hidden / 8), 256, 0, st>>>(w.yp, w.inv, w.wts, nrows, (__half *)out,
                                                                                 num_tokens, hidden, top_k);
     return launch_status(name);

@@ -1,9 +1,11 @@
 // Status reporting, device probing and the per-device default workspace.
 #include <stdarg.h>
 
+#include <atomic>
 #include <mutex>
 
 #include <stdlib.h>
+#include <string.h>
 
 #include "common.cuh"
 #include "tma.cuh"
@@ -32,27 +34,64 @@ static std::mutex g_mu;
 static void *g_ws[kMaxDev];
 static size_t g_ws_bytes[kMaxDev];
 static bool g_ws_owned[kMaxDev];
-static int g_sms[kMaxDev];
+static std::atomic<int> g_sms[kMaxDev];
 
-bool pdl_enabled() {
-    static int on = -1;
-    if (on < 0) {
-        const char *e = getenv("B200K_PDL");
-        on = (e && e[0] == '0') ? 0 : 1;
+// Environment overrides are read once per process and kept: at most 32 distinct names, looked up under a mutex
+// the first time and lock-free afterwards (entries are published with release stores and never change).
+namespace {
+struct EnvEntry {
+    std::atomic<const char *> name{nullptr};
+    int value = 0;
+    int first_char = 0;
+    bool set = false;
+};
+EnvEntry g_env[32];
+std::mutex g_env_mu;
+const EnvEntry *env_lookup(const char *name) {
+    for (auto &e : g_env) {
+        const char *n = e.name.load(std::memory_order_acquire);
+        if (!n) break;
+        if (n == name || !strcmp(n, name)) return &e;
     }
-    return on == 1;
+    std::lock_guard<std::mutex> lk(g_env_mu);
+    for (auto &e : g_env) {
+        const char *n = e.name.load(std::memory_order_relaxed);
+        if (n && !strcmp(n, name)) return &e;
+        if (!n) {
+            const char *v = getenv(name);
+            e.set = v && v[0];
+            e.value = e.set ? atoi(v) : 0;
+            e.first_char = e.set ? (unsigned char)v[0] : 0;
+            e.name.store(name, std::memory_order_release);   // callers pass string literals
+            return &e;
+        }
+    }
+    return nullptr;   // table full: treated as unset
 }
+}  // namespace
+
+int env_int(const char *name, int dflt) {
+    const EnvEntry *e = env_lookup(name);
+    return e && e->set ? e->value : dflt;
+}
+int env_char(const char *name) {
+    const EnvEntry *e = env_lookup(name);
+    return e && e->set ? e->first_char : 0;
+}
+
+bool pdl_enabled() { return env_char("B200K_PDL") != '0'; }
 
 int sm_count() {
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= kMaxDev) return 148;
-    if (g_sms[dev] == 0) {
-        int n = 0;
+    int n = g_sms[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
         cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-        g_sms[dev] = n > 0 ? n : 148;
+        n = n > 0 ? n : 148;
+        g_sms[dev].store(n, std::memory_order_relaxed);
     }
-    return g_sms[dev];
+    return n;
 }
 
 int default_workspace(void **ptr, size_t *bytes) {
@@ -80,14 +119,21 @@ int default_workspace(void **ptr, size_t *bytes) {
     return 0;
 }
 
+int *status_word() {
+    void *ws = nullptr;
+    size_t bytes = 0;
+    return default_workspace(&ws, &bytes) == 0 ? (int *)ws : nullptr;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 int make_tensor_map(CUtensorMap *map, CUtensorMapDataType dtype, int rank, const void *base, const uint64_t *dims,
                     const uint64_t *strides_bytes, const uint32_t *box, CUtensorMapSwizzle swizzle) {
-    static EncodeTiledFn encode = nullptr;
-    if (!encode) {
+    static std::atomic<EncodeTiledFn> encode_fn{nullptr};
+    EncodeTiledFn encode = encode_fn.load(std::memory_order_acquire);
+    if (!encode) {   // several threads may look it up at once: they all store the same pointer
         void *fn = nullptr;
         cudaDriverEntryPointQueryResult qres;
         cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
@@ -96,6 +142,7 @@ int make_tensor_map(CUtensorMap *map, CUtensorMapDataType dtype, int rank, const
             return fail(B200K_E_DEVICE, "cuTensorMapEncodeTiled is not available from the driver");
         }
         encode = (EncodeTiledFn)fn;
+        encode_fn.store(encode, std::memory_order_release);
     }
     cuuint64_t gdim[5], gstr[4];
     cuuint32_t bdim[5], estr[5];
@@ -149,5 +196,20 @@ extern "C" int b200k_set_workspace(void *workspace, size_t bytes) {
     g_ws[dev] = workspace;
     g_ws_bytes[dev] = bytes;
     g_ws_owned[dev] = false;
+    return 0;
+}
+
+extern "C" int b200k_workspace_status(const void *workspace, int *host_status_out, b200k_stream stream) {
+    B200K_REQUIRE(workspace && host_status_out, B200K_E_NULL, "b200k_workspace_status: NULL pointer");
+    cudaError_t e = cudaMemcpyAsync(host_status_out, workspace, sizeof(int), cudaMemcpyDeviceToHost, to_stream(stream));
+    if (e == cudaSuccess) e = cudaStreamSynchronize(to_stream(stream));
+    if (e != cudaSuccess) return fail((int)e, "b200k_workspace_status: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+extern "C" int b200k_workspace_clear_status(void *workspace, b200k_stream stream) {
+    B200K_REQUIRE(workspace, B200K_E_NULL, "b200k_workspace_clear_status: NULL pointer");
+    cudaError_t e = cudaMemsetAsync(workspace, 0, sizeof(int), to_stream(stream));
+    if (e != cudaSuccess) return fail((int)e, "b200k_workspace_clear_status: %s", cudaGetErrorString(e));
     return 0;
 }
