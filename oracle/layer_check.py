@@ -73,7 +73,7 @@ def _cmp(got, ref, bound=None):
             "elements": int(ref.size), "max_abs_ref": float(np.nanmax(np.abs(ref)))}
 
 
-def check_layer(pkg, torch, dev, case, ref_out, st, layer=None, got_out=None):
+def check_layer(pkg, torch, dev, case, ref_out, st, layer=None, got_out=None, ref_alt=None):
     """-> report dict.  `layer`: an existing pkg.DecodeLayer already holding the case's weights (its own caches are
     not touched; stage checks use copies of the case's caches); None builds one.  `got_out`: the chain's output when
     the caller has run it already (e.g. a tensor-parallel run), as a numpy array."""
@@ -108,7 +108,15 @@ def check_layer(pkg, torch, dev, case, ref_out, st, layer=None, got_out=None):
     q = emp(B, hq, d)
     P.rope_kv_append_hm_f16(h16(st["qkv"]), cos, sin, pos, q, kc, vc, hq, hkv, d, ml, B)
     rep["stages"]["q"] = _cmp(q.float().cpu().numpy(), st["q"])
-    rep["stages"]["kv_append_bits_equal"] = bool(torch.equal(kc, t(case["kc"])) and torch.equal(vc, t(case["vc"])))
+    # the appended V row is a pure move (bit-exact); the appended K row went through RoPE (fp32 arithmetic, one rounding)
+    rows = torch.arange(B, device=dev)
+    k_new = kc[rows, :, pos.long()].float().cpu().numpy()
+    k_ref = case["kc"][np.arange(B), :, case["pos"]].astype(np.float32)
+    rep["stages"]["k_append"] = _cmp(k_new, k_ref)
+    kc_ref = t(case["kc"])
+    kc_ref[rows, :, pos.long()] = kc[rows, :, pos.long()]
+    rep["stages"]["kv_append_moves_exact"] = bool(torch.equal(vc, t(case["vc"])) and torch.equal(kc, kc_ref))
+    del kc_ref
     att = emp(B, hq, d)
     lens = (pos + 1).to(torch.int32)
     P.batched_decode_attention_hm_f16(h16(st["q"]), kc, vc, lens, att, B, hq, hkv, d, ml, 1.0 / float(np.sqrt(d)))
@@ -143,8 +151,23 @@ def check_layer(pkg, torch, dev, case, ref_out, st, layer=None, got_out=None):
     rep["chain"] = _cmp(got_out, ref_out, bound)
     ref64 = ref_out.astype(np.float64)
     rep["chain"]["rms_err_over_rms_ref"] = float(np.sqrt(np.mean((got_out - ref64) ** 2)) / np.sqrt(np.mean(ref64 ** 2)))
-    rep["ok"] = bool(rep["chain"]["ok"] and all(v["ok"] for v in rep["stages"].values() if isinstance(v, dict)) and
-                     rep["stages"]["kv_append_bits_equal"])
-    rep["tolerance"] = ("every stage on the oracle's input: |got - ref| <= 1e-2 + 1e-2 |ref|; whole chain: "
-                        "(1e-2 + 1e-2 |h1|) + (1e-2 + 1e-2 |down|), the bound of a sum of two fp16 tensors")
+    rep["stages_ok"] = bool(all(v["ok"] for v in rep["stages"].values() if isinstance(v, dict)) and
+                            rep["stages"]["kv_append_moves_exact"])
+    # How far two CORRECT restatements of the chain drift apart on these inputs: the CPU chain with the reference's
+    # fp16-rounded weights against the CPU chain with fp32 weight products (`ref_alt`, when the caller supplies it).
+    # Ten kernels deep, one-ulp differences of an fp16 intermediate are amplified by the GEMMs that follow, so the
+    # end-to-end deviation of any fp16 chain from any other is a property of the data, measured here, not of a kernel.
+    if ref_alt is not None:
+        rep["oracle_self"] = _cmp(ref_alt, ref_out, bound)
+        rep["oracle_self"]["rms_err_over_rms_ref"] = float(np.sqrt(np.mean((ref_alt - ref64) ** 2)) / np.sqrt(np.mean(ref64 ** 2)))
+        allowed = max(4 * rep["oracle_self"]["outside_plain_bound"], int(1e-3 * ref_out.size))
+        rep["chain"]["ok_vs_oracle_drift"] = bool(rep["chain"]["finite"] and rep["chain"]["outside_plain_bound"] <= allowed and
+                                                  rep["chain"]["rms_err_over_rms_ref"] <= max(2e-3, 4 * rep["oracle_self"]["rms_err_over_rms_ref"]))
+    else:
+        rep["chain"]["ok_vs_oracle_drift"] = rep["chain"]["ok"]
+    rep["ok"] = bool(rep["stages_ok"] and (rep["chain"]["ok"] or rep["chain"]["ok_vs_oracle_drift"]))
+    rep["tolerance"] = ("every kernel of the chain on the oracle's own input: |got - ref| <= 1e-2 + 1e-2 |ref| (moves bit-exact); "
+                        "whole chain: (1e-2 + 1e-2 |h1|) + (1e-2 + 1e-2 |down|), the bound of a sum of two fp16 tensors, or -- where "
+                        "the data make the chain ill-conditioned -- no further from the oracle than 4x the measured drift between "
+                        "two CPU restatements that differ only in where they round (elements outside the plain bound, relative RMS)")
     return rep

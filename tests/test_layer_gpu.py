@@ -86,11 +86,14 @@ def test_layer_small_vs_numpy_oracle(pkg, oracle, use_graph, sym):
     layer.close()
 
 
-@pytest.mark.parametrize("zero_mean", [True, False])
-def test_layer_llama_shape_vs_c_oracle(pkg, oracle, zero_mean):
+def test_layer_llama_shape_vs_c_oracle(pkg, oracle):
     """BASELINE config 4 extents with a short context (the C oracle handles it in seconds): every kernel of the
-    chain on the oracle's own input at 1e-2 / 1e-2, and the whole chain end to end.  zero_mean=False is the
-    benchmark's own weight distribution (nibbles uniform 0..15 around the zero-point 8)."""
+    chain on the oracle's own input at 1e-2 / 1e-2, and the whole chain end to end.  Weights are zero-mean here
+    (nibbles 1..15 around the zero-point 8): with the benchmark's own distribution (nibbles 0..15, mean 7.5) the
+    14336-deep down projection amplifies the DC component and, for some seeds, the fp16 chain -- the CPU restatement
+    included -- overflows to infinity, which leaves nothing to compare.  The benchmark's parity gate runs that
+    distribution on the tensors it times (finite there)."""
+    zero_mean = True
     import layer_check
     rng = np.random.default_rng(4)
     B, H, hq, hkv, d, I, G, ml = 8, 4096, 32, 8, 128, 14336, 128, 300
@@ -99,7 +102,12 @@ def test_layer_llama_shape_vs_c_oracle(pkg, oracle, zero_mean):
                 qkv=p["qkv"], o=p["o"], gate_up=p["gate_up"], down=p["down"],
                 kc=rng.standard_normal((B, hkv, ml, d)).astype(np.float16), vc=rng.standard_normal((B, hkv, ml, d)).astype(np.float16),
                 hidden=rng.standard_normal((B, H)).astype(np.float16), pos=rng.integers(100, ml - 1, B).astype(np.int32))
-    ref, st, _ = layer_check.oracle_layer(layer_check.load_oracle_c(), case)
+    oc = layer_check.load_oracle_c()
+    # the fp32-weight restatement runs first: both append the row at pos[b], and the caches must end up holding the
+    # rows of the reference-faithful run, which is the one the kernels are compared with
+    ref_alt = layer_check.oracle_layer(oc, case, faithful=0, want_stages=False)[0]
+    ref, st, _ = layer_check.oracle_layer(oc, case)
     assert np.isfinite(ref).all()
-    rep = layer_check.check_layer(pkg, torch, DEV, case, ref, st)
+    rep = layer_check.check_layer(pkg, torch, DEV, case, ref, st, ref_alt=ref_alt)
+    assert rep["stages_ok"], rep
     assert rep["ok"], rep
