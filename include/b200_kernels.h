@@ -565,6 +565,20 @@ int b200k_comm_open_peers(struct b200k_comm *comm, const void *host_all_handles)
 int b200k_comm_slot(struct b200k_comm *comm, int slot, b200k_half **host_out_ptr);
 int b200k_comm_allreduce_f16(struct b200k_comm *comm, int slot, const b200k_half *input, b200k_half *output,
                              size_t count, b200k_stream stream);
+/* The all-reduce fused with the step that consumes it in a tensor-parallel layer (same protocol, same slot rules):
+ *   _add_f16           output = addend + fp16(sum over ranks)              (the closing residual add)
+ *   _add_rms_norm_f16  r = residual + fp16(sum over ranks); residual_out = fp16(r);
+ *                      output = rms_norm(r) from the unrounded r: the arithmetic of fused_add_rms_norm_f16
+ *                      (crates/triton-kernels/src/norms.rs:189-220) on the reduced tensor; one CTA per row,
+ *                      hidden_size a multiple of 8 up to 32768.
+ * Bit-identical to the plain all-reduce followed by residual_add_f16 / fused_add_rms_norm_f16. */
+int b200k_comm_allreduce_add_f16(struct b200k_comm *comm, int slot, const b200k_half *input,
+                                 const b200k_half *addend, b200k_half *output, size_t count,
+                                 b200k_stream stream);
+int b200k_comm_allreduce_add_rms_norm_f16(struct b200k_comm *comm, int slot, const b200k_half *input,
+                                          const b200k_half *residual, const b200k_half *weight,
+                                          b200k_half *output, b200k_half *residual_out, int hidden_size,
+                                          float inv_n, float eps, int num_rows, b200k_stream stream);
 int b200k_comm_status(struct b200k_comm *comm, int *host_status_out, b200k_stream stream);
 int b200k_comm_clear_status(struct b200k_comm *comm, b200k_stream stream);
 /* How long a kernel waits for its peers, in SM clock cycles (default 2e9, about a second; <= 0 restores it). */
@@ -576,7 +590,8 @@ int b200k_comm_buffer(struct b200k_comm *comm, void **host_out_ptr);
 int b200k_comm_set_peer_pointer(struct b200k_comm *comm, int peer_rank, void *peer_buffer);
 void b200k_comm_destroy(struct b200k_comm *comm);
 /* Attach to a layer: the o and down GEMMs then write into slots 0 and 1 and the layer chain runs the
- * two all-reduces itself (12 launches).  NULL detaches (single GPU). */
+ * two all-reduces itself, each fused with the step that consumes it (10 launches, as on one GPU).
+ * NULL detaches (single GPU). */
 int b200k_layer_set_comm(b200k_layer *layer, struct b200k_comm *comm);
 
 /* Whole layer on device buffers: hidden_in/out [batch, H] fp16, positions [batch] int32

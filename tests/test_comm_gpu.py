@@ -34,6 +34,25 @@ def test_allreduce_single_rank(pkg):
         torch.cuda.synchronize()
         assert torch.equal(out, x)
     assert comm.status() == 0
+    # the fused forms give the bits of the plain all-reduce followed by the separate kernel
+    L, st = pkg.lib(), torch.cuda.current_stream().cuda_stream
+    rows, h = 4, 1024
+    part = torch.randn(rows * h, device=dev, dtype=torch.float16)
+    res = torch.randn(rows * h, device=dev, dtype=torch.float16)
+    w = (torch.rand(h, device=dev) + 0.5).half()
+    red = torch.empty_like(part)
+    comm.all_reduce(1, red, rows * h, input=part)
+    want = torch.empty_like(part)
+    pkg.prelude.residual_add_f16(res, red, want, rows * h)
+    got = torch.empty_like(part)
+    L.call("b200k_comm_allreduce_add_f16", comm.handle, 0, part, res, got, rows * h, st)
+    assert torch.equal(got, want)
+    y0, r0, y1, r1 = (torch.empty_like(part) for _ in range(4))
+    pkg.prelude.fused_add_rms_norm_f16(red, res, w, y0, r0, h, 1.0 / h, 1e-5, rows)
+    L.call("b200k_comm_allreduce_add_rms_norm_f16", comm.handle, 1, part, res, w, y1, r1, h, 1.0 / h, 1e-5, rows, st)
+    torch.cuda.synchronize()
+    assert torch.equal(r1, r0) and torch.equal(y1, y0)
+    assert comm.status() == 0
     with pytest.raises(pkg.B200KError):
         comm.all_reduce(0, torch.zeros(n + 512, device=dev, dtype=torch.float16), n + 512, input=None)   # larger than a slot
     with pytest.raises(pkg.B200KError):
@@ -88,7 +107,7 @@ def _rank_main(rank, world, port, q):
                                 use_graph=True, k_cache=t(kc[:, rank * per:(rank + 1) * per]),
                                 v_cache=t(vc[:, rank * per:(rank + 1) * per]))
         layer.set_comm(comm)
-        assert layer.launches_per_forward == 12
+        assert layer.launches_per_forward == 10      # the two all-reduces are fused with the steps that consume them
         for step, pos in enumerate([[5, 0, 38], [6, 1, 39], [7, 2, 3]]):     # later steps replay the captured graph
             pos = np.array(pos, dtype=np.int32)
             hidden = rng.standard_normal((B, H)).astype(np.float16)

@@ -36,23 +36,22 @@ constexpr long long COMM_DEFAULT_WAIT_CYCLES = 2000000000LL;   // about a second
 __device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ __half2 u2h(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
+__device__ __forceinline__ uint32_t h22(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
     unsigned v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
 
-__global__ void __launch_bounds__(512)
-allreduce_oneshot_kernel(unsigned char *const *__restrict__ peers, int rank, int world, int slot, size_t slot_bytes,
-                         __half *__restrict__ out, size_t count, long long wait_cycles) {
-    pdl_wait();                 // the partial sums in my slot come from the kernel before
-    pdl_launch_dependents();
-    unsigned char *mine = peers[rank];
-    unsigned *my_flags = reinterpret_cast<unsigned *>(mine);
-    unsigned *seq_p = my_flags + 16, *done_p = my_flags + 17, *status_p = my_flags + 18;
-    __shared__ int s_fail;
-    const unsigned seq = *reinterpret_cast<volatile unsigned *>(seq_p) + 1;   // advanced by the last CTA to finish
-    if (threadIdx.x == 0) s_fail = 0;
+// Entry protocol shared by the all-reduce kernels: publish "my slot holds round `seq`" to every peer (CTA 0), wait --
+// bounded -- until every peer has published the same round.  Returns false when a peer never arrived (status word set).
+__device__ __forceinline__ bool exchange_enter(unsigned char *const *peers, int rank, int world, long long wait_cycles,
+                                               unsigned &seq, int *s_fail) {
+    unsigned *my_flags = reinterpret_cast<unsigned *>(peers[rank]);
+    unsigned *seq_p = my_flags + 16, *status_p = my_flags + 18;
+    seq = *reinterpret_cast<volatile unsigned *>(seq_p) + 1;   // advanced by the last CTA of the round before
+    if (threadIdx.x == 0) *s_fail = 0;
     __syncthreads();
     if (blockIdx.x == 0 && threadIdx.x < world) {
         __threadfence_system();   // the GEMM that filled my slot ran earlier on this stream
@@ -62,34 +61,24 @@ allreduce_oneshot_kernel(unsigned char *const *__restrict__ peers, int rank, int
         const long long t0 = clock64();
         while ((int)(ld_acquire_sys(my_flags + threadIdx.x) - seq) < 0) {
             if (clock64() - t0 > wait_cycles) {   // a peer never arrived: report, do not spin for ever
-                s_fail = 1;
+                *s_fail = 1;
                 atomicExch(status_p, 1u);
                 break;
             }
         }
     }
     __syncthreads();
-    if (!s_fail) {
-        const size_t nvec = count / 8;                          // 16-byte chunks
-        const size_t off = COMM_FLAGS_BYTES + (size_t)slot * slot_bytes;
-        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int r = 0; r < world; ++r) {
-                const uint4 v = reinterpret_cast<const uint4 *>(peers[r] + off)[i];
-                const float2 a = h2_to_f2(v.x), b = h2_to_f2(v.y), c = h2_to_f2(v.z), d = h2_to_f2(v.w);
-                acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
-                acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
-            }
-            uint4 o;
-            o.x = f2_to_h2(acc[0], acc[1]); o.y = f2_to_h2(acc[2], acc[3]);
-            o.z = f2_to_h2(acc[4], acc[5]); o.w = f2_to_h2(acc[6], acc[7]);
-            reinterpret_cast<uint4 *>(out)[i] = o;
-        }
-    }
+    return *s_fail == 0;
+}
+// Exit protocol: the last CTA of the grid to get here advances the round counter (kept in device memory, so a CUDA
+// graph that contains the call can be replayed).
+__device__ __forceinline__ void exchange_leave(unsigned char *const *peers, int rank, unsigned seq) {
+    unsigned *my_flags = reinterpret_cast<unsigned *>(peers[rank]);
+    unsigned *seq_p = my_flags + 16, *done_p = my_flags + 17;
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
-        if (atomicAdd(done_p, 1u) == gridDim.x - 1) {   // last CTA of this call
+        if (atomicAdd(done_p, 1u) == gridDim.x - 1) {
             *done_p = 0;
             __threadfence();
             *reinterpret_cast<volatile unsigned *>(seq_p) = seq;
@@ -97,7 +86,142 @@ allreduce_oneshot_kernel(unsigned char *const *__restrict__ peers, int rank, int
     }
 }
 
+// Sum over the ranks, in rank order, of 8 fp16 values at byte offset `off` of every rank's buffer: fp32 accumulate.
+__device__ __forceinline__ void peer_sum8(unsigned char *const *peers, int world, size_t off, float (&acc)[8]) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int r = 0; r < world; ++r) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(peers[r] + off);
+        const float2 a = h2_to_f2(v.x), b = h2_to_f2(v.y), c = h2_to_f2(v.z), d = h2_to_f2(v.w);
+        acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+        acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+    }
+}
+
+// out = all-reduce(slot)                         (addend == nullptr)
+// out = addend + fp16(all-reduce(slot))          (the closing residual add of a layer, fused: the sum is rounded to
+//                                                 fp16 first, as a separate all-reduce would have stored it)
+__global__ void __launch_bounds__(512)
+allreduce_oneshot_kernel(unsigned char *const *__restrict__ peers, int rank, int world, int slot, size_t slot_bytes,
+                         const __half *__restrict__ addend, __half *__restrict__ out, size_t count, long long wait_cycles) {
+    pdl_wait();                 // the partial sums in my slot come from the kernel before
+    pdl_launch_dependents();
+    __shared__ int s_fail;
+    unsigned seq;
+    if (exchange_enter(peers, rank, world, wait_cycles, seq, &s_fail)) {
+        const size_t nvec = count / 8;                          // 16-byte chunks
+        const size_t off = COMM_FLAGS_BYTES + (size_t)slot * slot_bytes;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+            float acc[8];
+            peer_sum8(peers, world, off + i * 16, acc);
+            uint4 o;
+            o.x = f2_to_h2(acc[0], acc[1]); o.y = f2_to_h2(acc[2], acc[3]);
+            o.z = f2_to_h2(acc[4], acc[5]); o.w = f2_to_h2(acc[6], acc[7]);
+            if (addend) {
+                const uint4 h = reinterpret_cast<const uint4 *>(addend)[i];
+                o.x = h22(__hadd2(u2h(h.x), u2h(o.x))); o.y = h22(__hadd2(u2h(h.y), u2h(o.y)));
+                o.z = h22(__hadd2(u2h(h.z), u2h(o.z))); o.w = h22(__hadd2(u2h(h.w), u2h(o.w)));
+            }
+            reinterpret_cast<uint4 *>(out)[i] = o;
+        }
+    }
+    exchange_leave(peers, rank, seq);
+}
+
+// all-reduce(slot) + residual add + rms_norm in one pass, one CTA per row of n values (the step after o_proj of a
+// tensor-parallel layer): r = residual + fp16(sum over ranks); residual_out = fp16(r); y = r * rsqrt(mean(r^2) + eps) * w
+// from the unrounded fp32 r, the arithmetic of fused_add_rms_norm_f16.  KPERM stores every 8 outputs of y as
+// (0,4,1,5,2,6,3,7), the order the int4 GEMM that follows consumes.
+template <bool KPERM>
+__global__ void __launch_bounds__(1024)
+allreduce_add_rmsnorm_kernel(unsigned char *const *__restrict__ peers, int rank, int world, int slot, size_t slot_bytes,
+                             const __half *__restrict__ residual, const __half *__restrict__ w, __half *__restrict__ y,
+                             __half *__restrict__ res_out, int n, float inv_n, float eps, long long wait_cycles) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ int s_fail;
+    __shared__ float red[32];
+    unsigned seq;
+    if (exchange_enter(peers, rank, world, wait_cycles, seq, &s_fail)) {
+        constexpr int ITERS = 4;
+        const int nv = n / 8;
+        const size_t row = (size_t)blockIdx.x * n;
+        const size_t off = COMM_FLAGS_BYTES + (size_t)slot * slot_bytes + row * 2;
+        float v[ITERS][8];
+        float ss = 0.f;
+#pragma unroll
+        for (int it = 0; it < ITERS; ++it) {
+            const int i = threadIdx.x + it * blockDim.x;
+            if (i < nv) {
+                float acc[8];
+                peer_sum8(peers, world, off + (size_t)i * 16, acc);
+                const uint4 h = *reinterpret_cast<const uint4 *>(residual + row + (size_t)i * 8);
+                const float2 a = h2_to_f2(h.x), b = h2_to_f2(h.y), c = h2_to_f2(h.z), d = h2_to_f2(h.w);
+                const float x[8] = {a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    v[it][j] = x[j] + __half2float(__float2half_rn(acc[j]));   // the reduced value is an fp16 tensor
+                    ss += v[it][j] * v[it][j];
+                }
+                uint4 o;
+                o.x = f2_to_h2(v[it][0], v[it][1]); o.y = f2_to_h2(v[it][2], v[it][3]);
+                o.z = f2_to_h2(v[it][4], v[it][5]); o.w = f2_to_h2(v[it][6], v[it][7]);
+                *reinterpret_cast<uint4 *>(res_out + row + (size_t)i * 8) = o;
+            }
+        }
+        const float inv = rsqrtf(block_sum(ss, red) * inv_n + eps);
+#pragma unroll
+        for (int it = 0; it < ITERS; ++it) {
+            const int i = threadIdx.x + it * blockDim.x;
+            if (i < nv) {
+                const uint4 wv = *reinterpret_cast<const uint4 *>(w + (size_t)i * 8);
+                const float2 a = h2_to_f2(wv.x), b = h2_to_f2(wv.y), c = h2_to_f2(wv.z), d = h2_to_f2(wv.w);
+                const float ww[8] = {a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y};
+                float o[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = v[it][j] * inv * ww[j];
+                uint4 u;
+                if (KPERM) {
+                    u.x = f2_to_h2(o[0], o[4]); u.y = f2_to_h2(o[1], o[5]); u.z = f2_to_h2(o[2], o[6]); u.w = f2_to_h2(o[3], o[7]);
+                } else {
+                    u.x = f2_to_h2(o[0], o[1]); u.y = f2_to_h2(o[2], o[3]); u.z = f2_to_h2(o[4], o[5]); u.w = f2_to_h2(o[6], o[7]);
+                }
+                *reinterpret_cast<uint4 *>(y + row + (size_t)i * 8) = u;
+            }
+        }
+    }
+    exchange_leave(peers, rank, seq);
+}
+
+int comm_allreduce_add_f16(struct ::b200k_comm *c, int slot, const __half *addend, __half *out, size_t count, cudaStream_t st);
 int comm_allreduce_f16(struct ::b200k_comm *c, int slot, __half *out, size_t count, cudaStream_t st) {
+    return comm_allreduce_add_f16(c, slot, nullptr, out, count, st);
+}
+
+int comm_allreduce_add_rmsnorm_f16(struct ::b200k_comm *c, int slot, const __half *residual, const __half *w, __half *y,
+                                   __half *res_out, int n, float inv_n, float eps, int rows, bool kperm, cudaStream_t st) {
+    B200K_REQUIRE(c && residual && w && y && res_out, B200K_E_NULL, "all-reduce + add + rms_norm: NULL pointer");
+    B200K_REQUIRE(slot == 0 || slot == 1, B200K_E_SHAPE, "all-reduce + add + rms_norm: slot %d", slot);
+    B200K_REQUIRE(n > 0 && n % 8 == 0 && n / 8 <= 4096 && rows >= 0 && (size_t)rows * n * 2 <= c->slot_bytes, B200K_E_SHAPE,
+                  "all-reduce + add + rms_norm: %d rows of %d (a multiple of 8, at most 32768) do not fit a slot of %zu bytes",
+                  rows, n, c->slot_bytes);
+    B200K_REQUIRE(aligned16(residual) && aligned16(w) && aligned16(y) && aligned16(res_out), B200K_E_ALIGN,
+                  "all-reduce + add + rms_norm: pointers must be 16-byte aligned");
+    for (int r = 0; r < c->world; ++r)
+        B200K_REQUIRE(c->peer[r], B200K_E_STATE, "all-reduce: peer %d is not mapped (b200k_comm_open_peers)", r);
+    if (rows == 0) return 0;
+    const int nv = n / 8;
+    const int threads = nv <= 128 ? 128 : (nv <= 256 ? 256 : (nv <= 512 ? 512 : 1024));
+    if (kperm)
+        launch_kernel(allreduce_add_rmsnorm_kernel<true>, dim3(rows), dim3(threads), 0, st, c->d_peers, c->rank, c->world, slot,
+                      c->slot_bytes, residual, w, y, res_out, n, inv_n, eps, c->wait_cycles);
+    else
+        launch_kernel(allreduce_add_rmsnorm_kernel<false>, dim3(rows), dim3(threads), 0, st, c->d_peers, c->rank, c->world, slot,
+                      c->slot_bytes, residual, w, y, res_out, n, inv_n, eps, c->wait_cycles);
+    return launch_status("all-reduce + add + rms_norm (peer to peer)");
+}
+
+int comm_allreduce_add_f16(struct ::b200k_comm *c, int slot, const __half *addend, __half *out, size_t count, cudaStream_t st) {
     B200K_REQUIRE(c && out, B200K_E_NULL, "all-reduce: NULL pointer");
     B200K_REQUIRE(slot == 0 || slot == 1, B200K_E_SHAPE, "all-reduce: slot %d", slot);
     B200K_REQUIRE(count % 8 == 0 && count * 2 <= c->slot_bytes, B200K_E_SHAPE,
@@ -107,7 +231,7 @@ int comm_allreduce_f16(struct ::b200k_comm *c, int slot, __half *out, size_t cou
     if (count == 0) return 0;
     int blocks = (int)((count / 8 + 511) / 512);
     if (blocks > 32) blocks = 32;
-    launch_kernel(allreduce_oneshot_kernel, dim3(blocks), dim3(512), 0, st, c->d_peers, c->rank, c->world, slot, c->slot_bytes, out, count, c->wait_cycles);
+    launch_kernel(allreduce_oneshot_kernel, dim3(blocks), dim3(512), 0, st, c->d_peers, c->rank, c->world, slot, c->slot_bytes, addend, out, count, c->wait_cycles);
     return launch_status("all-reduce (peer to peer)");
 }
 
@@ -221,6 +345,36 @@ extern "C" int b200k_comm_allreduce_f16(struct b200k_comm *comm, int slot, const
         if (e != cudaSuccess) return fail((int)e, "b200k_comm_allreduce_f16: %s", cudaGetErrorString(e));
     }
     return comm_allreduce_f16(comm, slot, (__half *)output, count, to_stream(stream));
+}
+
+static int stage_input(struct b200k_comm *comm, int slot, const b200k_half *input, size_t count, b200k_stream stream, const char *name) {
+    B200K_REQUIRE(comm, B200K_E_NULL, "%s: NULL pointer", name);
+    B200K_REQUIRE(slot == 0 || slot == 1, B200K_E_SHAPE, "%s: slot %d", name, slot);
+    B200K_REQUIRE(count * 2 <= comm->slot_bytes, B200K_E_SHAPE, "%s: %zu elements exceed the slot", name, count);
+    if (input) {
+        cudaError_t e = cudaMemcpyAsync(comm_slot(comm, slot), input, count * 2, cudaMemcpyDeviceToDevice, to_stream(stream));
+        if (e != cudaSuccess) return fail((int)e, "%s: %s", name, cudaGetErrorString(e));
+    }
+    return 0;
+}
+
+extern "C" int b200k_comm_allreduce_add_f16(struct b200k_comm *comm, int slot, const b200k_half *input, const b200k_half *addend,
+                                            b200k_half *output, size_t count, b200k_stream stream) {
+    B200K_REQUIRE(addend && output, B200K_E_NULL, "b200k_comm_allreduce_add_f16: NULL pointer");
+    int rc = stage_input(comm, slot, input, count, stream, "b200k_comm_allreduce_add_f16");
+    if (rc) return rc;
+    return comm_allreduce_add_f16(comm, slot, (const __half *)addend, (__half *)output, count, to_stream(stream));
+}
+
+extern "C" int b200k_comm_allreduce_add_rms_norm_f16(struct b200k_comm *comm, int slot, const b200k_half *input,
+                                                     const b200k_half *residual, const b200k_half *weight, b200k_half *output,
+                                                     b200k_half *residual_out, int hidden_size, float inv_n, float eps,
+                                                     int num_rows, b200k_stream stream) {
+    B200K_REQUIRE(hidden_size > 0 && num_rows >= 0, B200K_E_SHAPE, "b200k_comm_allreduce_add_rms_norm_f16: %d rows of %d", num_rows, hidden_size);
+    int rc = stage_input(comm, slot, input, (size_t)num_rows * hidden_size, stream, "b200k_comm_allreduce_add_rms_norm_f16");
+    if (rc) return rc;
+    return comm_allreduce_add_rmsnorm_f16(comm, slot, (const __half *)residual, (const __half *)weight, (__half *)output,
+                                          (__half *)residual_out, hidden_size, inv_n, eps, num_rows, false, to_stream(stream));
 }
 
 extern "C" int b200k_comm_slot(struct b200k_comm *comm, int slot, b200k_half **out_ptr) {

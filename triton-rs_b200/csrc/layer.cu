@@ -15,6 +15,9 @@ int rope_kv_append_lens_launch(const __half *qkv, const float *cos_t, const floa
                                int max_len, int batch, cudaStream_t st);
 // peer-to-peer all-reduce (comm.cu): the partial sums sit in slot `slot` of every rank's exchange buffer
 int comm_allreduce_f16(struct ::b200k_comm *comm, int slot, __half *out, size_t count, cudaStream_t st);
+int comm_allreduce_add_f16(struct ::b200k_comm *comm, int slot, const __half *addend, __half *out, size_t count, cudaStream_t st);
+int comm_allreduce_add_rmsnorm_f16(struct ::b200k_comm *comm, int slot, const __half *residual, const __half *w, __half *y,
+                                   __half *res_out, int n, float inv_n, float eps, int rows, bool kperm, cudaStream_t st);
 __half *comm_slot(struct ::b200k_comm *comm, int slot);
 size_t comm_slot_capacity(struct ::b200k_comm *comm);
 // producers that write their fp16 output with every 8 values stored as (0,4,1,5,2,6,3,7): the order the GPTQ
@@ -86,6 +89,17 @@ static int stage0(b200k_layer *L, const b200k_half *hidden, const int32_t *posit
     if (rc) return rc;
     return gemm(L, 1, L->att, o_out, b, H, hq * d, st);
 }
+// the MLP from the normed activations n2 up to the partial down output
+static int mlp(b200k_layer *L, b200k_half *dn_out, int b, b200k_stream st) {
+    const b200k_layer_config &c = L->cfg;
+    const int H = c.hidden, I = c.intermediate;
+    int rc;
+    if ((rc = gemm(L, 2, L->n2, L->gu, b, 2 * I, H, st))) return rc;
+    if (L->kperm) rc = silu_mul_interleaved_f16_kperm((const __half *)L->gu, (__half *)L->act, I, b * I, to_stream(st));
+    else rc = fused_silu_mul_interleaved_f16(L->gu, L->act, I, b * I, st);
+    if (rc) return rc;
+    return gemm(L, 3, L->act, dn_out, b, H, I, st);
+}
 // stage 1: reduced o + hidden -> h1, then the MLP up to the partial down output
 static int stage1(b200k_layer *L, const b200k_half *hidden, const b200k_half *o_red, b200k_half *dn_out, int b,
                   b200k_stream st) {
@@ -117,13 +131,17 @@ static int chain(b200k_layer *L, const b200k_half *hidden, const int32_t *positi
         if ((rc = stage1(L, hidden, L->o, L->dn, b, st))) return rc;
         return stage2(L, L->dn, out, b, st);
     }
-    // tensor parallel: the row-parallel GEMMs write their partial sums into the exchange buffer the
-    // peers can read; the all-reduce leaves the full sum in the local buffer the next stage reads
+    // tensor parallel: the row-parallel GEMMs write their partial sums into the exchange buffer the peers can read;
+    // each all-reduce is fused with the step that consumes it (residual add + rms_norm after o_proj, the closing
+    // residual add after down), so the reduced tensor never makes a round trip through memory: 10 launches
+    const b200k_layer_config &c = L->cfg;
     if ((rc = stage0(L, hidden, positions, (b200k_half *)comm_slot(L->comm, 0), b, st))) return rc;
-    if ((rc = comm_allreduce_f16(L->comm, 0, (__half *)L->o, count, to_stream(st)))) return rc;
-    if ((rc = stage1(L, hidden, L->o, (b200k_half *)comm_slot(L->comm, 1), b, st))) return rc;
-    if ((rc = comm_allreduce_f16(L->comm, 1, (__half *)L->dn, count, to_stream(st)))) return rc;
-    return stage2(L, L->dn, out, b, st);
+    if ((rc = comm_allreduce_add_rmsnorm_f16(L->comm, 0, (const __half *)hidden, (const __half *)L->ln2, (__half *)L->n2,
+                                             (__half *)L->h1, c.hidden, 1.0f / c.hidden, c.rms_eps, b, L->kperm, to_stream(st))))
+        return rc;
+    if ((rc = mlp(L, (b200k_half *)comm_slot(L->comm, 1), b, st))) return rc;
+    (void)count;
+    return comm_allreduce_add_f16(L->comm, 1, (const __half *)L->h1, (__half *)out, (size_t)b * c.hidden, to_stream(st));
 }
 
 static int check_ready(const b200k_layer *L, int batch, const char *name) {
@@ -234,7 +252,7 @@ extern "C" int b200k_layer_set_comm(b200k_layer *L, struct b200k_comm *comm) {
     return 0;
 }
 extern "C" int b200k_layer_launches_per_forward(const b200k_layer *L) {
-    return L ? L->launches + (L->comm ? 2 : 0) : 0;
+    return L ? L->launches : 0;      // tensor parallel: the two all-reduces replace the add + norm and the closing add
 }
 
 // The whole call as it would be issued eagerly: for host buffers the copies in and out around the chain.
