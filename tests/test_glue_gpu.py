@@ -203,3 +203,21 @@ def test_golden_glue(P):
     o = torch.empty((tok, heads, d), dtype=torch.float16, device=DEV)
     P.rope_full_f16(t(g["xr"]), t(g["cos"]), t(g["sin"]), t(g["pos"]), o, heads, d, tok)
     assert_close(o.float().cpu().numpy(), g["rope"], 2e-3, 2e-3)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+def test_rms_norm_at_the_reference_benchmark_size(P, oracle, dtype):
+    """32768 rows of 1024: the size the reference publishes its rms_norm timing at (bench_rms_norm.rs); short rows take
+    the warp-per-row kernel."""
+    rows, n = 32768, 1024
+    g = torch.Generator(device=DEV).manual_seed(9)
+    tdt = torch.float32 if dtype == np.float32 else torch.float16
+    x = torch.randn((rows, n), device=DEV, generator=g, dtype=tdt)
+    w = (torch.rand(n, device=DEV, generator=g) + 0.5).to(tdt)
+    y = torch.empty_like(x)
+    (P.rms_norm_f32 if dtype == np.float32 else P.rms_norm_f16)(x, w, y, n, 1.0 / n, 1e-6, rows)
+    sample = np.r_[0:64, rows - 64:rows]
+    ref = oracle.rms_norm(x[sample].cpu().numpy(), w.cpu().numpy(), 1e-6)
+    tol = (1e-4, 1e-4) if dtype == np.float32 else (1e-2, 1e-2)
+    assert_close(y[sample].float().cpu().numpy(), ref, *tol, "rms_norm 32768 x 1024")
+    assert torch.isfinite(y).all()

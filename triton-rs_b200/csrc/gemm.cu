@@ -523,7 +523,8 @@ using namespace b200k;
     g.s_am = stride_am; g.s_ak = stride_ak; g.s_qwk = stride_qwk; g.s_qwn = stride_qwn;               \
     g.s_sk = stride_sk; g.s_sn = stride_sn; g.s_cm = stride_cm; g.s_cn = stride_cn;                   \
     g.format = FMT; g.zero_offset = ZO; g.stream = to_stream(stream);                                 \
-    g.seg_offsets = nullptr; g.num_segments = 0; g.plan_out = nullptr; g.a_kperm = false;
+    g.seg_offsets = nullptr; g.num_segments = 0; g.plan_out = nullptr; g.a_kperm = false;                \
+    g.silu_inter = 0; g.tile_list = nullptr; g.tile_count = nullptr; g.max_tiles = 0;
 
 extern "C" int w4a16_gptq_gemm_f16_ws(const b200k_half *a, const int32_t *qweight, const b200k_half *scales,
                                       const int32_t *qzeros, b200k_half *c, int m_size, int n_size, int k_size,

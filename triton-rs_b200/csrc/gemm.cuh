@@ -22,6 +22,16 @@ struct GemmArgs {
     // [num_segments, K/8 (or K), ...] laid out contiguously; m = total rows.  nullptr: ordinary GEMM.
     const int *seg_offsets;
     int num_segments;
+    // fused silu_mul epilogue (tensor-core path, GPTQ): the weight holds 2 * silu_inter columns, gate columns first, up
+    // columns second (the half-split layout of fused_silu_mul_interleaved, elementwise.rs:199-206); c has silu_inter
+    // columns and receives silu(gate) * up.  n is then 2 * silu_inter.  0: plain GEMM.
+    int silu_inter;
+    // grouped mode only: compact list of (segment, first row) work items, one per token tile that holds rows, and their
+    // number (device memory, written by the kernel that builds the segments); max_tiles bounds the grid.  nullptr: one
+    // grid slice per segment and token tile of the worst case.
+    const int2 *tile_list;
+    const int *tile_count;
+    int max_tiles;
     bool a_kperm;     // activations pre-permuted per 8 consecutive k to (k0,k4,k1,k5,k2,k6,k3,k7) (tensor-core GPTQ path, GEMV)
     int *plan_out;    // host pointer: when set, the tensor-core family writes its launch plan there and launches nothing
     void *ws;         // scratch (may be nullptr when the chosen path needs none)
@@ -40,6 +50,8 @@ int gemv_launch(const GemmArgs &g);
 // and from every cudaError_t.
 constexpr int TC_NOT_COVERED = -1000;
 int gemm_tc_launch(const GemmArgs &g);
+// Token tile (MMA N extent) the tensor-core path uses for m rows in `segments` row segments (1: ordinary GEMM).
+int gemm_tc_token_tile(int m, int segments);
 
 // ---- nibble -> fp16 helpers (device) -----------------------------------------
 // For a 32-bit word w holding nibbles n0..n7 (n_i at bits 4i..4i+3):

@@ -60,6 +60,9 @@ struct TcArgs {
     int kb_per_split;  // K blocks per split
     int *status;
     const int *seg_offsets;   // grouped mode: row segments of A / C, one weight matrix per segment (blockIdx.z)
+    const int2 *tile_list;    // grouped mode: (segment, first row) per work item, or nullptr (blockIdx.z = segment, blockIdx.y = tile)
+    const int *tile_count;
+    int silu_inter;           // fused silu_mul epilogue: number of output columns (the weight holds twice as many), else 0
     int w_rows_per_seg;       // rows of the packed weight tensor per segment (K/8 for GPTQ, K for AWQ)
     int g_rows_per_seg;       // rows of the scale / zero tensors per segment (K / group)
 };
@@ -147,7 +150,10 @@ __device__ __forceinline__ uint32_t ring_phase(int i, int lg) { return (uint32_t
 // nibble trick yields a word's values; the 4 byte-permutes per word that would restore k order then disappear (they
 // run on the half-rate integer pipe, the busiest unit of this kernel).  A contraction may visit k in any order as
 // long as both operands agree.
-template <int FMT, int NG, bool TS, int NMMA, bool KPERM>
+// SILU: the CTA's 128 operand rows are 64 gate columns [64 bx, 64 bx + 64) and the 64 up columns I + the same; the epilogue
+// stores silu(gate) * up, 64 columns of an [M, I] output (the product the reference computes with a separate kernel,
+// fused_silu_mul_interleaved, on the GEMM's fp16 output; here it is taken from the fp32 accumulators).
+template <int FMT, int NG, bool TS, int NMMA, bool KPERM, bool SILU = false>
 __global__ void __launch_bounds__(tc_threads(NG), NG == 2 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap amap,
                const __grid_constant__ CUtensorMap smap, const __grid_constant__ CUtensorMap zmap, TcArgs P) {
@@ -172,15 +178,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * TC_BN;
+    const int n0 = SILU ? blockIdx.x * (TC_BN / 2) : blockIdx.x * TC_BN;     // SILU: first gate column; up columns at silu_inter + n0
     int m0 = blockIdx.y * TT, m_end = P.m, w_row0 = 0, g_row0 = 0;
     if (P.seg_offsets) {
-        pdl_wait();   // the segment offsets are written by the kernel before
-        // grouped mode: this CTA works on segment blockIdx.z with that segment's weights; no K split
-        const int e = blockIdx.z;
-        m0 += P.seg_offsets[e];
+        pdl_wait();   // the segment offsets (and the work list) are written by the kernel before
+        // grouped mode: this CTA works on one token tile of one segment with that segment's weights; no K split
+        int e;
+        if (P.tile_list) {
+            const int item = blockIdx.y;
+            if (item >= *P.tile_count) return;      // uniform across the CTA, before any barrier or TMEM allocation
+            const int2 w = P.tile_list[item];
+            e = w.x;
+            m0 = w.y;
+        } else {
+            e = blockIdx.z;
+            m0 += P.seg_offsets[e];
+        }
         m_end = P.seg_offsets[e + 1];
-        if (m0 >= m_end) return;            // uniform across the CTA, before any barrier or TMEM allocation
+        if (m0 >= m_end) return;
         w_row0 = e * P.w_rows_per_seg;
         g_row0 = e * P.g_rows_per_seg;
     }
@@ -252,14 +267,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 const uint32_t bar = smem_u32(&bars[B_RAWF + r]);
                 const uint32_t dst = smem_u32(raw + (size_t)r * TC_RAW_BYTES);
                 mbar_expect_tx(bar, TC_W_BYTES + TC_SC_BYTES + (P.qzeros ? TC_ZP_BYTES : 0));
-                if (FMT == FMT_GPTQ)
-                    tma_load_2d(dst, &wmap, n0, w_row0 + kb * (TC_BK / 8), bar);
-                else
-                    tma_load_2d(dst, &wmap, n0 / 8, w_row0 + kb * TC_BK, bar);
-                // the block's quantisation group rides along: scale row and packed zero-points
                 const int grp = (kb * TC_BK) >> group_shift;
-                tma_load_2d(dst + TC_W_BYTES, &smap, n0, g_row0 + grp, bar);
-                if (P.qzeros) tma_load_2d(dst + TC_W_BYTES + TC_SC_BYTES, &zmap, n0 / 8, g_row0 + grp, bar);
+                if (SILU) {
+                    // two boxes of 64 columns (gate, up) per tensor: the slot holds [8 rows][64] + [8 rows][64] words,
+                    // 64 + 64 scales, 8 + 8 zero-point words
+                    const int nu = P.silu_inter + n0;
+                    tma_load_2d(dst, &wmap, n0, w_row0 + kb * (TC_BK / 8), bar);
+                    tma_load_2d(dst + TC_W_BYTES / 2, &wmap, nu, w_row0 + kb * (TC_BK / 8), bar);
+                    tma_load_2d(dst + TC_W_BYTES, &smap, n0, g_row0 + grp, bar);
+                    tma_load_2d(dst + TC_W_BYTES + TC_SC_BYTES / 2, &smap, nu, g_row0 + grp, bar);
+                    if (P.qzeros) {
+                        tma_load_2d(dst + TC_W_BYTES + TC_SC_BYTES, &zmap, n0 / 8, g_row0 + grp, bar);
+                        tma_load_2d(dst + TC_W_BYTES + TC_SC_BYTES + TC_ZP_BYTES / 2, &zmap, nu / 8, g_row0 + grp, bar);
+                    }
+                } else {
+                    if (FMT == FMT_GPTQ)
+                        tma_load_2d(dst, &wmap, n0, w_row0 + kb * (TC_BK / 8), bar);
+                    else
+                        tma_load_2d(dst, &wmap, n0 / 8, w_row0 + kb * TC_BK, bar);
+                    // the block's quantisation group rides along: scale row and packed zero-points
+                    tma_load_2d(dst + TC_W_BYTES, &smap, n0, g_row0 + grp, bar);
+                    if (P.qzeros) tma_load_2d(dst + TC_W_BYTES + TC_SC_BYTES, &zmap, n0 / 8, g_row0 + grp, bar);
+                }
             }
         }
     } else if (warp == 3) {
@@ -333,8 +362,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                         P.zero_offset;
                 __half2 zlo, zhi;
                 zero_magic(z, zlo, zhi);
+                if (SILU) {      // two [8][64] boxes: gate columns (rows 0..63 of the operand), then up columns
+                    const uint32_t *rw2 = rw + (t >> 6) * (TC_W_BYTES / 8) + (t & 63);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) w[j] = rw[j * TC_BN + t];
+                    for (int j = 0; j < 8; ++j) w[j] = rw2[j * (TC_BN / 2)];
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) w[j] = rw[j * TC_BN + t];
+                }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bars[B_RAWE + r]));  // this warp is done with the packed tile
                 if (i >= SD) {
@@ -418,6 +453,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         const int row = q * 32 + lane;                // accumulator row = weight column n0 + row
         const int n = n0 + row;
         float *red = reinterpret_cast<float *>(smem);     // [TT][128] fp32, reuses the rings (all copies landed, all MMAs retired)
+        if (SILU) {
+            // rows 0..63 hold gate columns, rows 64..127 the matching up columns: the up half goes through shared memory
+            // to the warps that hold the gate half, which store silu(gate) * up
+            for (int base = 0; base < TT; base += 16 * NG) {      // every warp makes the same number of rounds (named barrier inside)
+                const int c0 = base + chunk0 * 16;
+                const bool active = c0 < TT;
+                uint32_t rr[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) rr[j] = 0u;
+                if (active && nkb > 0) {
+                    tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + c0, rr);
+                    if (NMMA == 2 && nkb > 1) {
+                        uint32_t r2[16];
+                        tmem_ld16(tmem_acc + ((uint32_t)(q * 32) << 16) + TT + c0, r2);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) rr[j] = __float_as_uint(__uint_as_float(rr[j]) + __uint_as_float(r2[j]));
+                    }
+                    tmem_ld_wait();
+                }
+                if (active && q >= 2) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) red[(c0 + j) * (TC_BN / 2) + row - TC_BN / 2] = __uint_as_float(rr[j]);
+                }
+                asm volatile("bar.sync 1, %0;" ::"r"(NG * 128) : "memory");      // the dequant / epilogue warps only
+                if (active && q < 2 && n < P.silu_inter) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int m = m0 + c0 + j;
+                        const float gt = __uint_as_float(rr[j]), up = red[(c0 + j) * (TC_BN / 2) + row];
+                        if (m < m_end) P.c[(long)m * P.s_cm + n] = __float2half_rn(gt / (1.f + expf(-gt)) * up);
+                    }
+                }
+                asm volatile("bar.sync 1, %0;" ::"r"(NG * 128) : "memory");      // before the next round overwrites the staging rows
+            }
+        } else
         for (int c0 = chunk0 * 16; c0 < TT; c0 += 16 * NG) {
             uint32_t rr[16];
             if (nkb > 0) {
@@ -473,6 +544,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     if (warp == 0) tmem_dealloc(tmem_acc, tmem_cols);
 }
 
+int gemm_tc_token_tile(int m, int segments);
 static int pick_tt(int m) {
     if (m <= 16) return 16;
     if (m <= 32) return 32;
@@ -481,7 +553,11 @@ static int pick_tt(int m) {
     return 256;
 }
 
+int gemm_tc_token_tile(int m, int segments) { return pick_tt(segments > 1 ? ceil_div(m, segments) : m); }
+
 int gemm_tc_launch(const GemmArgs &g) {
+    const bool silu = g.silu_inter > 0;
+    if (silu && (g.format != FMT_GPTQ || g.n != 2 * g.silu_inter || g.silu_inter % 64)) return TC_NOT_COVERED;
     if (g.k % TC_BK || g.group % TC_BK || (g.group & (g.group - 1)) || g.n % 8) return TC_NOT_COVERED;
     if (g.format == FMT_AWQ && !g.qzeros) return TC_NOT_COVERED;
     if (g.qzeros && (g.s_qzk % 4 || !aligned16(g.qzeros))) return TC_NOT_COVERED;   // zero-point rows travel by TMA: 16-byte pitch
@@ -489,7 +565,7 @@ int gemm_tc_launch(const GemmArgs &g) {
     // grouped: the token tile follows the average segment; the grid covers the worst case (every row in
     // one segment) and CTAs past their segment's end return at once
     const int tt = pick_tt(grouped ? ceil_div(g.m, g.num_segments) : g.m);
-    const int col_tiles = ceil_div(g.n, TC_BN), tok_tiles = ceil_div(g.m, tt);
+    const int col_tiles = silu ? g.silu_inter / 64 : ceil_div(g.n, TC_BN), tok_tiles = ceil_div(g.m, tt);
     const int kb_total = g.k / TC_BK;
     const int tiles = col_tiles * tok_tiles;
     // Shared memory: two CTAs per SM while the token tile is small, one otherwise.
@@ -534,7 +610,8 @@ int gemm_tc_launch(const GemmArgs &g) {
     // the machine is at most once covered and every CTA keeps a long K range.
     // The exchange tile ([tt][128] fp32) reuses the three rings, idle by then.
     const size_t ring_bytes = (size_t)dq_stages * a_bytes + (size_t)act_stages * act_bytes + (size_t)raw_stages * TC_RAW_BYTES;
-    const bool can_split = !grouped && ring_bytes >= (size_t)tt * TC_BN * 4;
+    const bool can_split = !grouped && !silu && ring_bytes >= (size_t)tt * TC_BN * 4;
+    if (silu && ring_bytes < (size_t)tt * TC_BN * 2) return TC_NOT_COVERED;      // the epilogue stages the up half in the rings' space
     int ksplit = 1;
     if (can_split) {
         const int sms = sm_count();
@@ -559,9 +636,10 @@ int gemm_tc_launch(const GemmArgs &g) {
     CUtensorMap wmap, amap, smap, zmap;
     int rc;
     const uint64_t nseg = grouped ? (uint64_t)g.num_segments : 1;
+    const uint32_t cbox = silu ? TC_BN / 2 : TC_BN;      // columns per TMA box (fused silu: a gate box and an up box)
     if (g.format == FMT_GPTQ) {
         const uint64_t dims[2] = {(uint64_t)g.n, (uint64_t)(g.k / 8) * nseg}, str[1] = {(uint64_t)g.s_qwk * 4};
-        const uint32_t box[2] = {TC_BN, TC_BK / 8};
+        const uint32_t box[2] = {cbox, TC_BK / 8};
         rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, g.qweight, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
     } else {
         const uint64_t dims[2] = {(uint64_t)(g.n / 8), (uint64_t)g.k * nseg}, str[1] = {(uint64_t)g.s_qwk * 4};
@@ -577,14 +655,14 @@ int gemm_tc_launch(const GemmArgs &g) {
     if (rc) return TC_NOT_COVERED;   // layout the TMA cannot describe: the strided family takes it
     {
         const uint64_t dims[2] = {(uint64_t)g.n, (uint64_t)(g.k / g.group) * nseg}, str[1] = {(uint64_t)g.s_sk * 2};
-        const uint32_t box[2] = {TC_BN, 1};
+        const uint32_t box[2] = {cbox, 1};
         rc = make_tensor_map(&smap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.scales, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
     }
     if (rc) return TC_NOT_COVERED;
     zmap = smap;
     if (g.qzeros) {
         const uint64_t dims[2] = {(uint64_t)(g.n / 8), (uint64_t)(g.k / g.group) * nseg}, str[1] = {(uint64_t)g.s_qzk * 4};
-        const uint32_t box[2] = {TC_BN / 8, 1};
+        const uint32_t box[2] = {cbox / 8, 1};
         rc = make_tensor_map(&zmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, g.qzeros, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
         if (rc) return TC_NOT_COVERED;
     }
@@ -597,24 +675,32 @@ int gemm_tc_launch(const GemmArgs &g) {
     P.tt = tt; P.dq_log2 = log2i(dq_stages); P.act_log2 = log2i(act_stages); P.raw_log2 = log2i(raw_stages); P.ksplit = ksplit;
     P.kb_per_split = ceil_div(kb_total, ksplit);
     P.seg_offsets = g.seg_offsets;
+    P.tile_list = grouped ? g.tile_list : nullptr;
+    P.tile_count = g.tile_count;
+    P.silu_inter = g.silu_inter;
     P.w_rows_per_seg = g.format == FMT_GPTQ ? g.k / 8 : g.k;
     P.g_rows_per_seg = g.k / g.group;
     P.status = (int *)g.ws;   // status word at the start of the scratch buffer
     if (!P.status) return fail(B200K_E_WORKSPACE, "w4a16 gemm (tensor core): workspace is NULL");
 
     if (g.a_kperm && !ts) return TC_NOT_COVERED;   // pre-permuted activations: only the tensor-memory operand variants take them
-    auto kern = g.format == FMT_AWQ ? (ng == 2 ? gemm_tc_kernel<FMT_AWQ, 2, false, 2, false> : gemm_tc_kernel<FMT_AWQ, 4, false, 1, false>)
+    if (silu && !ts) return TC_NOT_COVERED;
+    auto kern = silu ? (g.a_kperm ? (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, true, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, true, true>)
+                                  : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, false, true>))
+                : g.format == FMT_AWQ ? (ng == 2 ? gemm_tc_kernel<FMT_AWQ, 2, false, 2, false> : gemm_tc_kernel<FMT_AWQ, 4, false, 1, false>)
                 : ts ? (g.a_kperm ? (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, true>)
                                   : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, false>))
                      : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, false, 2, false> : gemm_tc_kernel<FMT_GPTQ, 4, false, 1, false>);
     {
-        static OncePerDevice once[4][2];
-        const int variant = g.format == FMT_AWQ ? 1 : (ts ? (g.a_kperm ? 3 : 2) : 0);
+        static OncePerDevice once[6][2];
+        const int variant = silu ? (g.a_kperm ? 5 : 4) : g.format == FMT_AWQ ? 1 : (ts ? (g.a_kperm ? 3 : 2) : 0);
         cudaError_t e = once[variant][ng == 4].run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); });
         if (e != cudaSuccess) return fail((int)e, "w4a16 gemm (tensor core): shared memory: %s", cudaGetErrorString(e));
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(col_tiles, tok_tiles, grouped ? g.num_segments : ksplit);
+    // grouped with a work list: one grid slice per listed (segment, token tile); without: the worst case per segment
+    const bool listed = grouped && g.tile_list;
+    cfg.gridDim = dim3(col_tiles, listed ? g.max_tiles : tok_tiles, grouped ? (listed ? 1 : g.num_segments) : ksplit);
     cfg.blockDim = dim3(tc_threads(ng), 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = g.stream;

@@ -114,6 +114,52 @@ rms_norm_kernel(const T *__restrict__ x, const T *__restrict__ res, const T *__r
     }
 }
 
+// Short rows (up to 32 * ITERS vectors of 16 bytes): one WARP per row, eight rows per CTA, shuffle reduction only.  A CTA per
+// 2 KiB row is bound by CTA launch rate, not by memory.
+template <typename T, bool FUSED_ADD, int ITERS>
+__global__ void __launch_bounds__(256)
+rms_norm_warp_kernel(const T *__restrict__ x, const T *__restrict__ res, const T *__restrict__ w,
+                     T *__restrict__ y, T *__restrict__ res_out, int n, float inv_n, float eps, int rows, bool kperm) {
+    constexpr int VEC = Elem<T>::VEC;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const size_t row_off = (size_t)row * n;
+    const int nv = n / VEC;
+    float v[ITERS][VEC];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int i = lane + it * 32;
+        if (i < nv) {
+            Elem<T>::load(x + row_off + i * VEC, v[it]);
+            if (FUSED_ADD) {
+                float r[VEC];
+                Elem<T>::load(res + row_off + i * VEC, r);
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) v[it][j] += r[j];
+                Elem<T>::store(res_out + row_off + i * VEC, v[it]);
+            }
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) ss += v[it][j] * v[it][j];
+        }
+    }
+    const float inv = rsqrtf(warp_sum(ss) * inv_n + eps);
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int i = lane + it * 32;
+        if (i < nv) {
+            float wv[VEC], o[VEC];
+            Elem<T>::load(w + i * VEC, wv);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) o[j] = v[it][j] * inv * wv[j];
+            if (kperm) Elem<T>::store_kperm(y + row_off + i * VEC, o);
+            else Elem<T>::store(y + row_off + i * VEC, o);
+        }
+    }
+}
+
 template <typename T, bool FUSED_ADD>
 static int rms_norm_launch(const char *name, const T *x, const T *res, const T *w, T *y, T *res_out,
                            int n, float inv_n, float eps, int rows, cudaStream_t st, bool kperm = false) {
@@ -127,7 +173,14 @@ static int rms_norm_launch(const char *name, const T *x, const T *res, const T *
     // In the fused kernel the in-place form (residual_out == residual) is allowed: each
     // element is read and written by the same thread.
     B200K_REQUIRE(!kperm || (vec && nv <= 4 * 1024 && VEC == 8), B200K_E_SHAPE, "%s: the permuted output needs fp16 rows of a multiple of 8, 16-byte aligned", name);
-    if (vec && nv <= 4 * 1024) {
+    if (vec && nv <= 256 && rows >= 8 * 148) {
+        // many short rows: a warp per row
+        const dim3 grid(ceil_div(rows, 8)), block(256);
+        if (nv <= 128)
+            launch_kernel(rms_norm_warp_kernel<T, FUSED_ADD, 4>, grid, block, 0, st, x, res, w, y, res_out, n, inv_n, eps, rows, kperm);
+        else
+            launch_kernel(rms_norm_warp_kernel<T, FUSED_ADD, 8>, grid, block, 0, st, x, res, w, y, res_out, n, inv_n, eps, rows, kperm);
+    } else if (vec && nv <= 4 * 1024) {
         int threads = nv <= 128 ? 128 : (nv <= 256 ? 256 : (nv <= 512 ? 512 : 1024));
         int iters = ceil_div(nv, threads);
         if (iters == 1)

@@ -1,5 +1,6 @@
-// Fused MoE (top-k routing, token permute, grouped int4 expert GEMMs, silu_mul, weighted
-// un-permute).  The reference has no such kernel; the pieces follow its conventions: GPTQ
+// Fused MoE (top-k routing, token permute, grouped int4 expert GEMMs with silu_mul in the first one's
+// epilogue, weighted un-permute): six launches -- route, permute (+ the GEMMs' work list), gather, w13 GEMM,
+// w2 GEMM, combine.  The reference has no such kernel; the pieces follow its conventions: GPTQ
 // weight layout of w4a16_gptq_gemm_typed, and the half-split gate|up layout of
 // fused_silu_mul_interleaved (gate = first half of a row, up = second half).
 //
@@ -57,10 +58,12 @@ __device__ __forceinline__ int moe_bucket(int e, int first, int local) {
 
 // Single CTA: counts, offsets, stable segmented order and its inverse, over `experts` buckets
 // (experts = local, or local + 1 when some ids fall outside [first, first + local)).
+// With `tiles`: also the work list of the grouped GEMMs -- one (expert, first row) item per token tile of `tt` rows that
+// holds rows of a local expert -- and its length, so that their grids need no slices for tiles that do not exist.
 __global__ void __launch_bounds__(1024)
 moe_permute_kernel(const int32_t *__restrict__ ids, int pairs, int experts, int first, int local,
                    int32_t *__restrict__ counts, int32_t *__restrict__ offsets, int32_t *__restrict__ sorted_pairs,
-                   int32_t *__restrict__ inv) {
+                   int32_t *__restrict__ inv, int tt, int2 *__restrict__ tiles, int32_t *__restrict__ ntiles) {
     __shared__ int s_count[MOE_MAX_E];
     __shared__ int s_off[MOE_MAX_E + 1];
     __shared__ int s_run[MOE_MAX_E];          // pairs of each expert placed so far
@@ -77,6 +80,12 @@ moe_permute_kernel(const int32_t *__restrict__ ids, int pairs, int experts, int 
             acc += s_count[e];
         }
         s_off[experts] = acc;
+        if (tiles) {
+            int cnt = 0;
+            for (int e = 0; e < local; ++e)
+                for (int m = s_off[e]; m < s_off[e + 1]; m += tt) tiles[cnt++] = make_int2(e, m);
+            *ntiles = cnt;
+        }
     }
     if (tid < experts) s_run[tid] = 0;
     __syncthreads();
@@ -151,31 +160,11 @@ moe_combine_kernel(const __half *__restrict__ yp, const int32_t *__restrict__ in
     }
 }
 
-// silu(gate) * up over the first *nrows rows of gate_up [rows, 2 inter] (gate = first half of a row)
-__global__ void __launch_bounds__(256)
-moe_silu_mul_kernel(const __half *__restrict__ gu, __half *__restrict__ act, const int32_t *__restrict__ nrows, int inter) {
-    const int iv = inter / 8;
-    const long total = (long)*nrows * iv;
-    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
-        const long row = i / iv;
-        const int c = (int)(i - row * iv);
-        const uint4 g = reinterpret_cast<const uint4 *>(gu)[row * 2 * iv + c];
-        const uint4 u = reinterpret_cast<const uint4 *>(gu)[row * 2 * iv + iv + c];
-        const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
-        uint32_t o[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float2 a = h2_to_f2(gw[j]), b = h2_to_f2(uw[j]);
-            o[j] = f2_to_h2(a.x / (1.f + expf(-a.x)) * b.x, a.y / (1.f + expf(-a.y)) * b.y);
-        }
-        reinterpret_cast<uint4 *>(act)[row * iv + c] = make_uint4(o[0], o[1], o[2], o[3]);
-    }
-}
-
 struct MoeWs {
-    int32_t *ids, *counts, *offsets, *sorted_pairs, *inv;
+    int32_t *ids, *counts, *offsets, *sorted_pairs, *inv, *ntiles;
+    int2 *tiles;
     float *wts;
-    __half *xp, *gu, *act, *yp;
+    __half *xp, *act, *yp;
     size_t bytes;
 };
 static MoeWs moe_ws_layout(void *base, int tokens, int hidden, int experts, int top_k, int inter) {
@@ -194,8 +183,9 @@ static MoeWs moe_ws_layout(void *base, int tokens, int hidden, int experts, int 
     w.offsets = (int32_t *)take((size_t)(experts + 1) * 4);
     w.sorted_pairs = (int32_t *)take(pairs * 4);
     w.inv = (int32_t *)take(pairs * 4);
+    w.ntiles = (int32_t *)take(4);
+    w.tiles = (int2 *)take((pairs / 16 + (size_t)experts + 1) * sizeof(int2));     // at most pairs / (smallest tile) + experts items
     w.xp = (__half *)take(pairs * hidden * 2);
-    w.gu = (__half *)take(pairs * 2 * (size_t)inter * 2);
     w.act = (__half *)take(pairs * (size_t)inter * 2);
     w.yp = (__half *)take(pairs * hidden * 2);
     w.bytes = off;
@@ -231,7 +221,7 @@ extern "C" int moe_permute(const int32_t *topk_ids, int32_t *counts, int32_t *of
                   "moe_permute: pairs %d, experts %d (<= %d)", num_pairs, num_experts, MOE_MAX_E);
     B200K_REQUIRE(topk_ids && counts && offsets && sorted_pairs && inverse, B200K_E_NULL, "moe_permute: NULL pointer");
     moe_permute_kernel<<<1, 1024, 0, to_stream(stream)>>>(topk_ids, num_pairs, num_experts, 0, num_experts, counts,
-                                                         offsets, sorted_pairs, inverse);
+                                                         offsets, sorted_pairs, inverse, 0, nullptr, nullptr);
     return launch_status("moe_permute");
 }
 
@@ -272,8 +262,10 @@ static int moe_run(const char *name, const b200k_half *x, const float *router_lo
     const int32_t *nrows = w.offsets + num_local;    // rows of the segmented list that belong to local experts
     int rc;
     if ((rc = moe_route_topk_f32(router_logits, w.ids, w.wts, num_tokens, num_experts, top_k, stream))) return rc;
+    const int tt = gemm_tc_token_tile(pairs, num_local);      // the token tile both expert GEMMs will use
+    const int max_tiles = ceil_div(pairs, tt) + num_local;
     moe_permute_kernel<<<1, 1024, 0, st>>>(w.ids, pairs, buckets, expert_first, num_local, w.counts, w.offsets,
-                                           w.sorted_pairs, w.inv);
+                                           w.sorted_pairs, w.inv, tt, w.tiles, w.ntiles);
     if ((rc = launch_status(name))) return rc;
     moe_gather_kernel<<<grid_for((long)pairs * hidden / 8), 256, 0, st>>>((const __half *)x, w.sorted_pairs, w.xp, nrows,
                                                                           hidden, top_k);
@@ -282,16 +274,16 @@ static int moe_run(const char *name, const b200k_half *x, const float *router_lo
     GemmArgs g = {};
     g.format = FMT_GPTQ; g.group = group_size; g.stream = st; g.ws = workspace; g.ws_bytes = workspace_bytes;
     g.seg_offsets = w.offsets; g.num_segments = num_local;
+    g.tile_list = w.tiles; g.tile_count = w.ntiles; g.max_tiles = max_tiles;
     g.s_ak = g.s_qwn = g.s_sn = g.s_qzn = g.s_cn = 1;
-    // up-projection: [pairs, H] x W13_e [H, 2I] -> [pairs, 2I]
-    g.a = w.xp; g.qweight = w13_qweight; g.scales = (const __half *)w13_scales; g.qzeros = w13_qzeros; g.c = w.gu;
-    g.m = pairs; g.n = 2 * intermediate; g.k = hidden;
-    g.s_am = hidden; g.s_qwk = g.n; g.s_sk = g.n; g.s_qzk = g.n / 8; g.s_cm = g.n;
+    // up-projection with the silu_mul fused into its epilogue: [pairs, H] x W13_e [H, gate I | up I] -> silu(gate) * up [pairs, I]
+    g.a = w.xp; g.qweight = w13_qweight; g.scales = (const __half *)w13_scales; g.qzeros = w13_qzeros; g.c = w.act;
+    g.m = pairs; g.n = 2 * intermediate; g.k = hidden; g.silu_inter = intermediate;
+    g.s_am = hidden; g.s_qwk = g.n; g.s_sk = g.n; g.s_qzk = g.n / 8; g.s_cm = intermediate;
     g.zero_offset = w13_qzeros ? 1 : 0;
     rc = gemm_tc_launch(g);
     if (rc) return rc == TC_NOT_COVERED ? fail(B200K_E_SHAPE, "%s: expert GEMM shape not covered by the tensor-core path", name) : rc;
-    moe_silu_mul_kernel<<<grid_for((long)pairs * intermediate / 8), 256, 0, st>>>(w.gu, w.act, nrows, intermediate);
-    if ((rc = launch_status(name))) return rc;
+    g.silu_inter = 0;
     // down-projection: [pairs, I] x W2_e [I, H] -> [pairs, H]
     g.a = w.act; g.qweight = w2_qweight; g.scales = (const __half *)w2_scales; g.qzeros = w2_qzeros; g.c = w.yp;
     g.n = hidden; g.k = intermediate;
