@@ -219,6 +219,33 @@ def test_flash_attn_full_vs_oracle(P, oracle, dtype, b, hq, hkv, q_len, kv_len, 
         assert_close(out.float().cpu().numpy(), ref, 1e-2, 1e-2, "prefill attention f16")
 
 
+@pytest.mark.parametrize("b,hq,hkv,q_len,kv_len,off", [
+    (1, 4, 2, 300, 300, 0),           # three query tiles, three KV tiles, ragged last tile of both
+    (2, 8, 2, 200, 500, 300),         # chunked prefill over 300 cached positions
+    (1, 2, 2, 260, 150, 0),           # queries past the end of the KV stream
+    (1, 8, 1, 128, 128, 0),           # exactly one tile; GQA group of 8
+    (2, 4, 4, 129, 1, 0),             # a single KV position
+    (1, 2, 1, 640, 640, 0),           # five tiles: both ring slots and both S buffers wrap twice
+])
+def test_flash_attn_full_f16_head_dim_128_tensor_core_path(P, oracle, b, hq, hkv, q_len, kv_len, off):
+    """head_dim 128 in fp16 runs on the tcgen05 kernel (128 x 128 tiles): tile boundaries, the causal diagonal inside a
+    tile, KV streams shorter and longer than the queries, and outputs beyond q_len untouched."""
+    d = 128
+    rng = np.random.default_rng(q_len * 3 + kv_len)
+    q = rng.standard_normal((b, hq, q_len, d)).astype(np.float16)
+    k = rng.standard_normal((b, hkv, kv_len, d)).astype(np.float16)
+    v = rng.standard_normal((b, hkv, kv_len, d)).astype(np.float16)
+    scale = 1.0 / np.sqrt(d)
+    ref = oracle.flash_attn_full(q, k, v, off, scale)
+    out = torch.full(q.shape, float("nan"), device=DEV, dtype=torch.float16)
+    st = torch.cuda.current_stream().cuda_stream
+    P.flash_attn_full_f16(t(q), t(k), t(v), out, b, hq, hkv, q_len, kv_len, d, off, scale, st)
+    assert_close(out.float().cpu().numpy(), ref, 1e-2, 1e-2, "prefill attention f16 (tensor core)")
+    out2 = torch.empty_like(out)
+    P.flash_attn_full_f16(t(q), t(k), t(v), out2, b, hq, hkv, q_len, kv_len, d, off, scale, st)
+    assert torch.equal(out, out2), "two runs differ"
+
+
 def test_flash_attn_full_rejects_bad_shapes(P, pkg):
     z = torch.zeros(16, device=DEV)
     st = torch.cuda.current_stream().cuda_stream

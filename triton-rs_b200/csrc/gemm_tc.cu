@@ -25,6 +25,7 @@
 #include <stdlib.h>
 
 #include "gemm.cuh"
+#include "tcgen05.cuh"
 #include "tma.cuh"
 
 namespace cg = cooperative_groups;
@@ -67,71 +68,6 @@ struct TcArgs {
     int g_rows_per_seg;       // rows of the scale / zero tensors per segment (K / group)
 };
 
-// ---- tcgen05 wrappers -------------------------------------------------------------
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// The same with the A operand read from tensor memory: 128 lanes = 128 operand rows, 8 columns of
-// 32 bits = 16 fp16 values of K per row.
-__device__ __forceinline__ void tc_mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// 32 columns of this warp's 32 lanes: register j of lane l -> TMEM (lane base + l, column base + j)
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
-          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
-          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
-// Addresses and offsets are in 16-byte units.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
-           ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46) | (2ull << 61);
-}
-// Instruction descriptor, kind::f16: D = f32, A = B = f16, A major as given, B K-major.
-__host__ __device__ __forceinline__ uint32_t umma_idesc(int m, int n, int a_mn_major) {
-    return (1u << 4) | ((uint32_t)a_mn_major << 15) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
 // The depths of the three rings are powers of two, so the slot of block i and the parity of the phase it
 // belongs to are bit fields of i: nothing but i is carried from block to block (ring cursors kept in
 // registers and advanced block by block cost a tenth of the dequant warps' instruction stream).
@@ -153,7 +89,8 @@ __device__ __forceinline__ uint32_t ring_phase(int i, int lg) { return (uint32_t
 // SILU: the CTA's 128 operand rows are 64 gate columns [64 bx, 64 bx + 64) and the 64 up columns I + the same; the epilogue
 // stores silu(gate) * up, 64 columns of an [M, I] output (the product the reference computes with a separate kernel,
 // fused_silu_mul_interleaved, on the GEMM's fp16 output; here it is taken from the fp32 accumulators).
-template <int FMT, int NG, bool TS, int NMMA, bool KPERM, bool SILU = false>
+// BF: activations, scales and output are bfloat16 (the MMA's operand format follows).
+template <int FMT, int NG, bool TS, int NMMA, bool KPERM, bool SILU = false, bool BF = false>
 __global__ void __launch_bounds__(tc_threads(NG), NG == 2 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap amap,
                const __grid_constant__ CUtensorMap smap, const __grid_constant__ CUtensorMap zmap, TcArgs P) {
@@ -311,7 +248,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         // commits to one barrier per block.
         const int mw = warp - 1;
         if (lane == 0 && mw < NMMA) {
-            const uint32_t idesc = umma_idesc(TC_BN, TT, FMT == FMT_AWQ ? 1 : 0);
+            const uint32_t idesc = umma_idesc(TC_BN, TT, FMT == FMT_AWQ ? 1 : 0) | (BF ? (1u << 7) | (1u << 10) : 0u);   // A, B format: f16 or bf16
             const uint64_t da0 = FMT == FMT_GPTQ ? umma_desc(smem_u32(a_tile), 16, 1024)       // K-major: 8-row groups 1 KiB apart
                                                  : umma_desc(smem_u32(a_tile), 8192, 1024);    // MN-major: 64-column halves 8 KiB apart, 8-k groups 1 KiB apart
             const uint64_t db0 = umma_desc(smem_u32(b_tile), 16, 1024);
@@ -355,13 +292,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             uint32_t w[8];
             if (FMT == FMT_GPTQ) {
                 // thread t = weight column t (operand row t): its 8 words are the 8 16-byte chunks of the row
-                const __half2 s2 = __half2half2(reinterpret_cast<const __half *>(slot + TC_W_BYTES)[t]);
+                const uint32_t s2 = (uint32_t)reinterpret_cast<const uint16_t *>(slot + TC_W_BYTES)[t] * 0x10001u;   // the column's scale in both halves
                 int z = 8;
                 if (P.qzeros)
                     z = (int)((reinterpret_cast<const uint32_t *>(slot + TC_W_BYTES + TC_SC_BYTES)[t >> 3] >> (4 * (t & 7))) & 15u) +
                         P.zero_offset;
-                __half2 zlo, zhi;
-                zero_magic(z, zlo, zhi);
+                uint32_t zm[4];
+                zero_magic4<BF>(z, zm);
                 if (SILU) {      // two [8][64] boxes: gate columns (rows 0..63 of the operand), then up columns
                     const uint32_t *rw2 = rw + (t >> 6) * (TC_W_BYTES / 8) + (t & 63);
 #pragma unroll
@@ -381,11 +318,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 uint32_t v[32];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    const uint32_t w8 = w[j] >> 8;
-                    const uint32_t v04 = h22u(__hmul2(__hsub2(u2h2(nib_lo(w[j])), zlo), s2));
-                    const uint32_t v15 = h22u(__hmul2(__hsub2(u2h2(nib_hi(w[j])), zhi), s2));
-                    const uint32_t v26 = h22u(__hmul2(__hsub2(u2h2(nib_lo(w8)), zlo), s2));
-                    const uint32_t v37 = h22u(__hmul2(__hsub2(u2h2(nib_hi(w8)), zhi), s2));
+                    uint32_t x[4];
+                    nib4<BF>(w[j], x);
+                    const uint32_t v04 = sub_mul<BF>(x[0], zm[0], s2), v15 = sub_mul<BF>(x[1], zm[1], s2);
+                    const uint32_t v26 = sub_mul<BF>(x[2], zm[2], s2), v37 = sub_mul<BF>(x[3], zm[3], s2);
                     uint4 o;
                     if (KPERM) {
                         o = make_uint4(v04, v15, v26, v37);    // (k0 k4) (k1 k5) (k2 k6) (k3 k7): the activations' order
@@ -411,9 +347,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 // thread t: word column n8 = t % 16 (8 weight columns), k rows t / 16 + 8 j
                 const int n8 = t & 15, kr = t >> 4;
                 const uint4 su = reinterpret_cast<const uint4 *>(slot + TC_W_BYTES)[n8];
-                const __half2 s01 = u2h2(su.x), s23 = u2h2(su.y), s45 = u2h2(su.z), s67 = u2h2(su.w);
-                const uint32_t zw = reinterpret_cast<const uint32_t *>(slot + TC_W_BYTES + TC_SC_BYTES)[n8], z8 = zw >> 8;
-                const __half2 z01 = u2h2(nib_lo(zw)), z23 = u2h2(nib_hi(zw)), z45 = u2h2(nib_lo(z8)), z67 = u2h2(nib_hi(z8));
+                const uint32_t zw = reinterpret_cast<const uint32_t *>(slot + TC_W_BYTES + TC_SC_BYTES)[n8];
+                uint32_t zq[4];
+                nib4<BF>(zw, zq);      // the zero word has the weights' nibble order: its pairs in biased form are the subtrahends
 #pragma unroll
                 for (int j = 0; j < 8; ++j) w[j] = rw[(kr + 8 * j) * 16 + n8];
                 __syncwarp();
@@ -426,12 +362,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const int kk = kr + 8 * j;
-                    const uint32_t w8 = w[j] >> 8;
+                    uint32_t x[4];
+                    nib4<BF>(w[j], x);
                     uint4 o;
-                    o.x = h22u(__hmul2(__hsub2(u2h2(nib_lo(w[j])), z01), s01));   // columns 0,1 (nibbles 0,4)
-                    o.y = h22u(__hmul2(__hsub2(u2h2(nib_hi(w[j])), z23), s23));   // columns 2,3 (nibbles 1,5)
-                    o.z = h22u(__hmul2(__hsub2(u2h2(nib_lo(w8)), z45), s45));     // columns 4,5 (nibbles 2,6)
-                    o.w = h22u(__hmul2(__hsub2(u2h2(nib_hi(w8)), z67), s67));     // columns 6,7 (nibbles 3,7)
+                    o.x = sub_mul<BF>(x[0], zq[0], su.x);   // columns 0,1 (nibbles 0,4)
+                    o.y = sub_mul<BF>(x[1], zq[1], su.y);   // columns 2,3 (nibbles 1,5)
+                    o.z = sub_mul<BF>(x[2], zq[2], su.z);   // columns 4,5 (nibbles 2,6)
+                    o.w = sub_mul<BF>(x[3], zq[3], su.w);   // columns 6,7 (nibbles 3,7)
                     *reinterpret_cast<uint4 *>(ahalf + kk * 128 + (((n8 & 7) ^ (kk & 7)) << 4)) = o;
                 }
             }
@@ -483,7 +420,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                     for (int j = 0; j < 16; ++j) {
                         const int m = m0 + c0 + j;
                         const float gt = __uint_as_float(rr[j]), up = red[(c0 + j) * (TC_BN / 2) + row];
-                        if (m < m_end) P.c[(long)m * P.s_cm + n] = __float2half_rn(gt / (1.f + expf(-gt)) * up);
+                        if (m < m_end) store_elem<BF>(P.c + (long)m * P.s_cm + n, gt / (1.f + expf(-gt)) * up);
                     }
                 }
                 asm volatile("bar.sync 1, %0;" ::"r"(NG * 128) : "memory");      // before the next round overwrites the staging rows
@@ -510,7 +447,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int m = m0 + c0 + j;
-                        if (m < m_end) P.c[(long)m * P.s_cm + n] = __float2half_rn(__uint_as_float(rr[j]));
+                        if (m < m_end) store_elem<BF>(P.c + (long)m * P.s_cm + n, __uint_as_float(rr[j]));
                     }
                 }
             } else {
@@ -534,7 +471,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 if (m >= m_end) break;
                 float acc = 0.f;
                 for (int r = 0; r < P.ksplit; ++r) acc += cluster.map_shared_rank(red, r)[mm * TC_BN + row];
-                if (n < P.n) P.c[(long)m * P.s_cm + n] = __float2half_rn(acc);
+                if (n < P.n) store_elem<BF>(P.c + (long)m * P.s_cm + n, acc);
             }
         }
         cluster.sync();
@@ -650,13 +587,13 @@ int gemm_tc_launch(const GemmArgs &g) {
     {
         const uint64_t dims[2] = {(uint64_t)g.k, (uint64_t)g.m}, str[1] = {(uint64_t)g.s_am * 2};
         const uint32_t box[2] = {TC_BK, (uint32_t)tt};
-        rc = make_tensor_map(&amap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        rc = make_tensor_map(&amap, g.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
     }
     if (rc) return TC_NOT_COVERED;   // layout the TMA cannot describe: the strided family takes it
     {
         const uint64_t dims[2] = {(uint64_t)g.n, (uint64_t)(g.k / g.group) * nseg}, str[1] = {(uint64_t)g.s_sk * 2};
         const uint32_t box[2] = {cbox, 1};
-        rc = make_tensor_map(&smap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.scales, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+        rc = make_tensor_map(&smap, g.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.scales, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
     }
     if (rc) return TC_NOT_COVERED;
     zmap = smap;
@@ -685,15 +622,18 @@ int gemm_tc_launch(const GemmArgs &g) {
 
     if (g.a_kperm && !ts) return TC_NOT_COVERED;   // pre-permuted activations: only the tensor-memory operand variants take them
     if (silu && !ts) return TC_NOT_COVERED;
-    auto kern = silu ? (g.a_kperm ? (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, true, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, true, true>)
+    if (g.bf16 && (silu || g.a_kperm || (g.format == FMT_GPTQ && !ts))) return TC_NOT_COVERED;
+    auto kern = g.bf16 ? (g.format == FMT_AWQ ? (ng == 2 ? gemm_tc_kernel<FMT_AWQ, 2, false, 2, false, false, true> : gemm_tc_kernel<FMT_AWQ, 4, false, 1, false, false, true>)
+                                              : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false, false, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, false, false, true>))
+                : silu ? (g.a_kperm ? (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, true, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, true, true>)
                                   : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, false, true>))
                 : g.format == FMT_AWQ ? (ng == 2 ? gemm_tc_kernel<FMT_AWQ, 2, false, 2, false> : gemm_tc_kernel<FMT_AWQ, 4, false, 1, false>)
                 : ts ? (g.a_kperm ? (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, true>)
                                   : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, false>))
                      : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, false, 2, false> : gemm_tc_kernel<FMT_GPTQ, 4, false, 1, false>);
     {
-        static OncePerDevice once[6][2];
-        const int variant = silu ? (g.a_kperm ? 5 : 4) : g.format == FMT_AWQ ? 1 : (ts ? (g.a_kperm ? 3 : 2) : 0);
+        static OncePerDevice once[8][2];
+        const int variant = g.bf16 ? (g.format == FMT_AWQ ? 7 : 6) : silu ? (g.a_kperm ? 5 : 4) : g.format == FMT_AWQ ? 1 : (ts ? (g.a_kperm ? 3 : 2) : 0);
         cudaError_t e = once[variant][ng == 4].run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); });
         if (e != cudaSuccess) return fail((int)e, "w4a16 gemm (tensor core): shared memory: %s", cudaGetErrorString(e));
     }

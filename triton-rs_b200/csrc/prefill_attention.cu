@@ -125,9 +125,21 @@ extern "C" int flash_attn_full_f32(const float *q, const float *k, const float *
                                  pos_offset, scale, stream);
 }
 
+namespace b200k {
+// tensor-core kernel (prefill_tc.cu): head_dim 128, pos_offset >= 0; -1000 when the call is outside what it covers
+int prefill_tc_launch(const __half *q, const __half *k, const __half *v, __half *out, int batch, int hq, int hkv, int q_len,
+                      int kv_len, int d, int pos_offset, float scale, cudaStream_t st);
+}  // namespace b200k
+
 extern "C" int flash_attn_full_f16(const b200k_half *q, const b200k_half *k, const b200k_half *v, b200k_half *output, int batch,
                                    int num_heads, int num_kv_heads, int q_len, int kv_len, int head_dim, int pos_offset,
                                    float scale, b200k_stream stream) {
+    if (q && k && v && output && batch > 0 && num_heads > 0 && num_kv_heads > 0 && env_char("B200K_PREFILL") != 'g') {
+        const int rc = prefill_tc_launch(reinterpret_cast<const __half *>(q), reinterpret_cast<const __half *>(k),
+                                         reinterpret_cast<const __half *>(v), reinterpret_cast<__half *>(output), batch, num_heads,
+                                         num_kv_heads, q_len, kv_len, head_dim, pos_offset, scale, to_stream(stream));
+        if (rc != -1000) return rc;
+    }
     return prefill_launch<__half>("flash_attn_full_f16", reinterpret_cast<const __half *>(q), reinterpret_cast<const __half *>(k),
                                   reinterpret_cast<const __half *>(v), reinterpret_cast<__half *>(output), batch, num_heads,
                                   num_kv_heads, q_len, kv_len, head_dim, pos_offset, scale, stream);
