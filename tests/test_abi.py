@@ -88,3 +88,24 @@ def test_oracle_is_not_reachable_from_the_package():
     for f in (ROOT / "triton-rs_b200").rglob("*"):
         if f.suffix in (".py", ".cu", ".cuh", ".h", ".cpp"):
             assert "oracle" not in f.read_text(), f
+
+
+def test_rust_sys_binding_is_generated_from_the_header(pkg):
+    """The committed Rust `-sys` source declares every prototype of the header, with the header's argument count,
+    and is what the generator writes today."""
+    import importlib.util
+    import re
+    spec = importlib.util.spec_from_file_location("rust_sys", pkg._lib.HERE / "rust_sys.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert mod.OUT.read_text() == mod.generate(), "run python triton-rs_b200/rust_sys.py"
+    text = mod.OUT.read_text()
+    protos = pkg.parse_header()
+    for name, (_, args) in protos.items():
+        m = re.search(r"pub fn " + name + r"\((.*?)\)", text, flags=re.S)
+        assert m, name
+        got = [a for a in m.group(1).split(",") if a.strip()]
+        assert len(got) == len(args), name
+    assert mod.rust_type("const b200k_half *") == "*const b200k_half"
+    assert mod.rust_type("void **") == "*mut *mut c_void"
+    assert mod.rust_type("struct b200k_comm **") == "*mut *mut b200k_comm"
