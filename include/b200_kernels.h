@@ -40,6 +40,7 @@ extern "C" {
 #endif
 
 typedef uint16_t b200k_half;
+typedef uint16_t b200k_bf16; /* bfloat16 stored as uint16_t */
 typedef void *b200k_stream; /* cudaStream_t */
 
 enum {
@@ -480,6 +481,64 @@ int rope_kv_append_hm_f16(const b200k_half *qkv, const float *cos_table,
                           b200k_half *q_out, b200k_half *k_cache, b200k_half *v_cache,
                           int num_q_heads, int num_kv_heads, int head_dim, int max_len,
                           int batch, b200k_stream stream);
+
+/* ------------------------------------------------------------------------- */
+/* bf16 editions                                                               */
+/* ------------------------------------------------------------------------- */
+/* The reference's `_typed` kernels are generic over T = f32 / f16 / bf16
+ * (crates/triton-dsl/examples/w4a16_gptq_gemm_typed.rs:65-67,
+ * crates/triton-dsl/tests/proc_macro_ferrum_typed.rs:6-19).  Same arguments as the _f16 entry points
+ * with bf16 tensors; arithmetic in fp32 inside, one rounding to bf16 at the store. */
+/* The two int4 GEMMs with bf16 activations, scales and output (dequantised weight rounded to bf16 before the
+ * product, as the reference's as_t::<T> does); qzeros NULL in the GPTQ edition = symmetric zero-point 8. */
+int w4a16_gptq_gemm_bf16(const b200k_bf16 *a, const int32_t *qweight, const b200k_bf16 *scales,
+                         const int32_t *qzeros, b200k_bf16 *c, int m_size, int n_size, int k_size,
+                         int group_size, int stride_am, int stride_ak, int stride_qwk,
+                         int stride_qwn, int stride_sk, int stride_sn, int stride_qzk,
+                         int stride_qzn, int stride_cm, int stride_cn, b200k_stream stream);
+int awq_gemm_int4_bf16(const b200k_bf16 *a, const int32_t *qweight, const b200k_bf16 *scales,
+                       const int32_t *qzeros, b200k_bf16 *c, int m_size, int n_size, int k_size,
+                       int group_size, int stride_am, int stride_ak, int stride_qwk,
+                       int stride_qwn, int stride_sk, int stride_sn, int stride_qzk,
+                       int stride_qzn, int stride_cm, int stride_cn, b200k_stream stream);
+/* decode_attention_typed / _hm_typed / paged_decode_attention_typed with T = bf16 (fp32 arithmetic inside). */
+int decode_attention_bf16(const b200k_bf16 *q, const b200k_bf16 *k_cache, const b200k_bf16 *v_cache,
+                          b200k_bf16 *output, int num_q_heads, int num_kv_heads, int head_dim,
+                          int valid_kv_len, float scale, b200k_stream stream);
+int decode_attention_hm_bf16(const b200k_bf16 *q, const b200k_bf16 *k_cache,
+                             const b200k_bf16 *v_cache, b200k_bf16 *output, int num_q_heads,
+                             int num_kv_heads, int head_dim, int capacity, int valid_kv_len,
+                             float scale, b200k_stream stream);
+int paged_decode_attention_bf16(const b200k_bf16 *q, const b200k_bf16 *k_block_pool,
+                                const b200k_bf16 *v_block_pool, const int32_t *block_table,
+                                b200k_bf16 *output, int num_q_heads, int num_kv_heads,
+                                int head_dim, int valid_kv_len, int block_size, float scale,
+                                b200k_stream stream);
+int rms_norm_bf16(const b200k_bf16 *input, const b200k_bf16 *weight, b200k_bf16 *output,
+                  int row_size, float inv_n, float eps, int num_rows, b200k_stream stream);
+int fused_add_rms_norm_bf16(const b200k_bf16 *input, const b200k_bf16 *residual,
+                            const b200k_bf16 *weight, b200k_bf16 *output,
+                            b200k_bf16 *residual_out, int hidden_size, float inv_n, float eps,
+                            int num_rows, b200k_stream stream);
+int residual_add_bf16(const b200k_bf16 *a, const b200k_bf16 *b, b200k_bf16 *out, int n,
+                      b200k_stream stream);
+int residual_add_inplace_bf16(b200k_bf16 *a, const b200k_bf16 *b, int n, b200k_stream stream);
+int fused_silu_mul_bf16(const b200k_bf16 *gate, const b200k_bf16 *up, b200k_bf16 *out, int n,
+                        b200k_stream stream);
+int fused_silu_mul_interleaved_bf16(const b200k_bf16 *gate_up, b200k_bf16 *out, int inter,
+                                    int total, b200k_stream stream);
+int rope_full_bf16(const b200k_bf16 *q, const float *cos_table, const float *sin_table,
+                   const int32_t *positions, b200k_bf16 *q_out, int num_heads, int head_dim,
+                   int num_tokens, b200k_stream stream);
+int kv_cache_append_hm_bf16(const b200k_bf16 *new_keys, const b200k_bf16 *new_values,
+                            b200k_bf16 *k_cache, b200k_bf16 *v_cache, const int32_t *cache_idx,
+                            int num_heads, int head_dim, int max_len, int batch,
+                            b200k_stream stream);
+int embedding_lookup_bf16(const b200k_bf16 *embeddings, const int32_t *indices,
+                          b200k_bf16 *output, int hidden_size, int num_tokens,
+                          b200k_stream stream);
+int softmax_bf16(const b200k_bf16 *input, b200k_bf16 *output, int rows, int cols,
+                 b200k_stream stream);
 
 /* ------------------------------------------------------------------------- */
 /* the two ends of a decode step                                               */

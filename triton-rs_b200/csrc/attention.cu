@@ -19,6 +19,8 @@
 
 #include <atomic>
 
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 #include "tma.cuh"
 
@@ -500,7 +502,9 @@ static int attn_split_launch(const char *name, AttnCall c) {
 template <typename T> __device__ __forceinline__ float ldf(const T *p);
 template <> __device__ __forceinline__ float ldf<float>(const float *p) { return *p; }
 template <> __device__ __forceinline__ float ldf<__half>(const __half *p) { return __half2float(*p); }
+template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
 template <typename T> __device__ __forceinline__ void stf(T *p, float v);
+template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ void stf<float>(float *p, float v) { *p = v; }
 template <> __device__ __forceinline__ void stf<__half>(__half *p, float v) { *p = __float2half_rn(v); }
 
@@ -687,6 +691,42 @@ extern "C" int paged_decode_attention_f16(const b200k_half *q, const b200k_half 
                   (long)block_size * num_kv_heads * head_dim};
     return decode_f16_common("paged_decode_attention_f16", q, k_block_pool, v_block_pool, output, num_q_heads,
                              num_kv_heads, head_dim, valid_kv_len, scale, L, KV_PAGED, block_size, stream);
+}
+
+// ---- bf16 editions of the three `_typed` decode kernels (attention.rs:51-164, 182-273, 399-490 are generic over T):
+// fp32 arithmetic on bf16 tensors, one CTA per (q head, split) on CUDA cores ---------------------------------------
+extern "C" int decode_attention_bf16(const b200k_bf16 *q, const b200k_bf16 *k_cache, const b200k_bf16 *v_cache,
+                                     b200k_bf16 *output, int num_q_heads, int num_kv_heads, int head_dim,
+                                     int valid_kv_len, float scale, b200k_stream stream) {
+    const char *name = "decode_attention_bf16";
+    int rc = attn_common_checks(name, q, k_cache, v_cache, output, num_q_heads, num_kv_heads, head_dim, valid_kv_len);
+    if (rc) return rc;
+    KvLayout L = {0, head_dim, (long)num_kv_heads * head_dim, nullptr, 0, 0};
+    return attn_generic_launch<__nv_bfloat16>(name, q, k_cache, v_cache, output, 1, num_q_heads, num_kv_heads, head_dim,
+                                              valid_kv_len, scale, L, to_stream(stream));
+}
+extern "C" int decode_attention_hm_bf16(const b200k_bf16 *q, const b200k_bf16 *k_cache, const b200k_bf16 *v_cache,
+                                        b200k_bf16 *output, int num_q_heads, int num_kv_heads, int head_dim, int capacity,
+                                        int valid_kv_len, float scale, b200k_stream stream) {
+    const char *name = "decode_attention_hm_bf16";
+    int rc = attn_common_checks(name, q, k_cache, v_cache, output, num_q_heads, num_kv_heads, head_dim, valid_kv_len);
+    if (rc) return rc;
+    B200K_REQUIRE(capacity >= valid_kv_len, B200K_E_SHAPE, "%s: capacity %d < valid_kv_len %d", name, capacity, valid_kv_len);
+    KvLayout L = {0, (long)capacity * head_dim, head_dim, nullptr, 0, 0};
+    return attn_generic_launch<__nv_bfloat16>(name, q, k_cache, v_cache, output, 1, num_q_heads, num_kv_heads, head_dim,
+                                              valid_kv_len, scale, L, to_stream(stream));
+}
+extern "C" int paged_decode_attention_bf16(const b200k_bf16 *q, const b200k_bf16 *k_block_pool, const b200k_bf16 *v_block_pool,
+                                           const int32_t *block_table, b200k_bf16 *output, int num_q_heads, int num_kv_heads,
+                                           int head_dim, int valid_kv_len, int block_size, float scale, b200k_stream stream) {
+    const char *name = "paged_decode_attention_bf16";
+    B200K_REQUIRE(block_table, B200K_E_NULL, "%s: block_table is NULL", name);
+    B200K_REQUIRE(block_size > 0, B200K_E_SHAPE, "%s: block_size %d", name, block_size);
+    int rc = attn_common_checks(name, q, k_block_pool, v_block_pool, output, num_q_heads, num_kv_heads, head_dim, valid_kv_len);
+    if (rc) return rc;
+    KvLayout L = {0, head_dim, (long)num_kv_heads * head_dim, block_table, block_size, (long)block_size * num_kv_heads * head_dim};
+    return attn_generic_launch<__nv_bfloat16>(name, q, k_block_pool, v_block_pool, output, 1, num_q_heads, num_kv_heads, head_dim,
+                                              valid_kv_len, scale, L, to_stream(stream));
 }
 
 // ---- fp16 batched, per-sequence lengths ---------------------------------------

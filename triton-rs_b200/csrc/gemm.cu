@@ -25,7 +25,14 @@ bool gemm_layout_is_canonical(const GemmArgs &g) {
 // Follows the reference arithmetic literally: integer nibble - zero, fp32 product
 // with the scale, rounded to fp16, fp32 accumulate.
 // ---------------------------------------------------------------------------
-template <int FMT>
+template <bool BF> __device__ __forceinline__ float ld_elem(const __half *p) {
+    return BF ? __bfloat162float(*reinterpret_cast<const __nv_bfloat16 *>(p)) : __half2float(*p);
+}
+template <bool BF> __device__ __forceinline__ float round_elem(float v) {
+    return BF ? __bfloat162float(__float2bfloat16_rn(v)) : __half2float(__float2half_rn(v));
+}
+
+template <int FMT, bool BF>
 __global__ void __launch_bounds__(128)
 gemm_strided_kernel(GemmArgs g) {
     const int n = blockIdx.x * 128 + threadIdx.x;
@@ -40,7 +47,7 @@ gemm_strided_kernel(GemmArgs g) {
     for (int k = 0; k < g.k; ++k) {
         if (k % g.group == 0) {
             const int grp = k / g.group;
-            scale = __half2float(g.scales[(long)grp * g.s_sk + (long)n * g.s_sn]);
+            scale = ld_elem<BF>(g.scales + (long)grp * g.s_sk + (long)n * g.s_sn);
             if (g.qzeros) {
                 const uint32_t zw = (uint32_t)g.qzeros[(long)grp * g.s_qzk + (long)(n / 8) * g.s_qzn];
                 const int slot = FMT == FMT_AWQ ? awq_slot(n % 8) : n % 8;
@@ -55,22 +62,25 @@ gemm_strided_kernel(GemmArgs g) {
             const uint32_t w = (uint32_t)g.qweight[(long)k * g.s_qwk + (long)(n / 8) * g.s_qwn];
             q = (int)((w >> (4 * awq_slot(n % 8))) & 15u);
         }
-        const float wv = __half2float(__float2half_rn((float)(q - zero) * scale));
+        const float wv = round_elem<BF>((float)(q - zero) * scale);
 #pragma unroll
         for (int r = 0; r < 8; ++r)
-            if (r < rows) acc[r] += __half2float(g.a[(long)(m0 + r) * g.s_am + (long)k * g.s_ak]) * wv;
+            if (r < rows) acc[r] += ld_elem<BF>(g.a + (long)(m0 + r) * g.s_am + (long)k * g.s_ak) * wv;
     }
 #pragma unroll
     for (int r = 0; r < 8; ++r)
-        if (r < rows) g.c[(long)(m0 + r) * g.s_cm + (long)n * g.s_cn] = __float2half_rn(acc[r]);
+        if (r < rows) store_elem<BF>(g.c + (long)(m0 + r) * g.s_cm + (long)n * g.s_cn, acc[r]);
 }
 
 int gemm_strided_launch(const GemmArgs &g) {
     dim3 grid(ceil_div(g.n, 128), ceil_div(g.m, 8));
-    if (g.format == FMT_GPTQ)
-        gemm_strided_kernel<FMT_GPTQ><<<grid, 128, 0, g.stream>>>(g);
-    else
-        gemm_strided_kernel<FMT_AWQ><<<grid, 128, 0, g.stream>>>(g);
+    if (g.format == FMT_GPTQ) {
+        if (g.bf16) gemm_strided_kernel<FMT_GPTQ, true><<<grid, 128, 0, g.stream>>>(g);
+        else gemm_strided_kernel<FMT_GPTQ, false><<<grid, 128, 0, g.stream>>>(g);
+    } else {
+        if (g.bf16) gemm_strided_kernel<FMT_AWQ, true><<<grid, 128, 0, g.stream>>>(g);
+        else gemm_strided_kernel<FMT_AWQ, false><<<grid, 128, 0, g.stream>>>(g);
+    }
     return launch_status("w4a16 gemm (strided)");
 }
 
@@ -500,7 +510,7 @@ static int gemm_dispatch(const char *name, GemmArgs g, bool own_ws) {
     }
     const int force = env_char("B200K_GEMM_PATH");  // tuning/testing override: s(trided) | g(emv) | t(c)
     if (force == 's') return gemm_strided_launch(g);
-    if (canon && g.m == 1 && g.k <= 65536 && force != 't') return gemv_launch(g);
+    if (canon && g.m == 1 && g.k <= 65536 && force != 't' && !g.bf16) return gemv_launch(g);
     if (canon) {
         if (!g.ws && own_ws) {
             int rc = default_workspace(&g.ws, &g.ws_bytes);
@@ -524,7 +534,7 @@ using namespace b200k;
     g.s_sk = stride_sk; g.s_sn = stride_sn; g.s_cm = stride_cm; g.s_cn = stride_cn;                   \
     g.format = FMT; g.zero_offset = ZO; g.stream = to_stream(stream);                                 \
     g.seg_offsets = nullptr; g.num_segments = 0; g.plan_out = nullptr; g.a_kperm = false;                \
-    g.silu_inter = 0; g.tile_list = nullptr; g.tile_count = nullptr; g.max_tiles = 0;
+    g.silu_inter = 0; g.tile_list = nullptr; g.tile_count = nullptr; g.max_tiles = 0; g.bf16 = false;
 
 extern "C" int w4a16_gptq_gemm_f16_ws(const b200k_half *a, const int32_t *qweight, const b200k_half *scales,
                                       const int32_t *qzeros, b200k_half *c, int m_size, int n_size, int k_size,
@@ -573,6 +583,31 @@ extern "C" int awq_gemm_int4_f16(const b200k_half *a, const int32_t *qweight, co
     return awq_gemm_int4_f16_ws(a, qweight, scales, qzeros, c, m_size, n_size, k_size, group_size, stride_am, stride_ak,
                                 stride_qwk, stride_qwn, stride_sk, stride_sn, stride_qzk, stride_qzn, stride_cm,
                                 stride_cn, nullptr, 0, stream);
+}
+
+// bf16 editions of the two GEMMs (the reference kernels are generic over T, w4a16_gptq_gemm_typed.rs:65-67): a, scales
+// and c are bf16; tensor-core path for contiguous operands, strided path otherwise.
+extern "C" int w4a16_gptq_gemm_bf16(const b200k_bf16 *a, const int32_t *qweight, const b200k_bf16 *scales,
+                                    const int32_t *qzeros, b200k_bf16 *c, int m_size, int n_size, int k_size,
+                                    int group_size, int stride_am, int stride_ak, int stride_qwk, int stride_qwn,
+                                    int stride_sk, int stride_sn, int stride_qzk, int stride_qzn, int stride_cm,
+                                    int stride_cn, b200k_stream stream) {
+    GEMM_ARGS_FILL(FMT_GPTQ, qzeros ? 1 : 0)
+    g.qzeros = qzeros; g.s_qzk = stride_qzk; g.s_qzn = qzeros ? stride_qzn : 1;      // qzeros NULL: symmetric zero-point 8
+    g.ws = nullptr; g.ws_bytes = 0;
+    g.bf16 = true;
+    return gemm_dispatch("w4a16_gptq_gemm_bf16", g, true);
+}
+extern "C" int awq_gemm_int4_bf16(const b200k_bf16 *a, const int32_t *qweight, const b200k_bf16 *scales,
+                                  const int32_t *qzeros, b200k_bf16 *c, int m_size, int n_size, int k_size,
+                                  int group_size, int stride_am, int stride_ak, int stride_qwk, int stride_qwn,
+                                  int stride_sk, int stride_sn, int stride_qzk, int stride_qzn, int stride_cm,
+                                  int stride_cn, b200k_stream stream) {
+    GEMM_ARGS_FILL(FMT_AWQ, 0)
+    g.qzeros = qzeros; g.s_qzk = stride_qzk; g.s_qzn = stride_qzn;
+    g.ws = nullptr; g.ws_bytes = 0;
+    g.bf16 = true;
+    return gemm_dispatch("awq_gemm_int4_bf16", g, true);
 }
 
 static int dequant_launch(const char *name, const int32_t *qw, const __half *sc, const int32_t *qz, __half *out,

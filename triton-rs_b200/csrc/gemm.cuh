@@ -1,6 +1,8 @@
 // Shared description of one W4A16 GEMM call, handed from the C-ABI entry points to
 // the kernel families (strided CUDA-core, split-K GEMV, tcgen05 tensor-core).
 #pragma once
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 
 namespace b200k {
@@ -32,6 +34,7 @@ struct GemmArgs {
     const int2 *tile_list;
     const int *tile_count;
     int max_tiles;
+    bool bf16;        // a, scales and c are bfloat16 instead of fp16 (tensor-core and strided families)
     bool a_kperm;     // activations pre-permuted per 8 consecutive k to (k0,k4,k1,k5,k2,k6,k3,k7) (tensor-core GPTQ path, GEMV)
     int *plan_out;    // host pointer: when set, the tensor-core family writes its launch plan there and launches nothing
     void *ws;         // scratch (may be nullptr when the chosen path needs none)
@@ -81,6 +84,49 @@ __device__ __forceinline__ uint32_t h22u(__half2 h) { return *reinterpret_cast<u
 __device__ __forceinline__ void zero_magic(int z, __half2 &zlo, __half2 &zhi) {
     zlo = u2h2((uint32_t)(0x6400 + z) * 0x10001u);
     zhi = u2h2((uint32_t)(0x5400 + (z << 4)) * 0x10001u);
+}
+
+// ---- the same for bf16 (7 mantissa bits): only a nibble at bits 0..3 of a half can be turned into a number by
+// OR-ing an exponent, (w & 0x000F000F) | 0x43004300 -> (128 + n0, 128 + n4); the other three pairs come from
+// w >> 4, w >> 8, w >> 12.  Subtracting (128 + z) is exact and one bf16 multiply by the scale rounds once, like the
+// reference's f32 product rounded to bf16 (a 5-bit integer times an 8-bit significand is exact in fp32).
+__device__ __forceinline__ uint32_t nib_bf(uint32_t w) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, 0x000F000F, 0x43004300, 0xEA;" : "=r"(r) : "r"(w));
+    return r;
+}
+// The four value pairs of a word, (n0,n4) (n1,n5) (n2,n6) (n3,n7), as biased numbers of the element type
+template <bool BF> __device__ __forceinline__ void nib4(uint32_t w, uint32_t (&x)[4]) {
+    if (BF) {
+        x[0] = nib_bf(w); x[1] = nib_bf(w >> 4); x[2] = nib_bf(w >> 8); x[3] = nib_bf(w >> 12);
+    } else {
+        const uint32_t w8 = w >> 8;
+        x[0] = nib_lo(w); x[1] = nib_hi(w); x[2] = nib_lo(w8); x[3] = nib_hi(w8);
+    }
+}
+// The biases of those four pairs plus a zero-point z, in both halves
+template <bool BF> __device__ __forceinline__ void zero_magic4(int z, uint32_t (&m)[4]) {
+    if (BF) {
+        m[0] = m[1] = m[2] = m[3] = (uint32_t)(0x4300 + z) * 0x10001u;
+    } else {
+        __half2 zl, zh;
+        zero_magic(z, zl, zh);
+        m[0] = m[2] = h22u(zl);
+        m[1] = m[3] = h22u(zh);
+    }
+}
+// (x - z) * s on a pair, in the element type: exact difference, one rounding
+template <bool BF> __device__ __forceinline__ uint32_t sub_mul(uint32_t x, uint32_t z, uint32_t s) {
+    if (BF) {
+        const __nv_bfloat162 r = __hmul2(__hsub2(*reinterpret_cast<__nv_bfloat162 *>(&x), *reinterpret_cast<__nv_bfloat162 *>(&z)),
+                                         *reinterpret_cast<__nv_bfloat162 *>(&s));
+        return *reinterpret_cast<const uint32_t *>(&r);
+    }
+    return h22u(__hmul2(__hsub2(u2h2(x), u2h2(z)), u2h2(s)));
+}
+template <bool BF> __device__ __forceinline__ void store_elem(__half *p, float v) {
+    if (BF) *reinterpret_cast<__nv_bfloat16 *>(p) = __float2bfloat16_rn(v);
+    else *p = __float2half_rn(v);
 }
 
 // position of column j (0..7) inside an AWQ word (awq_gemm_int4_typed.rs:137-151)

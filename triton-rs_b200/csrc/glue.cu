@@ -2,6 +2,8 @@
 // fused_silu_mul (+interleaved), RoPE, kv-cache append.  All are one pass over
 // their operands with 128-bit accesses where the extents and pointers allow it
 // and a scalar path otherwise; reductions and transcendental math are fp32.
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 
 namespace b200k {
@@ -33,6 +35,31 @@ template <> struct Elem<__half> {
     }
     __device__ static float ld1(const __half *p) { return __half2float(*p); }
     __device__ static void st1(__half *p, float v) { *p = __float2half_rn(v); }
+};
+// bf16: the upper 16 bits of an fp32; widened exactly, rounded to nearest even on the way back
+template <> struct Elem<__nv_bfloat16> {
+    static constexpr int VEC = 8;
+    __device__ static void load(const __nv_bfloat16 *p, float (&f)[8]) {
+        const uint4 u = *reinterpret_cast<const uint4 *>(p);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+        }
+    }
+    __device__ static uint32_t pack(float a, float b) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<const uint32_t *>(&h);
+    }
+    __device__ static void store(__nv_bfloat16 *p, const float (&f)[8]) {
+        *reinterpret_cast<uint4 *>(p) = make_uint4(pack(f[0], f[1]), pack(f[2], f[3]), pack(f[4], f[5]), pack(f[6], f[7]));
+    }
+    __device__ static void store_kperm(__nv_bfloat16 *p, const float (&f)[8]) {
+        *reinterpret_cast<uint4 *>(p) = make_uint4(pack(f[0], f[4]), pack(f[1], f[5]), pack(f[2], f[6]), pack(f[3], f[7]));
+    }
+    __device__ static float ld1(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
+    __device__ static void st1(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
 };
 template <> struct Elem<float> {
     static constexpr int VEC = 4;
@@ -546,4 +573,47 @@ extern "C" int rope_kv_append_hm_f16(const b200k_half *qkv, const float *cos_tab
     return rope_kv_append_lens_launch((const __half *)qkv, cos_table, sin_table, positions, (__half *)q_out,
                                       (__half *)k_cache, (__half *)v_cache, nullptr, num_q_heads, num_kv_heads,
                                       head_dim, max_len, batch, to_stream(s));
+}
+
+// ---------------------------------------------------------------------------
+// bf16 editions: the reference's `_typed` glue kernels are generic over T = f32 / f16 / bf16
+// (crates/triton-dsl/tests/proc_macro_ferrum_typed.rs:6-19); same kernels, same fp32 arithmetic inside.
+// ---------------------------------------------------------------------------
+typedef __nv_bfloat16 bf16;
+extern "C" int rms_norm_bf16(const b200k_bf16 *input, const b200k_bf16 *weight, b200k_bf16 *output, int row_size, float inv_n,
+                             float eps, int num_rows, b200k_stream stream) {
+    return rms_norm_launch<bf16, false>("rms_norm_bf16", (const bf16 *)input, nullptr, (const bf16 *)weight, (bf16 *)output, nullptr,
+                                        row_size, inv_n, eps, num_rows, to_stream(stream));
+}
+extern "C" int fused_add_rms_norm_bf16(const b200k_bf16 *input, const b200k_bf16 *residual, const b200k_bf16 *weight,
+                                       b200k_bf16 *output, b200k_bf16 *residual_out, int hidden_size, float inv_n, float eps,
+                                       int num_rows, b200k_stream stream) {
+    return rms_norm_launch<bf16, true>("fused_add_rms_norm_bf16", (const bf16 *)input, (const bf16 *)residual, (const bf16 *)weight,
+                                       (bf16 *)output, (bf16 *)residual_out, hidden_size, inv_n, eps, num_rows, to_stream(stream));
+}
+extern "C" int residual_add_bf16(const b200k_bf16 *a, const b200k_bf16 *b, b200k_bf16 *out, int n, b200k_stream stream) {
+    return binary_launch<bf16, OP_ADD>("residual_add_bf16", (const bf16 *)a, (const bf16 *)b, (bf16 *)out, n, to_stream(stream));
+}
+extern "C" int residual_add_inplace_bf16(b200k_bf16 *a, const b200k_bf16 *b, int n, b200k_stream stream) {
+    return binary_launch<bf16, OP_ADD>("residual_add_inplace_bf16", (const bf16 *)a, (const bf16 *)b, (bf16 *)a, n, to_stream(stream));
+}
+extern "C" int fused_silu_mul_bf16(const b200k_bf16 *gate, const b200k_bf16 *up, b200k_bf16 *out, int n, b200k_stream stream) {
+    return binary_launch<bf16, OP_SILU_MUL>("fused_silu_mul_bf16", (const bf16 *)gate, (const bf16 *)up, (bf16 *)out, n, to_stream(stream));
+}
+extern "C" int fused_silu_mul_interleaved_bf16(const b200k_bf16 *gate_up, b200k_bf16 *out, int inter, int total, b200k_stream stream) {
+    return silu_interleaved_launch<bf16>("fused_silu_mul_interleaved_bf16", (const bf16 *)gate_up, (bf16 *)out, inter, total, to_stream(stream));
+}
+extern "C" int rope_full_bf16(const b200k_bf16 *q, const float *cos_table, const float *sin_table, const int32_t *positions,
+                              b200k_bf16 *q_out, int num_heads, int head_dim, int num_tokens, b200k_stream stream) {
+    B200K_REQUIRE(positions, B200K_E_NULL, "rope_full_bf16: positions is NULL");
+    return rope_launch<bf16>("rope_full_bf16", (const bf16 *)q, cos_table, sin_table, positions, (bf16 *)q_out, num_heads, head_dim,
+                             num_tokens, to_stream(stream));
+}
+extern "C" int kv_cache_append_hm_bf16(const b200k_bf16 *new_keys, const b200k_bf16 *new_values, b200k_bf16 *k_cache,
+                                       b200k_bf16 *v_cache, const int32_t *cache_idx, int num_heads, int head_dim, int max_len,
+                                       int batch, b200k_stream stream) {
+    // a move of 16-bit elements: the fp16 kernel
+    return kv_append_launch<__half, true>("kv_cache_append_hm_bf16", (const __half *)new_keys, (const __half *)new_values,
+                                          (__half *)k_cache, (__half *)v_cache, cache_idx, num_heads, head_dim, max_len, batch,
+                                          to_stream(stream));
 }

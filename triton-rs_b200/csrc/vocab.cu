@@ -1,6 +1,8 @@
 // The two ends of a decode step around the layer stack: the embedding gather before the first
 // layer and the row softmax over the logits after the last (embedding.rs, reduction.rs of the
 // reference's kernel crate).  Both are bandwidth-bound single passes.
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 
 namespace b200k {
@@ -41,7 +43,9 @@ static int embedding_launch(const char *name, const T *table, const int32_t *ind
 template <typename T> __device__ __forceinline__ float to_f(T v);
 template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
 template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
 
@@ -109,4 +113,13 @@ extern "C" int softmax_f32(const float *input, float *output, int rows, int cols
 }
 extern "C" int softmax_f16(const b200k_half *input, b200k_half *output, int rows, int cols, b200k_stream stream) {
     return softmax_launch<__half>("softmax_f16", (const __half *)input, (__half *)output, rows, cols, to_stream(stream));
+}
+extern "C" int embedding_lookup_bf16(const b200k_bf16 *embeddings, const int32_t *indices, b200k_bf16 *output, int hidden_size,
+                                     int num_tokens, b200k_stream stream) {
+    // a gather of 16-bit elements: the fp16 kernel
+    return embedding_launch<__half>("embedding_lookup_bf16", (const __half *)embeddings, indices, (__half *)output, hidden_size,
+                                    num_tokens, to_stream(stream));
+}
+extern "C" int softmax_bf16(const b200k_bf16 *input, b200k_bf16 *output, int rows, int cols, b200k_stream stream) {
+    return softmax_launch<__nv_bfloat16>("softmax_bf16", (const __nv_bfloat16 *)input, (__nv_bfloat16 *)output, rows, cols, to_stream(stream));
 }
