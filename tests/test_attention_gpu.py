@@ -225,7 +225,9 @@ def test_flash_attn_full_vs_oracle(P, oracle, dtype, b, hq, hkv, q_len, kv_len, 
     (1, 2, 2, 260, 150, 0),           # queries past the end of the KV stream
     (1, 8, 1, 128, 128, 0),           # exactly one tile; GQA group of 8
     (2, 4, 4, 129, 1, 0),             # a single KV position
-    (1, 2, 1, 640, 640, 0),           # five tiles: both ring slots and both S buffers wrap twice
+    (1, 2, 1, 640, 640, 0),           # five tiles: both ring slots wrap twice; the last pair of query tiles is half empty
+    (1, 2, 2, 300, 1000, 700),        # chunked prefill: the queries start at position 700 of a longer KV stream
+    (1, 32, 8, 2048, 2048, 0),        # one 2048-token sequence of the Llama-3-8B head layout (the timed size)
 ])
 def test_flash_attn_full_f16_head_dim_128_tensor_core_path(P, oracle, b, hq, hkv, q_len, kv_len, off):
     """head_dim 128 in fp16 runs on the tcgen05 kernel (128 x 128 tiles): tile boundaries, the causal diagonal inside a

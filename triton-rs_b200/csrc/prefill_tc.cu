@@ -1,19 +1,26 @@
 // Causal prefill attention (flash_attn_full, fp16, head_dim 128) on the 5th-generation tensor cores.
 //
-// One CTA per (sequence, q head, tile of 128 query rows).  Both contractions of a KV tile of 128 positions are
-// tcgen05.mma instructions with their accumulators in tensor memory:
+// One CTA per (sequence, q head, PAIR of 128-row query tiles a, b).  Both contractions of a KV tile of 128 positions
+// are tcgen05.mma instructions with their accumulators in tensor memory:
 //     S = Q K^T     A = Q tile (shared memory, K-major), B = K tile (shared memory, K-major)      128 x 128 x 128
-//     O'= P V       A = P (fp16, written to tensor memory by the softmax warps), B = V tile (shared memory, MN-major)
-// Warp roles:  warps 0..3  softmax + output: thread = one query row = one tensor-memory lane; running max, sum and the
-//                          128 output values of its row stay in registers (fp32)
-//              warp 4      TMA producer: Q once, K and V tiles into two-deep rings (4-D tensor maps, 128-byte swizzle)
-//              warp 5      MMA issuer (one thread)
-// Per KV tile j the issuer queues S(j+1) ahead of P(j) V(j), so the tensor pipe computes the next scores while the
-// softmax warps turn S(j) into P(j), and P(j) V(j) runs while they take the row maxima of S(j+1):
-//     softmax(j):  wait S(j) -> row max, alpha = 2^(m_old - m_new) -> wait P(j-1)V(j-1): O = (O + O') * alpha
-//                  -> P(j) = 2^(S(j) - m_new), l = l * alpha + sum P(j) -> tensor memory -> signal
+//     O += P V      A = P (fp16, written to tensor memory by the softmax warps), B = V tile (shared memory, MN-major)
+// Tensor memory (512 columns): S_a [0,128)  S_b [128,256)  O_a [256,384)  O_b [384,512).  P_x overwrites the first 64
+// columns of S_x: a thread owns one query row = one lane, holds its whole S row in registers before it writes P, and the
+// tensor pipe runs one CTA's MMAs in issue order, so S_x(j+1) is issued behind P_x(j) V(j) and cannot overtake it.
+// Warp roles:  warps 0..3 / 4..7  softmax of tile a / b (thread = query row = tensor-memory lane)
+//              warp 8             TMA producer: both Q tiles once, K and V tiles into two-deep rings shared by a and b
+//                                 (4-D tensor maps, 128-byte swizzle)
+//              warp 9             MMA issuer (one thread)
+//              warps 10, 11       idle (they complete the warpgroup whose registers setmaxnreg gives away)
+// Issue order per KV tile j:  P_a(j)V(j), S_a(j+1), P_b(j)V(j), S_b(j+1): while one tile's softmax warps work, the tensor
+// pipe serves the other tile.
+// Softmax per row, base-2 domain: the output accumulates in tensor memory across KV tiles without being read back.  The
+// running maximum m is only raised when the tile's maximum exceeds it by more than 8 (a factor 256, far inside fp16 and
+// fp32 range); then the warp rescales its 32 rows of O in tensor memory (load, multiply, store) and l.  Otherwise P is
+// computed against the older m, which the final division by l cancels exactly.
 // Causal structure: query row i sees kv positions 0 .. min(pos_offset + i, kv_len - 1); KV tiles entirely above the
-// diagonal of the query tile are never loaded, tiles entirely below it skip the mask.
+// diagonal of a query tile are never multiplied for it (and never loaded if neither tile needs them), tiles entirely
+// below it skip the mask.
 // Every mbarrier wait is bounded; a wait that gives up sets the status word and the CTA drains.
 #include "tcgen05.cuh"
 #include "tma.cuh"
@@ -21,15 +28,18 @@
 namespace b200k {
 
 constexpr int PT_D = 128, PT_BQ = 128, PT_BKV = 128;
-constexpr int PT_THREADS = 192;
+constexpr int PT_SOFTMAX_WARPS = 8;
+constexpr int PT_THREADS = (PT_SOFTMAX_WARPS + 4) * 32;     // third warpgroup: TMA warp, MMA warp, two idle warps
+// Registers: 384 threads get 168 each at launch; the third warpgroup hands most of its share to the softmax warps
+// (2 x 128 x 232 + 128 x 40 = 384 x 168), whose rows of 128 scores live in registers.
+constexpr int PT_REGS_SOFTMAX = 232, PT_REGS_AUX = 40;
 constexpr int PT_TILE_BYTES = PT_BQ * PT_D * 2;           // 32 KiB: two halves of [128 rows][64 dims] (128-byte rows, swizzled)
 constexpr int PT_HALF_BYTES = PT_TILE_BYTES / 2;
 constexpr int PT_STAGES = 2;
-// tensor-memory columns
-constexpr uint32_t PT_COL_S = 0;        // S(j) at 128 * (j % 2)
-constexpr uint32_t PT_COL_O = 256;      // P V of the current tile (fp32)
-constexpr uint32_t PT_COL_P = 384;      // P as fp16 pairs: 64 columns
+constexpr uint32_t PT_COL_S = 0;        // S_x at 128 x; P_x on its first 64 columns
+constexpr uint32_t PT_COL_O = 256;      // O_x at 256 + 128 x
 constexpr uint32_t PT_COLS = 512;
+constexpr float PT_RESCALE_THRESHOLD = 8.f;
 
 struct PtArgs {
     __half *out;
@@ -44,32 +54,44 @@ enum {
     PB_KFREE = 3,                    // [2] K tile consumed (S MMAs retired)
     PB_VFULL = 5,                    // [2]
     PB_VFREE = 7,                    // [2] V tile consumed (P V MMAs retired)
-    PB_SFULL = 9,                    // [2] S(j) complete in tensor memory
-    PB_SFREE = 11,                   // [2] S(j) read by the softmax warps for the last time (4 arrivals)
-    PB_PFULL = 13,                   // P(j) written (4 arrivals)
-    PB_ODONE = 14,                   // P(j) V(j) retired
+    PB_SFULL = 9,                    // [2: tile a, b] S_x(j) complete in tensor memory (and every MMA issued before it)
+    PB_PFULL = 11,                   // [2: tile a, b] P_x(j) written (4 arrivals)
+    PB_OFINAL = 13,                  // [2: tile a, b] last P_x V retired
     PB_COUNT = 15
 };
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 __global__ void __launch_bounds__(PT_THREADS, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                   const __grid_constant__ CUtensorMap vmap, PtArgs A) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    unsigned char *q_tile = smem;                                   // 32 KiB
-    unsigned char *k_tile = q_tile + PT_TILE_BYTES;                 // [2][32 KiB]
+    unsigned char *q_tile = smem;                                   // [2][32 KiB]: tiles a, b
+    unsigned char *k_tile = q_tile + 2 * PT_TILE_BYTES;             // [2][32 KiB]
     unsigned char *v_tile = k_tile + PT_STAGES * PT_TILE_BYTES;     // [2][32 KiB]
     unsigned long long *bars = reinterpret_cast<unsigned long long *>(v_tile + PT_STAGES * PT_TILE_BYTES);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + PB_COUNT);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int qt = gridDim.x - 1 - blockIdx.x;        // long tiles first
+    const int qp = gridDim.x - 1 - blockIdx.x;        // long pairs first
     const int h = blockIdx.y, b = blockIdx.z, kvh = h / (A.hq / A.hkv);
-    const int q0 = qt * PT_BQ;
-    // KV tiles this query tile needs: positions 0 .. min(pos_offset + q0 + 127, kv_len - 1)
-    const int last_pos = min(A.pos_offset + min(q0 + PT_BQ, A.q_len) - 1, A.kv_len - 1);
-    const int ntiles = last_pos / PT_BKV + 1;
+    const int q0 = qp * 2 * PT_BQ;
+    // KV tiles that query tile x (rows q0 + 128 x ..) needs: positions 0 .. min(pos_offset + its last row, kv_len - 1);
+    // none when the tile lies beyond q_len
+    auto tiles_of = [&](int x) {
+        const int r0 = q0 + x * PT_BQ;
+        if (r0 >= A.q_len) return 0;
+        const int last_pos = min(A.pos_offset + min(r0 + PT_BQ, A.q_len) - 1, A.kv_len - 1);
+        return last_pos / PT_BKV + 1;
+    };
+    const int nt_a = tiles_of(0), nt_b = tiles_of(1);
+    const int ntiles = max(nt_a, nt_b);
 
     if (tid == 0) {
         mbar_init(smem_u32(&bars[PB_Q]), 1);
@@ -79,10 +101,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
             mbar_init(smem_u32(&bars[PB_VFULL + s]), 1);
             mbar_init(smem_u32(&bars[PB_VFREE + s]), 1);
             mbar_init(smem_u32(&bars[PB_SFULL + s]), 1);
-            mbar_init(smem_u32(&bars[PB_SFREE + s]), 4);
+            mbar_init(smem_u32(&bars[PB_PFULL + s]), 4);
+            mbar_init(smem_u32(&bars[PB_OFINAL + s]), 1);
         }
-        mbar_init(smem_u32(&bars[PB_PFULL]), 4);
-        mbar_init(smem_u32(&bars[PB_ODONE]), 1);
         *abort_flag = 0;
         mbar_init_fence();
     }
@@ -105,172 +126,194 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         }
     };
 
-    if (warp == 4) {
-        // ---------------- TMA producer ----------------
-        if (lane == 0) {
-            tma_prefetch_desc(&qmap);
-            tma_prefetch_desc(&kmap);
-            tma_prefetch_desc(&vmap);
-            const uint32_t qb = smem_u32(&bars[PB_Q]);
-            mbar_expect_tx(qb, PT_TILE_BYTES);
-            tma_load_4d(smem_u32(q_tile), &qmap, 0, q0, h, b, qb);
-            tma_load_4d(smem_u32(q_tile + PT_HALF_BYTES), &qmap, 64, q0, h, b, qb);
-            for (int j = 0; j < ntiles; ++j) {
-                const int s = j & 1;
-                const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-                if (j >= PT_STAGES) wait(PB_KFREE + s, ph ^ 1u);
-                const uint32_t kb = smem_u32(&bars[PB_KFULL + s]);
-                mbar_expect_tx(kb, PT_TILE_BYTES);
-                tma_load_4d(smem_u32(k_tile + s * PT_TILE_BYTES), &kmap, 0, j * PT_BKV, kvh, b, kb);
-                tma_load_4d(smem_u32(k_tile + s * PT_TILE_BYTES + PT_HALF_BYTES), &kmap, 64, j * PT_BKV, kvh, b, kb);
-                if (j >= PT_STAGES) wait(PB_VFREE + s, ph ^ 1u);
-                const uint32_t vb = smem_u32(&bars[PB_VFULL + s]);
-                mbar_expect_tx(vb, PT_TILE_BYTES);
-                tma_load_4d(smem_u32(v_tile + s * PT_TILE_BYTES), &vmap, 0, j * PT_BKV, kvh, b, vb);
-                tma_load_4d(smem_u32(v_tile + s * PT_TILE_BYTES + PT_HALF_BYTES), &vmap, 64, j * PT_BKV, kvh, b, vb);
-            }
-        }
-    } else if (warp == 5) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            const uint32_t idesc_s = umma_idesc(PT_BQ, PT_BKV, 0);          // A, B K-major
-            const uint32_t idesc_o = umma_idesc_b_mn(PT_BQ, PT_D);          // A from tensor memory, B (V) MN-major
-            const uint64_t dq = umma_desc(smem_u32(q_tile), 16, 1024);
-            auto issue_s = [&](int j) {
-                const int s = j & 1;
-                wait(PB_KFULL + s, (uint32_t)(j >> 1) & 1u);
-                if (j >= 2) wait(PB_SFREE + s, ((uint32_t)(j >> 1) & 1u) ^ 1u);      // S(j - 2) has been read
-                tc_fence_after();
-                const uint64_t dk = umma_desc(smem_u32(k_tile + s * PT_TILE_BYTES), 16, 1024);
-#pragma unroll
-                for (int kk = 0; kk < PT_D / 16; ++kk) {
-                    // 16 dims per MMA: 32 bytes inside the 128-byte swizzle row; dims 64.. live in the second half tile
-                    const uint64_t off = (uint64_t)(((kk >> 2) * PT_HALF_BYTES + (kk & 3) * 32) >> 4);
-                    tc_mma_f16(tmem + PT_COL_S + s * 128, dq + off, dk + off, idesc_s, kk > 0 ? 1u : 0u);
+    if (warp >= PT_SOFTMAX_WARPS) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PT_REGS_AUX));
+        if (warp == PT_SOFTMAX_WARPS) {
+            // ---------------- TMA producer ----------------
+            if (lane == 0) {
+                tma_prefetch_desc(&qmap);
+                tma_prefetch_desc(&kmap);
+                tma_prefetch_desc(&vmap);
+                const uint32_t qb = smem_u32(&bars[PB_Q]);
+                mbar_expect_tx(qb, 2 * PT_TILE_BYTES);         // rows beyond q_len arrive as zeros and still count
+                for (int x = 0; x < 2; ++x) {
+                    tma_load_4d(smem_u32(q_tile + x * PT_TILE_BYTES), &qmap, 0, q0 + x * PT_BQ, h, b, qb);
+                    tma_load_4d(smem_u32(q_tile + x * PT_TILE_BYTES + PT_HALF_BYTES), &qmap, 64, q0 + x * PT_BQ, h, b, qb);
                 }
-                tc_commit(smem_u32(&bars[PB_SFULL + s]));
-                tc_commit(smem_u32(&bars[PB_KFREE + s]));
-            };
-            wait(PB_Q, 0);
-            issue_s(0);
-            for (int j = 0; j < ntiles; ++j) {
-                if (j + 1 < ntiles) issue_s(j + 1);
-                const int s = j & 1;
-                wait(PB_VFULL + s, (uint32_t)(j >> 1) & 1u);
-                wait(PB_PFULL, (uint32_t)j & 1u);
+                for (int j = 0; j < ntiles; ++j) {
+                    const int s = j & 1;
+                    const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+                    if (j >= PT_STAGES) wait(PB_KFREE + s, ph ^ 1u);
+                    const uint32_t kb = smem_u32(&bars[PB_KFULL + s]);
+                    mbar_expect_tx(kb, PT_TILE_BYTES);
+                    tma_load_4d(smem_u32(k_tile + s * PT_TILE_BYTES), &kmap, 0, j * PT_BKV, kvh, b, kb);
+                    tma_load_4d(smem_u32(k_tile + s * PT_TILE_BYTES + PT_HALF_BYTES), &kmap, 64, j * PT_BKV, kvh, b, kb);
+                    if (j >= PT_STAGES) wait(PB_VFREE + s, ph ^ 1u);
+                    const uint32_t vb = smem_u32(&bars[PB_VFULL + s]);
+                    mbar_expect_tx(vb, PT_TILE_BYTES);
+                    tma_load_4d(smem_u32(v_tile + s * PT_TILE_BYTES), &vmap, 0, j * PT_BKV, kvh, b, vb);
+                    tma_load_4d(smem_u32(v_tile + s * PT_TILE_BYTES + PT_HALF_BYTES), &vmap, 64, j * PT_BKV, kvh, b, vb);
+                }
+            }
+        } else if (warp == PT_SOFTMAX_WARPS + 1) {
+            // ---------------- MMA issuer ----------------
+            if (lane == 0) {
+                const uint32_t idesc_s = umma_idesc(PT_BQ, PT_BKV, 0);          // A, B K-major
+                const uint32_t idesc_o = umma_idesc_b_mn(PT_BQ, PT_D);          // A from tensor memory, B (V) MN-major
+                // S_x(j) = Q_x K(j)^T; the caller has seen K(j) land
+                auto issue_s = [&](int x, int j) {
+                    const uint64_t dq = umma_desc(smem_u32(q_tile + x * PT_TILE_BYTES), 16, 1024);
+                    const uint64_t dk = umma_desc(smem_u32(k_tile + (j & 1) * PT_TILE_BYTES), 16, 1024);
+    #pragma unroll
+                    for (int kk = 0; kk < PT_D / 16; ++kk) {
+                        // 16 dims per MMA: 32 bytes inside the 128-byte swizzle row; dims 64.. live in the second half tile
+                        const uint64_t off = (uint64_t)(((kk >> 2) * PT_HALF_BYTES + (kk & 3) * 32) >> 4);
+                        tc_mma_f16(tmem + PT_COL_S + x * 128, dq + off, dk + off, idesc_s, kk > 0 ? 1u : 0u);
+                    }
+                    tc_commit(smem_u32(&bars[PB_SFULL + x]));
+                };
+                // O_x (+)= P_x(j) V(j); the caller has seen V(j) land
+                auto issue_pv = [&](int x, int j) {
+                    wait(PB_PFULL + x, (uint32_t)j & 1u);
+                    tc_fence_after();
+                    const uint64_t dv = umma_desc(smem_u32(v_tile + (j & 1) * PT_TILE_BYTES), PT_HALF_BYTES, 1024);   // MN-major: dim halves 16 KiB apart
+    #pragma unroll
+                    for (int kk = 0; kk < PT_BKV / 16; ++kk)      // 16 kv positions per MMA: 8 columns of P, 16 rows (2 KiB) of V
+                        tc_mma_f16_ts(tmem + PT_COL_O + x * 128, tmem + PT_COL_S + x * 128 + kk * 8, dv + (uint64_t)((kk * 2048) >> 4), idesc_o,
+                                      (j > 0 || kk > 0) ? 1u : 0u);
+                };
+                wait(PB_Q, 0);
+                wait(PB_KFULL, 0);
                 tc_fence_after();
-                const uint64_t dv = umma_desc(smem_u32(v_tile + s * PT_TILE_BYTES), PT_HALF_BYTES, 1024);   // MN-major: dim halves 16 KiB apart
-#pragma unroll
-                for (int kk = 0; kk < PT_BKV / 16; ++kk)      // 16 kv positions per MMA: 8 columns of P, 16 rows (2 KiB) of V
-                    tc_mma_f16_ts(tmem + PT_COL_O, tmem + PT_COL_P + kk * 8, dv + (uint64_t)((kk * 2048) >> 4), idesc_o, kk > 0 ? 1u : 0u);
-                tc_commit(smem_u32(&bars[PB_ODONE]));
-                tc_commit(smem_u32(&bars[PB_VFREE + s]));
+                if (nt_a > 0) issue_s(0, 0);
+                if (nt_b > 0) issue_s(1, 0);
+                tc_commit(smem_u32(&bars[PB_KFREE]));
+                for (int j = 0; j < ntiles; ++j) {
+                    const int s = j & 1, s1 = (j + 1) & 1;
+                    const bool more = j + 1 < ntiles;
+                    wait(PB_VFULL + s, (uint32_t)(j >> 1) & 1u);
+                    if (more) wait(PB_KFULL + s1, (uint32_t)((j + 1) >> 1) & 1u);
+                    tc_fence_after();
+    #pragma unroll
+                    for (int x = 0; x < 2; ++x) {
+                        const int nt_x = x ? nt_b : nt_a;
+                        if (j < nt_x) {
+                            issue_pv(x, j);
+                            if (j + 1 < nt_x) issue_s(x, j + 1);
+                            else tc_commit(smem_u32(&bars[PB_OFINAL + x]));
+                        }
+                    }
+                    tc_commit(smem_u32(&bars[PB_VFREE + s]));
+                    if (more) tc_commit(smem_u32(&bars[PB_KFREE + s1]));
+                }
             }
         }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(PT_REGS_SOFTMAX));
         // ---------------- softmax + output: thread = query row ----------------
-        const int row = warp * 32 + lane;                 // tensor-memory lane
-        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-        const int qi = q0 + row;
+        const int x = warp >> 2;                          // query tile of the pair
+        const int nt_x = x ? nt_b : nt_a;
+        const int row = (warp & 3) * 32 + lane;           // tensor-memory lane
+        const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t s_addr = lane_base + PT_COL_S + x * 128, o_addr = lane_base + PT_COL_O + x * 128;
+        const int r0 = q0 + x * PT_BQ, qi = r0 + row;
         const int limit = min(A.pos_offset + qi, A.kv_len - 1);      // last kv position this row sees
-        float o[PT_D];
-#pragma unroll
-        for (int i = 0; i < PT_D; ++i) o[i] = 0.f;
-        float m = -1e30f, l = 0.f;
-        for (int j = 0; j < ntiles; ++j) {
-            const int s = j & 1, k0 = j * PT_BKV;
-            const bool masked = k0 + PT_BKV - 1 > A.pos_offset + q0 || k0 + PT_BKV > A.kv_len;     // some row of the tile needs the mask
-            wait(PB_SFULL + s, (uint32_t)(j >> 1) & 1u);
+        float m = 0.f, l = 0.f;
+        for (int j = 0; j < nt_x; ++j) {
+            const int k0 = j * PT_BKV;
+            const bool masked = k0 + PT_BKV - 1 > A.pos_offset + r0 || k0 + PT_BKV > A.kv_len;     // some row of the tile needs the mask
+            wait(PB_SFULL + x, (uint32_t)j & 1u);
             tc_fence_after();
-            // pass 1: row maximum
-            float mx = -1e30f;
+            float sc[PT_BKV];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld32(lane_base + PT_COL_S + s * 128 + c * 32, r);
-                tmem_ld_wait();
+            for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sc[c * 32]));
+            tmem_ld_wait();
+            if (masked) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float v = __uint_as_float(r[i]);
-                    if (masked && k0 + c * 32 + i > limit) v = -1e30f;
-                    mx = fmaxf(mx, v);
+                for (int i = 0; i < PT_BKV; ++i)
+                    if (k0 + i > limit) sc[i] = -INFINITY;
+            }
+            float mx0 = sc[0], mx1 = sc[1], mx2 = sc[2], mx3 = sc[3];
+#pragma unroll
+            for (int i = 4; i < PT_BKV; i += 4) {
+                mx0 = fmaxf(mx0, sc[i]);
+                mx1 = fmaxf(mx1, sc[i + 1]);
+                mx2 = fmaxf(mx2, sc[i + 2]);
+                mx3 = fmaxf(mx3, sc[i + 3]);
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * A.scale_log2e;     // scaled, base-2 domain
+            if (j == 0) {
+                m = mx;                                    // tile 0 holds position 0, which every row sees: finite
+            } else {
+                const bool raise = mx - m > PT_RESCALE_THRESHOLD;
+                if (__any_sync(0xffffffffu, raise)) {
+                    // S_x(j) was issued behind P_x(j-1) V(j-1) and has completed, so O_x is at rest
+                    const float alpha = raise ? ex2_approx(m - mx) : 1.f;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t r[32];
+                        tmem_ld32(o_addr + c * 32, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                        tmem_st32(o_addr + c * 32, r);
+                    }
+                    l *= alpha;
+                    if (raise) m = mx;
                 }
             }
-            const float m_new = fmaxf(m, mx * A.scale_log2e);     // scores are compared in the scaled, base-2 domain
-            const float alpha = exp2f(m - m_new);
-            // the product of the tile before: O = (O + P V) * alpha
-            if (j > 0) {
-                wait(PB_ODONE, (uint32_t)(j - 1) & 1u);
-                tc_fence_after();
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t r[32];
-                    tmem_ld32(lane_base + PT_COL_O + c * 32, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(r[i])) * alpha;
-                }
-            }
-            // pass 2: P = 2^(s * scale * log2e - m_new), written to tensor memory as fp16 pairs
-            float psum = 0.f;
+            // P = 2^(s * scale * log2e - m), written over the row's own S columns as fp16 pairs
+            float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld32(lane_base + PT_COL_S + s * 128 + c * 32, r);
-                tmem_ld_wait();
                 uint32_t pk[16];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float p0 = exp2f(__uint_as_float(r[i]) * A.scale_log2e - m_new);
-                    float p1 = exp2f(__uint_as_float(r[i + 1]) * A.scale_log2e - m_new);
-                    if (masked) {
-                        if (k0 + c * 32 + i > limit) p0 = 0.f;
-                        if (k0 + c * 32 + i + 1 > limit) p1 = 0.f;
-                    }
-                    // the sum runs over the fp16-rounded probabilities that the second product sees
-                    const __half2 hp = __floats2half2_rn(p0, p1);
-                    const float2 back = __half22float2(hp);
-                    psum += back.x + back.y;
-                    pk[i >> 1] = *reinterpret_cast<const uint32_t *>(&hp);
+                for (int i = 0; i < 32; i += 4) {
+                    const float p0 = ex2_approx(fmaf(sc[c * 32 + i], A.scale_log2e, -m));
+                    const float p1 = ex2_approx(fmaf(sc[c * 32 + i + 1], A.scale_log2e, -m));
+                    const float p2 = ex2_approx(fmaf(sc[c * 32 + i + 2], A.scale_log2e, -m));
+                    const float p3 = ex2_approx(fmaf(sc[c * 32 + i + 3], A.scale_log2e, -m));
+                    ps0 += p0;
+                    ps1 += p1;
+                    ps2 += p2;
+                    ps3 += p3;
+                    pk[i >> 1] = f2_to_h2(p0, p1);
+                    pk[(i >> 1) + 1] = f2_to_h2(p2, p3);
                 }
-                // 16 columns of P per 32 scores
                 asm volatile(
                     "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-                    ::"r"(lane_base + PT_COL_P + c * 16), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]),
+                    ::"r"(s_addr + c * 16), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]),
                       "r"(pk[6]), "r"(pk[7]), "r"(pk[8]), "r"(pk[9]), "r"(pk[10]), "r"(pk[11]), "r"(pk[12]), "r"(pk[13]),
                       "r"(pk[14]), "r"(pk[15])
                     : "memory");
             }
             tmem_st_wait();
             tc_fence_before();
-            l = l * alpha + psum;
-            m = m_new;
+            l += (ps0 + ps1) + (ps2 + ps3);
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(smem_u32(&bars[PB_PFULL]));          // P(j) is in tensor memory
-                mbar_arrive(smem_u32(&bars[PB_SFREE + s]));      // S(j) will not be read again
-            }
+            if (lane == 0) mbar_arrive(smem_u32(&bars[PB_PFULL + x]));          // P_x(j) (and a rescaled O_x) is in tensor memory
         }
-        // the last tile's product
-        wait(PB_ODONE, (uint32_t)(ntiles - 1) & 1u);
-        tc_fence_after();
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        const bool live = qi < A.q_len;
-        __half *dst = A.out + (((long)b * A.hq + h) * A.q_len + qi) * PT_D;
+        if (nt_x > 0) {
+            wait(PB_OFINAL + x, 0);
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            const bool live = qi < A.q_len;
+            __half *dst = A.out + (((long)b * A.hq + h) * A.q_len + qi) * PT_D;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            uint32_t r[32];
-            tmem_ld32(lane_base + PT_COL_O + c * 32, r);
-            tmem_ld_wait();
-            if (live) {
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld32(o_addr + c * 32, r);
+                tmem_ld_wait();
+                if (live) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                    uint4 u;
-                    u.x = f2_to_h2((o[c * 32 + i] + __uint_as_float(r[i])) * inv, (o[c * 32 + i + 1] + __uint_as_float(r[i + 1])) * inv);
-                    u.y = f2_to_h2((o[c * 32 + i + 2] + __uint_as_float(r[i + 2])) * inv, (o[c * 32 + i + 3] + __uint_as_float(r[i + 3])) * inv);
-                    u.z = f2_to_h2((o[c * 32 + i + 4] + __uint_as_float(r[i + 4])) * inv, (o[c * 32 + i + 5] + __uint_as_float(r[i + 5])) * inv);
-                    u.w = f2_to_h2((o[c * 32 + i + 6] + __uint_as_float(r[i + 6])) * inv, (o[c * 32 + i + 7] + __uint_as_float(r[i + 7])) * inv);
-                    *reinterpret_cast<uint4 *>(dst + c * 32 + i) = u;
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 u;
+                        u.x = f2_to_h2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                        u.y = f2_to_h2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+                        u.z = f2_to_h2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+                        u.w = f2_to_h2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+                        *reinterpret_cast<uint4 *>(dst + c * 32 + i) = u;
+                    }
                 }
             }
         }
@@ -284,7 +327,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 int prefill_tc_launch(const __half *q, const __half *k, const __half *v, __half *out, int batch, int hq, int hkv, int q_len,
                       int kv_len, int d, int pos_offset, float scale, cudaStream_t st) {
     constexpr int NOT_COVERED = -1000;
-    if (d != PT_D || pos_offset < 0 || kv_len < 1 || q_len < 1 || hq % hkv) return NOT_COVERED;
+    if (d != PT_D || pos_offset < 0 || kv_len < 1 || q_len < 1 || hq % hkv || !(scale > 0.f)) return NOT_COVERED;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return NOT_COVERED;
     if (hq > 65535 || batch > 65535) return NOT_COVERED;
     int *status = status_word();
@@ -307,13 +350,13 @@ int prefill_tc_launch(const __half *q, const __half *k, const __half *v, __half 
     A.out = out; A.hq = hq; A.hkv = hkv; A.q_len = q_len; A.kv_len = kv_len; A.pos_offset = pos_offset;
     A.scale_log2e = scale * 1.4426950408889634f;
     A.status = status;
-    const size_t smem = (size_t)(1 + 2 * PT_STAGES) * PT_TILE_BYTES + PB_COUNT * 8 + 16 + 1024;
+    const size_t smem = (size_t)(2 + 2 * PT_STAGES) * PT_TILE_BYTES + PB_COUNT * 8 + 16 + 1024;
     {
         static OncePerDevice once;
         cudaError_t e = once.run([&] { return cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); });
         if (e != cudaSuccess) return fail((int)e, "flash_attn_full_f16: shared memory %zu: %s", smem, cudaGetErrorString(e));
     }
-    const dim3 grid(ceil_div(q_len, PT_BQ), hq, batch);
+    const dim3 grid(ceil_div(q_len, 2 * PT_BQ), hq, batch);
     prefill_tc_kernel<<<grid, PT_THREADS, smem, st>>>(qmap, kmap, vmap, A);
     return launch_status("flash_attn_full_f16");
 }
