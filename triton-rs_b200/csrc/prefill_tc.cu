@@ -164,7 +164,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                 auto issue_s = [&](int x, int j) {
                     const uint64_t dq = umma_desc(smem_u32(q_tile + x * PT_TILE_BYTES), 16, 1024);
                     const uint64_t dk = umma_desc(smem_u32(k_tile + (j & 1) * PT_TILE_BYTES), 16, 1024);
-    #pragma unroll
+#pragma unroll
                     for (int kk = 0; kk < PT_D / 16; ++kk) {
                         // 16 dims per MMA: 32 bytes inside the 128-byte swizzle row; dims 64.. live in the second half tile
                         const uint64_t off = (uint64_t)(((kk >> 2) * PT_HALF_BYTES + (kk & 3) * 32) >> 4);
@@ -177,7 +177,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                     wait(PB_PFULL + x, (uint32_t)j & 1u);
                     tc_fence_after();
                     const uint64_t dv = umma_desc(smem_u32(v_tile + (j & 1) * PT_TILE_BYTES), PT_HALF_BYTES, 1024);   // MN-major: dim halves 16 KiB apart
-    #pragma unroll
+#pragma unroll
                     for (int kk = 0; kk < PT_BKV / 16; ++kk)      // 16 kv positions per MMA: 8 columns of P, 16 rows (2 KiB) of V
                         tc_mma_f16_ts(tmem + PT_COL_O + x * 128, tmem + PT_COL_S + x * 128 + kk * 8, dv + (uint64_t)((kk * 2048) >> 4), idesc_o,
                                       (j > 0 || kk > 0) ? 1u : 0u);
@@ -194,7 +194,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                     wait(PB_VFULL + s, (uint32_t)(j >> 1) & 1u);
                     if (more) wait(PB_KFULL + s1, (uint32_t)((j + 1) >> 1) & 1u);
                     tc_fence_after();
-    #pragma unroll
+#pragma unroll
                     for (int x = 0; x < 2; ++x) {
                         const int nt_x = x ? nt_b : nt_a;
                         if (j < nt_x) {
