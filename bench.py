@@ -282,6 +282,20 @@ def component_metrics(pkg, torch, dev, gen):
                                   "frac_hbm": byts / ms / 1e6 / hbm_peak, "sum_len": int(lens.sum()),
                                   "timing": "inputs (537 MB) larger than L2"}
     del kc, vc
+    # causal prefill (flash_attn_full_f16), Llama-3-8B head layout: one 2048-token and one 8192-token sequence.  The
+    # contraction is counted causally (each query against the positions it sees: 4 * Hq * D * L (L + 1) / 2 flops)
+    for L in (2048, 8192):
+        pq = torch.randn((1, hq, L, d), device=dev, generator=gen, dtype=torch.float16)
+        pk = torch.randn((1, hkv, L, d), device=dev, generator=gen, dtype=torch.float16)
+        pv = torch.randn((1, hkv, L, d), device=dev, generator=gen, dtype=torch.float16)
+        po = torch.empty_like(pq)
+        fn = lambda: P.flash_attn_full_f16(pq, pk, pv, po, 1, hq, hkv, L, L, d, 0, 1.0 / float(np.sqrt(d)))
+        ms, iso = graph_time(fn, 4), isolated_time(fn, 8)
+        flops = 4.0 * hq * d * L * (L + 1) / 2
+        out[f"prefill_attention_l{L}"] = {"us": ms * 1e3, "us_isolated": iso * 1e3, "TFLOP/s": flops / ms / 1e9,
+                                          "frac_tensor": flops / ms / 1e9 / tf_peak,
+                                          "timing": "tensor-bound: K/V (%d MB) are re-read from L2 by design" % (4 * hkv * L * d // 2 ** 20)}
+        del pq, pk, pv, po
     # config 3: fused MoE, Mixtral-8x7B shape
     T, E, kk, H, I = 512, 8, 2, 4096, 14336
     w13q, w2q = ri(E, H // 8, 2 * I), ri(E, I // 8, H)
