@@ -317,7 +317,9 @@ int unified_attention_f32(const float *q, const float *k_cache, const float *v_c
  * contiguous); query row i sees kv positions 0 .. pos_offset + i.  Arguments in the reference's order, with the
  * grid's batch extent made an explicit argument after `output`.  All arithmetic in fp32 for either element type
  * (:773-779).  The reference asks for q_len and kv_len to be multiples of its tiles; any length is accepted
- * here, and masked positions contribute exactly 0 (its -1e30 additive mask underflows to the same).  D <= 256. */
+ * here, and masked positions contribute exactly 0 (its -1e30 additive mask underflows to the same).  D <= 256.
+ * The 16-bit editions at head_dim 128 (pos_offset >= 0, scale > 0) run on the tensor cores: scores and output
+ * accumulate in fp32, the probabilities enter the second product rounded to the element type. */
 int flash_attn_full_f32(const float *q, const float *k, const float *v, float *output, int batch,
                         int num_heads, int num_kv_heads, int q_len, int kv_len, int head_dim,
                         int pos_offset, float scale, b200k_stream stream);
@@ -539,6 +541,11 @@ int embedding_lookup_bf16(const b200k_bf16 *embeddings, const int32_t *indices,
                           b200k_stream stream);
 int softmax_bf16(const b200k_bf16 *input, b200k_bf16 *output, int rows, int cols,
                  b200k_stream stream);
+/* flash_attn_full with T = bf16 (tensor-core path at head_dim 128, as for fp16). */
+int flash_attn_full_bf16(const b200k_bf16 *q, const b200k_bf16 *k, const b200k_bf16 *v,
+                         b200k_bf16 *output, int batch, int num_heads, int num_kv_heads, int q_len,
+                         int kv_len, int head_dim, int pos_offset, float scale,
+                         b200k_stream stream);
 
 /* ------------------------------------------------------------------------- */
 /* the two ends of a decode step                                               */

@@ -144,3 +144,17 @@ def test_decode_attention_bf16(P, oracle):
     table = rng.permutation(nblocks)[: (n + bs - 1) // bs].astype(np.int32)
     P.paged_decode_attention_bf16(q, kp, vp, t(table), out, hq, hkv, d, n, bs, scale)
     assert_close(out.float().cpu().numpy(), oracle.paged_decode_attention(q32, kp32, vp32, table, n, bs, scale), what="paged bf16")
+
+
+@pytest.mark.parametrize("b,hq,hkv,q_len,kv_len,off", [(1, 4, 2, 300, 300, 0), (2, 4, 1, 200, 500, 300), (1, 2, 2, 70, 70, 0)])
+@pytest.mark.parametrize("d", [128, 64])
+def test_flash_attn_full_bf16(P, oracle, b, hq, hkv, q_len, kv_len, off, d):
+    """head_dim 128 takes the tensor-core kernel, 64 the general one."""
+    rng = np.random.default_rng(q_len + d)
+    q, q32 = bf(rng.standard_normal((b, hq, q_len, d)))
+    k, k32 = bf(rng.standard_normal((b, hkv, kv_len, d)))
+    v, v32 = bf(rng.standard_normal((b, hkv, kv_len, d)))
+    scale = 1.0 / np.sqrt(d)
+    out = torch.full(q.shape, float("nan"), device=DEV, dtype=torch.bfloat16)
+    P.flash_attn_full_bf16(q, k, v, out, b, hq, hkv, q_len, kv_len, d, off, scale)
+    assert_close(out.float().cpu().numpy(), oracle.flash_attn_full(q32, k32, v32, off, scale), what=f"prefill attention bf16 d={d}")

@@ -488,6 +488,15 @@ static int unpack_launch(const char *name, const int32_t *in, int8_t *out, int r
 // ---------------------------------------------------------------------------
 // validation + dispatch
 // ---------------------------------------------------------------------------
+// M = 1: the integer dot-product GEMV at group 128, the fp16 GEMV otherwise (B200K_GEMV=h forces the latter)
+static int gemv_any_launch(const GemmArgs &g) {
+    if (env_char("B200K_GEMV") != 'h') {
+        const int rc = gemv_i8_launch(g);
+        if (rc != TC_NOT_COVERED) return rc;
+    }
+    return gemv_launch(g);
+}
+
 static int gemm_dispatch(const char *name, GemmArgs g, bool own_ws) {
     B200K_REQUIRE(g.a && g.qweight && g.scales && g.c, B200K_E_NULL, "%s: NULL pointer", name);
     B200K_REQUIRE(g.format == FMT_GPTQ || g.qzeros, B200K_E_NULL, "%s: qzeros is NULL", name);
@@ -500,7 +509,7 @@ static int gemm_dispatch(const char *name, GemmArgs g, bool own_ws) {
     if (g.a_kperm) {
         // pre-permuted activations: only the families that consume that order (GPTQ GEMV and tensor-core path)
         B200K_REQUIRE(canon && g.format == FMT_GPTQ, B200K_E_SHAPE, "%s: needs the canonical GPTQ layout (contiguous, 16-byte aligned rows)", name);
-        if (g.m == 1 && g.k <= 65536) return gemv_launch(g);
+        if (g.m == 1 && g.k <= 65536) return gemv_any_launch(g);
         if (!g.ws && own_ws) {
             int rc = default_workspace(&g.ws, &g.ws_bytes);
             if (rc) return rc;
@@ -510,7 +519,7 @@ static int gemm_dispatch(const char *name, GemmArgs g, bool own_ws) {
     }
     const int force = env_char("B200K_GEMM_PATH");  // tuning/testing override: s(trided) | g(emv) | t(c)
     if (force == 's') return gemm_strided_launch(g);
-    if (canon && g.m == 1 && g.k <= 65536 && force != 't' && !g.bf16) return gemv_launch(g);
+    if (canon && g.m == 1 && g.k <= 65536 && force != 't' && !g.bf16) return gemv_any_launch(g);
     if (canon) {
         if (!g.ws && own_ws) {
             int rc = default_workspace(&g.ws, &g.ws_bytes);

@@ -48,6 +48,8 @@ bool gemm_layout_is_canonical(const GemmArgs &g);
 // Kernel families.  Each returns 0 on launch, a B200K_E_* / CUDA code on failure.
 int gemm_strided_launch(const GemmArgs &g);
 int gemv_launch(const GemmArgs &g);
+// Integer dot-product GEMV (gemv_i8.cu): M = 1, fp16, group 128; TC_NOT_COVERED otherwise.
+int gemv_i8_launch(const GemmArgs &g);
 // Tensor-core path (tcgen05 + TMEM).  Returns TC_NOT_COVERED when the shape is outside what it
 // covers (the caller then takes another family); the value is distinct from every B200K_E_* code
 // and from every cudaError_t.

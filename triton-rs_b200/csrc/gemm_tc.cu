@@ -490,7 +490,14 @@ static int pick_tt(int m) {
     return 256;
 }
 
-int gemm_tc_token_tile(int m, int segments) { return pick_tt(segments > 1 ? ceil_div(m, segments) : m); }
+// Grouped mode: segments are unequal (router counts scatter around the mean), and every token tile of a segment
+// dequantises the segment's weights again, whatever its width; the tile therefore leaves half the mean as head-room,
+// so that a segment somewhat above the mean still fits one tile.
+int gemm_tc_token_tile(int m, int segments) {
+    if (segments <= 1) return pick_tt(m);
+    const int mean = ceil_div(m, segments);
+    return pick_tt(mean + mean / 2);
+}
 
 int gemm_tc_launch(const GemmArgs &g) {
     const bool silu = g.silu_inter > 0;
@@ -499,9 +506,9 @@ int gemm_tc_launch(const GemmArgs &g) {
     if (g.format == FMT_AWQ && !g.qzeros) return TC_NOT_COVERED;
     if (g.qzeros && (g.s_qzk % 4 || !aligned16(g.qzeros))) return TC_NOT_COVERED;   // zero-point rows travel by TMA: 16-byte pitch
     const bool grouped = g.seg_offsets != nullptr;
-    // grouped: the token tile follows the average segment; the grid covers the worst case (every row in
-    // one segment) and CTAs past their segment's end return at once
-    const int tt = pick_tt(grouped ? ceil_div(g.m, g.num_segments) : g.m);
+    // grouped: the token tile follows the average segment (plus head-room); the grid covers the worst case (every row
+    // in one segment) and CTAs past their segment's end return at once
+    const int tt = gemm_tc_token_tile(g.m, grouped ? g.num_segments : 1);
     const int col_tiles = silu ? g.silu_inter / 64 : ceil_div(g.n, TC_BN), tok_tiles = ceil_div(g.m, tt);
     const int kb_total = g.k / TC_BK;
     const int tiles = col_tiles * tok_tiles;

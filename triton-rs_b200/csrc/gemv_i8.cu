@@ -1,0 +1,329 @@
+// W4A16 GEMV (M = 1, group 128) on the integer dot-product instruction.
+//
+// The fp16 GEMV spends about three instructions per weight (nibble -> fp16, subtract the zero-point, half2 FMA,
+// widening), and at 45 weights per clock per SM that the HBM stream of a B200 delivers, instruction issue is the
+// limit, not memory.  Here the nibbles are never converted:
+//     sum_k a_k (q_k - z) s  =  s * sa * ( sum_k A_k q_k  -  z * sum_k A_k ),     a_k ~ sa * A_k,
+// with the 128 activations of a quantisation group turned once into 15-bit integers A_k = 128 ah_k + al_k
+// (sa = max|a| / 16383 per group: the quantisation step is 3e-5 of the group's largest activation, an order of
+// magnitude below fp16's own spacing at that magnitude), and the sums over k taken by dp4a on bytes: one LOP3
+// extracts four nibbles of a packed word as four bytes, and two dp4a (ah, al) accumulate them in int32.  The odd
+// nibbles are used in place, as bytes 16 q, and their sums shifted down at the end of the group (exact).
+// The products are exact integers, so the only roundings are the activation quantisation and the final fp32
+// scaling: closer to the exact result than products with fp16-rounded weights, inside the same tolerance.
+//
+// Work split as in the fp16 GEMV: a cluster of KSPLIT CTAs shares one block of columns and splits K by
+// quantisation group over its warps; the cluster reduces through distributed shared memory in a fixed order.
+//   GPTQ [K/8, N]: a word = 8 k of one column; a thread owns 4 adjacent columns (one 16-byte load per packed row);
+//                  activation bytes are laid out per packed row as (k0,k2,k4,k6) and (k1,k3,k5,k7).
+//   AWQ  [K, N/8]: a word = 8 columns of one k; a thread owns one word column; four rows are transposed as 4 x 4
+//                  byte matrices (PRMT) so that a word holds four k of one column.
+#include <cooperative_groups.h>
+
+#include "gemm.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace b200k {
+
+constexpr int GI_THREADS = 256;
+constexpr int GI_WARPS = GI_THREADS / 32;
+constexpr int GI_GROUP = 128;
+
+__device__ __forceinline__ int dp4a_us(uint32_t w_unsigned_bytes, uint32_t a_signed_bytes, int acc) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(w_unsigned_bytes), "r"(a_signed_bytes), "r"(acc));
+    return d;
+}
+__device__ __forceinline__ uint32_t ldg_nc_word(const void *p) {
+    uint32_t r;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(r) : "l"(p));
+    return r;
+}
+
+// The 128 activations of one group -> 15-bit integers; lane i holds stored positions 4i .. 4i+3.  Returns the
+// lane's four high bytes and four low bytes (byte j = stored position 4i + j), the group's scale and sum(A).
+__device__ __forceinline__ void quantise_group(const __half *a_group, int lane, uint32_t &qh, uint32_t &ql, float &sa, int &asum) {
+    const uint2 u = *reinterpret_cast<const uint2 *>(a_group + lane * 4);
+    const float2 f01 = h2_to_f2(u.x), f23 = h2_to_f2(u.y);
+    float amax = fmaxf(fmaxf(fabsf(f01.x), fabsf(f01.y)), fmaxf(fabsf(f23.x), fabsf(f23.y)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    sa = amax * (1.f / 16383.f);
+    const float inv = amax > 0.f ? 16383.f / amax : 0.f;
+    const int i0 = __float2int_rn(f01.x * inv), i1 = __float2int_rn(f01.y * inv);
+    const int i2 = __float2int_rn(f23.x * inv), i3 = __float2int_rn(f23.y * inv);
+    asum = __reduce_add_sync(0xffffffffu, i0 + i1 + i2 + i3);
+    qh = (uint32_t)((i0 >> 7) & 255) | ((uint32_t)((i1 >> 7) & 255) << 8) | ((uint32_t)((i2 >> 7) & 255) << 16) |
+         ((uint32_t)((i3 >> 7) & 255) << 24);
+    ql = (uint32_t)(i0 & 127) | ((uint32_t)(i1 & 127) << 8) | ((uint32_t)(i2 & 127) << 16) | ((uint32_t)(i3 & 127) << 24);
+}
+
+// Fixed-order reduction of per-thread totals: over the k-warps of the CTA, then over the CTAs of the cluster
+// (distributed shared memory); rank 0 stores fp16.  NV = values per thread (4 or 8), laid out as float4s.
+template <int NV>
+__device__ __forceinline__ void reduce_and_store(float (&tot)[NV], float4 *red4, int part, int parts, int slot, int slots_per_part,
+                                                 int ksplit, bool live, __half *dst) {
+    cg::cluster_group cluster = cg::this_cluster();
+    constexpr int Q = NV / 4;
+    if (part > 0) {
+#pragma unroll
+        for (int q = 0; q < Q; ++q)
+            red4[(((part - 1) * slots_per_part + slot) * Q) + q] = make_float4(tot[4 * q], tot[4 * q + 1], tot[4 * q + 2], tot[4 * q + 3]);
+    }
+    __syncthreads();
+    if (part == 0) {
+        for (int j = 0; j < parts - 1; ++j) {
+#pragma unroll
+            for (int q = 0; q < Q; ++q) {
+                const float4 o = red4[((j * slots_per_part + slot) * Q) + q];
+                tot[4 * q] += o.x; tot[4 * q + 1] += o.y; tot[4 * q + 2] += o.z; tot[4 * q + 3] += o.w;
+            }
+        }
+    }
+    __syncthreads();
+    if (part == 0) {
+#pragma unroll
+        for (int q = 0; q < Q; ++q) red4[slot * Q + q] = make_float4(tot[4 * q], tot[4 * q + 1], tot[4 * q + 2], tot[4 * q + 3]);
+    }
+    cluster.sync();
+    if (cluster.block_rank() == 0 && part == 0 && live) {
+        float s[NV];
+#pragma unroll
+        for (int c = 0; c < NV; ++c) s[c] = 0.f;
+        for (int r = 0; r < ksplit; ++r) {
+            const float4 *peer = cluster.map_shared_rank(red4, r);
+#pragma unroll
+            for (int q = 0; q < Q; ++q) {
+                const float4 o = peer[slot * Q + q];
+                s[4 * q] += o.x; s[4 * q + 1] += o.y; s[4 * q + 2] += o.z; s[4 * q + 3] += o.w;
+            }
+        }
+        uint32_t o[NV / 2];
+#pragma unroll
+        for (int c = 0; c < NV / 2; ++c) o[c] = f2_to_h2(s[2 * c], s[2 * c + 1]);
+        if (NV == 4) *reinterpret_cast<uint2 *>(dst) = make_uint2(o[0], o[1]);
+        else *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[NV / 2 - 2], o[NV / 2 - 1]);
+    }
+    cluster.sync();  // peers keep their shared memory alive until rank 0 has read it
+}
+
+// CW = column-warps per CTA (each covers 128 columns); the other 8 / CW warps split K.
+template <int CW>
+__global__ void __launch_bounds__(GI_THREADS)
+gemv_gptq_i8_kernel(GemmArgs g, int ksplit) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint4 *act = reinterpret_cast<uint4 *>(smem_raw);                              // [GI_WARPS][16 packed rows]: (Eh, Oh, El, Ol)
+    float4 *red4 = reinterpret_cast<float4 *>(smem_raw + GI_WARPS * 16 * sizeof(uint4));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int cw = warp % CW, kw = warp / CW;
+    constexpr int KW = GI_WARPS / CW;
+    const int col = blockIdx.x * (128 * CW) + cw * 128 + lane * 4;
+    const int kslot = blockIdx.y * KW + kw, kslots = ksplit * KW;
+    const int groups = g.k / GI_GROUP;
+    const bool live = col < g.n;
+    uint4 *my_act = act + warp * 16;
+
+    uint4 wreg[16];
+    uint2 su = make_uint2(0, 0);
+    uint32_t zw = 0;
+    auto request = [&](int grp) {
+        if (g.qzeros) zw = ldg_nc_word(g.qzeros + (long)grp * g.s_qzk + col / 8);
+        su = *reinterpret_cast<const uint2 *>(g.scales + (long)grp * g.s_sk + col);
+        const int32_t *wp = g.qweight + (long)grp * 16 * g.s_qwk + col;
+#pragma unroll
+        for (int r = 0; r < 16; ++r) wreg[r] = ldg_nc_v4(wp + (long)r * g.s_qwk);
+    };
+    if (live && kslot < groups) request(kslot);
+
+    pdl_wait();                 // the activation vector comes from the kernel before; the weights do not
+    pdl_launch_dependents();
+
+    float tot[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int grp = kslot; grp < groups; grp += kslots) {
+        if (live && grp != kslot) request(grp);
+        // activations of the group -> bytes, per packed row r (lanes 2r, 2r+1): even k and odd k of the row
+        uint32_t qh, ql;
+        float sa;
+        int asum;
+        quantise_group(g.a + (long)grp * GI_GROUP, lane, qh, ql, sa, asum);
+        {
+            const uint32_t ph = __shfl_xor_sync(0xffffffffu, qh, 1), pl = __shfl_xor_sync(0xffffffffu, ql, 1);
+            const bool odd = lane & 1;
+            const uint32_t h0 = odd ? ph : qh, h1 = odd ? qh : ph;      // stored positions 0..3 and 4..7 of the row
+            const uint32_t l0 = odd ? pl : ql, l1 = odd ? ql : pl;
+            // plain order: positions are k0..k7; pre-permuted order: (k0,k4,k1,k5 | k2,k6,k3,k7)
+            const uint32_t sel_e = g.a_kperm ? 0x5140u : 0x6420u, sel_o = g.a_kperm ? 0x7362u : 0x7531u;
+            const uint2 mine = odd ? make_uint2(__byte_perm(l0, l1, sel_e), __byte_perm(l0, l1, sel_o))
+                                   : make_uint2(__byte_perm(h0, h1, sel_e), __byte_perm(h0, h1, sel_o));
+            __syncwarp();       // the previous group's reads of this warp's rows are done
+            reinterpret_cast<uint2 *>(my_act + (lane >> 1))[odd ? 1 : 0] = mine;
+            __syncwarp();
+        }
+        if (!live) continue;
+        int ae[4][2], ao[4][2];     // per column: sums over even / odd k (odd: 16 x) against (ah, al)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) ae[c][0] = ae[c][1] = ao[c][0] = ao[c][1] = 0;
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            const uint4 av = my_act[r];
+            const uint32_t w[4] = {wreg[r].x, wreg[r].y, wreg[r].z, wreg[r].w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint32_t e = w[c] & 0x0F0F0F0Fu, o = w[c] & 0xF0F0F0F0u;
+                ae[c][0] = dp4a_us(e, av.x, ae[c][0]);
+                ae[c][1] = dp4a_us(e, av.z, ae[c][1]);
+                ao[c][0] = dp4a_us(o, av.y, ao[c][0]);
+                ao[c][1] = dp4a_us(o, av.w, ao[c][1]);
+            }
+        }
+        const float2 s01 = h2_to_f2(su.x), s23 = h2_to_f2(su.y);
+        const float sc[4] = {s01.x, s01.y, s23.x, s23.y};
+        const uint32_t zsh = zw >> (4 * (col % 8));
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int z = g.qzeros ? (int)((zsh >> (4 * c)) & 15u) + g.zero_offset : 8;
+            const int dot = 128 * (ae[c][0] + (ao[c][0] >> 4)) + ae[c][1] + (ao[c][1] >> 4);
+            tot[c] += (float)(dot - z * asum) * (sc[c] * sa);
+        }
+    }
+    reduce_and_store<4>(tot, red4, kw, KW, cw * 32 + lane, 32 * CW, ksplit, live, g.c + col);
+}
+
+__global__ void __launch_bounds__(GI_THREADS)
+gemv_awq_i8_kernel(GemmArgs g, int ksplit) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint2 *act = reinterpret_cast<uint2 *>(smem_raw);                              // [GI_WARPS][32]: (ah, al) of 4 consecutive k
+    float4 *red4 = reinterpret_cast<float4 *>(smem_raw + GI_WARPS * 16 * sizeof(uint4));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int col = blockIdx.x * 256 + lane * 8;      // 8 columns per thread, 256 per warp
+    const int kslot = blockIdx.y * GI_WARPS + warp, kslots = ksplit * GI_WARPS;
+    const int groups = g.k / GI_GROUP;
+    const bool live = col < g.n;
+    uint2 *my_act = act + warp * 32;
+    constexpr int BATCH = 32;                         // k rows requested before any is used
+
+    uint32_t w[BATCH];
+    uint4 su = make_uint4(0, 0, 0, 0);
+    uint32_t zw = 0;
+    auto request_meta = [&](int grp) {
+        zw = ldg_nc_word(g.qzeros + (long)grp * g.s_qzk + col / 8);
+        su = *reinterpret_cast<const uint4 *>(g.scales + (long)grp * g.s_sk + col);
+    };
+    auto request_rows = [&](int k0) {
+        const int32_t *wp = g.qweight + (long)k0 * g.s_qwk + col / 8;
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j) w[j] = ldg_nc_word(wp + (long)j * g.s_qwk);
+    };
+    if (live && kslot < groups) {
+        request_meta(kslot);
+        request_rows(kslot * GI_GROUP);
+    }
+
+    pdl_wait();
+    pdl_launch_dependents();
+
+    float tot[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) tot[c] = 0.f;
+    for (int grp = kslot; grp < groups; grp += kslots) {
+        if (live && grp != kslot) request_meta(grp);
+        uint32_t qh, ql;
+        float sa;
+        int asum;
+        quantise_group(g.a + (long)grp * GI_GROUP, lane, qh, ql, sa, asum);
+        __syncwarp();
+        my_act[lane] = make_uint2(qh, ql);          // bytes already in k order: lane i = k 4i .. 4i+3
+        __syncwarp();
+        if (!live) continue;
+        // byte b of the even-nibble words = nibble 2b = column (0,4,1,5)[b]; of the odd-nibble words = nibble 2b+1 =
+        // column (2,6,3,7)[b] (the AWQ order [0,4,1,5,2,6,3,7] maps column -> nibble)
+        int ae[4][2], ao[4][2];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) ae[c][0] = ae[c][1] = ao[c][0] = ao[c][1] = 0;
+        const int k0 = grp * GI_GROUP;
+        for (int kk = 0; kk < GI_GROUP; kk += BATCH) {
+            if (!(grp == kslot && kk == 0)) request_rows(k0 + kk);
+#pragma unroll
+            for (int j = 0; j < BATCH; j += 4) {
+                const uint2 av = my_act[(kk + j) >> 2];
+                uint32_t e[4], o[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    e[i] = w[j + i] & 0x0F0F0F0Fu;
+                    o[i] = w[j + i] & 0xF0F0F0F0u;
+                }
+                // 4 x 4 byte transposes: word i (row k+i, four columns) -> word c (column c, rows k .. k+3)
+                const uint32_t e01l = __byte_perm(e[0], e[1], 0x5140), e23l = __byte_perm(e[2], e[3], 0x5140);
+                const uint32_t e01h = __byte_perm(e[0], e[1], 0x7362), e23h = __byte_perm(e[2], e[3], 0x7362);
+                const uint32_t o01l = __byte_perm(o[0], o[1], 0x5140), o23l = __byte_perm(o[2], o[3], 0x5140);
+                const uint32_t o01h = __byte_perm(o[0], o[1], 0x7362), o23h = __byte_perm(o[2], o[3], 0x7362);
+                const uint32_t ce[4] = {__byte_perm(e01l, e23l, 0x5410), __byte_perm(e01l, e23l, 0x7632),
+                                        __byte_perm(e01h, e23h, 0x5410), __byte_perm(e01h, e23h, 0x7632)};
+                const uint32_t co[4] = {__byte_perm(o01l, o23l, 0x5410), __byte_perm(o01l, o23l, 0x7632),
+                                        __byte_perm(o01h, o23h, 0x5410), __byte_perm(o01h, o23h, 0x7632)};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    ae[c][0] = dp4a_us(ce[c], av.x, ae[c][0]);
+                    ae[c][1] = dp4a_us(ce[c], av.y, ae[c][1]);
+                    ao[c][0] = dp4a_us(co[c], av.x, ao[c][0]);
+                    ao[c][1] = dp4a_us(co[c], av.y, ao[c][1]);
+                }
+            }
+        }
+        const float2 sA = h2_to_f2(su.x), sB = h2_to_f2(su.y), sC = h2_to_f2(su.z), sD = h2_to_f2(su.w);
+        const float sc[8] = {sA.x, sA.y, sB.x, sB.y, sC.x, sC.y, sD.x, sD.y};
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int ce_col = (b & 1) * 4 + (b >> 1);          // (0,4,1,5)[b]
+            const int co_col = ce_col + 2;                      // (2,6,3,7)[b]
+            const int ze = (int)((zw >> (8 * b)) & 15u), zo = (int)((zw >> (8 * b + 4)) & 15u);
+            const int de = 128 * ae[b][0] + ae[b][1];
+            const int dn = 128 * (ao[b][0] >> 4) + (ao[b][1] >> 4);
+            tot[ce_col] += (float)(de - ze * asum) * (sc[ce_col] * sa);
+            tot[co_col] += (float)(dn - zo * asum) * (sc[co_col] * sa);
+        }
+    }
+    reduce_and_store<8>(tot, red4, warp, GI_WARPS, lane, 32, ksplit, live, g.c + col);
+}
+
+// The integer GEMV covers: M = 1, fp16, group 128, canonical layout (the caller has checked the layout).
+int gemv_i8_launch(const GemmArgs &g) {
+    if (g.m != 1 || g.group != GI_GROUP || g.bf16 || g.k % GI_GROUP) return TC_NOT_COVERED;
+    const int groups = g.k / GI_GROUP;
+    int cw = 2;
+    if (g.format == FMT_GPTQ && ceil_div(g.n, 256) * 8 < 2 * sm_count()) cw = 1;
+    const int colblocks = g.format == FMT_GPTQ ? ceil_div(g.n, 128 * cw) : ceil_div(g.n, 256);
+    const int kwarps = g.format == FMT_GPTQ ? GI_WARPS / cw : GI_WARPS;
+    // enough CTAs for ~2 per SM, cluster size a power of two <= 8, no warp without a group
+    int ksplit = 1;
+    while (ksplit < 8 && colblocks * ksplit < 2 * sm_count() && ksplit * 2 * kwarps <= groups) ksplit *= 2;
+    {   // tuning override
+        const int v = env_int("B200K_GEMV_KSPLIT", 0);
+        if ((v == 1 || v == 2 || v == 4 || v == 8) && v * kwarps <= groups) ksplit = v;
+    }
+    const size_t smem = GI_WARPS * 16 * sizeof(uint4) + (size_t)GI_WARPS * 256 * sizeof(float);
+    auto kern = g.format != FMT_GPTQ ? gemv_awq_i8_kernel : cw == 2 ? gemv_gptq_i8_kernel<2> : gemv_gptq_i8_kernel<1>;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(colblocks, ksplit, 1);
+    cfg.blockDim = dim3(GI_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = g.stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = ksplit;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, g, ksplit);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail((int)e, "gemv launch: %s", cudaGetErrorString(e));
+    }
+    return 0;
+}
+
+}  // namespace b200k

@@ -8,6 +8,8 @@
 // rows of one head so that their K / V rows are shared through L1; four KV positions per step so that the
 // four warp reductions overlap.  The decode kernels are the bandwidth-tuned ones; a tensor-core prefill
 // (tcgen05, the pipeline of the int4 GEMM) is the follow-up.
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 
 namespace b200k {
@@ -19,6 +21,8 @@ __device__ __forceinline__ float ldf(const float *p) { return __ldg(p); }
 __device__ __forceinline__ float ldf(const __half *p) { return __half2float(__ldg(p)); }
 __device__ __forceinline__ void stf(float *p, float v) { *p = v; }
 __device__ __forceinline__ void stf(__half *p, float v) { *p = __float2half_rn(v); }
+__device__ __forceinline__ float ldf(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void stf(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
 
 template <typename T>
 __global__ void __launch_bounds__(PF_WARPS * 32)
@@ -128,7 +132,7 @@ extern "C" int flash_attn_full_f32(const float *q, const float *k, const float *
 namespace b200k {
 // tensor-core kernel (prefill_tc.cu): head_dim 128, pos_offset >= 0; -1000 when the call is outside what it covers
 int prefill_tc_launch(const __half *q, const __half *k, const __half *v, __half *out, int batch, int hq, int hkv, int q_len,
-                      int kv_len, int d, int pos_offset, float scale, cudaStream_t st);
+                      int kv_len, int d, int pos_offset, float scale, bool bf16, cudaStream_t st);
 }  // namespace b200k
 
 extern "C" int flash_attn_full_f16(const b200k_half *q, const b200k_half *k, const b200k_half *v, b200k_half *output, int batch,
@@ -137,10 +141,25 @@ extern "C" int flash_attn_full_f16(const b200k_half *q, const b200k_half *k, con
     if (q && k && v && output && batch > 0 && num_heads > 0 && num_kv_heads > 0 && env_char("B200K_PREFILL") != 'g') {
         const int rc = prefill_tc_launch(reinterpret_cast<const __half *>(q), reinterpret_cast<const __half *>(k),
                                          reinterpret_cast<const __half *>(v), reinterpret_cast<__half *>(output), batch, num_heads,
-                                         num_kv_heads, q_len, kv_len, head_dim, pos_offset, scale, to_stream(stream));
+                                         num_kv_heads, q_len, kv_len, head_dim, pos_offset, scale, false, to_stream(stream));
         if (rc != -1000) return rc;
     }
     return prefill_launch<__half>("flash_attn_full_f16", reinterpret_cast<const __half *>(q), reinterpret_cast<const __half *>(k),
                                   reinterpret_cast<const __half *>(v), reinterpret_cast<__half *>(output), batch, num_heads,
                                   num_kv_heads, q_len, kv_len, head_dim, pos_offset, scale, stream);
+}
+
+extern "C" int flash_attn_full_bf16(const b200k_bf16 *q, const b200k_bf16 *k, const b200k_bf16 *v, b200k_bf16 *output, int batch,
+                                    int num_heads, int num_kv_heads, int q_len, int kv_len, int head_dim, int pos_offset,
+                                    float scale, b200k_stream stream) {
+    if (q && k && v && output && batch > 0 && num_heads > 0 && num_kv_heads > 0 && env_char("B200K_PREFILL") != 'g') {
+        const int rc = prefill_tc_launch(reinterpret_cast<const __half *>(q), reinterpret_cast<const __half *>(k),
+                                         reinterpret_cast<const __half *>(v), reinterpret_cast<__half *>(output), batch, num_heads,
+                                         num_kv_heads, q_len, kv_len, head_dim, pos_offset, scale, true, to_stream(stream));
+        if (rc != -1000) return rc;
+    }
+    return prefill_launch<__nv_bfloat16>("flash_attn_full_bf16", reinterpret_cast<const __nv_bfloat16 *>(q),
+                                         reinterpret_cast<const __nv_bfloat16 *>(k), reinterpret_cast<const __nv_bfloat16 *>(v),
+                                         reinterpret_cast<__nv_bfloat16 *>(output), batch, num_heads, num_kv_heads, q_len, kv_len,
+                                         head_dim, pos_offset, scale, stream);
 }

@@ -1,4 +1,4 @@
-// Causal prefill attention (flash_attn_full, fp16, head_dim 128) on the 5th-generation tensor cores.
+// Causal prefill attention (flash_attn_full, fp16 or bf16, head_dim 128) on the 5th-generation tensor cores.
 //
 // One CTA per (sequence, q head, PAIR of 128-row query tiles a, b).  Both contractions of a KV tile of 128 positions
 // are tcgen05.mma instructions with their accumulators in tensor memory:
@@ -22,6 +22,8 @@
 // diagonal of a query tile are never multiplied for it (and never loaded if neither tile needs them), tiles entirely
 // below it skip the mask.
 // Every mbarrier wait is bounded; a wait that gives up sets the status word and the CTA drains.
+#include <cuda_bf16.h>
+
 #include "tcgen05.cuh"
 #include "tma.cuh"
 
@@ -60,12 +62,22 @@ enum {
     PB_COUNT = 15
 };
 
+// two fp32 -> one word of two 16-bit elements (fp16 or bf16), round to nearest even
+template <bool BF> __device__ __forceinline__ uint32_t pack2(float a, float b) {
+    if (BF) {
+        const __nv_bfloat162 r = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<const uint32_t *>(&r);
+    }
+    return f2_to_h2(a, b);
+}
+
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
 
+template <bool BF>
 __global__ void __launch_bounds__(PT_THREADS, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                   const __grid_constant__ CUtensorMap vmap, PtArgs A) {
@@ -158,8 +170,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
         } else if (warp == PT_SOFTMAX_WARPS + 1) {
             // ---------------- MMA issuer ----------------
             if (lane == 0) {
-                const uint32_t idesc_s = umma_idesc(PT_BQ, PT_BKV, 0);          // A, B K-major
-                const uint32_t idesc_o = umma_idesc_b_mn(PT_BQ, PT_D);          // A from tensor memory, B (V) MN-major
+                const uint32_t fmt = BF ? (1u << 7) | (1u << 10) : 0u;           // A, B element format: f16 or bf16
+                const uint32_t idesc_s = umma_idesc(PT_BQ, PT_BKV, 0) | fmt;     // A, B K-major
+                const uint32_t idesc_o = umma_idesc_b_mn(PT_BQ, PT_D) | fmt;     // A from tensor memory, B (V) MN-major
                 // S_x(j) = Q_x K(j)^T; the caller has seen K(j) land
                 auto issue_s = [&](int x, int j) {
                     const uint64_t dq = umma_desc(smem_u32(q_tile + x * PT_TILE_BYTES), 16, 1024);
@@ -277,8 +290,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
                     ps1 += p1;
                     ps2 += p2;
                     ps3 += p3;
-                    pk[i >> 1] = f2_to_h2(p0, p1);
-                    pk[(i >> 1) + 1] = f2_to_h2(p2, p3);
+                    pk[i >> 1] = pack2<BF>(p0, p1);
+                    pk[(i >> 1) + 1] = pack2<BF>(p2, p3);
                 }
                 asm volatile(
                     "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
@@ -308,10 +321,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
                         uint4 u;
-                        u.x = f2_to_h2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
-                        u.y = f2_to_h2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
-                        u.z = f2_to_h2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
-                        u.w = f2_to_h2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+                        u.x = pack2<BF>(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                        u.y = pack2<BF>(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+                        u.z = pack2<BF>(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+                        u.w = pack2<BF>(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
                         *reinterpret_cast<uint4 *>(dst + c * 32 + i) = u;
                     }
                 }
@@ -324,8 +337,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
 }
 
 // Returns TC-style "not covered" (-1000) when the shape is outside this kernel (the caller then runs the general one).
+// bf16: the four tensors hold bfloat16 (passed as 16-bit words).
 int prefill_tc_launch(const __half *q, const __half *k, const __half *v, __half *out, int batch, int hq, int hkv, int q_len,
-                      int kv_len, int d, int pos_offset, float scale, cudaStream_t st) {
+                      int kv_len, int d, int pos_offset, float scale, bool bf16, cudaStream_t st) {
     constexpr int NOT_COVERED = -1000;
     if (d != PT_D || pos_offset < 0 || kv_len < 1 || q_len < 1 || hq % hkv || !(scale > 0.f)) return NOT_COVERED;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return NOT_COVERED;
@@ -334,31 +348,33 @@ int prefill_tc_launch(const __half *q, const __half *k, const __half *v, __half 
     if (!status) return NOT_COVERED;
     const uint64_t row = PT_D * 2;
     CUtensorMap qmap, kmap, vmap;
+    const CUtensorMapDataType dtype = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const uint32_t box[4] = {64, PT_BQ, 1, 1};
     {
         const uint64_t dims[4] = {PT_D, (uint64_t)q_len, (uint64_t)hq, (uint64_t)batch};
         const uint64_t str[3] = {row, (uint64_t)q_len * row, (uint64_t)hq * q_len * row};
-        if (make_tensor_map(&qmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, q, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return NOT_COVERED;
+        if (make_tensor_map(&qmap, dtype, 4, q, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return NOT_COVERED;
     }
     {
         const uint64_t dims[4] = {PT_D, (uint64_t)kv_len, (uint64_t)hkv, (uint64_t)batch};
         const uint64_t str[3] = {row, (uint64_t)kv_len * row, (uint64_t)hkv * kv_len * row};
-        if (make_tensor_map(&kmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, k, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return NOT_COVERED;
-        if (make_tensor_map(&vmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, v, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return NOT_COVERED;
+        if (make_tensor_map(&kmap, dtype, 4, k, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return NOT_COVERED;
+        if (make_tensor_map(&vmap, dtype, 4, v, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return NOT_COVERED;
     }
     PtArgs A;
     A.out = out; A.hq = hq; A.hkv = hkv; A.q_len = q_len; A.kv_len = kv_len; A.pos_offset = pos_offset;
     A.scale_log2e = scale * 1.4426950408889634f;
     A.status = status;
     const size_t smem = (size_t)(2 + 2 * PT_STAGES) * PT_TILE_BYTES + PB_COUNT * 8 + 16 + 1024;
+    auto kern = bf16 ? prefill_tc_kernel<true> : prefill_tc_kernel<false>;
     {
-        static OncePerDevice once;
-        cudaError_t e = once.run([&] { return cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); });
-        if (e != cudaSuccess) return fail((int)e, "flash_attn_full_f16: shared memory %zu: %s", smem, cudaGetErrorString(e));
+        static OncePerDevice once[2];
+        cudaError_t e = once[bf16].run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); });
+        if (e != cudaSuccess) return fail((int)e, "flash_attn_full: shared memory %zu: %s", smem, cudaGetErrorString(e));
     }
     const dim3 grid(ceil_div(q_len, 2 * PT_BQ), hq, batch);
-    prefill_tc_kernel<<<grid, PT_THREADS, smem, st>>>(qmap, kmap, vmap, A);
-    return launch_status("flash_attn_full_f16");
+    kern<<<grid, PT_THREADS, smem, st>>>(qmap, kmap, vmap, A);
+    return launch_status(bf16 ? "flash_attn_full_bf16" : "flash_attn_full_f16");
 }
 
 }  // namespace b200k

@@ -381,6 +381,11 @@ extern "C" {
     pub fn softmax_bf16(
         input: *const b200k_bf16, output: *mut b200k_bf16, rows: c_int, cols: c_int, stream: b200k_stream
     ) -> c_int;
+    pub fn flash_attn_full_bf16(
+        q: *const b200k_bf16, k: *const b200k_bf16, v: *const b200k_bf16, output: *mut b200k_bf16,
+        batch: c_int, num_heads: c_int, num_kv_heads: c_int, q_len: c_int, kv_len: c_int, head_dim: c_int,
+        pos_offset: c_int, scale: f32, stream: b200k_stream
+    ) -> c_int;
     pub fn embedding_lookup_f32(
         embeddings: *const f32, indices: *const i32, output: *mut f32, hidden_size: c_int, num_tokens: c_int,
         stream: b200k_stream
