@@ -137,6 +137,16 @@ int awq_gemm_int4_f16_ws(const b200k_half *a, const int32_t *qweight, const b200
                          int stride_qzk, int stride_qzn, int stride_cm, int stride_cn,
                          void *workspace, size_t workspace_bytes, b200k_stream stream);
 
+/* Gate/up projection with the activation fused (no counterpart in the reference, whose consumer runs the GEMM and
+ * fused_silu_mul_interleaved as two kernels): c [M, inter] = silu(a Wgate) * (a Wup) for one GPTQ weight [K, 2 inter]
+ * whose first `inter` columns are the gate projection (the half-split layout of fused_silu_mul_interleaved,
+ * crates/triton-kernels/src/elementwise.rs:199-206).  Contiguous tensors; tensor-core family only (K % 64,
+ * inter % 64, group a power of two >= 64), other shapes are refused with B200K_E_SHAPE.  The products are not
+ * rounded to fp16 before the activation, so the result is at least as close to the fp32 value as the two-kernel
+ * sequence. */
+int w4a16_gptq_gemm_silu_mul_f16(const b200k_half *a, const int32_t *qweight, const b200k_half *scales,
+                                 const int32_t *qzeros, b200k_half *c, int m_size, int inter_size,
+                                 int k_size, int group_size, b200k_stream stream);
 /* GPTQ GEMM on activations whose every 8 consecutive k are stored as (k0,k4,k1,k5,k2,k6,k3,k7) -- the order in
  * which the nibble arithmetic yields a packed word's values, so the kernel skips the byte-permutes that would
  * restore k order (a contraction may visit k in any order when both operands agree).  Contiguous tensors only
@@ -656,7 +666,7 @@ int b200k_comm_buffer(struct b200k_comm *comm, void **host_out_ptr);
 int b200k_comm_set_peer_pointer(struct b200k_comm *comm, int peer_rank, void *peer_buffer);
 void b200k_comm_destroy(struct b200k_comm *comm);
 /* Attach to a layer: the o and down GEMMs then write into slots 0 and 1 and the layer chain runs the
- * two all-reduces itself, each fused with the step that consumes it (10 launches, as on one GPU).
+ * two all-reduces itself, each fused with the step that consumes it (9 launches, as on one GPU).
  * NULL detaches (single GPU). */
 int b200k_layer_set_comm(b200k_layer *layer, struct b200k_comm *comm);
 

@@ -159,3 +159,23 @@ def test_prepermuted_activations_give_identical_bits(P, M, K, N, G, sym):
     P.w4a16_gptq_gemm_kperm_f16(ap, qw, sc, qz, out, M, N, K, G, st)
     torch.cuda.synchronize()
     assert torch.equal(out.view(torch.int16), ref.view(torch.int16))
+
+
+@pytest.mark.parametrize("m,k,inter,sym", [(64, 1024, 512, False), (5, 512, 192, True), (1, 256, 64, False), (200, 512, 128, False)])
+def test_gate_up_gemm_with_fused_silu_mul(P, oracle, m, k, inter, sym):
+    """w4a16_gptq_gemm_silu_mul_f16 = silu(a Wgate) * (a Wup), gate columns first, against the two-step oracle
+    (GEMM in fp32, then fused_silu_mul_interleaved)."""
+    a, qw, sc, qz = make_case(oracle, "gptq", m, k, 2 * inter, 128, seed=m + inter, sym=sym)
+    gu = oracle.w4a16_gptq_gemm(a, qw, sc, qz, 128, zero_offset=1, faithful=True)
+    ref = oracle.fused_silu_mul_interleaved(gu, inter)
+    out = torch.full((m, inter), float("nan"), dtype=torch.float16, device=DEV)
+    P.w4a16_gptq_gemm_silu_mul_f16(t(a), t(qw), t(sc), None if qz is None else t(qz), out, m, inter, k, 128)
+    # the product of two GEMM outputs: each within 1e-2 of its value, so the bound is propagated through silu(g) * u
+    g_, u_ = gu[:, :inter], gu[:, inter:]
+    sil = g_ / (1.0 + np.exp(-g_))
+    bound = 1e-2 + 1e-2 * np.abs(ref) + (1e-2 + 1e-2 * np.abs(g_)) * 1.1 * np.abs(u_) + (1e-2 + 1e-2 * np.abs(u_)) * np.abs(sil)
+    got = out.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    assert (np.abs(got - ref) <= bound).all(), float(np.abs(got - ref).max())
+    # and plainly close: the fused form skips one fp16 rounding, it does not add error
+    assert_close(got, ref, 2e-2, 2e-2, "fused gate_up + silu")

@@ -542,7 +542,7 @@ using namespace b200k;
     g.s_am = stride_am; g.s_ak = stride_ak; g.s_qwk = stride_qwk; g.s_qwn = stride_qwn;               \
     g.s_sk = stride_sk; g.s_sn = stride_sn; g.s_cm = stride_cm; g.s_cn = stride_cn;                   \
     g.format = FMT; g.zero_offset = ZO; g.stream = to_stream(stream);                                 \
-    g.seg_offsets = nullptr; g.num_segments = 0; g.plan_out = nullptr; g.a_kperm = false;                \
+    g.seg_offsets = nullptr; g.num_segments = 0; g.plan_out = nullptr; g.a_kperm = false; g.c_kperm = false; \
     g.silu_inter = 0; g.tile_list = nullptr; g.tile_count = nullptr; g.max_tiles = 0; g.bf16 = false;
 
 extern "C" int w4a16_gptq_gemm_f16_ws(const b200k_half *a, const int32_t *qweight, const b200k_half *scales,
@@ -686,6 +686,37 @@ extern "C" int w4a16_gptq_gemm_kperm_f16(const b200k_half *a_permuted, const int
     g.ws = nullptr; g.ws_bytes = 0;
     g.a_kperm = true;
     return gemm_dispatch("w4a16_gptq_gemm_kperm_f16", g, true);
+}
+
+namespace b200k {
+int gptq_gemm_silu_mul_launch(const __half *a, const int32_t *qweight, const __half *scales, const int32_t *qzeros, __half *c,
+                              int m, int inter, int k, int group, bool a_kperm, bool c_kperm, cudaStream_t stream) {
+    GemmArgs g = {};
+    g.a = a; g.qweight = qweight; g.scales = scales; g.qzeros = qzeros; g.c = c;
+    g.m = m; g.n = 2 * inter; g.k = k; g.group = group;
+    g.s_am = k; g.s_ak = 1; g.s_qwk = 2 * inter; g.s_qwn = 1; g.s_sk = 2 * inter; g.s_sn = 1;
+    g.s_qzk = 2 * inter / 8; g.s_qzn = 1; g.s_cm = inter; g.s_cn = 1;
+    g.format = FMT_GPTQ; g.zero_offset = qzeros ? 1 : 0; g.stream = stream;
+    g.silu_inter = inter; g.a_kperm = a_kperm; g.c_kperm = c_kperm;
+    if (m <= 0 || inter <= 0 || k <= 0 || group <= 0 || k % group || !gemm_layout_is_canonical(g)) return TC_NOT_COVERED;
+    int rc = default_workspace(&g.ws, &g.ws_bytes);
+    if (rc) return rc;
+    return gemm_tc_launch(g);
+}
+}  // namespace b200k
+
+extern "C" int w4a16_gptq_gemm_silu_mul_f16(const b200k_half *a, const int32_t *qweight, const b200k_half *scales,
+                                            const int32_t *qzeros, b200k_half *c, int m_size, int inter_size, int k_size,
+                                            int group_size, b200k_stream stream) {
+    B200K_REQUIRE(a && qweight && scales && c, B200K_E_NULL, "w4a16_gptq_gemm_silu_mul_f16: NULL pointer");
+    if (m_size == 0) return 0;
+    const int rc = gptq_gemm_silu_mul_launch((const __half *)a, qweight, (const __half *)scales, qzeros, (__half *)c, m_size,
+                                             inter_size, k_size, group_size, false, false, to_stream(stream));
+    return rc == TC_NOT_COVERED
+               ? fail(B200K_E_SHAPE, "w4a16_gptq_gemm_silu_mul_f16: shape not covered (contiguous 16-byte aligned tensors, "
+                                     "K %% 64, inter %% 64, group a power of two >= 64; M %d, inter %d, K %d, group %d)",
+                      m_size, inter_size, k_size, group_size)
+               : rc;
 }
 
 extern "C" int b200k_gemm_tc_plan(int m_size, int n_size, int k_size, int group_size, int awq, int *host_plan_out) {

@@ -35,6 +35,7 @@ struct GemmArgs {
     const int *tile_count;
     int max_tiles;
     bool bf16;        // a, scales and c are bfloat16 instead of fp16 (tensor-core and strided families)
+    bool c_kperm;     // fused silu_mul epilogue only: write the output in the pre-permuted order (it feeds a GEMM that reads it so)
     bool a_kperm;     // activations pre-permuted per 8 consecutive k to (k0,k4,k1,k5,k2,k6,k3,k7) (tensor-core GPTQ path, GEMV)
     int *plan_out;    // host pointer: when set, the tensor-core family writes its launch plan there and launches nothing
     void *ws;         // scratch (may be nullptr when the chosen path needs none)
@@ -50,6 +51,10 @@ int gemm_strided_launch(const GemmArgs &g);
 int gemv_launch(const GemmArgs &g);
 // Integer dot-product GEMV (gemv_i8.cu): M = 1, fp16, group 128; TC_NOT_COVERED otherwise.
 int gemv_i8_launch(const GemmArgs &g);
+// C [M, inter] = silu(A Wgate) * (A Wup) for a GPTQ weight [K, 2 * inter] whose first `inter` columns are the gate
+// projection (tensor-core family, silu in the GEMM's epilogue).  TC_NOT_COVERED when the shape is outside it.
+int gptq_gemm_silu_mul_launch(const __half *a, const int32_t *qweight, const __half *scales, const int32_t *qzeros, __half *c,
+                              int m, int inter, int k, int group, bool a_kperm, bool c_kperm, cudaStream_t stream);
 // Tensor-core path (tcgen05 + TMEM).  Returns TC_NOT_COVERED when the shape is outside what it
 // covers (the caller then takes another family); the value is distinct from every B200K_E_* code
 // and from every cudaError_t.

@@ -43,7 +43,10 @@ constexpr int TC_A_BYTES = TC_BN * TC_BK * 2;   // 16 KiB dequantised tile
 constexpr int TC_W_BYTES = TC_BN * TC_BK / 2;   // 4 KiB packed weight words of one K block
 constexpr int TC_SC_BYTES = TC_BN * 2;          // the block's scale row (one group) for the 128 columns
 constexpr int TC_ZP_BYTES = TC_BN / 2;          // and its 16 packed zero-point words
-constexpr int TC_RAW_BYTES = TC_W_BYTES + TC_SC_BYTES + TC_ZP_BYTES + 64;   // 4.5 KiB ring slot
+// 4.5 KiB ring slot.  A TMA destination must be 128-byte aligned, so with the fused silu epilogue, where the gate and
+// the up columns arrive as two boxes per tensor, the up half of the zero-point words sits 128 bytes behind the gate half.
+constexpr int TC_ZP_UP_OFFSET = 128;
+constexpr int TC_RAW_BYTES = TC_W_BYTES + TC_SC_BYTES + TC_ZP_UP_OFFSET + 128;
 
 struct TcArgs {
     const __half *scales;
@@ -64,6 +67,7 @@ struct TcArgs {
     const int2 *tile_list;    // grouped mode: (segment, first row) per work item, or nullptr (blockIdx.z = segment, blockIdx.y = tile)
     const int *tile_count;
     int silu_inter;           // fused silu_mul epilogue: number of output columns (the weight holds twice as many), else 0
+    int c_kperm;              // fused silu_mul epilogue: store every 8 consecutive output columns as (0,4,1,5,2,6,3,7)
     int w_rows_per_seg;       // rows of the packed weight tensor per segment (K/8 for GPTQ, K for AWQ)
     int g_rows_per_seg;       // rows of the scale / zero tensors per segment (K / group)
 };
@@ -215,7 +219,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                     tma_load_2d(dst + TC_W_BYTES + TC_SC_BYTES / 2, &smap, nu, g_row0 + grp, bar);
                     if (P.qzeros) {
                         tma_load_2d(dst + TC_W_BYTES + TC_SC_BYTES, &zmap, n0 / 8, g_row0 + grp, bar);
-                        tma_load_2d(dst + TC_W_BYTES + TC_SC_BYTES + TC_ZP_BYTES / 2, &zmap, nu / 8, g_row0 + grp, bar);
+                        tma_load_2d(dst + TC_W_BYTES + TC_SC_BYTES + TC_ZP_UP_OFFSET, &zmap, nu / 8, g_row0 + grp, bar);
                     }
                 } else {
                     if (FMT == FMT_GPTQ)
@@ -294,9 +298,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 // thread t = weight column t (operand row t): its 8 words are the 8 16-byte chunks of the row
                 const uint32_t s2 = (uint32_t)reinterpret_cast<const uint16_t *>(slot + TC_W_BYTES)[t] * 0x10001u;   // the column's scale in both halves
                 int z = 8;
-                if (P.qzeros)
-                    z = (int)((reinterpret_cast<const uint32_t *>(slot + TC_W_BYTES + TC_SC_BYTES)[t >> 3] >> (4 * (t & 7))) & 15u) +
+                if (P.qzeros) {
+                    const int zword = SILU ? (t >> 6) * (TC_ZP_UP_OFFSET / 4) + ((t & 63) >> 3) : t >> 3;
+                    z = (int)((reinterpret_cast<const uint32_t *>(slot + TC_W_BYTES + TC_SC_BYTES)[zword] >> (4 * (t & 7))) & 15u) +
                         P.zero_offset;
+                }
                 uint32_t zm[4];
                 zero_magic4<BF>(z, zm);
                 if (SILU) {      // two [8][64] boxes: gate columns (rows 0..63 of the operand), then up columns
@@ -416,11 +422,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 }
                 asm volatile("bar.sync 1, %0;" ::"r"(NG * 128) : "memory");      // the dequant / epilogue warps only
                 if (active && q < 2 && n < P.silu_inter) {
+                    // the consumer of a pre-permuted activation tensor reads column k of an 8-block at slot 2 (k & 3) + (k >> 2)
+                    const int n_st = P.c_kperm ? (n & ~7) | ((n & 3) << 1) | ((n >> 2) & 1) : n;
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int m = m0 + c0 + j;
                         const float gt = __uint_as_float(rr[j]), up = red[(c0 + j) * (TC_BN / 2) + row];
-                        if (m < m_end) store_elem<BF>(P.c + (long)m * P.s_cm + n, gt / (1.f + expf(-gt)) * up);
+                        if (m < m_end) store_elem<BF>(P.c + (long)m * P.s_cm + n_st, gt / (1.f + expf(-gt)) * up);
                     }
                 }
                 asm volatile("bar.sync 1, %0;" ::"r"(NG * 128) : "memory");      // before the next round overwrites the staging rows
@@ -622,6 +630,7 @@ int gemm_tc_launch(const GemmArgs &g) {
     P.tile_list = grouped ? g.tile_list : nullptr;
     P.tile_count = g.tile_count;
     P.silu_inter = g.silu_inter;
+    P.c_kperm = g.c_kperm ? 1 : 0;
     P.w_rows_per_seg = g.format == FMT_GPTQ ? g.k / 8 : g.k;
     P.g_rows_per_seg = g.k / g.group;
     P.status = (int *)g.ws;   // status word at the start of the scratch buffer

@@ -7,7 +7,7 @@
 #include <map>
 #include <vector>
 
-#include "common.cuh"
+#include "gemm.cuh"
 
 namespace b200k {
 int rope_kv_append_lens_launch(const __half *qkv, const float *cos_t, const float *sin_t, const int32_t *positions,
@@ -48,6 +48,7 @@ struct b200k_layer {
     std::map<std::array<uintptr_t, 5>, cudaGraphExec_t> graphs;
     cudaStream_t cap_stream;                 // capture happens here: the caller's stream may be the legacy default stream
     int launches;
+    bool fused_silu;   // gate_up GEMM with silu(gate) * up in its epilogue (GPTQ weights, tensor-core shapes)
     bool kperm;   // GEMM inputs travel in the pre-permuted order (GPTQ weights, shapes the tensor-core path covers)
 };
 
@@ -94,9 +95,16 @@ static int mlp(b200k_layer *L, b200k_half *dn_out, int b, b200k_stream st) {
     const b200k_layer_config &c = L->cfg;
     const int H = c.hidden, I = c.intermediate;
     int rc;
-    if ((rc = gemm(L, 2, L->n2, L->gu, b, 2 * I, H, st))) return rc;
-    if (L->kperm) rc = silu_mul_interleaved_f16_kperm((const __half *)L->gu, (__half *)L->act, I, b * I, to_stream(st));
-    else rc = fused_silu_mul_interleaved_f16(L->gu, L->act, I, b * I, st);
+    // gate_up GEMM with silu(gate) * up in its epilogue: no [b, 2I] intermediate, one launch fewer.  A single token
+    // stays on the two-kernel path, whose GEMM is the M = 1 GEMV.
+    rc = L->fused_silu && b > 1 ? gptq_gemm_silu_mul_launch((const __half *)L->n2, L->qw[2], (const __half *)L->sc[2], L->qz[2],
+                                                            (__half *)L->act, b, I, H, c.group_size, L->kperm, L->kperm, to_stream(st))
+                                : TC_NOT_COVERED;
+    if (rc == TC_NOT_COVERED) {
+        if ((rc = gemm(L, 2, L->n2, L->gu, b, 2 * I, H, st))) return rc;
+        if (L->kperm) rc = silu_mul_interleaved_f16_kperm((const __half *)L->gu, (__half *)L->act, I, b * I, to_stream(st));
+        else rc = fused_silu_mul_interleaved_f16(L->gu, L->act, I, b * I, st);
+    }
     if (rc) return rc;
     return gemm(L, 3, L->act, dn_out, b, H, I, st);
 }
@@ -112,11 +120,7 @@ static int stage1(b200k_layer *L, const b200k_half *hidden, const b200k_half *o_
     else
         rc = fused_add_rms_norm_f16(o_red, hidden, L->ln2, L->n2, L->h1, H, 1.0f / H, c.rms_eps, b, st);
     if (rc) return rc;
-    if ((rc = gemm(L, 2, L->n2, L->gu, b, 2 * I, H, st))) return rc;
-    if (L->kperm) rc = silu_mul_interleaved_f16_kperm((const __half *)L->gu, (__half *)L->act, I, b * I, to_stream(st));
-    else rc = fused_silu_mul_interleaved_f16(L->gu, L->act, I, b * I, st);
-    if (rc) return rc;
-    return gemm(L, 3, L->act, dn_out, b, H, I, st);
+    return mlp(L, dn_out, b, st);
 }
 static int stage2(b200k_layer *L, const b200k_half *dn_red, b200k_half *out, int b, b200k_stream st) {
     return residual_add_f16(L->h1, dn_red, out, b * L->cfg.hidden, st);
@@ -192,8 +196,10 @@ extern "C" int b200k_layer_create(const b200k_layer_config *config, b200k_layer 
     L->pos = (int32_t *)(base + off);
     off += (B * 4 + 255) / 256 * 256;
     L->lens = (int32_t *)(base + off);
-    // rms_norm, gemm, rope+append, attention, gemm, add+norm, gemm, silu, gemm, add
-    L->launches = 10;
+    // rms_norm, gemm, rope+append, attention, gemm, add+norm, gemm (+ silu in its epilogue, or a silu kernel), gemm, add
+    L->fused_silu = c.weight_format == 0 && env_char("B200K_LAYER_FUSED_SILU") != '0' && c.group_size >= 64 &&
+                    (c.group_size & (c.group_size - 1)) == 0 && c.hidden % 64 == 0 && c.intermediate % 64 == 0;
+    L->launches = L->fused_silu ? 9 : 10;
     {
         // Pre-permuted GEMM inputs: GPTQ weights and extents the tensor-core GEMM family covers for all four projections
         // (K a multiple of 64, group a power of two >= 64, N a multiple of 32).  B200K_LAYER_KPERM=0 turns it off.

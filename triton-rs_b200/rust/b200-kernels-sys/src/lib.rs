@@ -95,6 +95,11 @@ extern "C" {
         stride_qzk: c_int, stride_qzn: c_int, stride_cm: c_int, stride_cn: c_int, workspace: *mut c_void,
         workspace_bytes: usize, stream: b200k_stream
     ) -> c_int;
+    pub fn w4a16_gptq_gemm_silu_mul_f16(
+        a: *const b200k_half, qweight: *const i32, scales: *const b200k_half, qzeros: *const i32,
+        c: *mut b200k_half, m_size: c_int, inter_size: c_int, k_size: c_int, group_size: c_int,
+        stream: b200k_stream
+    ) -> c_int;
     pub fn permute_k8_f16(
         input: *const b200k_half, output: *mut b200k_half, rows: c_int, k_size: c_int, stream: b200k_stream
     ) -> c_int;
