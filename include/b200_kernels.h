@@ -666,7 +666,7 @@ int b200k_comm_buffer(struct b200k_comm *comm, void **host_out_ptr);
 int b200k_comm_set_peer_pointer(struct b200k_comm *comm, int peer_rank, void *peer_buffer);
 void b200k_comm_destroy(struct b200k_comm *comm);
 /* Attach to a layer: the o and down GEMMs then write into slots 0 and 1 and the layer chain runs the
- * two all-reduces itself, each fused with the step that consumes it (9 launches, as on one GPU).
+ * two all-reduces itself, each fused with the step that consumes it (10 launches, as on one GPU).
  * NULL detaches (single GPU). */
 int b200k_layer_set_comm(b200k_layer *layer, struct b200k_comm *comm);
 

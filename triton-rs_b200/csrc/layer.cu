@@ -197,7 +197,9 @@ extern "C" int b200k_layer_create(const b200k_layer_config *config, b200k_layer 
     off += (B * 4 + 255) / 256 * 256;
     L->lens = (int32_t *)(base + off);
     // rms_norm, gemm, rope+append, attention, gemm, add+norm, gemm (+ silu in its epilogue, or a silu kernel), gemm, add
-    L->fused_silu = c.weight_format == 0 && env_char("B200K_LAYER_FUSED_SILU") != '0' && c.group_size >= 64 &&
+    // The fused form is off unless B200K_LAYER_FUSED_SILU=1: at 64 tokens its GEMM (two 64-column boxes per tensor, the up
+    // half exchanged through shared memory in the epilogue) costs 10 us more than the plain one, the launch it saves 3 us.
+    L->fused_silu = c.weight_format == 0 && env_char("B200K_LAYER_FUSED_SILU") == '1' && c.group_size >= 64 &&
                     (c.group_size & (c.group_size - 1)) == 0 && c.hidden % 64 == 0 && c.intermediate % 64 == 0;
     L->launches = L->fused_silu ? 9 : 10;
     {

@@ -91,8 +91,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constan
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int qp = gridDim.x - 1 - blockIdx.x;        // long pairs first
-    const int h = blockIdx.y, b = blockIdx.z, kvh = h / (A.hq / A.hkv);
+    // CTAs are dispatched in block-index order, x fastest: x runs over (sequence, head), y over the query pairs from the
+    // last (longest KV range) to the first, so the long CTAs of every head start before any short one
+    const int qp = gridDim.y - 1 - blockIdx.y;
+    const int h = blockIdx.x % A.hq, b = blockIdx.x / A.hq, kvh = h / (A.hq / A.hkv);
     const int q0 = qp * 2 * PT_BQ;
     // KV tiles that query tile x (rows q0 + 128 x ..) needs: positions 0 .. min(pos_offset + its last row, kv_len - 1);
     // none when the tile lies beyond q_len
@@ -343,7 +345,7 @@ int prefill_tc_launch(const __half *q, const __half *k, const __half *v, __half 
     constexpr int NOT_COVERED = -1000;
     if (d != PT_D || pos_offset < 0 || kv_len < 1 || q_len < 1 || hq % hkv || !(scale > 0.f)) return NOT_COVERED;
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return NOT_COVERED;
-    if (hq > 65535 || batch > 65535) return NOT_COVERED;
+    if (ceil_div(q_len, 2 * PT_BQ) > 65535 || (long)hq * batch > 0x7fffffffL) return NOT_COVERED;
     int *status = status_word();
     if (!status) return NOT_COVERED;
     const uint64_t row = PT_D * 2;
@@ -372,7 +374,7 @@ int prefill_tc_launch(const __half *q, const __half *k, const __half *v, __half 
         cudaError_t e = once[bf16].run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); });
         if (e != cudaSuccess) return fail((int)e, "flash_attn_full: shared memory %zu: %s", smem, cudaGetErrorString(e));
     }
-    const dim3 grid(ceil_div(q_len, 2 * PT_BQ), hq, batch);
+    const dim3 grid(hq * batch, ceil_div(q_len, 2 * PT_BQ), 1);
     kern<<<grid, PT_THREADS, smem, st>>>(qmap, kmap, vmap, A);
     return launch_status(bf16 ? "flash_attn_full_bf16" : "flash_attn_full_f16");
 }
