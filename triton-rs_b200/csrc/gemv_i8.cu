@@ -190,6 +190,41 @@ gemv_gptq_i8_kernel(GemmArgs g, int ksplit) {
     reduce_and_store<4>(tot, red4, kw, KW, cw * 32 + lane, 32 * CW, ksplit, live, g.c + col);
 }
 
+// UR consecutive activations (one per lane group) -> 15-bit integers with their own scale: lane i returns the bytes of
+// positions 4i .. 4i+3 of the unit (lanes >= UR / 4 return zeros).  UR = 128: a whole quantisation group, 4 values per
+// lane; UR = 32: one value per lane, packed by fours.
+template <int UR>
+__device__ __forceinline__ void quantise_unit(const __half *a_unit, int lane, uint32_t &qh, uint32_t &ql, float &sa, int &asum) {
+    if (UR == 128) {
+        quantise_group(a_unit, lane, qh, ql, sa, asum);
+        return;
+    }
+    const float f = __half2float(a_unit[lane]);
+    float amax = fabsf(f);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    sa = amax * (1.f / 16383.f);
+    const float inv = amax > 0.f ? 16383.f / amax : 0.f;
+    const int i0 = __float2int_rn(f * inv);
+    asum = __reduce_add_sync(0xffffffffu, i0);
+    // lane l holds position l: gather positions 4i .. 4i+3 into lane i
+    uint32_t h = 0, l = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int v = __shfl_sync(0xffffffffu, i0, (lane * 4 + j) & 31);
+        h |= (uint32_t)((v >> 7) & 255) << (8 * j);
+        l |= (uint32_t)(v & 127) << (8 * j);
+    }
+    qh = lane < 8 ? h : 0u;
+    ql = lane < 8 ? l : 0u;
+}
+
+// A warp covers 256 columns (one word per lane and row) and walks units of UR rows: a whole quantisation group, or a
+// quarter of one when the matrix is too narrow to fill the machine with whole groups per warp.  Every unit quantises its
+// own activations (its own scale: the identity above holds for any subset of k).  Rows are requested in half-batches of
+// 16 held in NB register buffers that rotate: while one is multiplied, NB - 1 are in flight (narrow matrices have few
+// warps, so each must keep more bytes in flight).
+template <int UR, int NB>
 __global__ void __launch_bounds__(GI_THREADS)
 gemv_awq_i8_kernel(GemmArgs g, int ksplit) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -197,27 +232,36 @@ gemv_awq_i8_kernel(GemmArgs g, int ksplit) {
     float4 *red4 = reinterpret_cast<float4 *>(smem_raw + GI_WARPS * 16 * sizeof(uint4));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int col = blockIdx.x * 256 + lane * 8;      // 8 columns per thread, 256 per warp
-    const int kslot = blockIdx.y * GI_WARPS + warp, kslots = ksplit * GI_WARPS;
-    const int groups = g.k / GI_GROUP;
+    const int uslot = blockIdx.y * GI_WARPS + warp, uslots = ksplit * GI_WARPS;
+    const int units = g.k / UR;
     const bool live = col < g.n;
     uint2 *my_act = act + warp * 32;
-    constexpr int BATCH = 32;                         // k rows requested before any is used
+    constexpr int HB = 16;                            // rows per half-batch
+    constexpr int HPU = UR / HB;                      // half-batches per unit
+    constexpr int UPG = GI_GROUP / UR;                // units per quantisation group
 
-    uint32_t w[BATCH];
+    uint32_t w[NB][HB];
     uint4 su = make_uint4(0, 0, 0, 0);
     uint32_t zw = 0;
-    auto request_meta = [&](int grp) {
-        zw = ldg_nc_word(g.qzeros + (long)grp * g.s_qzk + col / 8);
-        su = *reinterpret_cast<const uint4 *>(g.scales + (long)grp * g.s_sk + col);
+    auto request_meta = [&](int unit) {
+        if (unit < units) {
+            zw = ldg_nc_word(g.qzeros + (long)(unit / UPG) * g.s_qzk + col / 8);
+            su = *reinterpret_cast<const uint4 *>(g.scales + (long)(unit / UPG) * g.s_sk + col);
+        }
     };
-    auto request_rows = [&](int k0) {
-        const int32_t *wp = g.qweight + (long)k0 * g.s_qwk + col / 8;
+    // half-batch number t of this warp's sequence (unit uslot + (t / HPU) uslots, part t % HPU) -> buffer b
+    auto request_rows = [&](uint32_t (&buf)[HB], int first_unit, int t) {
+        const int unit = first_unit + (t / HPU) * uslots;
+        if (unit < units) {
+            const int32_t *wp = g.qweight + (long)(unit * UR + (t % HPU) * HB) * g.s_qwk + col / 8;
 #pragma unroll
-        for (int j = 0; j < BATCH; ++j) w[j] = ldg_nc_word(wp + (long)j * g.s_qwk);
+            for (int j = 0; j < HB; ++j) buf[j] = ldg_nc_word(wp + (long)j * g.s_qwk);
+        }
     };
-    if (live && kslot < groups) {
-        request_meta(kslot);
-        request_rows(kslot * GI_GROUP);
+    if (live) {
+        request_meta(uslot);
+#pragma unroll
+        for (int b = 0; b < NB; ++b) request_rows(w[b], uslot, b);
     }
 
     pdl_wait();
@@ -226,84 +270,116 @@ gemv_awq_i8_kernel(GemmArgs g, int ksplit) {
     float tot[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) tot[c] = 0.f;
-    for (int grp = kslot; grp < groups; grp += kslots) {
-        if (live && grp != kslot) request_meta(grp);
-        uint32_t qh, ql;
-        float sa;
-        int asum;
-        quantise_group(g.a + (long)grp * GI_GROUP, lane, qh, ql, sa, asum);
-        __syncwarp();
-        my_act[lane] = make_uint2(qh, ql);          // bytes already in k order: lane i = k 4i .. 4i+3
-        __syncwarp();
-        if (!live) continue;
-        // byte b of the even-nibble words = nibble 2b = column (0,4,1,5)[b]; of the odd-nibble words = nibble 2b+1 =
-        // column (2,6,3,7)[b] (the AWQ order [0,4,1,5,2,6,3,7] maps column -> nibble)
-        int ae[4][2], ao[4][2];
+    // HPU and NB are powers of two, so the buffer of half-batch t is t % NB with t counted from this warp's first unit; a
+    // pass of the loop below covers max(HPU, NB) half-batches, i.e. one or more whole units, and ends on buffer 0 again
+    constexpr int UPP = NB > HPU ? NB / HPU : 1;      // units per pass
+    for (int u0 = uslot; u0 < units; u0 += UPP * uslots) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) ae[c][0] = ae[c][1] = ao[c][0] = ao[c][1] = 0;
-        const int k0 = grp * GI_GROUP;
-        for (int kk = 0; kk < GI_GROUP; kk += BATCH) {
-            if (!(grp == kslot && kk == 0)) request_rows(k0 + kk);
+        for (int uu = 0; uu < UPP; ++uu) {
+            const int u = u0 + uu * uslots;
+            if (u >= units) break;
+            uint32_t qh, ql;
+            float sa;
+            int asum;
+            quantise_unit<UR>(g.a + (long)u * UR, lane, qh, ql, sa, asum);
+            __syncwarp();
+            my_act[lane] = make_uint2(qh, ql);          // bytes already in k order: lane i = k 4i .. 4i+3
+            __syncwarp();
+            if (!live) continue;
+            const uint4 su_now = su;
+            const uint32_t zw_now = zw;
+            request_meta(u + uslots);
+            // byte b of the even-nibble words = nibble 2b = column (0,4,1,5)[b]; of the odd-nibble words = nibble 2b+1 =
+            // column (2,6,3,7)[b] (the AWQ order [0,4,1,5,2,6,3,7] maps column -> nibble)
+            int ae[4][2], ao[4][2];
 #pragma unroll
-            for (int j = 0; j < BATCH; j += 4) {
-                const uint2 av = my_act[(kk + j) >> 2];
-                uint32_t e[4], o[4];
+            for (int c = 0; c < 4; ++c) ae[c][0] = ae[c][1] = ao[c][0] = ao[c][1] = 0;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    e[i] = w[j + i] & 0x0F0F0F0Fu;
-                    o[i] = w[j + i] & 0xF0F0F0F0u;
+            for (int hb = 0; hb < HPU; ++hb) {
+                const int t = uu * HPU + hb;            // half-batch number within the pass
+                uint32_t (&buf)[HB] = w[t % NB];
+#pragma unroll
+                for (int j = 0; j < HB; j += 4) {
+                    const uint2 av = my_act[(hb * HB + j) >> 2];
+                    uint32_t e[4], o[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        e[i] = buf[j + i] & 0x0F0F0F0Fu;
+                        o[i] = buf[j + i] & 0xF0F0F0F0u;
+                    }
+                    // 4 x 4 byte transposes: word i (row k+i, four columns) -> word c (column c, rows k .. k+3)
+                    const uint32_t e01l = __byte_perm(e[0], e[1], 0x5140), e23l = __byte_perm(e[2], e[3], 0x5140);
+                    const uint32_t e01h = __byte_perm(e[0], e[1], 0x7362), e23h = __byte_perm(e[2], e[3], 0x7362);
+                    const uint32_t o01l = __byte_perm(o[0], o[1], 0x5140), o23l = __byte_perm(o[2], o[3], 0x5140);
+                    const uint32_t o01h = __byte_perm(o[0], o[1], 0x7362), o23h = __byte_perm(o[2], o[3], 0x7362);
+                    const uint32_t ce[4] = {__byte_perm(e01l, e23l, 0x5410), __byte_perm(e01l, e23l, 0x7632),
+                                            __byte_perm(e01h, e23h, 0x5410), __byte_perm(e01h, e23h, 0x7632)};
+                    const uint32_t co[4] = {__byte_perm(o01l, o23l, 0x5410), __byte_perm(o01l, o23l, 0x7632),
+                                            __byte_perm(o01h, o23h, 0x5410), __byte_perm(o01h, o23h, 0x7632)};
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        ae[c][0] = dp4a_us(ce[c], av.x, ae[c][0]);
+                        ae[c][1] = dp4a_us(ce[c], av.y, ae[c][1]);
+                        ao[c][0] = dp4a_us(co[c], av.x, ao[c][0]);
+                        ao[c][1] = dp4a_us(co[c], av.y, ao[c][1]);
+                    }
                 }
-                // 4 x 4 byte transposes: word i (row k+i, four columns) -> word c (column c, rows k .. k+3)
-                const uint32_t e01l = __byte_perm(e[0], e[1], 0x5140), e23l = __byte_perm(e[2], e[3], 0x5140);
-                const uint32_t e01h = __byte_perm(e[0], e[1], 0x7362), e23h = __byte_perm(e[2], e[3], 0x7362);
-                const uint32_t o01l = __byte_perm(o[0], o[1], 0x5140), o23l = __byte_perm(o[2], o[3], 0x5140);
-                const uint32_t o01h = __byte_perm(o[0], o[1], 0x7362), o23h = __byte_perm(o[2], o[3], 0x7362);
-                const uint32_t ce[4] = {__byte_perm(e01l, e23l, 0x5410), __byte_perm(e01l, e23l, 0x7632),
-                                        __byte_perm(e01h, e23h, 0x5410), __byte_perm(e01h, e23h, 0x7632)};
-                const uint32_t co[4] = {__byte_perm(o01l, o23l, 0x5410), __byte_perm(o01l, o23l, 0x7632),
-                                        __byte_perm(o01h, o23h, 0x5410), __byte_perm(o01h, o23h, 0x7632)};
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    ae[c][0] = dp4a_us(ce[c], av.x, ae[c][0]);
-                    ae[c][1] = dp4a_us(ce[c], av.y, ae[c][1]);
-                    ao[c][0] = dp4a_us(co[c], av.x, ao[c][0]);
-                    ao[c][1] = dp4a_us(co[c], av.y, ao[c][1]);
-                }
+                request_rows(buf, u0, t + NB);          // the half-batch that uses this buffer next
             }
-        }
-        const float2 sA = h2_to_f2(su.x), sB = h2_to_f2(su.y), sC = h2_to_f2(su.z), sD = h2_to_f2(su.w);
-        const float sc[8] = {sA.x, sA.y, sB.x, sB.y, sC.x, sC.y, sD.x, sD.y};
+            const float2 sA = h2_to_f2(su_now.x), sB = h2_to_f2(su_now.y), sC = h2_to_f2(su_now.z), sD = h2_to_f2(su_now.w);
+            const float sc[8] = {sA.x, sA.y, sB.x, sB.y, sC.x, sC.y, sD.x, sD.y};
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            const int ce_col = (b & 1) * 4 + (b >> 1);          // (0,4,1,5)[b]
-            const int co_col = ce_col + 2;                      // (2,6,3,7)[b]
-            const int ze = (int)((zw >> (8 * b)) & 15u), zo = (int)((zw >> (8 * b + 4)) & 15u);
-            const int de = 128 * ae[b][0] + ae[b][1];
-            const int dn = 128 * (ao[b][0] >> 4) + (ao[b][1] >> 4);
-            tot[ce_col] += (float)(de - ze * asum) * (sc[ce_col] * sa);
-            tot[co_col] += (float)(dn - zo * asum) * (sc[co_col] * sa);
+            for (int b = 0; b < 4; ++b) {
+                const int ce_col = (b & 1) * 4 + (b >> 1);          // (0,4,1,5)[b]
+                const int co_col = ce_col + 2;                      // (2,6,3,7)[b]
+                const int ze = (int)((zw_now >> (8 * b)) & 15u), zo = (int)((zw_now >> (8 * b + 4)) & 15u);
+                const int de = 128 * ae[b][0] + ae[b][1];
+                const int dn = 128 * (ao[b][0] >> 4) + (ao[b][1] >> 4);
+                tot[ce_col] += (float)(de - ze * asum) * (sc[ce_col] * sa);
+                tot[co_col] += (float)(dn - zo * asum) * (sc[co_col] * sa);
+            }
         }
     }
     reduce_and_store<8>(tot, red4, warp, GI_WARPS, lane, 32, ksplit, live, g.c + col);
 }
 
-// The integer GEMV covers: M = 1, fp16, group 128, canonical layout (the caller has checked the layout).
+static inline int imin(int a, int b) { return a < b ? a : b; }
+static inline int imax(int a, int b) { return a > b ? a : b; }
+
 int gemv_i8_launch(const GemmArgs &g) {
     if (g.m != 1 || g.group != GI_GROUP || g.bf16 || g.k % GI_GROUP) return TC_NOT_COVERED;
     const int groups = g.k / GI_GROUP;
-    int cw = 2;
-    if (g.format == FMT_GPTQ && ceil_div(g.n, 256) * 8 < 2 * sm_count()) cw = 1;
+    // GPTQ: 256 columns per CTA (2 column-warps x 4 k-warps), or 128 (1 x 8) when 256-column blocks with the largest
+    // cluster would leave SMs without a CTA.  AWQ: 256 columns per CTA, all 8 warps split K, by whole groups, or by
+    // quarter groups when K is short and whole groups per warp with the largest cluster would leave most SMs without a CTA.
+    const int cw = g.format != FMT_GPTQ ? 1 : ceil_div(g.n, 256) * 8 < 2 * sm_count() ? 1 : 2;
     const int colblocks = g.format == FMT_GPTQ ? ceil_div(g.n, 128 * cw) : ceil_div(g.n, 256);
-    const int kwarps = g.format == FMT_GPTQ ? GI_WARPS / cw : GI_WARPS;
-    // enough CTAs for ~2 per SM, cluster size a power of two <= 8, no warp without a group
+    const int kwarps = GI_WARPS / cw;
+    int unit_rows = GI_GROUP;
+    if (g.format == FMT_AWQ && groups < 64 && colblocks * imin(8, imax(1, groups / (2 * kwarps))) < sm_count()) unit_rows = 32;
+    {   // tuning override
+        const int v = env_int("B200K_GEMV_UNIT", 0);
+        if (g.format == FMT_AWQ && (v == 32 || v == 128)) unit_rows = v;
+    }
+    const int units = g.k / unit_rows;
+    // enough CTAs for ~2 per SM, cluster size a power of two <= 8, no warp without a unit
     int ksplit = 1;
-    while (ksplit < 8 && colblocks * ksplit < 2 * sm_count() && ksplit * 2 * kwarps <= groups) ksplit *= 2;
+    while (ksplit < 8 && colblocks * ksplit < 2 * sm_count() && ksplit * 2 * kwarps <= units) ksplit *= 2;
     {   // tuning override
         const int v = env_int("B200K_GEMV_KSPLIT", 0);
-        if ((v == 1 || v == 2 || v == 4 || v == 8) && v * kwarps <= groups) ksplit = v;
+        if ((v == 1 || v == 2 || v == 4 || v == 8) && v * kwarps <= units) ksplit = v;
     }
     const size_t smem = GI_WARPS * 16 * sizeof(uint4) + (size_t)GI_WARPS * 256 * sizeof(float);
-    auto kern = g.format != FMT_GPTQ ? gemv_awq_i8_kernel : cw == 2 ? gemv_gptq_i8_kernel<2> : gemv_gptq_i8_kernel<1>;
+    void (*kern)(GemmArgs, int);
+    if (g.format == FMT_GPTQ) kern = cw == 2 ? gemv_gptq_i8_kernel<2> : gemv_gptq_i8_kernel<1>;
+    else {
+        // four half-batches per warp in flight (measured: ahead of two at every shape of the Llama-3-8B projections)
+        int nb = 4;
+        const int v = env_int("B200K_GEMV_DEPTH", 0);      // tuning override
+        if (v == 2 || v == 4) nb = v;
+        kern = unit_rows == 32 ? (nb == 4 ? gemv_awq_i8_kernel<32, 4> : gemv_awq_i8_kernel<32, 2>)
+                               : (nb == 4 ? gemv_awq_i8_kernel<128, 4> : gemv_awq_i8_kernel<128, 2>);
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(colblocks, ksplit, 1);
     cfg.blockDim = dim3(GI_THREADS, 1, 1);
