@@ -350,6 +350,99 @@ def component_metrics(pkg, torch, dev, gen):
     return out
 
 
+def tp_component_metrics(pkg, torch, dist, dev, rank, world, gen, shape, comm):
+    """N > 1: what one rank runs, kernel by kernel (CUDA-graph replay over rotating weights, max over ranks): the four
+    GEMMs of the layer at their rank-local extents, the all-reduce alone, and the expert-parallel fused MoE of config 3
+    (E / N experts per rank, replicated tokens, one all-reduce of the partial outputs)."""
+    P = pkg.prelude
+    hbm_peak, tf_peak, _ = peaks()
+    ls = shape.local(world)
+    H, d, G = shape.hidden, shape.head_dim, shape.group_size
+
+    def ri(*s):
+        return torch.randint(-2 ** 31, 2 ** 31 - 1, s, device=dev, dtype=torch.int32, generator=gen)
+
+    def replay_ms(fn, calls, reps=5):
+        st = torch.cuda.Stream()
+        with torch.cuda.stream(st):
+            for _ in range(3):
+                fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=st):
+            for _ in range(calls):
+                fn()
+        best = 1e30
+        for _ in range(reps + 1):
+            dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); gr.replay(); b.record()
+            torch.cuda.synchronize()
+            best = min(best, a.elapsed_time(b) / calls)
+        t = torch.tensor([best], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    out = {}
+    cells = {"qkv": (H, (ls.num_q_heads + 2 * ls.num_kv_heads) * d), "o": (ls.num_q_heads * d, H),
+             "gate_up": (H, 2 * ls.intermediate), "down": (ls.intermediate, H)}
+    for name, (k, n) in cells.items():
+        nbuf = max(2, int(300e6 // (k * n // 2)))
+        qws = [ri(k // 8, n) for _ in range(nbuf)]
+        sc = (torch.rand((k // G, n), device=dev, generator=gen) * 0.018 + 0.002).half()
+        qz = torch.full((k // G, n // 8), 0x77777777, device=dev, dtype=torch.int32)
+        a = torch.randn((BATCH, k), device=dev, generator=gen, dtype=torch.float16)
+        c = torch.empty((BATCH, n), device=dev, dtype=torch.float16)
+        i = [0]
+
+        def fn():
+            i[0] = (i[0] + 1) % nbuf
+            P.gptq_gemm(a, qws[i[0]], sc, qz, G, out=c)
+        ms = replay_ms(fn, 2 * nbuf)
+        byts = k * n // 2 + (k // G) * n * 2 + (k // G) * n // 2 + 2 * BATCH * k + 2 * BATCH * n
+        out[f"gemm_{name}_m{BATCH}_k{k}_n{n}"] = {"us": ms * 1e3, "GB/s": byts / ms / 1e6, "frac_hbm": byts / ms / 1e6 / hbm_peak}
+        del qws
+    # the exchange alone: one all-reduce of the layer's [64, H] fp16 partial sums, slots alternating
+    x = torch.randn((BATCH, H), device=dev, generator=gen, dtype=torch.float16)
+    y = torch.empty_like(x)
+    sl = [0]
+
+    def ar():
+        sl[0] ^= 1
+        comm.all_reduce(sl[0], y, BATCH * H, input=x)
+    ms = replay_ms(ar, 8)
+    out["all_reduce_64x4096_f16"] = {"us": ms * 1e3, "bytes_in_per_rank": (world - 1) * BATCH * H * 2}
+    # config 3 expert-parallel
+    T, E, kk, Hm, I = 512, 8, 2, 4096, 14336
+    if E % world == 0:
+        per = E // world
+        big = pkg.Comm.from_process_group(T * Hm * 2)
+        mgen = torch.Generator(device=dev).manual_seed(99)                  # same tokens and logits on every rank
+        xm = torch.randn((T, Hm), device=dev, generator=mgen, dtype=torch.float16)
+        lg = torch.randn((T, E), device=dev, generator=mgen)
+        w13q, w2q = ri(per, Hm // 8, 2 * I), ri(per, I // 8, Hm)
+        w13s = (torch.rand((per, Hm // G, 2 * I), device=dev, generator=gen) * 0.018 + 0.002).half()
+        w2s = (torch.rand((per, I // G, Hm), device=dev, generator=gen) * 0.018 + 0.002).half()
+        part = torch.empty((T, Hm), dtype=torch.float16, device=dev)
+        full = torch.empty_like(part)
+        sl2 = [0]
+
+        def moe():
+            sl2[0] ^= 1
+            P.fused_moe_gptq_ep_f16(xm, lg, w13q, w13s, None, w2q, w2s, None, part, T, Hm, E, rank * per, per, kk, I, G, None, 0)
+            big.all_reduce(sl2[0], full, T * Hm, input=part)
+        ms = replay_ms(moe, 2)
+        flops = T * kk * (2 * Hm * 2 * I + 2 * I * Hm)
+        out["fused_moe_c3_expert_parallel"] = {"us": ms * 1e3, "TFLOP/s_all_ranks": flops / ms / 1e9,
+                                               "experts_per_rank": per, "all_reduce_bytes": T * Hm * 2,
+                                               "comm_status": big.status()}
+        torch.cuda.synchronize()
+        dist.barrier()
+        big.close()
+    return out
+
+
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -567,6 +660,11 @@ def run_gpu_arm(args):
     clocks = sampler.stop() if rank == 0 else None
 
     components = component_metrics(pkg, torch, dev, gen) if world == 1 and not args.no_components else None
+    if world > 1 and own_comm and not args.no_components:
+        components = tp_component_metrics(pkg, torch, dist, dev, rank, world, gen, shape, comm)
+        components["decode_attention_rank_local"] = {"us": attn_ms * 1e3, "kv_heads": ls.num_kv_heads,
+                                                     "GB/s": (2 * BATCH * ls.num_kv_heads * ml * d * 2) / attn_ms / 1e6}
+        note("tensor-parallel components timed")
 
     # device-side failure channels: any bounded wait that gave up, any clamped index, on any rank, voids the number
     status = ctypes.c_int(-1)

@@ -111,3 +111,27 @@ def test_layer_llama_shape_vs_c_oracle(pkg, oracle):
     rep = layer_check.check_layer(pkg, torch, DEV, case, ref, st, ref_alt=ref_alt)
     assert rep["stages_ok"], rep
     assert rep["ok"], rep
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_layer_rank_local_extents_vs_c_oracle(pkg, oracle, world):
+    """The kernels one rank of a tensor-parallel group of `world` runs: BASELINE config 4 with q heads, kv heads and
+    intermediate columns divided by `world` (batch 64, context 4096), as a layer of its own (the exchanges left out),
+    against the C oracle at those extents.  Also the vehicle for the per-kernel launch lists of the rank-local shapes
+    (one GPU is enough: ncu never sees a multi-rank command)."""
+    import layer_check
+    rng = np.random.default_rng(40 + world)
+    B, H, hq, hkv, d, I, G, ml = 64, 4096, 32 // world, 8 // world, 128, 14336 // world, 128, 4097
+    p = make_layer(oracle, rng, H, hq, hkv, d, I, G, ml, zero_mean=True)
+    kc = rng.standard_normal((B, hkv, ml, d), dtype=np.float32).astype(np.float16)
+    vc = rng.standard_normal((B, hkv, ml, d), dtype=np.float32).astype(np.float16)
+    case = dict(H=H, hq=hq, hkv=hkv, d=d, I=I, G=G, ml=ml, eps=1e-5, cos=p["cos"], sin=p["sin"], ln1=p["ln1"], ln2=p["ln2"],
+                qkv=p["qkv"], o=p["o"], gate_up=p["gate_up"], down=p["down"], kc=kc, vc=vc,
+                hidden=rng.standard_normal((B, H)).astype(np.float16), pos=np.full(B, ml - 1, dtype=np.int32))
+    oc = layer_check.load_oracle_c()
+    ref_alt = layer_check.oracle_layer(oc, case, faithful=0, want_stages=False)[0]
+    ref, st, _ = layer_check.oracle_layer(oc, case)
+    assert np.isfinite(ref).all()
+    rep = layer_check.check_layer(pkg, torch, DEV, case, ref, st, ref_alt=ref_alt)
+    assert rep["stages_ok"], rep
+    assert rep["ok"], rep

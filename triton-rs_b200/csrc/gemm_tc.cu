@@ -252,7 +252,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         // commits to one barrier per block.
         const int mw = warp - 1;
         if (lane == 0 && mw < NMMA) {
-            const uint32_t idesc = umma_idesc(TC_BN, TT, FMT == FMT_AWQ ? 1 : 0) | (BF ? (1u << 7) | (1u << 10) : 0u);   // A, B format: f16 or bf16
+            // MMA N = the rows this tile really holds, rounded up to 16: a segment of 130 rows in a 256-row tile, or the
+            // last tile of an ordinary GEMM, costs the tensor pipe what it uses (accumulator columns beyond stay unwritten
+            // and are never stored)
+            const int tt_mma = min(TT, ((min(m_end, m0 + TT) - m0 + 15) >> 4) << 4);
+            const uint32_t idesc = umma_idesc(TC_BN, tt_mma, FMT == FMT_AWQ ? 1 : 0) | (BF ? (1u << 7) | (1u << 10) : 0u);   // A, B format: f16 or bf16
             const uint64_t da0 = FMT == FMT_GPTQ ? umma_desc(smem_u32(a_tile), 16, 1024)       // K-major: 8-row groups 1 KiB apart
                                                  : umma_desc(smem_u32(a_tile), 8192, 1024);    // MN-major: 64-column halves 8 KiB apart, 8-k groups 1 KiB apart
             const uint64_t db0 = umma_desc(smem_u32(b_tile), 16, 1024);
