@@ -440,6 +440,28 @@ def tp_component_metrics(pkg, torch, dist, dev, rank, world, gen, shape, comm):
         torch.cuda.synchronize()
         dist.barrier()
         big.close()
+        # the same MoE by token exchange: every rank holds T / N of the tokens and E / N experts
+        if T % world == 0:
+            L = pkg.lib()
+            t_loc = T // world
+            xc = pkg.Comm.from_process_group(L.call("fused_moe_a2a_slot_bytes", t_loc, Hm, kk, world))
+            x_loc = xm[rank * t_loc:(rank + 1) * t_loc].contiguous()
+            lg_loc = lg[rank * t_loc:(rank + 1) * t_loc].contiguous()
+            o_loc = torch.empty((t_loc, Hm), dtype=torch.float16, device=dev)
+
+            def moe_x():
+                L.call("fused_moe_gptq_a2a_f16", xc.handle, x_loc, lg_loc, w13q, w13s, None, w2q, w2s, None, o_loc, t_loc, Hm, E, kk, I, G,
+                       7, None, 0, torch.cuda.current_stream().cuda_stream)
+            ms = replay_ms(moe_x, 2)
+            # the two forms must agree on this rank's tokens (same pairs, same experts, same weights): checked against the
+            # all-reduce form computed above
+            close = bool(torch.allclose(o_loc.float(), full[rank * t_loc:(rank + 1) * t_loc].float(), rtol=2e-2, atol=2e-2))
+            out["fused_moe_c3_token_exchange"] = {"us": ms * 1e3, "TFLOP/s_all_ranks": flops / ms / 1e9, "experts_per_rank": per,
+                                                  "rows_out_per_rank": t_loc * kk, "agrees_with_all_reduce_form": close,
+                                                  "comm_status": xc.status()}
+            torch.cuda.synchronize()
+            dist.barrier()
+            xc.close()
     return out
 
 

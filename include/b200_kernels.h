@@ -665,6 +665,27 @@ int b200k_comm_set_timeout_cycles(struct b200k_comm *comm, int64_t cycles);
 int b200k_comm_buffer(struct b200k_comm *comm, void **host_out_ptr);
 int b200k_comm_set_peer_pointer(struct b200k_comm *comm, int peer_rank, void *peer_buffer);
 void b200k_comm_destroy(struct b200k_comm *comm);
+/* Expert parallelism by token exchange (dispatch / combine): rank r of the group holds tokens_local tokens and the
+ * experts [r E/N, (r + 1) E/N) (w13 / w2 stacks of E/N matrices, layouts as fused_moe_gptq_f16).  Every rank makes the
+ * same call; a call routes the local tokens, writes each (token, choice) row into the exchange buffer of the rank that
+ * owns the expert (peer stores), runs the local experts on what it received, and gathers the k result rows of each
+ * local token from their owners (peer loads) with the routing weights: out_local [tokens_local, H].  Per rank
+ * tokens_local * top_k rows travel each way, against the (N - 1) * N * tokens_local rows read by the all-reduce of
+ * fused_moe_gptq_ep_f16 partial outputs.  The exchange buffer's slots must hold fused_moe_a2a_slot_bytes(...) bytes
+ * (b200k_comm_create); num_experts % N == 0.  Waits for peers are bounded (b200k_comm_set_timeout_cycles) and report
+ * through b200k_comm_status.  `phases`: 7 in a real group (one process per GPU).  The bits run the three phases
+ * separately -- 1 dispatch, 2 experts, 4 combine, each waiting only for what earlier phases of the other ranks
+ * published -- so that a harness holding every rank's buffers on one GPU can run phase by phase over the ranks;
+ * kernels that wait for one another must never be queued in the other order on one GPU.  workspace: as
+ * fused_moe_gptq_f16, sized by fused_moe_workspace_bytes(N * tokens_local, ...); ranks that share a GPU need one each.
+ * No counterpart in the reference. */
+size_t fused_moe_a2a_slot_bytes(int tokens_local, int hidden, int top_k, int world);
+int fused_moe_gptq_a2a_f16(struct b200k_comm *comm, const b200k_half *x_local, const float *router_logits_local,
+                           const int32_t *w13_qweight, const b200k_half *w13_scales, const int32_t *w13_qzeros,
+                           const int32_t *w2_qweight, const b200k_half *w2_scales, const int32_t *w2_qzeros,
+                           b200k_half *out_local, int tokens_local, int hidden, int num_experts, int top_k,
+                           int intermediate, int group_size, int phases, void *workspace,
+                           size_t workspace_bytes, b200k_stream stream);
 /* Attach to a layer: the o and down GEMMs then write into slots 0 and 1 and the layer chain runs the
  * two all-reduces itself, each fused with the step that consumes it (10 launches, as on one GPU).
  * NULL detaches (single GPU). */

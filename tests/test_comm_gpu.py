@@ -148,6 +148,28 @@ def _rank_main(rank, world, port, q):
         got = full.float().cpu().numpy()
         assert_close_terms(got, ref, mag, k, what="ep moe")
         assert comm.status() == 0
+
+        # ---- expert-parallel MoE by token exchange: every rank holds a slice of the tokens and of the experts ----
+        T_loc = 20
+        T = world * T_loc
+        x = rng.standard_normal((T, H)).astype(np.float16)
+        logits = rng.standard_normal((T, E)).astype(np.float32)
+        ref, mag = o.fused_moe_gptq(x, logits, w13q, w13s, w2q, w2s, k, G, faithful=True, with_mag=True)
+        L = pkg.lib()
+        big = pkg.Comm.from_process_group(L.call("fused_moe_a2a_slot_bytes", T_loc, H, k, world))
+        mine = torch.empty((T_loc, H), dtype=torch.float16, device=dev)
+        wl = (t(w13q[lo:hi]), t(w13s[lo:hi]), t(w2q[lo:hi]), t(w2s[lo:hi]))
+        for rnd in range(3):                     # later rounds reuse every region of the exchange buffers
+            dist.barrier()
+            L.call("fused_moe_gptq_a2a_f16", big.handle, t(x[rank * T_loc:(rank + 1) * T_loc]), t(logits[rank * T_loc:(rank + 1) * T_loc]),
+                   wl[0], wl[1], None, wl[2], wl[3], None, mine, T_loc, H, E, k, I, G, 7, None, 0, st)
+            torch.cuda.synchronize()
+            assert big.status() == 0
+            got = mine.float().cpu().numpy()
+            sl = slice(rank * T_loc, (rank + 1) * T_loc)
+            assert_close_terms(got, ref[sl], mag[sl], k, what=f"token-exchange moe, round {rnd}")
+        dist.barrier()
+        big.close()
         dist.barrier()
         layer.close()
         comm.close()

@@ -147,3 +147,61 @@ def test_expert_parallel_rejects_bad_ranges(P):
     for first, local in [(-1, 2), (7, 2), (0, 0), (0, 9)]:
         with pytest.raises(Exception):
             P.fused_moe_gptq_ep_f16(z, z, z, z, None, z, z, None, z, 4, 128, 8, first, local, 2, 128, 128, None, 0)
+
+
+@pytest.mark.parametrize("world,T_loc,E,k,H,I", [(2, 24, 8, 2, 256, 384), (4, 16, 8, 2, 256, 256), (8, 8, 8, 3, 128, 256)])
+def test_token_exchange_expert_parallel_group_on_one_gpu(P, pkg, oracle, world, T_loc, E, k, H, I):
+    """fused_moe_gptq_a2a_f16 for a whole group held on ONE GPU: every rank has its own exchange buffer (the peers'
+    buffers installed as plain pointers) and its own workspace, and the three phases are run phase by phase over the
+    ranks, so that no kernel ever waits for one queued behind it.  Each rank owns T_loc tokens and E / world experts;
+    the outputs, put back together, are the fused MoE of all tokens.  Run twice: the second round reuses every region."""
+    import ctypes
+    L = pkg.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    rng = np.random.default_rng(world * 100 + T_loc)
+    G, T, per = 128, world * T_loc, E // world
+    w13q = np.stack([oracle.pack_gptq_qweight(rng.integers(1, 16, (H, 2 * I), dtype=np.int32)) for _ in range(E)])
+    w13s = rng.uniform(0.002, 0.02, (E, H // G, 2 * I)).astype(np.float16)
+    w2q = np.stack([oracle.pack_gptq_qweight(rng.integers(1, 16, (I, H), dtype=np.int32)) for _ in range(E)])
+    w2s = rng.uniform(0.002, 0.02, (E, I // G, H)).astype(np.float16)
+    slot = L.call("fused_moe_a2a_slot_bytes", T_loc, H, k, world)
+    comms = [ctypes.c_void_p() for _ in range(world)]
+    bufs = [ctypes.c_void_p() for _ in range(world)]
+    for r in range(world):
+        L.call("b200k_comm_create", r, world, slot, ctypes.addressof(comms[r]))
+        L.call("b200k_comm_buffer", comms[r].value, ctypes.addressof(bufs[r]))
+    for r in range(world):
+        for q in range(world):
+            if q != r:
+                L.call("b200k_comm_set_peer_pointer", comms[r].value, q, bufs[q].value)
+    ws_bytes = L.call("fused_moe_workspace_bytes", T, H, E, k, I)
+    ws = [torch.zeros(ws_bytes, dtype=torch.uint8, device=DEV) for _ in range(world)]
+    wd = [(t(w13q[r * per:(r + 1) * per]), t(w13s[r * per:(r + 1) * per]), t(w2q[r * per:(r + 1) * per]), t(w2s[r * per:(r + 1) * per]))
+          for r in range(world)]
+    for rnd in range(2):
+        x = rng.standard_normal((T, H)).astype(np.float16)
+        logits = rng.standard_normal((T, E)).astype(np.float32)
+        if rnd == 1:
+            logits[:, 0] += 4.0                    # skewed round: expert 0 takes a choice of every token
+        xs = [t(x[r * T_loc:(r + 1) * T_loc]) for r in range(world)]
+        ls = [t(logits[r * T_loc:(r + 1) * T_loc]) for r in range(world)]
+        outs = [torch.full((T_loc, H), float("nan"), dtype=torch.float16, device=DEV) for _ in range(world)]
+        for phase in (1, 2, 4):
+            for r in range(world):
+                a, b, c, d = wd[r]
+                L.call("fused_moe_gptq_a2a_f16", comms[r].value, xs[r], ls[r], a, b, None, c, d, None, outs[r], T_loc, H, E, k, I, G,
+                       phase, ws[r], ws_bytes, st)
+        torch.cuda.synchronize()
+        for r in range(world):
+            v = ctypes.c_int(-1)
+            L.call("b200k_comm_status", comms[r].value, ctypes.addressof(v), st)
+            assert v.value == 0, (rnd, r)
+        got = np.concatenate([o.float().cpu().numpy() for o in outs])
+        ref, mag = oracle.fused_moe_gptq(x, logits, w13q, w13s, w2q, w2s, k, G, faithful=True, with_mag=True)
+        assert np.isfinite(got).all()
+        assert_close_terms(got, ref, mag, k, what=f"token-exchange MoE, world {world}, round {rnd}")
+    with pytest.raises(pkg.B200KError):            # a group that does not divide the experts
+        L.call("fused_moe_gptq_a2a_f16", comms[0].value, xs[0], ls[0], wd[0][0], wd[0][1], None, wd[0][2], wd[0][3], None, outs[0],
+               T_loc, H, world + 1 if (world + 1) % world else world + 3, k, I, G, 7, ws[0], ws_bytes, st)
+    for c in comms:
+        L.raw("b200k_comm_destroy")(c.value)

@@ -15,7 +15,7 @@
 // contains the call can be replayed.  Slots alternate between the two all-reduces of a layer; a slot is
 // rewritten only after a later all-reduce has passed its barrier, i.e. after every peer finished
 // reading it.
-#include "common.cuh"
+#include "comm.cuh"
 
 struct b200k_comm {
     int rank, world;
@@ -29,20 +29,12 @@ struct b200k_comm {
 
 namespace b200k {
 
-constexpr size_t COMM_FLAGS_BYTES = 4096;   // [0,32): flags (one per peer, written by that peer); [64]: sequence; [68]: done counter; [72]: status
+// (layout of the flags page: comm.cuh)
 constexpr int COMM_MAX_WORLD = 8;
 constexpr long long COMM_DEFAULT_WAIT_CYCLES = 2000000000LL;   // about a second of SM clock
 
-__device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 __device__ __forceinline__ __half2 u2h(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
 __device__ __forceinline__ uint32_t h22(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
 
 // Entry protocol shared by the all-reduce kernels: publish "my slot holds round `seq`" to every peer (CTA 0), wait --
 // bounded -- until every peer has published the same round.  Returns false when a peer never arrived (status word set).
@@ -240,6 +232,16 @@ __half *comm_slot(struct ::b200k_comm *c, int slot) {
 }
 
 size_t comm_slot_capacity(struct ::b200k_comm *c) { return c ? c->slot_bytes : 0; }
+
+CommView comm_view(struct ::b200k_comm *c) {
+    CommView v = {};
+    if (!c) return v;
+    v.d_peers = c->d_peers; v.local = c->local; v.rank = c->rank; v.world = c->world;
+    v.slot_bytes = c->slot_bytes; v.wait_cycles = c->wait_cycles;
+    v.mapped = true;
+    for (int r = 0; r < c->world; ++r) v.mapped = v.mapped && c->peer[r] != nullptr;
+    return v;
+}
 
 }  // namespace b200k
 

@@ -447,6 +447,15 @@ extern "C" {
         comm: *mut b200k_comm, peer_rank: c_int, peer_buffer: *mut c_void
     ) -> c_int;
     pub fn b200k_comm_destroy(comm: *mut b200k_comm);
+    pub fn fused_moe_a2a_slot_bytes(tokens_local: c_int, hidden: c_int, top_k: c_int, world: c_int) -> usize;
+    pub fn fused_moe_gptq_a2a_f16(
+        comm: *mut b200k_comm, x_local: *const b200k_half, router_logits_local: *const f32,
+        w13_qweight: *const i32, w13_scales: *const b200k_half, w13_qzeros: *const i32,
+        w2_qweight: *const i32, w2_scales: *const b200k_half, w2_qzeros: *const i32,
+        out_local: *mut b200k_half, tokens_local: c_int, hidden: c_int, num_experts: c_int, top_k: c_int,
+        intermediate: c_int, group_size: c_int, phases: c_int, workspace: *mut c_void, workspace_bytes: usize,
+        stream: b200k_stream
+    ) -> c_int;
     pub fn b200k_layer_set_comm(layer: *mut b200k_layer, comm: *mut b200k_comm) -> c_int;
     pub fn b200k_layer_forward(
         layer: *mut b200k_layer, hidden_in: *const b200k_half, positions: *const i32,
