@@ -455,9 +455,13 @@ def tp_component_metrics(pkg, torch, dist, dev, rank, world, gen, shape, comm):
             ms = replay_ms(moe_x, 2)
             # the two forms must agree on this rank's tokens (same pairs, same experts, same weights): checked against the
             # all-reduce form computed above
-            close = bool(torch.allclose(o_loc.float(), full[rank * t_loc:(rank + 1) * t_loc].float(), rtol=2e-2, atol=2e-2))
+            # all-reduce form computed above.  That form rounds every rank's partial sum to fp16 before adding them, and the
+            # partial sums cancel, so the yardstick is the magnitude of the outputs, not of each element
+            want = full[rank * t_loc:(rank + 1) * t_loc].float()
+            diff, top = float((o_loc.float() - want).abs().max()), float(want.abs().max())
             out["fused_moe_c3_token_exchange"] = {"us": ms * 1e3, "TFLOP/s_all_ranks": flops / ms / 1e9, "experts_per_rank": per,
-                                                  "rows_out_per_rank": t_loc * kk, "agrees_with_all_reduce_form": close,
+                                                  "rows_out_per_rank": t_loc * kk, "max_abs_diff_vs_all_reduce_form": diff,
+                                                  "max_abs_output": top, "agrees_with_all_reduce_form": bool(diff <= 5e-3 * top),
                                                   "comm_status": xc.status()}
             torch.cuda.synchronize()
             dist.barrier()
