@@ -205,3 +205,48 @@ def test_token_exchange_expert_parallel_group_on_one_gpu(P, pkg, oracle, world, 
                T_loc, H, world + 1 if (world + 1) % world else world + 3, k, I, G, 7, ws[0], ws_bytes, st)
     for c in comms:
         L.raw("b200k_comm_destroy")(c.value)
+
+
+def test_token_exchange_group_at_config_3_extents_equals_the_single_gpu_entry(P, pkg):
+    """BASELINE config 3 (512 tokens, 8 experts, top-2, hidden 4096, intermediate 14336) split over a group of 4 held on
+    one GPU: every pair goes through the same expert GEMM rows and the same weighted sum as in fused_moe_gptq_f16, so
+    the outputs are identical bit for bit."""
+    import ctypes
+    L = pkg.lib()
+    world, T, E, k, H, I, G = 4, 512, 8, 2, 4096, 14336, 128
+    T_loc, per = T // world, E // world
+    gen = torch.Generator(device=DEV).manual_seed(5)
+    ri = lambda *s: torch.randint(-2 ** 31, 2 ** 31 - 1, s, device=DEV, dtype=torch.int32, generator=gen)
+    w13q, w2q = ri(E, H // 8, 2 * I), ri(E, I // 8, H)
+    w13s = (torch.rand((E, H // G, 2 * I), device=DEV, generator=gen) * 0.018 + 0.002).half()
+    w2s = (torch.rand((E, I // G, H), device=DEV, generator=gen) * 0.018 + 0.002).half()
+    x = torch.randn((T, H), device=DEV, generator=gen).half()
+    lg = torch.randn((T, E), device=DEV, generator=gen)
+    st = torch.cuda.current_stream().cuda_stream
+    ref = torch.empty((T, H), dtype=torch.float16, device=DEV)
+    P.fused_moe_gptq_f16(x, lg, w13q, w13s, None, w2q, w2s, None, ref, T, H, E, k, I, G, None, 0)
+    slot = L.call("fused_moe_a2a_slot_bytes", T_loc, H, k, world)
+    comms = [ctypes.c_void_p() for _ in range(world)]
+    bufs = [ctypes.c_void_p() for _ in range(world)]
+    for r in range(world):
+        L.call("b200k_comm_create", r, world, slot, ctypes.addressof(comms[r]))
+        L.call("b200k_comm_buffer", comms[r].value, ctypes.addressof(bufs[r]))
+    for r in range(world):
+        for q in range(world):
+            if q != r:
+                L.call("b200k_comm_set_peer_pointer", comms[r].value, q, bufs[q].value)
+    wsb = L.call("fused_moe_workspace_bytes", T, H, E, k, I)
+    ws = [torch.zeros(wsb, dtype=torch.uint8, device=DEV) for _ in range(world)]
+    outs = [torch.full((T_loc, H), float("nan"), dtype=torch.float16, device=DEV) for _ in range(world)]
+    for phase in (1, 2, 4):
+        for r in range(world):
+            sl = slice(r * per, (r + 1) * per)
+            L.call("fused_moe_gptq_a2a_f16", comms[r].value, x[r * T_loc:(r + 1) * T_loc].contiguous(),
+                   lg[r * T_loc:(r + 1) * T_loc].contiguous(), w13q[sl].contiguous(), w13s[sl].contiguous(), None,
+                   w2q[sl].contiguous(), w2s[sl].contiguous(), None, outs[r], T_loc, H, E, k, I, G, phase, ws[r], wsb, st)
+    torch.cuda.synchronize()
+    got = torch.cat(outs)
+    assert torch.isfinite(ref).all()
+    assert torch.equal(got, ref)
+    for c in comms:
+        L.raw("b200k_comm_destroy")(c.value)
