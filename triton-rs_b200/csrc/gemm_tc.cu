@@ -236,19 +236,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         // ---------------- TMA producer, activation tiles: SA blocks ahead ----------------
         if (lane == 0) {
             tma_prefetch_desc(&amap);
-            const int act_box_rows = TT < 64 ? TT : 64;
-            const int act_boxes = (min(m_end, m0 + TT) - m0 + act_box_rows - 1) / act_box_rows;
             pdl_wait();   // the activations come from the kernel before
             for (int i = 0; i < nkb; ++i) {
                 const int s = ring_slot(i, LSA);
                 if (i >= SA) wait(B_ACTE + s, ring_phase(i, LSA) ^ 1u);
                 const uint32_t bar = smem_u32(&bars[B_ACTF + s]);
-                // boxes of at most 64 rows, only as many as hold rows of this tile: a segment of 130 rows in a 256-row
-                // tile fetches 192 rows from L2, not 256 (rows the MMA does not read keep whatever the slot held)
-                mbar_expect_tx(bar, (uint32_t)(act_boxes * act_box_rows * TC_BK * 2));
-                for (int bx = 0; bx < act_boxes; ++bx)
-                    tma_load_2d(smem_u32(b_tile + (size_t)s * b_bytes + (size_t)bx * act_box_rows * TC_BK * 2), &amap,
-                                (kb_begin + i) * TC_BK, m0 + bx * act_box_rows, bar);
+                mbar_expect_tx(bar, b_bytes);
+                tma_load_2d(smem_u32(b_tile + (size_t)s * b_bytes), &amap, (kb_begin + i) * TC_BK, m0, bar);
             }
         }
     } else if (warp == 1 || warp == 2) {
@@ -611,7 +605,7 @@ int gemm_tc_launch(const GemmArgs &g) {
     if (rc) return TC_NOT_COVERED;
     {
         const uint64_t dims[2] = {(uint64_t)g.k, (uint64_t)g.m}, str[1] = {(uint64_t)g.s_am * 2};
-        const uint32_t box[2] = {TC_BK, (uint32_t)(tt < 64 ? tt : 64)};     // the producer stacks boxes of 64 rows
+        const uint32_t box[2] = {TC_BK, (uint32_t)tt};
         rc = make_tensor_map(&amap, g.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
     }
     if (rc) return TC_NOT_COVERED;   // layout the TMA cannot describe: the strided family takes it
