@@ -109,3 +109,12 @@ def test_rust_sys_binding_is_generated_from_the_header(pkg):
     assert mod.rust_type("const b200k_half *") == "*const b200k_half"
     assert mod.rust_type("void **") == "*mut *mut c_void"
     assert mod.rust_type("struct b200k_comm **") == "*mut *mut b200k_comm"
+
+
+def test_token_exchange_slot_size_formula(pkg):
+    """fused_moe_a2a_slot_bytes = rows of every rank's pairs (256-byte rounded) + their id table; no device needed."""
+    L = pkg.lib()
+    for t_loc, h, k, world in [(64, 4096, 2, 8), (20, 256, 2, 2), (1, 64, 1, 1), (7, 128, 3, 4)]:
+        slots = world * t_loc * k
+        want = (slots * h * 2 + 255) // 256 * 256 + slots * 4
+        assert L.call("fused_moe_a2a_slot_bytes", t_loc, h, k, world) == want
