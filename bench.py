@@ -268,6 +268,34 @@ def component_metrics(pkg, torch, dev, gen):
             "frac_hbm": byts / ms / 1e6 / hbm_peak, "frac_tensor": 2 * m * k * n / ms / 1e9 / tf_peak,
             "timing": "cold (rotating weight buffers)"}
         del qws
+    # the same 16 cells with the weight pre-packed once into the K-packed layout (b200k_prepack_awq, an optional loader step)
+    for (k, n) in [(4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096)]:
+        nbuf = max(2, int(400e6 // (k * n // 2)))
+        sc = (torch.rand((k // G, n), device=dev, generator=gen) * 0.018 + 0.002).half()
+        qz = ri(k // G, n // 8)
+        qzp = torch.empty_like(qz)
+        qwps = []
+        for _ in range(nbuf):
+            qw = ri(k, n // 8)
+            qwp = torch.empty((k // 8, n), device=dev, dtype=torch.int32)
+            P.b200k_prepack_awq(qw, qz, qwp, qzp, k, n, G)
+            qwps.append(qwp)
+            del qw
+        for m in (1, 16, 128, 1024):
+            a = torch.randn((m, k), device=dev, generator=gen, dtype=torch.float16)
+            c = torch.empty((m, n), device=dev, dtype=torch.float16)
+            i = [0]
+
+            def fn():
+                i[0] = (i[0] + 1) % nbuf
+                P.awq_gemm_int4_prepacked_f16(a, qwps[i[0]], sc, qzp, c, m, n, k, G)
+            ms = graph_time(fn, 2 * nbuf)
+            byts = k * n // 2 + (k // G) * n * 2 + (k // G) * n // 2 + 2 * m * k + 2 * m * n
+            out[f"awq_prepacked_gemm_m{m}_k{k}_n{n}"] = {
+                "us": ms * 1e3, "GB/s": byts / ms / 1e6, "TFLOP/s": 2 * m * k * n / ms / 1e9,
+                "frac_hbm": byts / ms / 1e6 / hbm_peak, "frac_tensor": 2 * m * k * n / ms / 1e9 / tf_peak,
+                "timing": "cold (rotating weight buffers); weight rewritten once by b200k_prepack_awq, outside the timed region"}
+        del qwps
     # config 1: decode attention, batch 32, lengths U[512, 8192]
     b, hq, hkv, d, ml = 32, 32, 8, 128, 8192
     q = torch.randn((b, hq, d), device=dev, generator=gen, dtype=torch.float16)
@@ -402,6 +430,31 @@ def tp_component_metrics(pkg, torch, dist, dev, rank, world, gen, shape, comm):
         ms = replay_ms(fn, 2 * nbuf)
         byts = k * n // 2 + (k // G) * n * 2 + (k // G) * n // 2 + 2 * BATCH * k + 2 * BATCH * n
         out[f"gemm_{name}_m{BATCH}_k{k}_n{n}"] = {"us": ms * 1e3, "GB/s": byts / ms / 1e6, "frac_hbm": byts / ms / 1e6 / hbm_peak}
+        del qws
+    # config 2 under tensor parallelism: the AWQ GEMM of every (K, N) cell at its rank-local extents (qkv and gate_up
+    # column-parallel: N / world; o and down row-parallel: K / world, their partial sums completed by the all-reduce
+    # timed below), M = 1, 16, 128, 1024
+    for (k, n, split) in [(4096, 6144, "n"), (4096, 4096, "k"), (4096, 28672, "n"), (14336, 4096, "k")]:
+        kl, nl = (k // world, n) if split == "k" else (k, n // world)
+        if kl % G or nl % 64:
+            continue
+        nbuf = max(2, int(200e6 // (kl * nl // 2)))
+        qws = [ri(kl, nl // 8) for _ in range(nbuf)]
+        sc = (torch.rand((kl // G, nl), device=dev, generator=gen) * 0.018 + 0.002).half()
+        qz = ri(kl // G, nl // 8)
+        for m in (1, 16, 128, 1024):
+            a = torch.randn((m, kl), device=dev, generator=gen, dtype=torch.float16)
+            c = torch.empty((m, nl), device=dev, dtype=torch.float16)
+            i = [0]
+
+            def fn():
+                i[0] = (i[0] + 1) % nbuf
+                P.awq_gemm(a, qws[i[0]], sc, qz, G, out=c)
+            ms = replay_ms(fn, 2 * nbuf, reps=3)
+            byts = kl * nl // 2 + (kl // G) * nl * 2 + (kl // G) * nl // 2 + 2 * m * kl + 2 * m * nl
+            out[f"awq_gemm_tp_m{m}_k{kl}_n{nl}"] = {"us": ms * 1e3, "GB/s": byts / ms / 1e6, "frac_hbm": byts / ms / 1e6 / hbm_peak,
+                                                   "TFLOP/s": 2 * m * kl * nl / ms / 1e9, "frac_tensor": 2 * m * kl * nl / ms / 1e9 / tf_peak,
+                                                   "full_cell": f"K {k}, N {n}, {'row' if split == 'k' else 'column'}-parallel"}
         del qws
     # the exchange alone: one all-reduce of the layer's [64, H] fp16 partial sums, slots alternating
     x = torch.randn((BATCH, H), device=dev, generator=gen, dtype=torch.float16)

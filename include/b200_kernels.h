@@ -182,6 +182,18 @@ int dequant_int4_sym_to_fp16(const int32_t *qweight, const b200k_half *scales,
                              b200k_half *output, int k_dim, int n_dim, int group_size,
                              b200k_stream stream);
 
+/* Optional loader step for AWQ checkpoints (no counterpart in the reference, which reads the on-disk layout in every
+ * call): b200k_prepack_awq rewrites qweight [K, N/8] (AWQ nibble order) once as [K/8, N] -- a word = 8 consecutive k of one
+ * column, the layout of w4a16_gptq_gemm_f16 -- and qzeros [K/G, N/8] into straight nibble order; scales are used as they
+ * are.  awq_gemm_int4_prepacked_f16 multiplies by such a tensor (contiguous operands) with AWQ's zero-point rule (no + 1).
+ * Same values as awq_gemm_int4_f16 on the original tensor; the K-packed layout is the faster one here (16-byte loads and no
+ * byte transposes in the M = 1 kernel, the dequantised operand written straight to tensor memory in the tensor-core one). */
+int b200k_prepack_awq(const int32_t *qweight, const int32_t *qzeros, int32_t *qweight_packed,
+                      int32_t *qzeros_packed, int k_size, int n_size, int group_size, b200k_stream stream);
+int awq_gemm_int4_prepacked_f16(const b200k_half *a, const int32_t *qweight_packed, const b200k_half *scales,
+                                const int32_t *qzeros_packed, b200k_half *c, int m_size, int n_size,
+                                int k_size, int group_size, b200k_stream stream);
+
 /* Bit-exact unpack probes (no counterpart kernel in the reference; they expose the
  * nibble orders its GEMMs use so that tests can compare them with ==):
  *   gptq_qweight: [K/8,N] -> int8 [K,N]          (w4a16_gptq_gemm_typed.rs:167-173)

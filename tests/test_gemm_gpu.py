@@ -179,3 +179,28 @@ def test_gate_up_gemm_with_fused_silu_mul(P, oracle, m, k, inter, sym):
     assert (np.abs(got - ref) <= bound).all(), float(np.abs(got - ref).max())
     # and plainly close: the fused form skips one fp16 rounding, it does not add error
     assert_close(got, ref, 2e-2, 2e-2, "fused gate_up + silu")
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 4096, 512), (1, 256, 264), (16, 1024, 256), (130, 512, 384)])
+def test_awq_prepacked_into_the_k_packed_layout(P, oracle, m, k, n):
+    """b200k_prepack_awq: the rewritten tensor holds the same nibbles (compared with == through the unpack probes), and
+    awq_gemm_int4_prepacked_f16 on it gives the product of the original AWQ tensor."""
+    g = 128
+    a, qw, sc, qz = make_case(oracle, "awq", m, k, n, g, seed=k + n)
+    qwd, qzd = t(qw), t(qz)
+    qwp = torch.empty((k // 8, n), dtype=torch.int32, device=DEV)
+    qzp = torch.empty((k // g, n // 8), dtype=torch.int32, device=DEV)
+    P.b200k_prepack_awq(qwd, qzd, qwp, qzp, k, n, g)
+    u0 = torch.empty((k, n), dtype=torch.int8, device=DEV)
+    u1 = torch.empty_like(u0)
+    P.b200k_unpack_awq(qwd, u0, k, n)
+    P.b200k_unpack_gptq_qweight(qwp, u1, k, n)
+    assert torch.equal(u0, u1)
+    z0 = torch.empty((k // g, n), dtype=torch.int8, device=DEV)
+    z1 = torch.empty_like(z0)
+    P.b200k_unpack_awq(qzd, z0, k // g, n)
+    P.b200k_unpack_gptq_qzeros(qzp, z1, k // g, n, 0)
+    assert torch.equal(z0, z1)
+    c = torch.full((m, n), float("nan"), dtype=torch.float16, device=DEV)
+    P.awq_gemm_int4_prepacked_f16(t(a), qwp, t(sc), qzp, c, m, n, k, g)
+    assert_close(c.float().cpu().numpy(), oracle.awq_gemm_int4(a, qw, sc, qz, g), what="prepacked awq gemm")

@@ -719,6 +719,64 @@ extern "C" int w4a16_gptq_gemm_silu_mul_f16(const b200k_half *a, const int32_t *
                : rc;
 }
 
+
+// ---------------------------------------------------------------------------
+// Optional loader step: an AWQ tensor rewritten once into the K-packed layout
+// ---------------------------------------------------------------------------
+namespace b200k {
+// out [K/8, N]: word (r, n) holds the nibbles of rows 8r .. 8r+7 of column n, lowest row in the lowest nibble
+__global__ void __launch_bounds__(256) prepack_awq_weight_kernel(const int32_t *__restrict__ in, int32_t *__restrict__ out, int k, int n) {
+    const long total = (long)(k / 8) * n;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const int r = (int)(i / n), col = (int)(i - (long)r * n);
+        const int sh = 4 * awq_slot(col & 7);
+        uint32_t w = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) w |= (((uint32_t)in[(long)(8 * r + j) * (n / 8) + col / 8] >> sh) & 15u) << (4 * j);
+        out[i] = (int32_t)w;
+    }
+}
+// zero-point words: the same columns, nibble j = column 8 n8 + j
+__global__ void __launch_bounds__(256) prepack_awq_zeros_kernel(const int32_t *__restrict__ in, int32_t *__restrict__ out, long words) {
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < words; i += (long)gridDim.x * blockDim.x) {
+        const uint32_t z = (uint32_t)in[i];
+        uint32_t w = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) w |= ((z >> (4 * awq_slot(j))) & 15u) << (4 * j);
+        out[i] = (int32_t)w;
+    }
+}
+}  // namespace b200k
+
+extern "C" int b200k_prepack_awq(const int32_t *qweight, const int32_t *qzeros, int32_t *qweight_packed, int32_t *qzeros_packed,
+                                 int k_size, int n_size, int group_size, b200k_stream stream) {
+    B200K_REQUIRE(qweight && qzeros && qweight_packed && qzeros_packed, B200K_E_NULL, "b200k_prepack_awq: NULL pointer");
+    B200K_REQUIRE(k_size > 0 && n_size > 0 && group_size > 0 && k_size % 8 == 0 && n_size % 8 == 0 && k_size % group_size == 0,
+                  B200K_E_SHAPE, "b200k_prepack_awq: K %d, N %d, group %d (K %% 8, N %% 8, K %% group must be 0)", k_size, n_size, group_size);
+    cudaStream_t st = to_stream(stream);
+    const long wt = (long)(k_size / 8) * n_size, zt = (long)(k_size / group_size) * (n_size / 8);
+    const long cap = (long)sm_count() * 16;
+    long bw = (wt + 255) / 256, bz = (zt + 255) / 256;
+    prepack_awq_weight_kernel<<<(int)(bw > cap ? cap : bw), 256, 0, st>>>(qweight, qweight_packed, k_size, n_size);
+    int rc = launch_status("b200k_prepack_awq");
+    if (rc) return rc;
+    prepack_awq_zeros_kernel<<<(int)(bz > cap ? cap : bz), 256, 0, st>>>(qzeros, qzeros_packed, zt);
+    return launch_status("b200k_prepack_awq");
+}
+
+extern "C" int awq_gemm_int4_prepacked_f16(const b200k_half *a, const int32_t *qweight_packed, const b200k_half *scales,
+                                           const int32_t *qzeros_packed, b200k_half *c, int m_size, int n_size, int k_size,
+                                           int group_size, b200k_stream stream) {
+    const int32_t *qweight = qweight_packed;
+    const int stride_am = k_size, stride_ak = 1, stride_qwk = n_size, stride_qwn = 1, stride_sk = n_size, stride_sn = 1,
+              stride_cm = n_size, stride_cn = 1;
+    B200K_REQUIRE(qzeros_packed, B200K_E_NULL, "awq_gemm_int4_prepacked_f16: qzeros is NULL");
+    GEMM_ARGS_FILL(FMT_GPTQ, 0)      // K-packed words, straight zero nibbles, and AWQ's zero-point rule: no + 1
+    g.qzeros = qzeros_packed; g.s_qzk = n_size / 8; g.s_qzn = 1;
+    g.ws = nullptr; g.ws_bytes = 0;
+    return gemm_dispatch("awq_gemm_int4_prepacked_f16", g, true);
+}
+
 extern "C" int b200k_gemm_tc_plan(int m_size, int n_size, int k_size, int group_size, int awq, int *host_plan_out) {
     B200K_REQUIRE(host_plan_out, B200K_E_NULL, "b200k_gemm_tc_plan: NULL pointer");
     GemmArgs g = {};

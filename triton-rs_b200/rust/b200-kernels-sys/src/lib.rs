@@ -119,6 +119,15 @@ extern "C" {
         qweight: *const i32, scales: *const b200k_half, output: *mut b200k_half, k_dim: c_int, n_dim: c_int,
         group_size: c_int, stream: b200k_stream
     ) -> c_int;
+    pub fn b200k_prepack_awq(
+        qweight: *const i32, qzeros: *const i32, qweight_packed: *mut i32, qzeros_packed: *mut i32,
+        k_size: c_int, n_size: c_int, group_size: c_int, stream: b200k_stream
+    ) -> c_int;
+    pub fn awq_gemm_int4_prepacked_f16(
+        a: *const b200k_half, qweight_packed: *const i32, scales: *const b200k_half,
+        qzeros_packed: *const i32, c: *mut b200k_half, m_size: c_int, n_size: c_int, k_size: c_int,
+        group_size: c_int, stream: b200k_stream
+    ) -> c_int;
     pub fn b200k_unpack_gptq_qweight(
         qweight: *const i32, out: *mut i8, k_dim: c_int, n_dim: c_int, stream: b200k_stream
     ) -> c_int;
