@@ -324,6 +324,27 @@ def component_metrics(pkg, torch, dev, gen):
                                           "frac_tensor": flops / ms / 1e9 / tf_peak,
                                           "timing": "tensor-bound: K/V (%d MB) are re-read from L2 by design" % (4 * hkv * L * d // 2 ** 20)}
         del pq, pk, pv, po
+    # unified prefill + decode over a paged fp32 pool (unified_attention_f32): 4 sequences prefilling 256 tokens each and
+    # 28 decoding one token at context 2048, blocks of 16 positions; a CUDA-core kernel (fp32 arithmetic throughout)
+    useq = [(256, 256)] * 4 + [(1, 2048)] * 28
+    ubs = 16
+    bps = max(-(-sl // ubs) for _, sl in useq)
+    nblk = len(useq) * bps
+    uq = torch.randn((sum(ql for ql, _ in useq), hq, d), device=dev, generator=gen)
+    ukp = torch.randn((nblk, ubs, hkv, d), device=dev, generator=gen)
+    uvp = torch.randn((nblk, ubs, hkv, d), device=dev, generator=gen)
+    utab = torch.randperm(nblk, device=dev, generator=gen).to(torch.int32).reshape(len(useq), bps).contiguous()
+    usl = torch.tensor([sl for _, sl in useq], device=dev, dtype=torch.int32)
+    uqs = torch.tensor(np.concatenate([[0], np.cumsum([ql for ql, _ in useq])]), device=dev, dtype=torch.int32)
+    uo = torch.empty_like(uq)
+    fn = lambda: P.unified_attention_f32(uq, ukp, uvp, uo, utab, usl, uqs, hq, hkv, d, ubs, bps, 1.0 / float(np.sqrt(d)), len(useq))
+    ms, iso = graph_time(fn, 2), isolated_time(fn, 6)
+    kv_bytes = sum(sl for _, sl in useq) * hkv * d * 4 * 2
+    uflops = sum(4.0 * hq * d * (ql * (sl - ql) + ql * (ql + 1) / 2) for ql, sl in useq)
+    out["unified_attention_f32_mixed"] = {"us": ms * 1e3, "us_isolated": iso * 1e3, "GB/s_kv_once": kv_bytes / ms / 1e6,
+                                          "TFLOP/s": uflops / ms / 1e9, "batch": "4 x 256-token prefill + 28 x decode at ctx 2048",
+                                          "timing": "KV pool 0.5 GB, larger than L2"}
+    del ukp, uvp
     # config 3: fused MoE, Mixtral-8x7B shape
     T, E, kk, H, I = 512, 8, 2, 4096, 14336
     w13q, w2q = ri(E, H // 8, 2 * I), ri(E, I // 8, H)
