@@ -47,10 +47,21 @@ __device__ __forceinline__ long kv_row_offset(const KvLayout &L, int b, int kvh,
 // split-KV fp16 family
 // ---------------------------------------------------------------------------
 constexpr int AT_D = 128;               // head_dim
-constexpr int AT_THREADS = 128;         // 4 warps; warp w owns rows [16w, 16w+16) of every tile
-constexpr int AT_TILE = 64;             // positions per stage
-constexpr int AT_STAGES = 3;            // each stage holds a K tile and a V tile
-constexpr int AT_HALF_BYTES = AT_TILE * 128;   // one TMA box: 64 rows x 64 dims (128 bytes), 128-byte swizzle
+#ifndef B200K_AT_WARPS
+#define B200K_AT_WARPS 4
+#endif
+#ifndef B200K_AT_STAGES
+#define B200K_AT_STAGES 3
+#endif
+constexpr int AT_THREADS = 32 * B200K_AT_WARPS;   // warp w owns rows [16w, 16w+16) of every tile
+constexpr int AT_TILE = 16 * B200K_AT_WARPS;      // positions per stage
+constexpr int AT_STAGES = B200K_AT_STAGES;        // each stage holds a K tile and a V tile
+#ifdef B200K_AT_CTAS
+constexpr int AT_CTAS_PER_SM = B200K_AT_CTAS;
+#else
+constexpr int AT_CTAS_PER_SM = (size_t)AT_STAGES * 4 * AT_TILE * 128 <= 100 * 1024 ? 2 : 1;
+#endif
+constexpr int AT_HALF_BYTES = AT_TILE * 128;   // one TMA box: AT_TILE rows x 64 dims (128 bytes), 128-byte swizzle
 constexpr int AT_TILE_BYTES = 2 * AT_HALF_BYTES;
 constexpr int AT_MAX_CH = 2048;         // largest chunk (positions)
 constexpr int AT_NH = 8;                // head columns of one MMA (GQA group size <= 8)
@@ -116,7 +127,7 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
 //       O^T[dim, head] += V^T[dim, pos] . P^T[pos, head]  (A = V tile via ldmatrix.trans,
 //                                                          B = P^T via movmatrix)
 // with up to 8 q heads of one GQA group in the 8 MMA columns.
-__global__ void __launch_bounds__(AT_THREADS, 2)
+__global__ void __launch_bounds__(AT_THREADS, AT_CTAS_PER_SM)
 attn_split_f16_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                       AttnSplitArgs A) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
