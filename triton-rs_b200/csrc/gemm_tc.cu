@@ -569,7 +569,9 @@ int gemm_tc_launch(const GemmArgs &g) {
     const bool can_split = !grouped && !silu && ring_bytes >= (size_t)tt * TC_BN * 4;
     if (silu && ring_bytes < (size_t)tt * TC_BN * 2) return TC_NOT_COVERED;      // the epilogue stages the up half in the rings' space
     int ksplit = 1;
-    if (can_split) {
+    // (a cluster launch with its two cluster barriers and the exchange costs ~5 us, a K block ~0.33 us per CTA: measured at 64
+    // tokens, 8 blocks in one CTA take 5.7 us, split over a pair of CTAs 9.8 us.  Up to 8 blocks there is nothing to split.)
+    if (can_split && kb_total > 8) {
         const int sms = sm_count();
         while (ksplit < 8 && tiles * ksplit < (sms * 7) / 8 && kb_total / (ksplit * 2) >= 4) ksplit *= 2;
         if (ksplit < 8 && ksplit > 1 && tiles * ksplit <= sms && kb_total / (ksplit * 2) >= 24) ksplit *= 2;
