@@ -204,3 +204,31 @@ def test_awq_prepacked_into_the_k_packed_layout(P, oracle, m, k, n):
     c = torch.full((m, n), float("nan"), dtype=torch.float16, device=DEV)
     P.awq_gemm_int4_prepacked_f16(t(a), qwp, t(sc), qzp, c, m, n, k, g)
     assert_close(c.float().cpu().numpy(), oracle.awq_gemm_int4(a, qw, sc, qz, g), what="prepacked awq gemm")
+
+
+@pytest.mark.parametrize("fmt", ["gptq", "awq"])
+@pytest.mark.parametrize("k,n", [(4096, 512), (14336, 256)])
+def test_gemv_with_massive_activations(P, oracle, fmt, k, n):
+    """M = 1 with activation outliers (a few channels a thousand times the rest, as the massive activations of LLMs): the
+    integer GEMV quantises activations per group of 128, which cannot hold both scales, and must fall back to fp32 for
+    the groups that contain an outlier.  Also an all-zero group and an all-zero vector."""
+    g = 128
+    a, qw, sc, qz = make_case(oracle, fmt, 1, k, n, g, seed=k + n + 1)
+    a = a.astype(np.float32)
+    a[0, 5] = 2000.0                     # outlier in group 0
+    a[0, 3 * g + 77] = -900.0            # and one in group 3
+    a[0, g:2 * g] = 0.0                  # group 1: all zero
+    a[0, 2 * g:3 * g] *= 1e-3            # group 2: tiny values only
+    a = a.astype(np.float16)
+    got = run_gemm(P, fmt, a, qw, sc, qz, g).float().cpu().numpy()
+    ref = ref_gemm(oracle, fmt, a, qw, sc, qz, g)
+    assert_close(got, ref, what=f"{fmt} gemv with outliers")
+    # without the outliers' own terms the rest of the sum must still be right: compare the difference of two runs that
+    # differ only in the outlier values (their groups stay on the fp32 path in both)
+    a2 = a.copy()
+    a2[0, 5] = 1000.0
+    got2 = run_gemm(P, fmt, a2, qw, sc, qz, g).float().cpu().numpy()
+    ref2 = ref_gemm(oracle, fmt, a2, qw, sc, qz, g)
+    assert_close(got2, ref2, what=f"{fmt} gemv with outliers, second vector")
+    z = np.zeros_like(a)
+    assert not run_gemm(P, fmt, z, qw, sc, qz, g).float().cpu().numpy().any()

@@ -11,6 +11,9 @@
 // nibbles are used in place, as bytes 16 q, and their sums shifted down at the end of the group (exact).
 // The products are exact integers, so the only roundings are the activation quantisation and the final fp32
 // scaling: closer to the exact result than products with fp16-rounded weights, inside the same tolerance.
+// A group in which one activation dwarfs the rest (max |a| > 64 mean |a|: the "massive activation" channels of LLMs) would
+// leave the other values too few levels; such a group is multiplied in fp32 instead, nibble by nibble (three times the
+// instructions, for the few groups it concerns).
 //
 // Work split as in the fp16 GEMV: a cluster of KSPLIT CTAs shares one block of columns and splits K by
 // quantisation group over its warps; the cluster reduces through distributed shared memory in a fixed order.
@@ -43,12 +46,20 @@ __device__ __forceinline__ uint32_t ldg_nc_word(const void *p) {
 
 // The 128 activations of one group -> 15-bit integers; lane i holds stored positions 4i .. 4i+3.  Returns the
 // lane's four high bytes and four low bytes (byte j = stored position 4i + j), the group's scale and sum(A).
-__device__ __forceinline__ void quantise_group(const __half *a_group, int lane, uint32_t &qh, uint32_t &ql, float &sa, int &asum) {
+// `outlier`: one activation holds more than half of the group's total magnitude (max |a| > 64 mean |a|).  The 15-bit grid
+// is then too coarse for the other 127 values (its step is max |a| / 16383), and the caller multiplies that group in fp32.
+__device__ __forceinline__ void quantise_group(const __half *a_group, int lane, uint32_t &qh, uint32_t &ql, float &sa, int &asum,
+                                               bool &outlier) {
     const uint2 u = *reinterpret_cast<const uint2 *>(a_group + lane * 4);
     const float2 f01 = h2_to_f2(u.x), f23 = h2_to_f2(u.y);
     float amax = fmaxf(fmaxf(fabsf(f01.x), fabsf(f01.y)), fmaxf(fabsf(f23.x), fabsf(f23.y)));
+    float aabs = (fabsf(f01.x) + fabsf(f01.y)) + (fabsf(f23.x) + fabsf(f23.y));
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    for (int o = 16; o > 0; o >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        aabs += __shfl_xor_sync(0xffffffffu, aabs, o);
+    }
+    outlier = 2.f * amax > aabs;
     sa = amax * (1.f / 16383.f);
     const float inv = amax > 0.f ? 16383.f / amax : 0.f;
     const int i0 = __float2int_rn(f01.x * inv), i1 = __float2int_rn(f01.y * inv);
@@ -146,7 +157,33 @@ gemv_gptq_i8_kernel(GemmArgs g, int ksplit) {
         uint32_t qh, ql;
         float sa;
         int asum;
-        quantise_group(g.a + (long)grp * GI_GROUP, lane, qh, ql, sa, asum);
+        bool outlier;
+        quantise_group(g.a + (long)grp * GI_GROUP, lane, qh, ql, sa, asum, outlier);
+        if (outlier) {
+            // fp32 for this group: sum_k a_k (q_k - z), every lane reading the same activation (one broadcast load each)
+            if (!live) continue;
+            const float2 s01 = h2_to_f2(su.x), s23 = h2_to_f2(su.y);
+            const float sc[4] = {s01.x, s01.y, s23.x, s23.y};
+            const uint32_t zsh = zw >> (4 * (col % 8));
+            float zf[4], accx[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) zf[c] = (float)(g.qzeros ? (int)((zsh >> (4 * c)) & 15u) + g.zero_offset : 8);
+            const __half *ag = g.a + (long)grp * GI_GROUP;
+#pragma unroll
+            for (int r = 0; r < 16; ++r) {
+                const uint32_t w[4] = {wreg[r].x, wreg[r].y, wreg[r].z, wreg[r].w};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int pos = g.a_kperm ? ((j & 3) * 2 + (j >> 2)) : j;      // where k = 8r + j sits in its 8-block
+                    const float av = __half2float(ag[8 * r + pos]);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) accx[c] = fmaf(av, (float)((w[c] >> (4 * j)) & 15u) - zf[c], accx[c]);
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tot[c] += accx[c] * sc[c];
+            continue;
+        }
         {
             const uint32_t ph = __shfl_xor_sync(0xffffffffu, qh, 1), pl = __shfl_xor_sync(0xffffffffu, ql, 1);
             const bool odd = lane & 1;
@@ -194,15 +231,20 @@ gemv_gptq_i8_kernel(GemmArgs g, int ksplit) {
 // positions 4i .. 4i+3 of the unit (lanes >= UR / 4 return zeros).  UR = 128: a whole quantisation group, 4 values per
 // lane; UR = 32: one value per lane, packed by fours.
 template <int UR>
-__device__ __forceinline__ void quantise_unit(const __half *a_unit, int lane, uint32_t &qh, uint32_t &ql, float &sa, int &asum) {
+__device__ __forceinline__ void quantise_unit(const __half *a_unit, int lane, uint32_t &qh, uint32_t &ql, float &sa, int &asum,
+                                              bool &outlier) {
     if (UR == 128) {
-        quantise_group(a_unit, lane, qh, ql, sa, asum);
+        quantise_group(a_unit, lane, qh, ql, sa, asum, outlier);
         return;
     }
     const float f = __half2float(a_unit[lane]);
-    float amax = fabsf(f);
+    float amax = fabsf(f), aabs = fabsf(f);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    for (int o = 16; o > 0; o >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        aabs += __shfl_xor_sync(0xffffffffu, aabs, o);
+    }
+    outlier = 2.f * amax > aabs;      // one value holds more than half of the unit's magnitude
     sa = amax * (1.f / 16383.f);
     const float inv = amax > 0.f ? 16383.f / amax : 0.f;
     const int i0 = __float2int_rn(f * inv);
@@ -219,13 +261,33 @@ __device__ __forceinline__ void quantise_unit(const __half *a_unit, int lane, ui
     ql = lane < 8 ? l : 0u;
 }
 
+// fp32 product of `rows` rows of one word column (8 weight columns) with their activations: acc[c] = sum_k a_k (q_kc - z_c).
+// Out of line on purpose: it is the rare path, and inlined it costs the fast path its registers.
+__device__ __noinline__ void awq_rows_fp32(const __half *a, const int32_t *wp, long stride, int rows, uint32_t zw, float *acc) {
+    float x[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) x[c] = 0.f;
+#pragma unroll 2
+    for (int j = 0; j < rows; ++j) {
+        const float av = __half2float(a[j]);            // every lane reads the same activation: one broadcast load
+        const uint32_t wj = ldg_nc_word(wp + (long)j * stride);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const int sh = 4 * awq_slot(c);
+            x[c] = fmaf(av, (float)((wj >> sh) & 15u) - (float)((zw >> sh) & 15u), x[c]);
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[c] = x[c];
+}
+
 // A warp covers 256 columns (one word per lane and row) and walks units of UR rows: a whole quantisation group, or a
 // quarter of one when the matrix is too narrow to fill the machine with whole groups per warp.  Every unit quantises its
 // own activations (its own scale: the identity above holds for any subset of k).  Rows are requested in half-batches of
 // 16 held in NB register buffers that rotate: while one is multiplied, NB - 1 are in flight (narrow matrices have few
 // warps, so each must keep more bytes in flight).
 template <int UR, int NB>
-__global__ void __launch_bounds__(GI_THREADS)
+__global__ void __launch_bounds__(GI_THREADS, 2)      // 128 registers: narrow matrices need two CTAs per SM to run in one wave
 gemv_awq_i8_kernel(GemmArgs g, int ksplit) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint2 *act = reinterpret_cast<uint2 *>(smem_raw);                              // [GI_WARPS][32]: (ah, al) of 4 consecutive k
@@ -281,7 +343,8 @@ gemv_awq_i8_kernel(GemmArgs g, int ksplit) {
             uint32_t qh, ql;
             float sa;
             int asum;
-            quantise_unit<UR>(g.a + (long)u * UR, lane, qh, ql, sa, asum);
+            bool outlier;
+            quantise_unit<UR>(g.a + (long)u * UR, lane, qh, ql, sa, asum, outlier);
             __syncwarp();
             my_act[lane] = make_uint2(qh, ql);          // bytes already in k order: lane i = k 4i .. 4i+3
             __syncwarp();
@@ -291,6 +354,18 @@ gemv_awq_i8_kernel(GemmArgs g, int ksplit) {
             request_meta(u + uslots);
             // byte b of the even-nibble words = nibble 2b = column (0,4,1,5)[b]; of the odd-nibble words = nibble 2b+1 =
             // column (2,6,3,7)[b] (the AWQ order [0,4,1,5,2,6,3,7] maps column -> nibble)
+            if (outlier) {
+                // fp32 for this unit; its rows are read again (from L2: rare), the register buffers only turn
+                float accx[8];
+                awq_rows_fp32(g.a + (long)u * UR, g.qweight + (long)u * UR * g.s_qwk + col / 8, g.s_qwk, UR, zw_now, accx);
+                const float2 sA = h2_to_f2(su_now.x), sB = h2_to_f2(su_now.y), sC = h2_to_f2(su_now.z), sD = h2_to_f2(su_now.w);
+                const float sc[8] = {sA.x, sA.y, sB.x, sB.y, sC.x, sC.y, sD.x, sD.y};
+#pragma unroll
+                for (int c = 0; c < 8; ++c) tot[c] += accx[c] * sc[c];
+#pragma unroll
+                for (int hb = 0; hb < HPU; ++hb) request_rows(w[(uu * HPU + hb) % NB], u0, uu * HPU + hb + NB);
+                continue;
+            }
             int ae[4][2], ao[4][2];
 #pragma unroll
             for (int c = 0; c < 4; ++c) ae[c][0] = ae[c][1] = ao[c][0] = ao[c][1] = 0;
