@@ -507,8 +507,9 @@ static int pick_tt(int m) {
 // so that a segment somewhat above the mean still fits one tile.
 int gemm_tc_token_tile(int m, int segments) {
     if (segments <= 1) return pick_tt(m);
-    const int mean = ceil_div(m, segments);
-    return pick_tt(mean + mean / 2);
+    const int mean = ceil_div(m, segments), want = mean + mean / 2;
+    // 192 rows (between the powers of two): leaves tensor memory for an operand ring of eight tiles behind the accumulator
+    return want > 128 && want <= 192 ? 192 : pick_tt(want);
 }
 
 int gemm_tc_launch(const GemmArgs &g) {
