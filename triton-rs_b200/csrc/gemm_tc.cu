@@ -149,23 +149,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     uint32_t tmem_cols = 32;
     while (tmem_cols < (TS ? a_col0 + 32u * SD : (uint32_t)(NMMA * TT))) tmem_cols <<= 1;
 
-    if (tid == 0) {
-        for (int s = 0; s < SA; ++s) {
-            mbar_init(smem_u32(&bars[B_ACTF + s]), 1);
-            mbar_init(smem_u32(&bars[B_ACTE + s]), 1);
-        }
-        for (int s = 0; s < SD; ++s) {
-            mbar_init(smem_u32(&bars[B_DQF + s]), TC_GROUP_WARPS);
-            mbar_init(smem_u32(&bars[B_DQE + s]), 1);
-        }
-        for (int r = 0; r < R; ++r) {
-            mbar_init(smem_u32(&bars[B_RAWF + r]), 1);
-            mbar_init(smem_u32(&bars[B_RAWE + r]), TC_GROUP_WARPS);
-        }
-        mbar_init(smem_u32(&bars[B_ACC]), NMMA);
-        *abort_flag = 0;
-        mbar_init_fence();
+    // one barrier per thread (up to ~60 of them: initialised one after the other by a single thread they cost a microsecond)
+    if (tid <= B_ACC) {
+        const int count = (tid >= B_DQF && tid < B_DQE) || (tid >= B_RAWE && tid < B_ACC) ? TC_GROUP_WARPS : tid == B_ACC ? NMMA : 1;
+        mbar_init(smem_u32(&bars[tid]), count);
     }
+    if (tid == 0) *abort_flag = 0;
+    if (tid <= B_ACC) mbar_init_fence();
     if (warp == 0) {
         tmem_alloc(smem_u32(tmem_slot), tmem_cols);
         tmem_relinquish();
