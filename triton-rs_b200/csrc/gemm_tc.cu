@@ -516,10 +516,13 @@ int gemm_tc_launch(const GemmArgs &g) {
     const int kb_total = g.k / TC_BK;
     const int tiles = col_tiles * tok_tiles;
     // Shared memory: two CTAs per SM while the token tile is small, one otherwise.
-    const int ctas_per_sm = tt <= 64 ? 2 : 1;
+    // A 128-token tile of an ordinary GEMM also runs as two CTAs of two dequant groups per SM (the same four groups per SM
+    // as one CTA of four): the grid then fills the SMs in units half as large.
+    const bool pair128 = tt == 128 && !grouped && !silu && !g.bf16 && env_int("B200K_TC_PAIR128", 1) != 0;
+    const int ctas_per_sm = tt <= 64 || pair128 ? 2 : 1;
     const int budget = (ctas_per_sm == 2 ? 111 : 222) * 1024;
     const int act_bytes = tt * TC_BK * 2;
-    const int ng = tt <= 64 ? 2 : 4;                 // dequant groups
+    const int ng = ctas_per_sm == 2 ? 2 : 4;         // dequant groups
     // operand tile in tensor memory (GPTQ) or in shared memory (AWQ; B200K_TC_OPERAND=smem forces it)
     bool ts = g.format == FMT_GPTQ;
     if (env_char("B200K_TC_OPERAND") == 's') ts = false;
@@ -530,15 +533,16 @@ int gemm_tc_launch(const GemmArgs &g) {
     // is at least as deep as the operand ring (the last SD blocks never hand theirs back) and an activation
     // tile is requested SA - SD blocks ahead; the ring of packed words takes what is left, 16 at most.
     const int nmma = tt <= 64 ? 2 : 1;           // issuing warps (each with its own accumulator)
+    const bool g2m1 = ng == 2 && nmma == 1;      // the paired 128-token form
     auto pow2_floor = [](int v) { int p = 1; while (p * 2 <= v) p *= 2; return p; };
     auto log2i = [](int v) { int l = 0; while ((1 << l) < v) ++l; return l; };
     int dq_stages, act_stages;
     if (ts) {   // operand tiles cost 32 TMEM columns each: 256 columns per CTA with two CTAs per SM, 512 with one
         dq_stages = 4;
-        act_stages = tt <= 128 ? 8 : 4;
+        act_stages = tt <= 128 && !pair128 ? 8 : 4;
     } else {
-        dq_stages = tt <= 64 ? 2 : 4;
-        act_stages = tt <= 32 ? 8 : 4;
+        dq_stages = tt <= 64 || pair128 ? 2 : 4;
+        act_stages = tt <= 32 ? 8 : pair128 ? 2 : 4;
     }
     if (const int v = env_int("B200K_TC_DQ_STAGES", 0)) dq_stages = pow2_floor(v < 1 ? 1 : v);     // tuning overrides
     if (const int v = env_int("B200K_TC_ACT_STAGES", 0)) act_stages = pow2_floor(v < 1 ? 1 : v);
@@ -640,14 +644,17 @@ int gemm_tc_launch(const GemmArgs &g) {
                                               : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false, false, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, false, false, true>))
                 : silu ? (g.a_kperm ? (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, true, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, true, true>)
                                   : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, false, true>))
+                : g2m1 ? (g.format == FMT_AWQ ? gemm_tc_kernel<FMT_AWQ, 2, false, 1, false>
+                          : ts ? (g.a_kperm ? gemm_tc_kernel<FMT_GPTQ, 2, true, 1, true> : gemm_tc_kernel<FMT_GPTQ, 2, true, 1, false>)
+                               : gemm_tc_kernel<FMT_GPTQ, 2, false, 1, false>)
                 : g.format == FMT_AWQ ? (ng == 2 ? gemm_tc_kernel<FMT_AWQ, 2, false, 2, false> : gemm_tc_kernel<FMT_AWQ, 4, false, 1, false>)
                 : ts ? (g.a_kperm ? (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, true>)
                                   : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, false>))
                      : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, false, 2, false> : gemm_tc_kernel<FMT_GPTQ, 4, false, 1, false>);
     {
-        static OncePerDevice once[8][2];
+        static OncePerDevice once[8][3];
         const int variant = g.bf16 ? (g.format == FMT_AWQ ? 7 : 6) : silu ? (g.a_kperm ? 5 : 4) : g.format == FMT_AWQ ? 1 : (ts ? (g.a_kperm ? 3 : 2) : 0);
-        cudaError_t e = once[variant][ng == 4].run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); });
+        cudaError_t e = once[variant][g2m1 ? 2 : ng == 4].run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); });
         if (e != cudaSuccess) return fail((int)e, "w4a16 gemm (tensor core): shared memory: %s", cudaGetErrorString(e));
     }
     cudaLaunchConfig_t cfg = {};
