@@ -485,6 +485,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
 
 int gemm_tc_token_tile(int m, int segments);
 static int pick_tt(int m) {
+    if (const int v = env_int("B200K_TC_TT", 0)) return v;      // tuning override
     if (m <= 16) return 16;
     if (m <= 32) return 32;
     if (m <= 64) return 64;
@@ -511,14 +512,43 @@ int gemm_tc_launch(const GemmArgs &g) {
     const bool grouped = g.seg_offsets != nullptr;
     // grouped: the token tile follows the average segment (plus head-room); the grid covers the worst case (every row
     // in one segment) and CTAs past their segment's end return at once
-    const int tt = gemm_tc_token_tile(g.m, grouped ? g.num_segments : 1);
-    const int col_tiles = silu ? g.silu_inter / 64 : ceil_div(g.n, TC_BN), tok_tiles = ceil_div(g.m, tt);
+    int tt = gemm_tc_token_tile(g.m, grouped ? g.num_segments : 1);
     const int kb_total = g.k / TC_BK;
+    // Above 64 tokens an ordinary GEMM has two forms: a 256-token tile on one CTA of four dequant groups per SM, or a
+    // 128-token tile on two CTAs of two groups per SM (the same four groups, grid units half as large).  Form and K split
+    // are chosen together by a cost model fitted to measurements: a CTA costs ~4 us of set-up and drain plus its K blocks
+    // (0.48 us each at 256 tokens, where the activation tiles' way from L2 sets the pace; 0.62 us when two 128-token CTAs
+    // share an SM, 0.45 us when one has it alone), CTAs beyond the resident ones wait for a whole wave, and a K split costs
+    // ~5 us plus the exchange of the partial tiles.
+    bool pair128 = false;
+    int planned_split = 0;
+    if (!grouped && !silu && g.m > 64 && !env_int("B200K_TC_TT", 0)) {
+        const int sms = sm_count(), cols = ceil_div(g.n, TC_BN);
+        const bool pair_ok = env_int("B200K_TC_PAIR128", 1) != 0;
+        float best = 1e30f;
+        for (int form = 0; form < 2; ++form) {      // 0: paired 128-token tiles, 1: 256-token tiles (128 with four groups up to 128 tokens)
+            if (form == 0 && !pair_ok) continue;
+            if (form == 1 && pair_ok && g.m <= 128) continue;
+            const int t = form == 0 || g.m <= 128 ? 128 : 256;
+            const int toks = ceil_div(g.m, t), slots = form == 0 ? 2 * sms : sms;
+            for (int ks = 1; ks <= 8; ks *= 2) {
+                if (ks > 1 && (kb_total <= 8 || kb_total / ks < 4)) break;
+                if (ks > 1 && cols * toks * (ks / 2) >= slots) break;     // a grid that fills the machine is not split further
+                const int ctas = cols * toks * ks, waves = ceil_div(ctas, slots);
+                const float per_block = form == 0 ? (ctas > sms ? 0.62f : 0.45f) : (t == 256 ? 0.48f : 0.22f);
+                const float us = waves * (4.f + ceil_div(kb_total, ks) * per_block) + (ks > 1 ? 5.f + t / 64.f : 0.f);
+                if (us < best) {
+                    best = us;
+                    tt = t;
+                    pair128 = form == 0;
+                    planned_split = ks;
+                }
+            }
+        }
+    }
+    const int col_tiles = silu ? g.silu_inter / 64 : ceil_div(g.n, TC_BN), tok_tiles = ceil_div(g.m, tt);
     const int tiles = col_tiles * tok_tiles;
-    // Shared memory: two CTAs per SM while the token tile is small, one otherwise.
-    // A 128-token tile of an ordinary GEMM also runs as two CTAs of two dequant groups per SM (the same four groups per SM
-    // as one CTA of four): the grid then fills the SMs in units half as large.
-    const bool pair128 = tt == 128 && !grouped && !silu && !g.bf16 && env_int("B200K_TC_PAIR128", 1) != 0;
+    // Shared memory: two CTAs per SM while the token tile is small (or in the paired form), one otherwise.
     const int ctas_per_sm = tt <= 64 || pair128 ? 2 : 1;
     const int budget = (ctas_per_sm == 2 ? 111 : 222) * 1024;
     const int act_bytes = tt * TC_BK * 2;
@@ -566,7 +596,9 @@ int gemm_tc_launch(const GemmArgs &g) {
     int ksplit = 1;
     // (a cluster launch with its two cluster barriers and the exchange costs ~5 us, a K block ~0.33 us per CTA: measured at 64
     // tokens, 8 blocks in one CTA take 5.7 us, split over a pair of CTAs 9.8 us.  Up to 8 blocks there is nothing to split.)
-    if (can_split && kb_total > 8) {
+    if (planned_split) {
+        ksplit = can_split ? planned_split : 1;
+    } else if (can_split && kb_total > 8) {
         const int sms = sm_count();
         while (ksplit < 8 && tiles * ksplit < (sms * 7) / 8 && kb_total / (ksplit * 2) >= 4) ksplit *= 2;
         if (ksplit < 8 && ksplit > 1 && tiles * ksplit <= sms && kb_total / (ksplit * 2) >= 24) ksplit *= 2;
@@ -640,7 +672,8 @@ int gemm_tc_launch(const GemmArgs &g) {
     if (g.a_kperm && !ts) return TC_NOT_COVERED;   // pre-permuted activations: only the tensor-memory operand variants take them
     if (silu && !ts) return TC_NOT_COVERED;
     if (g.bf16 && (silu || g.a_kperm || (g.format == FMT_GPTQ && !ts))) return TC_NOT_COVERED;
-    auto kern = g.bf16 ? (g.format == FMT_AWQ ? (ng == 2 ? gemm_tc_kernel<FMT_AWQ, 2, false, 2, false, false, true> : gemm_tc_kernel<FMT_AWQ, 4, false, 1, false, false, true>)
+    auto kern = g.bf16 && g2m1 ? (g.format == FMT_AWQ ? gemm_tc_kernel<FMT_AWQ, 2, false, 1, false, false, true> : gemm_tc_kernel<FMT_GPTQ, 2, true, 1, false, false, true>)
+                : g.bf16 ? (g.format == FMT_AWQ ? (ng == 2 ? gemm_tc_kernel<FMT_AWQ, 2, false, 2, false, false, true> : gemm_tc_kernel<FMT_AWQ, 4, false, 1, false, false, true>)
                                               : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false, false, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, false, false, true>))
                 : silu ? (g.a_kperm ? (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, true, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, true, true>)
                                   : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, false, true>))
