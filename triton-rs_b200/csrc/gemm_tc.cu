@@ -43,10 +43,8 @@ constexpr int TC_A_BYTES = TC_BN * TC_BK * 2;   // 16 KiB dequantised tile
 constexpr int TC_W_BYTES = TC_BN * TC_BK / 2;   // 4 KiB packed weight words of one K block
 constexpr int TC_SC_BYTES = TC_BN * 2;          // the block's scale row (one group) for the 128 columns
 constexpr int TC_ZP_BYTES = TC_BN / 2;          // and its 16 packed zero-point words
-// 4.5 KiB ring slot.  A TMA destination must be 128-byte aligned, so with the fused silu epilogue, where the gate and
-// the up columns arrive as two boxes per tensor, the up half of the zero-point words sits 128 bytes behind the gate half.
-constexpr int TC_ZP_UP_OFFSET = 128;
-constexpr int TC_RAW_BYTES = TC_W_BYTES + TC_SC_BYTES + TC_ZP_UP_OFFSET + 128;
+// ring slot: a multiple of 128 bytes (TMA destinations are 128-byte aligned)
+constexpr int TC_RAW_BYTES = TC_W_BYTES + TC_SC_BYTES + 128;
 
 struct TcArgs {
     const __half *scales;
@@ -200,17 +198,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 mbar_expect_tx(bar, TC_W_BYTES + TC_SC_BYTES + (P.qzeros ? TC_ZP_BYTES : 0));
                 const int grp = (kb * TC_BK) >> group_shift;
                 if (SILU) {
-                    // two boxes of 64 columns (gate, up) per tensor: the slot holds [8 rows][64] + [8 rows][64] words,
-                    // 64 + 64 scales, 8 + 8 zero-point words
-                    const int nu = P.silu_inter + n0;
-                    tma_load_2d(dst, &wmap, n0, w_row0 + kb * (TC_BK / 8), bar);
-                    tma_load_2d(dst + TC_W_BYTES / 2, &wmap, nu, w_row0 + kb * (TC_BK / 8), bar);
-                    tma_load_2d(dst + TC_W_BYTES, &smap, n0, g_row0 + grp, bar);
-                    tma_load_2d(dst + TC_W_BYTES + TC_SC_BYTES / 2, &smap, nu, g_row0 + grp, bar);
-                    if (P.qzeros) {
-                        tma_load_2d(dst + TC_W_BYTES + TC_SC_BYTES, &zmap, n0 / 8, g_row0 + grp, bar);
-                        tma_load_2d(dst + TC_W_BYTES + TC_SC_BYTES + TC_ZP_UP_OFFSET, &zmap, nu / 8, g_row0 + grp, bar);
-                    }
+                    // the tensors are described as [rows][2][I]: one box of 64 columns x {gate, up} per tensor lands as
+                    // [8 rows][gate 64 | up 64] words, 64 + 64 scales, 8 + 8 zero-point words -- the layout of an
+                    // ordinary 128-column tile, at half the copies two boxes per tensor would take
+                    tma_load_3d(dst, &wmap, n0, 0, w_row0 + kb * (TC_BK / 8), bar);
+                    tma_load_3d(dst + TC_W_BYTES, &smap, n0, 0, g_row0 + grp, bar);
+                    if (P.qzeros) tma_load_3d(dst + TC_W_BYTES + TC_SC_BYTES, &zmap, n0 / 8, 0, g_row0 + grp, bar);
                 } else {
                     if (FMT == FMT_GPTQ)
                         tma_load_2d(dst, &wmap, n0, w_row0 + kb * (TC_BK / 8), bar);
@@ -293,20 +286,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 const uint32_t s2 = (uint32_t)reinterpret_cast<const uint16_t *>(slot + TC_W_BYTES)[t] * 0x10001u;   // the column's scale in both halves
                 int z = 8;
                 if (P.qzeros) {
-                    const int zword = SILU ? (t >> 6) * (TC_ZP_UP_OFFSET / 4) + ((t & 63) >> 3) : t >> 3;
-                    z = (int)((reinterpret_cast<const uint32_t *>(slot + TC_W_BYTES + TC_SC_BYTES)[zword] >> (4 * (t & 7))) & 15u) +
+                    z = (int)((reinterpret_cast<const uint32_t *>(slot + TC_W_BYTES + TC_SC_BYTES)[t >> 3] >> (4 * (t & 7))) & 15u) +
                         P.zero_offset;
                 }
                 uint32_t zm[4];
                 zero_magic4<BF>(z, zm);
-                if (SILU) {      // two [8][64] boxes: gate columns (rows 0..63 of the operand), then up columns
-                    const uint32_t *rw2 = rw + (t >> 6) * (TC_W_BYTES / 8) + (t & 63);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) w[j] = rw2[j * (TC_BN / 2)];
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) w[j] = rw[j * TC_BN + t];
-                }
+                for (int j = 0; j < 8; ++j) w[j] = rw[j * TC_BN + t];     // (fused silu: rows 0..63 gate columns, 64..127 up columns)
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bars[B_RAWE + r]));  // this warp is done with the packed tile
                 if (i >= SD) {
@@ -621,10 +607,16 @@ int gemm_tc_launch(const GemmArgs &g) {
     CUtensorMap wmap, amap, smap, zmap;
     int rc;
     const uint64_t nseg = grouped ? (uint64_t)g.num_segments : 1;
-    const uint32_t cbox = silu ? TC_BN / 2 : TC_BN;      // columns per TMA box (fused silu: a gate box and an up box)
-    if (g.format == FMT_GPTQ) {
+    if (silu) {
+        // [rows][2][I] views of the packed words, scales and zero-points: a box takes 64 gate columns and the 64 up columns
+        // I further on in one copy
+        const uint64_t inter = (uint64_t)g.silu_inter;
+        const uint64_t dims[3] = {inter, 2, (uint64_t)(g.k / 8) * nseg}, str[2] = {inter * 4, (uint64_t)g.s_qwk * 4};
+        const uint32_t box[3] = {TC_BN / 2, 2, TC_BK / 8};
+        rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, g.qweight, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+    } else if (g.format == FMT_GPTQ) {
         const uint64_t dims[2] = {(uint64_t)g.n, (uint64_t)(g.k / 8) * nseg}, str[1] = {(uint64_t)g.s_qwk * 4};
-        const uint32_t box[2] = {cbox, TC_BK / 8};
+        const uint32_t box[2] = {TC_BN, TC_BK / 8};
         rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, g.qweight, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
     } else {
         const uint64_t dims[2] = {(uint64_t)(g.n / 8), (uint64_t)g.k * nseg}, str[1] = {(uint64_t)g.s_qwk * 4};
@@ -638,16 +630,28 @@ int gemm_tc_launch(const GemmArgs &g) {
         rc = make_tensor_map(&amap, g.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
     }
     if (rc) return TC_NOT_COVERED;   // layout the TMA cannot describe: the strided family takes it
-    {
+    const CUtensorMapDataType elem = g.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    if (silu) {
+        const uint64_t inter = (uint64_t)g.silu_inter;
+        const uint64_t dims[3] = {inter, 2, (uint64_t)(g.k / g.group) * nseg}, str[2] = {inter * 2, (uint64_t)g.s_sk * 2};
+        const uint32_t box[3] = {TC_BN / 2, 2, 1};
+        rc = make_tensor_map(&smap, elem, 3, g.scales, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+    } else {
         const uint64_t dims[2] = {(uint64_t)g.n, (uint64_t)(g.k / g.group) * nseg}, str[1] = {(uint64_t)g.s_sk * 2};
-        const uint32_t box[2] = {cbox, 1};
-        rc = make_tensor_map(&smap, g.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.scales, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+        const uint32_t box[2] = {TC_BN, 1};
+        rc = make_tensor_map(&smap, elem, 2, g.scales, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
     }
     if (rc) return TC_NOT_COVERED;
     zmap = smap;
-    if (g.qzeros) {
+    if (g.qzeros && silu) {
+        const uint64_t inter8 = (uint64_t)g.silu_inter / 8;
+        const uint64_t dims[3] = {inter8, 2, (uint64_t)(g.k / g.group) * nseg}, str[2] = {inter8 * 4, (uint64_t)g.s_qzk * 4};
+        const uint32_t box[3] = {TC_BN / 16, 2, 1};
+        rc = make_tensor_map(&zmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, g.qzeros, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc) return TC_NOT_COVERED;
+    } else if (g.qzeros) {
         const uint64_t dims[2] = {(uint64_t)(g.n / 8), (uint64_t)(g.k / g.group) * nseg}, str[1] = {(uint64_t)g.s_qzk * 4};
-        const uint32_t box[2] = {cbox / 8, 1};
+        const uint32_t box[2] = {TC_BN / 8, 1};
         rc = make_tensor_map(&zmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, g.qzeros, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
         if (rc) return TC_NOT_COVERED;
     }
