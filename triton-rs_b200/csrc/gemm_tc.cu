@@ -480,13 +480,18 @@ static int pick_tt(int m) {
 }
 
 // Grouped mode: segments are unequal (router counts scatter around the mean), and every token tile of a segment
-// dequantises the segment's weights again, whatever its width; the tile therefore leaves half the mean as head-room,
-// so that a segment somewhat above the mean still fits one tile.
+// dequantises the segment's weights again, whatever its width.  The tile therefore leaves head-room above the mean -- a
+// quarter of it, or three standard deviations of a count that scatters like a Poisson variable, whichever is more -- so that a
+// segment above the mean still fits one tile.  Up to 192 rows the tile is a multiple of 16 and two CTAs share an SM
+// (tensor memory: 256 columns each); above, one CTA per SM with 256-row tiles.
 int gemm_tc_token_tile(int m, int segments) {
     if (segments <= 1) return pick_tt(m);
-    const int mean = ceil_div(m, segments), want = mean + mean / 2;
-    // 192 rows (between the powers of two): leaves tensor memory for an operand ring of eight tiles behind the accumulator
-    return want > 128 && want <= 192 ? 192 : pick_tt(want);
+    if (const int v = env_int("B200K_TC_GTT", 0)) return v;      // tuning override
+    const int mean = ceil_div(m, segments);
+    const int spread = (int)(3.f * sqrtf((float)mean)) + 1;
+    const int want = mean + (mean / 4 > spread ? mean / 4 : spread);
+    if (want <= 64) return pick_tt(want);
+    return want <= 192 ? (want + 15) / 16 * 16 : 256;
 }
 
 int gemm_tc_launch(const GemmArgs &g) {
@@ -506,7 +511,7 @@ int gemm_tc_launch(const GemmArgs &g) {
     // (0.48 us each at 256 tokens, where the activation tiles' way from L2 sets the pace; 0.62 us when two 128-token CTAs
     // share an SM, 0.45 us when one has it alone), CTAs beyond the resident ones wait for a whole wave, and a K split costs
     // ~5 us plus the exchange of the partial tiles.
-    bool pair128 = false;
+    bool pair128 = grouped && tt > 64 && tt <= 192 && env_int("B200K_TC_GPAIR", 1) != 0;     // (ordinary GEMMs: decided below)
     int planned_split = 0;
     if (!grouped && !silu && g.m > 64 && !env_int("B200K_TC_TT", 0)) {
         const int sms = sm_count(), cols = ceil_div(g.n, TC_BN);
@@ -554,11 +559,11 @@ int gemm_tc_launch(const GemmArgs &g) {
     auto log2i = [](int v) { int l = 0; while ((1 << l) < v) ++l; return l; };
     int dq_stages, act_stages;
     if (ts) {   // operand tiles cost 32 TMEM columns each: 256 columns per CTA with two CTAs per SM, 512 with one
-        dq_stages = 4;
+        dq_stages = pair128 && tt > 128 ? 2 : 4;      // two CTAs per SM: tile + 32 x depth <= 256 columns
         act_stages = tt <= 128 && !pair128 ? 8 : 4;
     } else {
         dq_stages = tt <= 64 || pair128 ? 2 : 4;
-        act_stages = tt <= 32 ? 8 : pair128 ? 2 : 4;
+        act_stages = tt <= 32 ? 8 : pair128 && tt > 128 ? 2 : 4;
     }
     if (const int v = env_int("B200K_TC_DQ_STAGES", 0)) dq_stages = pow2_floor(v < 1 ? 1 : v);     // tuning overrides
     if (const int v = env_int("B200K_TC_ACT_STAGES", 0)) act_stages = pow2_floor(v < 1 ? 1 : v);
@@ -679,6 +684,7 @@ int gemm_tc_launch(const GemmArgs &g) {
     auto kern = g.bf16 && g2m1 ? (g.format == FMT_AWQ ? gemm_tc_kernel<FMT_AWQ, 2, false, 1, false, false, true> : gemm_tc_kernel<FMT_GPTQ, 2, true, 1, false, false, true>)
                 : g.bf16 ? (g.format == FMT_AWQ ? (ng == 2 ? gemm_tc_kernel<FMT_AWQ, 2, false, 2, false, false, true> : gemm_tc_kernel<FMT_AWQ, 4, false, 1, false, false, true>)
                                               : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false, false, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, false, false, true>))
+                : silu && g2m1 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 1, false, true>
                 : silu ? (g.a_kperm ? (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, true, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, true, true>)
                                   : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, false, true>))
                 : g2m1 ? (g.format == FMT_AWQ ? gemm_tc_kernel<FMT_AWQ, 2, false, 1, false>
