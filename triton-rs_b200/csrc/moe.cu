@@ -385,7 +385,9 @@ static int moe_run(const char *name, const b200k_half *x, const float *router_lo
     const int32_t *nrows = w.offsets + num_local;    // rows of the segmented list that belong to local experts
     int rc;
     if ((rc = moe_route_topk_f32(router_logits, w.ids, w.wts, num_tokens, num_experts, top_k, stream))) return rc;
-    const int tt = gemm_tc_token_tile(pairs, num_local);      // the token tile both expert GEMMs will use
+    // the token tile both expert GEMMs will use follows the rows EXPECTED on the local experts; the grids cover the worst case
+    const int expected = (int)((long)pairs * num_local / num_experts) > 0 ? (int)((long)pairs * num_local / num_experts) : 1;
+    const int tt = gemm_tc_token_tile(expected, num_local);
     const int max_tiles = ceil_div(pairs, tt) + num_local;
     moe_permute_kernel<<<1, 1024, 0, st>>>(w.ids, pairs, buckets, expert_first, num_local, w.counts, w.offsets,
                                            w.sorted_pairs, w.inv, tt, w.tiles, w.ntiles);
@@ -397,7 +399,7 @@ static int moe_run(const char *name, const b200k_half *x, const float *router_lo
     GemmArgs g = {};
     g.format = FMT_GPTQ; g.group = group_size; g.stream = st; g.ws = workspace; g.ws_bytes = workspace_bytes;
     g.seg_offsets = w.offsets; g.num_segments = num_local;
-    g.tile_list = w.tiles; g.tile_count = w.ntiles; g.max_tiles = max_tiles;
+    g.tile_list = w.tiles; g.tile_count = w.ntiles; g.max_tiles = max_tiles; g.expected_m = expected;
     g.s_ak = g.s_qwn = g.s_sn = g.s_qzn = g.s_cn = 1;
     // up-projection with the silu_mul fused into its epilogue: [pairs, H] x W13_e [H, gate I | up I] -> silu(gate) * up [pairs, I]
     g.a = w.xp; g.qweight = w13_qweight; g.scales = (const __half *)w13_scales; g.qzeros = w13_qzeros; g.c = w.act;
@@ -493,7 +495,8 @@ extern "C" int fused_moe_gptq_a2a_f16(struct b200k_comm *comm, const b200k_half 
         const int32_t *recv_ids = reinterpret_cast<const int32_t *>(cv.local + ids_off);
         const __half *recv_rows = reinterpret_cast<const __half *>(cv.local + rows_off);
         const int32_t *nrows = w.offsets + per;
-        const int tt = gemm_tc_token_tile(slots, per);
+        const int expected = (int)((long)slots * per / num_experts) > 0 ? (int)((long)slots * per / num_experts) : 1;
+        const int tt = gemm_tc_token_tile(expected, per);      // planned for the expected rows, grids for the worst case
         const int max_tiles = ceil_div(slots, tt) + per;
         moe_permute_kernel<<<1, 1024, 0, st>>>(recv_ids, slots, per + 1, rank * per, per, w.counts, w.offsets, w.sorted_pairs, w.inv, tt,
                                                w.tiles, w.ntiles);
@@ -503,7 +506,7 @@ extern "C" int fused_moe_gptq_a2a_f16(struct b200k_comm *comm, const b200k_half 
         GemmArgs g = {};
         g.format = FMT_GPTQ; g.group = group_size; g.stream = st; g.ws = workspace; g.ws_bytes = workspace_bytes;
         g.seg_offsets = w.offsets; g.num_segments = per;
-        g.tile_list = w.tiles; g.tile_count = w.ntiles; g.max_tiles = max_tiles;
+        g.tile_list = w.tiles; g.tile_count = w.ntiles; g.max_tiles = max_tiles; g.expected_m = expected;
         g.s_ak = g.s_qwn = g.s_sn = g.s_qzn = g.s_cn = 1;
         g.a = w.xp; g.qweight = w13_qweight; g.scales = (const __half *)w13_scales; g.qzeros = w13_qzeros; g.c = w.act;
         g.m = slots; g.n = 2 * intermediate; g.k = hidden; g.silu_inter = intermediate;
