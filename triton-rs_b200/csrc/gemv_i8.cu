@@ -286,20 +286,27 @@ __device__ __noinline__ void awq_rows_fp32(const __half *a, const int32_t *wp, l
 // own activations (its own scale: the identity above holds for any subset of k).  Rows are requested in half-batches of
 // 16 held in NB register buffers that rotate: while one is multiplied, NB - 1 are in flight (narrow matrices have few
 // warps, so each must keep more bytes in flight).
-template <int UR, int NB>
+// CW = columns per warp.  256: a lane owns one word column (8 weight columns) over all rows of the warp's units.  128: a
+// half-warp owns 16 word columns and half the rows of every unit (the halves are added by a shuffle at the end), which
+// doubles the column blocks of a narrow matrix: at N = 4096 the widest cluster gives 128 CTAs of 256 columns, fewer than SMs.
+template <int UR, int NB, int CW>
 __global__ void __launch_bounds__(GI_THREADS, 2)      // 128 registers: narrow matrices need two CTAs per SM to run in one wave
 gemv_awq_i8_kernel(GemmArgs g, int ksplit) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint2 *act = reinterpret_cast<uint2 *>(smem_raw);                              // [GI_WARPS][32]: (ah, al) of 4 consecutive k
     float4 *red4 = reinterpret_cast<float4 *>(smem_raw + GI_WARPS * 16 * sizeof(uint4));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int col = blockIdx.x * 256 + lane * 8;      // 8 columns per thread, 256 per warp
+    constexpr bool HALF = CW == 128;
+    const int hp = HALF ? lane >> 4 : 0;              // which half of a unit's rows this lane reads
+    const int wl = HALF ? lane & 15 : lane;           // word column within the warp's block
+    constexpr int RL = HALF ? UR / 2 : UR;            // rows of a unit per lane
+    const int col = blockIdx.x * CW + wl * 8;         // 8 columns per thread
     const int uslot = blockIdx.y * GI_WARPS + warp, uslots = ksplit * GI_WARPS;
     const int units = g.k / UR;
     const bool live = col < g.n;
     uint2 *my_act = act + warp * 32;
     constexpr int HB = 16;                            // rows per half-batch
-    constexpr int HPU = UR / HB;                      // half-batches per unit
+    constexpr int HPU = RL / HB;                      // half-batches per unit (and lane)
     constexpr int UPG = GI_GROUP / UR;                // units per quantisation group
 
     uint32_t w[NB][HB];
@@ -315,7 +322,7 @@ gemv_awq_i8_kernel(GemmArgs g, int ksplit) {
     auto request_rows = [&](uint32_t (&buf)[HB], int first_unit, int t) {
         const int unit = first_unit + (t / HPU) * uslots;
         if (unit < units) {
-            const int32_t *wp = g.qweight + (long)(unit * UR + (t % HPU) * HB) * g.s_qwk + col / 8;
+            const int32_t *wp = g.qweight + (long)(unit * UR + hp * RL + (t % HPU) * HB) * g.s_qwk + col / 8;
 #pragma unroll
             for (int j = 0; j < HB; ++j) buf[j] = ldg_nc_word(wp + (long)j * g.s_qwk);
         }
@@ -357,7 +364,7 @@ gemv_awq_i8_kernel(GemmArgs g, int ksplit) {
             if (outlier) {
                 // fp32 for this unit; its rows are read again (from L2: rare), the register buffers only turn
                 float accx[8];
-                awq_rows_fp32(g.a + (long)u * UR, g.qweight + (long)u * UR * g.s_qwk + col / 8, g.s_qwk, UR, zw_now, accx);
+                awq_rows_fp32(g.a + (long)u * UR + hp * RL, g.qweight + ((long)u * UR + hp * RL) * g.s_qwk + col / 8, g.s_qwk, RL, zw_now, accx);
                 const float2 sA = h2_to_f2(su_now.x), sB = h2_to_f2(su_now.y), sC = h2_to_f2(su_now.z), sD = h2_to_f2(su_now.w);
                 const float sc[8] = {sA.x, sA.y, sB.x, sB.y, sC.x, sC.y, sD.x, sD.y};
 #pragma unroll
@@ -375,7 +382,7 @@ gemv_awq_i8_kernel(GemmArgs g, int ksplit) {
                 uint32_t (&buf)[HB] = w[t % NB];
 #pragma unroll
                 for (int j = 0; j < HB; j += 4) {
-                    const uint2 av = my_act[(hb * HB + j) >> 2];
+                    const uint2 av = my_act[(hp * RL + hb * HB + j) >> 2];
                     uint32_t e[4], o[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
@@ -410,12 +417,18 @@ gemv_awq_i8_kernel(GemmArgs g, int ksplit) {
                 const int ze = (int)((zw_now >> (8 * b)) & 15u), zo = (int)((zw_now >> (8 * b + 4)) & 15u);
                 const int de = 128 * ae[b][0] + ae[b][1];
                 const int dn = 128 * (ao[b][0] >> 4) + (ao[b][1] >> 4);
-                tot[ce_col] += (float)(de - ze * asum) * (sc[ce_col] * sa);
-                tot[co_col] += (float)(dn - zo * asum) * (sc[co_col] * sa);
+                // (two halves of the rows in two half-warps: the zero-point term of the whole unit goes with the first)
+                const int asum_h = hp == 0 ? asum : 0;
+                tot[ce_col] += (float)(de - ze * asum_h) * (sc[ce_col] * sa);
+                tot[co_col] += (float)(dn - zo * asum_h) * (sc[co_col] * sa);
             }
         }
     }
-    reduce_and_store<8>(tot, red4, warp, GI_WARPS, lane, 32, ksplit, live, g.c + col);
+    if (HALF) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) tot[c] += __shfl_xor_sync(0xffffffffu, tot[c], 16);
+    }
+    reduce_and_store<8>(tot, red4, warp, GI_WARPS, wl, HALF ? 16 : 32, ksplit, live && hp == 0, g.c + col);
 }
 
 static inline int imin(int a, int b) { return a < b ? a : b; }
@@ -427,11 +440,18 @@ int gemv_i8_launch(const GemmArgs &g) {
     // GPTQ: 256 columns per CTA (2 column-warps x 4 k-warps), or 128 (1 x 8) when 256-column blocks with the largest
     // cluster would leave SMs without a CTA.  AWQ: 256 columns per CTA, all 8 warps split K, by whole groups, or by
     // quarter groups when K is short and whole groups per warp with the largest cluster would leave most SMs without a CTA.
-    const int cw = g.format != FMT_GPTQ ? 1 : ceil_div(g.n, 256) * 8 < 2 * sm_count() ? 1 : 2;
-    const int colblocks = g.format == FMT_GPTQ ? ceil_div(g.n, 128 * cw) : ceil_div(g.n, 256);
+    const bool narrow = ceil_div(g.n, 256) * 8 < 2 * sm_count();
+    const int cw = g.format != FMT_GPTQ ? 1 : narrow ? 1 : 2;
+    int awq_cols = narrow ? 128 : 256;       // AWQ: columns per warp (= per CTA)
+    {   // tuning override
+        const int v = env_int("B200K_GEMV_AWQ_COLS", 0);
+        if (v == 128 || v == 256) awq_cols = v;
+    }
+    const int colblocks = g.format == FMT_GPTQ ? ceil_div(g.n, 128 * cw) : ceil_div(g.n, awq_cols);
     const int kwarps = GI_WARPS / cw;
     int unit_rows = GI_GROUP;
-    if (g.format == FMT_AWQ && groups < 64 && colblocks * imin(8, imax(1, groups / (2 * kwarps))) < sm_count()) unit_rows = 32;
+    // (measured with 128-column blocks: whole groups win -- 4096 x 4096 4.6 against 6.1 us, 4096 x 6144 5.6 against 10.6 us)
+    if (g.format == FMT_AWQ && awq_cols == 256 && groups < 64 && colblocks * imin(8, imax(1, groups / (2 * kwarps))) < sm_count()) unit_rows = 32;
     {   // tuning override
         const int v = env_int("B200K_GEMV_UNIT", 0);
         if (g.format == FMT_AWQ && (v == 32 || v == 128)) unit_rows = v;
@@ -452,8 +472,12 @@ int gemv_i8_launch(const GemmArgs &g) {
         int nb = 4;
         const int v = env_int("B200K_GEMV_DEPTH", 0);      // tuning override
         if (v == 2 || v == 4) nb = v;
-        kern = unit_rows == 32 ? (nb == 4 ? gemv_awq_i8_kernel<32, 4> : gemv_awq_i8_kernel<32, 2>)
-                               : (nb == 4 ? gemv_awq_i8_kernel<128, 4> : gemv_awq_i8_kernel<128, 2>);
+        if (awq_cols == 128)
+            kern = unit_rows == 32 ? (nb == 4 ? gemv_awq_i8_kernel<32, 4, 128> : gemv_awq_i8_kernel<32, 2, 128>)
+                                   : (nb == 4 ? gemv_awq_i8_kernel<128, 4, 128> : gemv_awq_i8_kernel<128, 2, 128>);
+        else
+            kern = unit_rows == 32 ? (nb == 4 ? gemv_awq_i8_kernel<32, 4, 256> : gemv_awq_i8_kernel<32, 2, 256>)
+                                   : (nb == 4 ? gemv_awq_i8_kernel<128, 4, 256> : gemv_awq_i8_kernel<128, 2, 256>);
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(colblocks, ksplit, 1);
