@@ -201,3 +201,90 @@ def test_two_ranks_allreduce_and_tp_layer():
             if p.is_alive():
                 p.kill()
     assert all(v == "ok" for v in results.values()), results
+
+
+# ---- the two-shot form (large tensors on three or more ranks), forced on smaller groups through its override ----
+_ONE_RANK_TWOSHOT = r"""
+import importlib, sys
+import torch
+sys.path.insert(0, sys.argv[1])
+pkg = importlib.import_module("triton-rs_b200")
+dev = "cuda:0"
+n = 64 * 4096 + 8
+comm = pkg.Comm(0, 1, n * 2, exchange=None)
+x = torch.randn(n, device=dev, dtype=torch.float16)
+res = torch.randn(n, device=dev, dtype=torch.float16)
+out = torch.zeros_like(x)
+for slot in (0, 1, 0, 1):
+    comm.all_reduce(slot, out, n, input=x)
+    torch.cuda.synchronize()
+    assert torch.equal(out, x), slot
+got = torch.empty_like(x)
+pkg.lib().call("b200k_comm_allreduce_add_f16", comm.handle, 0, x, res, got, n, torch.cuda.current_stream().cuda_stream)
+torch.cuda.synchronize()
+assert torch.equal(got, res + x)
+assert comm.status() == 0
+comm.close()
+print("ok")
+"""
+
+
+def test_twoshot_allreduce_single_rank():
+    import subprocess
+    env = dict(os.environ, B200K_COMM_TWOSHOT="1")
+    r = subprocess.run([sys.executable, "-c", _ONE_RANK_TWOSHOT, str(ROOT)], env=env, capture_output=True, text=True, timeout=240)
+    assert r.returncode == 0 and r.stdout.strip().endswith("ok"), r.stdout + r.stderr
+
+
+def _rank_twoshot(rank, world, port, q):
+    try:
+        sys.path.insert(0, str(ROOT))
+        import importlib
+        import torch.distributed as dist
+        pkg = importlib.import_module("triton-rs_b200")
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        n_max = 512 * 4096
+        comm = pkg.Comm.from_process_group(n_max * 2)
+        rng = np.random.default_rng(11)
+        for it, n in enumerate([8, 64 * 4096, 1000 * 8, 512 * 4096, 512 * 4096, 4096 + 8]):
+            parts = [rng.standard_normal(n).astype(np.float16) for _ in range(world)]   # same stream of numbers on every rank
+            out = torch.zeros(n, device=dev, dtype=torch.float16)
+            dist.barrier()                # the kernel waits for its peers for about a second only
+            comm.all_reduce(it & 1, out, n, input=torch.from_numpy(parts[rank]).to(dev))
+            torch.cuda.synchronize()
+            assert np.array_equal(out.cpu().numpy().view(np.uint16), _expected(parts).view(np.uint16)), f"two-shot all-reduce n={n}"
+        assert comm.status() == 0
+        dist.barrier()
+        comm.close()
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        q.put((rank, "".join(traceback.format_exception(e))))
+
+
+@pytest.mark.timeout(300)
+def test_two_ranks_twoshot_allreduce(monkeypatch):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    monkeypatch.setenv("B200K_COMM_TWOSHOT", "1")      # inherited by the ranks; read once per process by the library
+    world, port = 2, 29741
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rank_twoshot, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = {}
+    try:
+        for _ in range(world):
+            r, msg = q.get(timeout=240)
+            results[r] = msg
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    assert all(v == "ok" for v in results.values()), results

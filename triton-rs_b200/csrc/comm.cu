@@ -128,6 +128,74 @@ allreduce_oneshot_kernel(unsigned char *const *__restrict__ peers, int rank, int
     exchange_leave(peers, rank, seq);
 }
 
+// Two-shot form for large tensors.  Rank r sums the r-th share of the vectors over all ranks (the same rank-order fp32
+// sum, one rounding) and stores the fp16 result into the OTHER slot of every rank; after a second round of flags every
+// rank copies that slot out.  One-shot makes every rank read (world - 1) x count over NVLink; here a rank reads
+// (world - 1) / world x count and writes as much.  The other slot is free for the duration: between the entry barrier of
+// this call (every rank has left the call before it) and the next call on it (slots are used alternately) nobody reads it.
+// The CTAs of a grid wait on one another through the peers (the last CTA through its share publishes this rank's flag),
+// so the whole grid must be resident: at most 128 CTAs.
+__global__ void __launch_bounds__(512)
+allreduce_twoshot_kernel(unsigned char *const *__restrict__ peers, int rank, int world, int slot, size_t slot_bytes,
+                         const __half *__restrict__ addend, __half *__restrict__ out, size_t count, long long wait_cycles) {
+    pdl_wait();                 // the partial sums in my slot come from the kernel before
+    pdl_launch_dependents();
+    __shared__ int s_fail;
+    unsigned seq;
+    unsigned *my_flags = reinterpret_cast<unsigned *>(peers[rank]);
+    const bool entered = exchange_enter(peers, rank, world, wait_cycles, seq, &s_fail);
+    const size_t nvec = count / 8;                          // 16-byte chunks
+    const size_t off_in = COMM_FLAGS_BYTES + (size_t)slot * slot_bytes, off_res = COMM_FLAGS_BYTES + (size_t)(slot ^ 1) * slot_bytes;
+    if (entered) {
+        const size_t share = (nvec + world - 1) / world;
+        const size_t lo = (size_t)rank * share < nvec ? (size_t)rank * share : nvec, hi = lo + share < nvec ? lo + share : nvec;
+        for (size_t i = lo + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < hi; i += (size_t)gridDim.x * blockDim.x) {
+            float acc[8];
+            peer_sum8(peers, world, off_in + i * 16, acc);
+            uint4 o;
+            o.x = f2_to_h2(acc[0], acc[1]); o.y = f2_to_h2(acc[2], acc[3]);
+            o.z = f2_to_h2(acc[4], acc[5]); o.w = f2_to_h2(acc[6], acc[7]);
+#pragma unroll
+            for (int r = 0; r < COMM_MAX_WORLD; ++r)
+                if (r < world) *reinterpret_cast<uint4 *>(peers[r] + off_res + i * 16) = o;
+        }
+    }
+    // second round: this rank's share is in every rank's result slot once all CTAs of the grid are through
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        if (atomicAdd(my_flags + COMM_W_AR2_COUNT, 1u) == gridDim.x - 1) {
+            my_flags[COMM_W_AR2_COUNT] = 0;
+            __threadfence_system();
+            for (int r = 0; r < world; ++r) st_release_sys(reinterpret_cast<unsigned *>(peers[r]) + COMM_W_AR2 + rank, seq);
+        }
+    }
+    if (entered && threadIdx.x < world) {
+        const long long t0 = clock64();
+        while ((int)(ld_acquire_sys(my_flags + COMM_W_AR2 + threadIdx.x) - seq) < 0) {
+            if (clock64() - t0 > wait_cycles) {   // a peer never delivered: report, do not spin for ever
+                s_fail = 1;
+                atomicExch(my_flags + COMM_W_STATUS, 1u);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    if (entered && !s_fail) {
+        const uint4 *res = reinterpret_cast<const uint4 *>(peers[rank] + off_res);
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+            uint4 o = res[i];
+            if (addend) {
+                const uint4 h = reinterpret_cast<const uint4 *>(addend)[i];
+                o.x = h22(__hadd2(u2h(h.x), u2h(o.x))); o.y = h22(__hadd2(u2h(h.y), u2h(o.y)));
+                o.z = h22(__hadd2(u2h(h.z), u2h(o.z))); o.w = h22(__hadd2(u2h(h.w), u2h(o.w)));
+            }
+            reinterpret_cast<uint4 *>(out)[i] = o;
+        }
+    }
+    exchange_leave(peers, rank, seq);
+}
+
 // all-reduce(slot) + residual add + rms_norm in one pass, one CTA per row of n values (the step after o_proj of a
 // tensor-parallel layer): r = residual + fp16(sum over ranks); residual_out = fp16(r); y = r * rsqrt(mean(r^2) + eps) * w
 // from the unrounded fp32 r, the arithmetic of fused_add_rms_norm_f16.  KPERM stores every 8 outputs of y as
@@ -231,7 +299,15 @@ int comm_allreduce_add_f16(struct ::b200k_comm *c, int slot, const __half *adden
     if (count == 0) return 0;
     int blocks = (int)((count / 8 + 511) / 512);
     if (blocks > 128) blocks = 128;
-    launch_kernel(allreduce_oneshot_kernel, dim3(blocks), dim3(512), 0, st, c->d_peers, c->rank, c->world, slot, c->slot_bytes, addend, out, count, c->wait_cycles);
+    // Two-shot when what it saves on the wire outweighs its second round of flags (~5 us): one-shot moves (world - 1) x bytes
+    // into every rank, two-shot 2 (world - 1) / world x bytes (measured link rate ~700 GB/s)
+    const double saved_bytes = (double)count * 2 * (c->world - 1) * (1.0 - 2.0 / c->world);
+    bool two_shot = c->world >= 3 && saved_bytes > 3.5e6;
+    if (const int v = env_char("B200K_COMM_TWOSHOT")) two_shot = v == '1';      // tuning / test override
+    if (two_shot)
+        launch_kernel(allreduce_twoshot_kernel, dim3(blocks), dim3(512), 0, st, c->d_peers, c->rank, c->world, slot, c->slot_bytes, addend, out, count, c->wait_cycles);
+    else
+        launch_kernel(allreduce_oneshot_kernel, dim3(blocks), dim3(512), 0, st, c->d_peers, c->rank, c->world, slot, c->slot_bytes, addend, out, count, c->wait_cycles);
     return launch_status("all-reduce (peer to peer)");
 }
 

@@ -10,8 +10,10 @@ constexpr size_t COMM_FLAGS_BYTES = 4096;
 // Words of the flags page, [0, 4096) of every rank's buffer (unsigned, index = byte offset / 4):
 //   [0, 8)   all-reduce flags, one per peer, written by that peer      [16] all-reduce round   [17] its done counter
 //   [18]     status word (any bounded wait that gave up)
+//   [20, 28) two-shot all-reduce: "rank r has delivered its share" flags   [28] its done counter
 //   [32, 40) token exchange: "rank r has delivered its tokens" flags   [40, 48) "rank r has published its results" flags
 //   [48]     token-exchange round   [49], [50], [51] done counters of its three phases
+constexpr int COMM_W_AR2 = 20, COMM_W_AR2_COUNT = 28;
 constexpr int COMM_W_STATUS = 18, COMM_W_A2A_SENT = 32, COMM_W_A2A_DONE = 40, COMM_W_A2A_ROUND = 48, COMM_W_A2A_COUNT = 49;
 
 struct CommView {
