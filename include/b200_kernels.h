@@ -645,7 +645,11 @@ int b200k_layer_set_kv_cache(b200k_layer *layer, b200k_half *k_cache, b200k_half
  * (b200k_comm_slot).  Every rank must make the same sequence of calls; use slots alternately (a slot
  * may be rewritten once a LATER all-reduce has been enqueued behind the one that read it).  The
  * kernel waits for its peers at most about a second, then sets the status word (b200k_comm_status
- * != 0) and leaves `output` unwritten.  Plain peer loads and stores only. */
+ * != 0) and leaves `output` unwritten.  Plain peer loads and stores only.
+ * Large tensors on three or more ranks (b200k_comm_allreduce_f16 and _add_f16) take a two-shot form:
+ * every rank reduces one share and stores it into the OTHER slot of all ranks, a second round of
+ * flags, then a local copy; same bits, a fraction of the NVLink traffic.  The other slot's content
+ * is therefore lost during such a call -- which the alternation rule already allows. */
 struct b200k_comm;
 int b200k_comm_create(int rank, int world, size_t slot_bytes, struct b200k_comm **out_comm);
 int b200k_comm_ipc_handle(struct b200k_comm *comm, void *host_handle_64_bytes);
