@@ -299,10 +299,11 @@ int comm_allreduce_add_f16(struct ::b200k_comm *c, int slot, const __half *adden
     if (count == 0) return 0;
     int blocks = (int)((count / 8 + 511) / 512);
     if (blocks > 128) blocks = 128;
-    // Two-shot when what it saves on the wire outweighs its second round of flags (~5 us): one-shot moves (world - 1) x bytes
-    // into every rank, two-shot 2 (world - 1) / world x bytes (measured link rate ~700 GB/s)
+    // Two-shot when what it saves on the wire outweighs its second round (remote stores fenced, flags, copy-out: measured
+    // 14 us at four ranks and 512 KB, where the one-shot form takes 14.6 us in all): one-shot moves (world - 1) x bytes into
+    // every rank, two-shot 2 (world - 1) / world x bytes, at ~700 GB/s
     const double saved_bytes = (double)count * 2 * (c->world - 1) * (1.0 - 2.0 / c->world);
-    bool two_shot = c->world >= 3 && saved_bytes > 3.5e6;
+    bool two_shot = c->world >= 3 && saved_bytes > 10e6;
     if (const int v = env_char("B200K_COMM_TWOSHOT")) two_shot = v == '1';      // tuning / test override
     if (two_shot)
         launch_kernel(allreduce_twoshot_kernel, dim3(blocks), dim3(512), 0, st, c->d_peers, c->rank, c->world, slot, c->slot_bytes, addend, out, count, c->wait_cycles);
