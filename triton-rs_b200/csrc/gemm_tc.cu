@@ -92,7 +92,12 @@ __device__ __forceinline__ uint32_t ring_phase(int i, int lg) { return (uint32_t
 // stores silu(gate) * up, 64 columns of an [M, I] output (the product the reference computes with a separate kernel,
 // fused_silu_mul_interleaved, on the GEMM's fp16 output; here it is taken from the fp32 accumulators).
 // BF: activations, scales and output are bfloat16 (the MMA's operand format follows).
-template <int FMT, int NG, bool TS, int NMMA, bool KPERM, bool SILU = false, bool BF = false>
+// Wide steps (KK = 2; operand in tensor memory, token tiles up to 64): a pipeline step covers 128 k -- one
+// TMA box of 16 packed rows, the step's scale row and zero words once, two swizzled activation boxes, two operand
+// sub-tiles of 32 TMEM columns, eight MMAs and one commit.  Every role's hand-over (a barrier in, a barrier out, the
+// issue of its copies or MMAs) is then paid once per 128 k; at token tiles <= 64 those hand-overs, not the arithmetic
+// or the tensor pipe, are most of a 64-k block's time.
+template <int FMT, int NG, bool TS, int NMMA, bool KPERM, bool SILU = false, bool BF = false, int KK = 1>
 __global__ void __launch_bounds__(tc_threads(NG), NG == 2 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap amap,
                const __grid_constant__ CUtensorMap smap, const __grid_constant__ CUtensorMap zmap, TcArgs P) {
@@ -100,11 +105,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int LSD = P.dq_log2, LSA = P.act_log2, LR = P.raw_log2, TT = P.tt;
     const int SD = 1 << LSD, SA = 1 << LSA, R = 1 << LR;
-    const int b_bytes = TT * TC_BK * 2;
+    static_assert(KK == 1 || (KK == 2 && TS && !SILU), "wide steps: operand in tensor memory, no fused epilogue");
+    const int b_bytes = TT * TC_BK * 2 * KK;                    // KK swizzled boxes of [TT][128 B], one behind the other
+    const int w_bytes = TC_W_BYTES * KK, raw_bytes = w_bytes + TC_SC_BYTES + 128;
     unsigned char *a_tile = smem;                               // [SD][16 KiB] (absent when the operand tile lives in TMEM)
-    unsigned char *b_tile = a_tile + (TS ? 0 : (size_t)SD * TC_A_BYTES);   // [SA][TT * 128]
-    unsigned char *raw = b_tile + (size_t)SA * b_bytes;         // [R][4 KiB]
-    unsigned long long *bars = reinterpret_cast<unsigned long long *>(raw + (size_t)R * TC_RAW_BYTES);
+    unsigned char *b_tile = a_tile + (TS ? 0 : (size_t)SD * TC_A_BYTES);   // [SA][KK][TT * 128]
+    unsigned char *raw = b_tile + (size_t)SA * b_bytes;         // [R][4 or 8 KiB + scales + zero words]
+    unsigned long long *bars = reinterpret_cast<unsigned long long *>(raw + (size_t)R * raw_bytes);
     // barrier map
     const int B_ACTF = 0;               // [SA] activation tile landed (TMA)
     const int B_ACTE = SA;              // [SA] activation tile consumed (released by the dequant group that sees its MMAs retired)
@@ -138,7 +145,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         w_row0 = e * P.w_rows_per_seg;
         g_row0 = e * P.g_rows_per_seg;
     }
-    const int kb_total = P.k / TC_BK;
+    const int kb_total = P.k / (TC_BK * KK);        // pipeline steps ("K blocks" below) over the whole K
     // K split: blockIdx.z, except in grouped mode without a work list, where blockIdx.z is the segment
     const int kb_begin = P.seg_offsets && !P.tile_list ? 0 : blockIdx.z * P.kb_per_split;
     const int kb_end = min(kb_total, kb_begin + P.kb_per_split);
@@ -146,7 +153,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     // TMEM columns: NMMA fp32 accumulators [128 lanes][TT]; with TS, SD operand tiles of 32 columns behind them
     const uint32_t a_col0 = NMMA * TT < 32 ? 32 : NMMA * TT;
     uint32_t tmem_cols = 32;
-    while (tmem_cols < (TS ? a_col0 + 32u * SD : (uint32_t)(NMMA * TT))) tmem_cols <<= 1;
+    while (tmem_cols < (TS ? a_col0 + 32u * KK * SD : (uint32_t)(NMMA * TT))) tmem_cols <<= 1;
 
     // one barrier per thread (up to ~60 of them: initialised one after the other by a single thread they cost a microsecond)
     if (tid <= B_ACC) {
@@ -195,24 +202,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 const int r = ring_slot(i, LR), kb = kb_begin + i;
                 if (i >= R) wait(B_RAWE + r, ring_phase(i, LR) ^ 1u);
                 const uint32_t bar = smem_u32(&bars[B_RAWF + r]);
-                const uint32_t dst = smem_u32(raw + (size_t)r * TC_RAW_BYTES);
-                mbar_expect_tx(bar, TC_W_BYTES + TC_SC_BYTES + (P.qzeros ? TC_ZP_BYTES : 0));
-                const int grp = (kb * TC_BK) >> group_shift;
+                const uint32_t dst = smem_u32(raw + (size_t)r * raw_bytes);
+                mbar_expect_tx(bar, w_bytes + TC_SC_BYTES + (P.qzeros ? TC_ZP_BYTES : 0));
+                const int grp = (kb * TC_BK * KK) >> group_shift;
                 if (SILU) {
                     // the tensors are described as [rows][2][I]: one box of 64 columns x {gate, up} per tensor lands as
                     // [8 rows][gate 64 | up 64] words, 64 + 64 scales, 8 + 8 zero-point words -- the layout of an
                     // ordinary 128-column tile, at half the copies two boxes per tensor would take
                     tma_load_3d(dst, &wmap, n0, 0, w_row0 + kb * (TC_BK / 8), bar);
-                    tma_load_3d(dst + TC_W_BYTES, &smap, n0, 0, g_row0 + grp, bar);
-                    if (P.qzeros) tma_load_3d(dst + TC_W_BYTES + TC_SC_BYTES, &zmap, n0 / 8, 0, g_row0 + grp, bar);
+                    tma_load_3d(dst + w_bytes, &smap, n0, 0, g_row0 + grp, bar);
+                    if (P.qzeros) tma_load_3d(dst + w_bytes + TC_SC_BYTES, &zmap, n0 / 8, 0, g_row0 + grp, bar);
                 } else {
                     if (FMT == FMT_GPTQ)
-                        tma_load_2d(dst, &wmap, n0, w_row0 + kb * (TC_BK / 8), bar);
+                        tma_load_2d(dst, &wmap, n0, w_row0 + kb * (TC_BK / 8) * KK, bar);      // the map's box holds 8 KK rows
                     else
                         tma_load_2d(dst, &wmap, n0 / 8, w_row0 + kb * TC_BK, bar);
                     // the block's quantisation group rides along: scale row and packed zero-points
-                    tma_load_2d(dst + TC_W_BYTES, &smap, n0, g_row0 + grp, bar);
-                    if (P.qzeros) tma_load_2d(dst + TC_W_BYTES + TC_SC_BYTES, &zmap, n0 / 8, g_row0 + grp, bar);
+                    tma_load_2d(dst + w_bytes, &smap, n0, g_row0 + grp, bar);
+                    if (P.qzeros) tma_load_2d(dst + w_bytes + TC_SC_BYTES, &zmap, n0 / 8, g_row0 + grp, bar);
                 }
             }
         }
@@ -226,7 +233,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 if (i >= SA) wait(B_ACTE + s, ring_phase(i, LSA) ^ 1u);
                 const uint32_t bar = smem_u32(&bars[B_ACTF + s]);
                 mbar_expect_tx(bar, b_bytes);
-                tma_load_2d(smem_u32(b_tile + (size_t)s * b_bytes), &amap, (kb_begin + i) * TC_BK, m0, bar);
+                for (int h = 0; h < KK; ++h)
+                    tma_load_2d(smem_u32(b_tile + (size_t)s * b_bytes + (size_t)h * TT * 128), &amap, ((kb_begin + i) * KK + h) * TC_BK, m0, bar);
             }
         }
     } else if (warp == 1 || warp == 2) {
@@ -252,13 +260,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                 tc_fence_after();
                 const uint64_t da = da0 + (uint64_t)((sd * TC_A_BYTES) >> 4);
                 const uint64_t db = db0 + (uint64_t)((sa * b_bytes) >> 4);
+                for (int h = 0; h < KK; ++h) {
 #pragma unroll
-                for (int j = 0; j < TC_BK / 16; ++j) {
-                    if (TS)
-                        tc_mma_f16_ts(acc, tmem_acc + a_col0 + sd * 32 + j * 8, db + (uint64_t)(j * 2), idesc,
-                                      (i >= NMMA || j > 0) ? 1u : 0u);
-                    else
-                        tc_mma_f16(acc, da + (uint64_t)(j * a_step), db + (uint64_t)(j * 2), idesc, (i >= NMMA || j > 0) ? 1u : 0u);
+                    for (int j = 0; j < TC_BK / 16; ++j) {
+                        const uint32_t accumulate = (i >= NMMA || h > 0 || j > 0) ? 1u : 0u;
+                        if (TS)
+                            tc_mma_f16_ts(acc, tmem_acc + a_col0 + (sd * KK + h) * 32 + j * 8,
+                                          db + (uint64_t)((h * TT * 128) >> 4) + (uint64_t)(j * 2), idesc, accumulate);
+                        else
+                            tc_mma_f16(acc, da + (uint64_t)(j * a_step), db + (uint64_t)(j * 2), idesc, accumulate);
+                    }
                 }
                 tc_commit(smem_u32(&bars[B_DQE + sd]));   // operand tile (and, through it, the activation tile) reusable once these retire
             }
@@ -279,21 +290,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             const bool ok_dqe = i < SD || mbar_test_wait(smem_u32(&bars[B_DQE + s]), ring_phase(i, LSD) ^ 1u);
             const bool ok_act = mbar_test_wait(smem_u32(&bars[B_ACTF + ring_slot(i, LSA)]), ring_phase(i, LSA));
             wait_after_test(ok_raw, B_RAWF + r, ring_phase(i, LR));                               // packed words, scales, zero-points landed
-            const unsigned char *slot = raw + (size_t)r * TC_RAW_BYTES;
+            const unsigned char *slot = raw + (size_t)r * raw_bytes;
             const uint32_t *rw = reinterpret_cast<const uint32_t *>(slot);
-            uint32_t w[8];
+            uint32_t w[8 * KK];
             if (FMT == FMT_GPTQ) {
-                // thread t = weight column t (operand row t): its 8 words are the 8 16-byte chunks of the row
-                const uint32_t s2 = (uint32_t)reinterpret_cast<const uint16_t *>(slot + TC_W_BYTES)[t] * 0x10001u;   // the column's scale in both halves
+                // thread t = weight column t (operand row t): its 8 words per 64 k are the 8 16-byte chunks of the row
+                const uint32_t s2 = (uint32_t)reinterpret_cast<const uint16_t *>(slot + w_bytes)[t] * 0x10001u;   // the column's scale in both halves
                 int z = 8;
                 if (P.qzeros) {
-                    z = (int)((reinterpret_cast<const uint32_t *>(slot + TC_W_BYTES + TC_SC_BYTES)[t >> 3] >> (4 * (t & 7))) & 15u) +
+                    z = (int)((reinterpret_cast<const uint32_t *>(slot + w_bytes + TC_SC_BYTES)[t >> 3] >> (4 * (t & 7))) & 15u) +
                         P.zero_offset;
                 }
                 uint32_t zm[4];
                 zero_magic4<BF>(z, zm);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) w[j] = rw[j * TC_BN + t];     // (fused silu: rows 0..63 gate columns, 64..127 up columns)
+                if (KK == 2) {
+#pragma unroll
+                    for (int j = 8; j < 8 * KK; ++j) w[j] = rw[j * TC_BN + t];
+                }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bars[B_RAWE + r]));  // this warp is done with the packed tile
                 if (i >= SD) {
@@ -302,31 +317,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                     if (warp_in_group == 0 && lane == 0) mbar_arrive(smem_u32(&bars[B_ACTE + ring_slot(i - SD, LSA)]));
                 }
                 unsigned char *arow = a_tile + (size_t)s * TC_A_BYTES + t * 128;
-                uint32_t v[32];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    uint32_t x[4];
-                    nib4<BF>(w[j], x);
-                    const uint32_t v04 = sub_mul<BF>(x[0], zm[0], s2), v15 = sub_mul<BF>(x[1], zm[1], s2);
-                    const uint32_t v26 = sub_mul<BF>(x[2], zm[2], s2), v37 = sub_mul<BF>(x[3], zm[3], s2);
-                    uint4 o;
-                    if (KPERM) {
-                        o = make_uint4(v04, v15, v26, v37);    // (k0 k4) (k1 k5) (k2 k6) (k3 k7): the activations' order
-                    } else {
-                        o.x = __byte_perm(v04, v15, 0x5410);   // k0 k1
-                        o.y = __byte_perm(v26, v37, 0x5410);   // k2 k3
-                        o.z = __byte_perm(v04, v15, 0x7632);   // k4 k5
-                        o.w = __byte_perm(v26, v37, 0x7632);   // k6 k7
+                for (int h = 0; h < KK; ++h) {
+                    uint32_t v[32];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        uint32_t x[4];
+                        nib4<BF>(w[h * 8 + j], x);
+                        const uint32_t v04 = sub_mul<BF>(x[0], zm[0], s2), v15 = sub_mul<BF>(x[1], zm[1], s2);
+                        const uint32_t v26 = sub_mul<BF>(x[2], zm[2], s2), v37 = sub_mul<BF>(x[3], zm[3], s2);
+                        uint4 o;
+                        if (KPERM) {
+                            o = make_uint4(v04, v15, v26, v37);    // (k0 k4) (k1 k5) (k2 k6) (k3 k7): the activations' order
+                        } else {
+                            o.x = __byte_perm(v04, v15, 0x5410);   // k0 k1
+                            o.y = __byte_perm(v26, v37, 0x5410);   // k2 k3
+                            o.z = __byte_perm(v04, v15, 0x7632);   // k4 k5
+                            o.w = __byte_perm(v26, v37, 0x7632);   // k6 k7
+                        }
+                        if (TS) {
+                            v[4 * j] = o.x; v[4 * j + 1] = o.y; v[4 * j + 2] = o.z; v[4 * j + 3] = o.w;
+                        } else {
+                            *reinterpret_cast<uint4 *>(arow + ((j ^ (t & 7)) << 4)) = o;
+                        }
                     }
-                    if (TS) {
-                        v[4 * j] = o.x; v[4 * j + 1] = o.y; v[4 * j + 2] = o.z; v[4 * j + 3] = o.w;
-                    } else {
-                        *reinterpret_cast<uint4 *>(arow + ((j ^ (t & 7)) << 4)) = o;
-                    }
+                    // lane t of tensor memory = operand row t; columns = this sub-block's 64 k, two per column
+                    if (TS) tmem_st32(tmem_acc + ((uint32_t)(t & 96) << 16) + a_col0 + (s * KK + h) * 32, v);
                 }
                 if (TS) {
-                    // lane t of tensor memory = operand row t; columns = this block's 64 k, two per column
-                    tmem_st32(tmem_acc + ((uint32_t)(t & 96) << 16) + a_col0 + s * 32, v);
                     tmem_st_wait();
                     tc_fence_before();
                 }
@@ -543,11 +561,15 @@ int gemm_tc_launch(const GemmArgs &g) {
     // Shared memory: two CTAs per SM while the token tile is small (or in the paired form), one otherwise.
     const int ctas_per_sm = tt <= 64 || pair128 ? 2 : 1;
     const int budget = (ctas_per_sm == 2 ? 111 : 222) * 1024;
-    const int act_bytes = tt * TC_BK * 2;
     const int ng = ctas_per_sm == 2 ? 2 : 4;         // dequant groups
     // operand tile in tensor memory (GPTQ) or in shared memory (AWQ; B200K_TC_OPERAND=smem forces it)
     bool ts = g.format == FMT_GPTQ;
     if (env_char("B200K_TC_OPERAND") == 's') ts = false;
+    // pipeline steps of 128 k (two 64-k sub-blocks) at token tiles up to 64 of an ordinary GEMM with the operand in tensor memory
+    const int kk = ts && !grouped && !silu && tt <= 64 && g.k % (2 * TC_BK) == 0 && g.group % (2 * TC_BK) == 0 &&
+                           env_int("B200K_TC_KK", 2) == 2 ? 2 : 1;
+    const int act_bytes = tt * TC_BK * 2 * kk;
+    const int raw_bytes = TC_W_BYTES * kk + TC_SC_BYTES + 128;
     const int a_bytes = ts ? 0 : TC_A_BYTES;
     // Ring depths, powers of two (slot and phase of a block are then bit fields of its index).  The operand ring
     // is shallow (producer and consumer are on chip) and at least as deep as there are dequant groups; an
@@ -560,8 +582,8 @@ int gemm_tc_launch(const GemmArgs &g) {
     auto log2i = [](int v) { int l = 0; while ((1 << l) < v) ++l; return l; };
     int dq_stages, act_stages;
     if (ts) {   // operand tiles cost 32 TMEM columns each: 256 columns per CTA with two CTAs per SM, 512 with one
-        dq_stages = pair128 && tt > 128 ? 2 : 4;      // two CTAs per SM: tile + 32 x depth <= 256 columns
-        act_stages = tt <= 128 && !pair128 ? 8 : 4;
+        dq_stages = (pair128 && tt > 128) || kk == 2 ? 2 : 4;      // two CTAs per SM: accumulators + 32 kk x depth <= 256 columns
+        act_stages = kk == 2 ? 4 : tt <= 128 && !pair128 ? 8 : 4;
     } else {
         dq_stages = tt <= 64 || pair128 ? 2 : 4;
         act_stages = tt <= 32 ? 8 : pair128 && tt > 128 ? 2 : 4;
@@ -569,11 +591,11 @@ int gemm_tc_launch(const GemmArgs &g) {
     if (const int v = env_int("B200K_TC_DQ_STAGES", 0)) dq_stages = pow2_floor(v < 1 ? 1 : v);     // tuning overrides
     if (const int v = env_int("B200K_TC_ACT_STAGES", 0)) act_stages = pow2_floor(v < 1 ? 1 : v);
     if (dq_stages < ng) dq_stages = ng;
-    if (ts && (nmma * tt < 32 ? 32 : nmma * tt) + 32 * dq_stages > (ctas_per_sm == 2 ? 256 : 512)) return TC_NOT_COVERED;
+    if (ts && (nmma * tt < 32 ? 32 : nmma * tt) + 32 * kk * dq_stages > (ctas_per_sm == 2 ? 256 : 512)) return TC_NOT_COVERED;
     if (act_stages < dq_stages) act_stages = dq_stages;
-    int raw_stages = (budget - dq_stages * a_bytes - act_stages * act_bytes - 1024) / TC_RAW_BYTES;
+    int raw_stages = (budget - dq_stages * a_bytes - act_stages * act_bytes - 1024) / raw_bytes;
     if (raw_stages < 2) return TC_NOT_COVERED;
-    raw_stages = pow2_floor(raw_stages > 16 ? 16 : raw_stages);
+    raw_stages = pow2_floor(raw_stages > 16 / kk ? 16 / kk : raw_stages);
     {
         const int v = env_int("B200K_TC_RAW_STAGES", 0);
         if (v >= 2 && v <= raw_stages) raw_stages = pow2_floor(v);
@@ -582,7 +604,7 @@ int gemm_tc_launch(const GemmArgs &g) {
     // whatever its length, so: the fewest CTAs that still occupy most SMs; one more doubling only when
     // the machine is at most once covered and every CTA keeps a long K range.
     // The exchange tile ([tt][128] fp32) reuses the three rings, idle by then.
-    const size_t ring_bytes = (size_t)dq_stages * a_bytes + (size_t)act_stages * act_bytes + (size_t)raw_stages * TC_RAW_BYTES;
+    const size_t ring_bytes = (size_t)dq_stages * a_bytes + (size_t)act_stages * act_bytes + (size_t)raw_stages * raw_bytes;
     const bool listed = grouped && g.tile_list;
     const bool can_split = (!grouped || listed) && !silu && ring_bytes >= (size_t)tt * TC_BN * 4;
     if (silu && ring_bytes < (size_t)tt * TC_BN * 2) return TC_NOT_COVERED;      // the epilogue stages the up half in the rings' space
@@ -609,11 +631,11 @@ int gemm_tc_launch(const GemmArgs &g) {
     if (g.plan_out) {
         int *o = g.plan_out;
         o[0] = tt; o[1] = ng; o[2] = dq_stages; o[3] = act_stages; o[4] = raw_stages; o[5] = ksplit;
-        o[6] = ceil_div(kb_total, ksplit); o[7] = tok_tiles * col_tiles; o[8] = nmma; o[9] = ts ? 1 : 0;
+        o[6] = ceil_div(kb_total / kk, ksplit); o[7] = tok_tiles * col_tiles; o[8] = nmma; o[9] = ts ? 1 : 0;
         return 0;
     }
     const size_t smem = (size_t)dq_stages * a_bytes + (size_t)act_stages * act_bytes +
-                        (size_t)raw_stages * TC_RAW_BYTES + (2 * act_stages + 2 * dq_stages + 2 * raw_stages + 1) * 8 +
+                        (size_t)raw_stages * raw_bytes + (2 * act_stages + 2 * dq_stages + 2 * raw_stages + 1) * 8 +
                         16 + 1024;
 
     // tensor maps: packed weight words (no swizzle) and activations (128-byte swizzle)
@@ -629,7 +651,7 @@ int gemm_tc_launch(const GemmArgs &g) {
         rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, g.qweight, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
     } else if (g.format == FMT_GPTQ) {
         const uint64_t dims[2] = {(uint64_t)g.n, (uint64_t)(g.k / 8) * nseg}, str[1] = {(uint64_t)g.s_qwk * 4};
-        const uint32_t box[2] = {TC_BN, TC_BK / 8};
+        const uint32_t box[2] = {TC_BN, (uint32_t)(TC_BK / 8 * kk)};
         rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, g.qweight, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
     } else {
         const uint64_t dims[2] = {(uint64_t)(g.n / 8), (uint64_t)g.k * nseg}, str[1] = {(uint64_t)g.s_qwk * 4};
@@ -675,7 +697,7 @@ int gemm_tc_launch(const GemmArgs &g) {
     P.s_sk = g.s_sk; P.s_qzk = g.s_qzk; P.s_cm = g.s_cm;
     P.zero_offset = g.zero_offset;
     P.tt = tt; P.dq_log2 = log2i(dq_stages); P.act_log2 = log2i(act_stages); P.raw_log2 = log2i(raw_stages); P.ksplit = ksplit;
-    P.kb_per_split = ceil_div(kb_total, ksplit);
+    P.kb_per_split = ceil_div(kb_total / kk, ksplit);      // in pipeline steps
     P.seg_offsets = g.seg_offsets;
     P.tile_list = grouped ? g.tile_list : nullptr;
     P.tile_count = g.tile_count;
@@ -689,7 +711,9 @@ int gemm_tc_launch(const GemmArgs &g) {
     if (g.a_kperm && !ts) return TC_NOT_COVERED;   // pre-permuted activations: only the tensor-memory operand variants take them
     if (silu && !ts) return TC_NOT_COVERED;
     if (g.bf16 && (silu || g.a_kperm || (g.format == FMT_GPTQ && !ts))) return TC_NOT_COVERED;
-    auto kern = g.bf16 && g2m1 ? (g.format == FMT_AWQ ? gemm_tc_kernel<FMT_AWQ, 2, false, 1, false, false, true> : gemm_tc_kernel<FMT_GPTQ, 2, true, 1, false, false, true>)
+    auto kern = kk == 2 ? (g.bf16 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false, false, true, 2>
+                                  : g.a_kperm ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, true, false, false, 2> : gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false, false, false, 2>)
+                : g.bf16 && g2m1 ? (g.format == FMT_AWQ ? gemm_tc_kernel<FMT_AWQ, 2, false, 1, false, false, true> : gemm_tc_kernel<FMT_GPTQ, 2, true, 1, false, false, true>)
                 : g.bf16 ? (g.format == FMT_AWQ ? (ng == 2 ? gemm_tc_kernel<FMT_AWQ, 2, false, 2, false, false, true> : gemm_tc_kernel<FMT_AWQ, 4, false, 1, false, false, true>)
                                               : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false, false, true> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, false, false, true>))
                 : silu && g2m1 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 1, false, true>
@@ -703,9 +727,9 @@ int gemm_tc_launch(const GemmArgs &g) {
                                   : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, false>))
                      : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, false, 2, false> : gemm_tc_kernel<FMT_GPTQ, 4, false, 1, false>);
     {
-        static OncePerDevice once[8][3];
+        static OncePerDevice once[8][4];
         const int variant = g.bf16 ? (g.format == FMT_AWQ ? 7 : 6) : silu ? (g.a_kperm ? 5 : 4) : g.format == FMT_AWQ ? 1 : (ts ? (g.a_kperm ? 3 : 2) : 0);
-        cudaError_t e = once[variant][g2m1 ? 2 : ng == 4].run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); });
+        cudaError_t e = once[variant][kk == 2 ? 3 : g2m1 ? 2 : ng == 4].run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); });
         if (e != cudaSuccess) return fail((int)e, "w4a16 gemm (tensor core): shared memory: %s", cudaGetErrorString(e));
     }
     cudaLaunchConfig_t cfg = {};
