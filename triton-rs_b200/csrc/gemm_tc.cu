@@ -566,7 +566,7 @@ int gemm_tc_launch(const GemmArgs &g) {
     bool ts = g.format == FMT_GPTQ;
     if (env_char("B200K_TC_OPERAND") == 's') ts = false;
     // pipeline steps of 128 k (two 64-k sub-blocks) at token tiles up to 64 of an ordinary GEMM with the operand in tensor memory
-    const int kk = ts && !grouped && !silu && tt <= 64 && g.k % (2 * TC_BK) == 0 && g.group % (2 * TC_BK) == 0 &&
+    const int kk = ts && !grouped && !silu && (tt <= 64 || (pair128 && tt == 128 && env_int("B200K_TC_KK128", 1))) && g.k % (2 * TC_BK) == 0 && g.group % (2 * TC_BK) == 0 &&
                            env_int("B200K_TC_KK", 2) == 2 ? 2 : 1;
     const int act_bytes = tt * TC_BK * 2 * kk;
     const int raw_bytes = TC_W_BYTES * kk + TC_SC_BYTES + 128;
@@ -583,7 +583,7 @@ int gemm_tc_launch(const GemmArgs &g) {
     int dq_stages, act_stages;
     if (ts) {   // operand tiles cost 32 TMEM columns each: 256 columns per CTA with two CTAs per SM, 512 with one
         dq_stages = (pair128 && tt > 128) || kk == 2 ? 2 : 4;      // two CTAs per SM: accumulators + 32 kk x depth <= 256 columns
-        act_stages = kk == 2 ? 4 : tt <= 128 && !pair128 ? 8 : 4;
+        act_stages = kk == 2 ? (tt > 64 ? 2 : 4) : tt <= 128 && !pair128 ? 8 : 4;
     } else {
         dq_stages = tt <= 64 || pair128 ? 2 : 4;
         act_stages = tt <= 32 ? 8 : pair128 && tt > 128 ? 2 : 4;
@@ -711,7 +711,9 @@ int gemm_tc_launch(const GemmArgs &g) {
     if (g.a_kperm && !ts) return TC_NOT_COVERED;   // pre-permuted activations: only the tensor-memory operand variants take them
     if (silu && !ts) return TC_NOT_COVERED;
     if (g.bf16 && (silu || g.a_kperm || (g.format == FMT_GPTQ && !ts))) return TC_NOT_COVERED;
-    auto kern = kk == 2 ? (g.bf16 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false, false, true, 2>
+    auto kern = kk == 2 && g2m1 ? (g.bf16 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 1, false, false, true, 2>
+                                          : g.a_kperm ? gemm_tc_kernel<FMT_GPTQ, 2, true, 1, true, false, false, 2> : gemm_tc_kernel<FMT_GPTQ, 2, true, 1, false, false, false, 2>)
+                : kk == 2 ? (g.bf16 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false, false, true, 2>
                                   : g.a_kperm ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, true, false, false, 2> : gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false, false, false, 2>)
                 : g.bf16 && g2m1 ? (g.format == FMT_AWQ ? gemm_tc_kernel<FMT_AWQ, 2, false, 1, false, false, true> : gemm_tc_kernel<FMT_GPTQ, 2, true, 1, false, false, true>)
                 : g.bf16 ? (g.format == FMT_AWQ ? (ng == 2 ? gemm_tc_kernel<FMT_AWQ, 2, false, 2, false, false, true> : gemm_tc_kernel<FMT_AWQ, 4, false, 1, false, false, true>)
@@ -727,9 +729,9 @@ int gemm_tc_launch(const GemmArgs &g) {
                                   : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false> : gemm_tc_kernel<FMT_GPTQ, 4, true, 1, false>))
                      : (ng == 2 ? gemm_tc_kernel<FMT_GPTQ, 2, false, 2, false> : gemm_tc_kernel<FMT_GPTQ, 4, false, 1, false>);
     {
-        static OncePerDevice once[8][4];
+        static OncePerDevice once[8][5];
         const int variant = g.bf16 ? (g.format == FMT_AWQ ? 7 : 6) : silu ? (g.a_kperm ? 5 : 4) : g.format == FMT_AWQ ? 1 : (ts ? (g.a_kperm ? 3 : 2) : 0);
-        cudaError_t e = once[variant][kk == 2 ? 3 : g2m1 ? 2 : ng == 4].run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); });
+        cudaError_t e = once[variant][kk == 2 ? (g2m1 ? 4 : 3) : g2m1 ? 2 : ng == 4].run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); });
         if (e != cudaSuccess) return fail((int)e, "w4a16 gemm (tensor core): shared memory: %s", cudaGetErrorString(e));
     }
     cudaLaunchConfig_t cfg = {};
