@@ -105,7 +105,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int LSD = P.dq_log2, LSA = P.act_log2, LR = P.raw_log2, TT = P.tt;
     const int SD = 1 << LSD, SA = 1 << LSA, R = 1 << LR;
-    static_assert(KK == 1 || (KK == 2 && TS && !SILU), "wide steps: operand in tensor memory, no fused epilogue");
+    static_assert(KK == 1 || (KK == 2 && TS), "wide steps: operand in tensor memory");
     const int b_bytes = TT * TC_BK * 2 * KK;                    // KK swizzled boxes of [TT][128 B], one behind the other
     const int w_bytes = TC_W_BYTES * KK, raw_bytes = w_bytes + TC_SC_BYTES + 128;
     unsigned char *a_tile = smem;                               // [SD][16 KiB] (absent when the operand tile lives in TMEM)
@@ -209,7 +209,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                     // the tensors are described as [rows][2][I]: one box of 64 columns x {gate, up} per tensor lands as
                     // [8 rows][gate 64 | up 64] words, 64 + 64 scales, 8 + 8 zero-point words -- the layout of an
                     // ordinary 128-column tile, at half the copies two boxes per tensor would take
-                    tma_load_3d(dst, &wmap, n0, 0, w_row0 + kb * (TC_BK / 8), bar);
+                    tma_load_3d(dst, &wmap, n0, 0, w_row0 + kb * (TC_BK / 8) * KK, bar);
                     tma_load_3d(dst + w_bytes, &smap, n0, 0, g_row0 + grp, bar);
                     if (P.qzeros) tma_load_3d(dst + w_bytes + TC_SC_BYTES, &zmap, n0 / 8, 0, g_row0 + grp, bar);
                 } else {
@@ -566,7 +566,7 @@ int gemm_tc_launch(const GemmArgs &g) {
     bool ts = g.format == FMT_GPTQ;
     if (env_char("B200K_TC_OPERAND") == 's') ts = false;
     // pipeline steps of 128 k (two 64-k sub-blocks) at token tiles up to 64 of an ordinary GEMM with the operand in tensor memory
-    const int kk = ts && !grouped && !silu && (tt <= 64 || (pair128 && tt == 128 && env_int("B200K_TC_KK128", 1))) && g.k % (2 * TC_BK) == 0 && g.group % (2 * TC_BK) == 0 &&
+    const int kk = ts && !(g.bf16 && (silu || grouped)) && (tt <= 64 || (pair128 && tt <= 128 && env_int("B200K_TC_KK128", 1))) && g.k % (2 * TC_BK) == 0 && g.group % (2 * TC_BK) == 0 &&
                            env_int("B200K_TC_KK", 2) == 2 ? 2 : 1;
     const int act_bytes = tt * TC_BK * 2 * kk;
     const int raw_bytes = TC_W_BYTES * kk + TC_SC_BYTES + 128;
@@ -647,7 +647,7 @@ int gemm_tc_launch(const GemmArgs &g) {
         // I further on in one copy
         const uint64_t inter = (uint64_t)g.silu_inter;
         const uint64_t dims[3] = {inter, 2, (uint64_t)(g.k / 8) * nseg}, str[2] = {inter * 4, (uint64_t)g.s_qwk * 4};
-        const uint32_t box[3] = {TC_BN / 2, 2, TC_BK / 8};
+        const uint32_t box[3] = {TC_BN / 2, 2, (uint32_t)(TC_BK / 8 * kk)};
         rc = make_tensor_map(&wmap, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, g.qweight, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE);
     } else if (g.format == FMT_GPTQ) {
         const uint64_t dims[2] = {(uint64_t)g.n, (uint64_t)(g.k / 8) * nseg}, str[1] = {(uint64_t)g.s_qwk * 4};
@@ -711,7 +711,9 @@ int gemm_tc_launch(const GemmArgs &g) {
     if (g.a_kperm && !ts) return TC_NOT_COVERED;   // pre-permuted activations: only the tensor-memory operand variants take them
     if (silu && !ts) return TC_NOT_COVERED;
     if (g.bf16 && (silu || g.a_kperm || (g.format == FMT_GPTQ && !ts))) return TC_NOT_COVERED;
-    auto kern = kk == 2 && g2m1 ? (g.bf16 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 1, false, false, true, 2>
+    auto kern = kk == 2 && silu ? (g2m1 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 1, false, true, false, 2>
+                                        : g.a_kperm ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, true, true, false, 2> : gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false, true, false, 2>)
+                : kk == 2 && g2m1 ? (g.bf16 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 1, false, false, true, 2>
                                           : g.a_kperm ? gemm_tc_kernel<FMT_GPTQ, 2, true, 1, true, false, false, 2> : gemm_tc_kernel<FMT_GPTQ, 2, true, 1, false, false, false, 2>)
                 : kk == 2 ? (g.bf16 ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false, false, true, 2>
                                   : g.a_kperm ? gemm_tc_kernel<FMT_GPTQ, 2, true, 2, true, false, false, 2> : gemm_tc_kernel<FMT_GPTQ, 2, true, 2, false, false, false, 2>)
