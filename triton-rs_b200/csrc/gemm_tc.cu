@@ -535,6 +535,7 @@ int gemm_tc_launch(const GemmArgs &g) {
     if (!grouped && !silu && g.m > 64 && !env_int("B200K_TC_TT", 0)) {
         const int sms = sm_count(), cols = ceil_div(g.n, TC_BN);
         const bool pair_ok = env_int("B200K_TC_PAIR128", 1) != 0;
+        const bool wide = g.format == FMT_GPTQ && g.k % (2 * TC_BK) == 0 && g.group % (2 * TC_BK) == 0 && env_char("B200K_TC_OPERAND") != 's';
         float best = 1e30f;
         for (int form = 0; form < 2; ++form) {      // 0: paired 128-token tiles, 1: 256-token tiles (128 with four groups up to 128 tokens)
             if (form == 0 && !pair_ok) continue;
@@ -545,7 +546,8 @@ int gemm_tc_launch(const GemmArgs &g) {
                 if (ks > 1 && (kb_total <= 8 || kb_total / ks < 4)) break;
                 if (ks > 1 && cols * toks * (ks / 2) >= slots) break;     // a grid that fills the machine is not split further
                 const int ctas = cols * toks * ks, waves = ceil_div(ctas, slots);
-                const float per_block = form == 0 ? (ctas > sms ? 0.62f : 0.45f) : (t == 256 ? 0.48f : 0.22f);
+                // (the paired form with 128-k steps, GPTQ layouts: 0.49 us per 64 k measured where 64-k steps take 0.62)
+                const float per_block = form == 0 ? (ctas > sms ? 0.62f : 0.45f) * (wide ? 0.78f : 1.f) : (t == 256 ? 0.48f : 0.22f);
                 const float us = waves * (4.f + ceil_div(kb_total, ks) * per_block) + (ks > 1 ? 5.f + t / 64.f : 0.f);
                 if (us < best) {
                     best = us;
