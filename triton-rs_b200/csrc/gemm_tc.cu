@@ -6,19 +6,22 @@
 // instruction, and the dequantised weight tile is the A operand.
 //
 // Per CTA: one 128-column slab of the weight, one token tile, one K split.  Roles:
-//   warp 0      TMA producer: packed int4 words (no swizzle) and the activation tile
-//               (128-byte swizzle) of K block kb into ring stage kb % STAGES
-//   warps 2..5  dequant: nibbles -> fp16 in registers (magic-number trick, exact
-//               (q - zero), one fp16 multiply by the scale = the reference's rounding),
-//               written as the UMMA operand tile in the 128-byte-swizzled canonical
-//               layout -- K-major for GPTQ (a word holds 8 consecutive k of one column =
-//               one 16-byte chunk of a row), MN-major for AWQ (a word holds 8 adjacent
-//               columns of one k = one 16-byte chunk of a k-row)
-//   warp 1      one thread issues 4 x tcgen05.mma (K = 16 each) per K block and commits
-//               to the stage's "consumed" barrier
-//   warps 2..5  epilogue: tcgen05.ld of the 128 x TT fp32 accumulator, fp16 store; with a
-//               K split the CTAs of a cluster exchange partial tiles through distributed
-//               shared memory and each reduces a share of the rows in a fixed order
+//   warp 0      TMA producer of the packed int4 words of a pipeline step (64 or 128 k), with the step's
+//               scale row and packed zero-points (ring of up to 16 steps: this is all the HBM traffic)
+//   warp 3      TMA producer of the activation tiles (128-byte swizzle; from L2)
+//   warps 4..   NG = 2 or 4 groups of 4 dequant warps, taking the steps round-robin: nibbles -> fp16 (or
+//               bf16) in registers (magic-number trick, exact (q - zero), one multiply by the scale =
+//               the reference's rounding).  GPTQ: a thread owns one weight column = one TMEM lane and
+//               writes its 64 k of a sub-block with tcgen05.st into a ring of operand tiles in TENSOR
+//               MEMORY (the MMA reads A from there).  AWQ: a word holds 8 adjacent columns of one k, so
+//               the tile goes to shared memory in the UMMA MN-major 128-byte-swizzled layout.
+//   warps 1, 2  MMA issuers: one thread issues 4 x tcgen05.mma (K = 16 each) per 64 k and commits to the
+//               step's "operand consumed" barrier; at token tiles <= 64 two issuers with an accumulator
+//               each take the steps alternately
+//   warps 4..   epilogue: tcgen05.ld of the 128 x TT fp32 accumulator(s), fp16 store (optionally silu(gate) * up
+//               of paired columns); with a K split the CTAs of a cluster exchange partial tiles through
+//               distributed shared memory and each reduces a share of the rows in a fixed order
+// Grouped mode (fused MoE): a row segment per expert with its own weight matrix, token tiles from a work list.
 // Every wait on an mbarrier is bounded; a wait that gives up sets a status word and the
 // kernel drains and frees its TMEM as usual.
 #include <cooperative_groups.h>
