@@ -5,7 +5,7 @@
 // handles by the host code (one process per GPU) and mapped by every peer.  A row-parallel GEMM writes
 // its partial sums straight into a slot of its own buffer; the all-reduce kernel then
 //   1. publishes "my slot is complete" by storing a sequence number into its flag on every peer
-//      (system-scope release after a system fence),
+//      (system-scope release store),
 //   2. waits -- bounded, ~1 s, reporting through a status word -- until every peer's flag carries the
 //      same sequence number,
 //   3. sums the slot of all ranks in rank order with plain peer loads (nothing is reduced inside the switch),
@@ -14,7 +14,8 @@
 // The sequence number lives in device memory and is advanced by the kernel, so a CUDA graph that
 // contains the call can be replayed.  Slots alternate between the two all-reduces of a layer; a slot is
 // rewritten only after a later all-reduce has passed its barrier, i.e. after every peer finished
-// reading it.
+// reading it.  The consumers of a layer's exchanges are fused into the same kernel (residual add; residual add +
+// rms_norm), and large tensors take a two-shot form (allreduce_twoshot_kernel).
 #include "comm.cuh"
 
 struct b200k_comm {
