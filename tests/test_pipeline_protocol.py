@@ -78,3 +78,41 @@ def test_launch_plans_cannot_deadlock(pkg, m, k, n, awq):
         assert max(32, nmma * tt) + 32 * sd <= (256 if tt <= 64 else 512)
     for nkb in {kb_per_split, max(1, (k // 64) - kb_per_split * (ksplit - 1)), 1, 2, 3, 7}:
         assert not simulate(ng, sd, sa, r, nkb, nmma), (plan[:], nkb)
+
+
+def _plan(pkg, m, n, k, awq=0, group=128):
+    plan = (ctypes.c_int * 10)()
+    pkg.lib().call("b200k_gemm_tc_plan", m, n, k, group, awq, ctypes.addressof(plan))
+    names = ("tt", "ng", "sd", "sa", "r", "ksplit", "steps", "tiles", "nmma", "flags")
+    return dict(zip(names, plan))
+
+
+def test_launch_plans_fill_whole_waves(pkg):
+    """Above 64 tokens form and K split are planned together: the grids of the Llama-3-8B projections stay within the
+    resident slots of 148 SMs (two CTAs per SM in the two-group forms, one in the four-group form) wherever one wave can
+    hold them, and a grid that already fills the machine is not split."""
+    sms = 148
+    for awq in (0, 1):
+        for m, n, k in [(128, 6144, 4096), (128, 4096, 4096), (128, 28672, 4096), (128, 4096, 14336),
+                        (1024, 4096, 4096), (1024, 4096, 14336), (512, 6144, 4096)]:
+            p = _plan(pkg, m, n, k, awq)
+            ctas = p["tiles"] * p["ksplit"]
+            slots = sms * (2 if p["ng"] == 2 else 1)
+            assert ctas <= slots, (m, n, k, awq, p)
+    assert _plan(pkg, 128, 28672, 4096)["ng"] == 2          # 224 tiles: one wave as two CTAs per SM, two waves otherwise
+    assert _plan(pkg, 1024, 4096, 4096)["ksplit"] == 1      # 128 tiles of 256 tokens: one wave, nothing to split
+    assert _plan(pkg, 1024, 6144, 4096)["ksplit"] == 1      # 192 tiles fill the machine
+
+
+def test_pipeline_steps_of_128_k_where_tensor_memory_allows(pkg):
+    """GPTQ layouts with group 128: token tiles up to 64 and the paired 128-token form take steps of 128 k (K / 128 steps
+    per CTA and split); group 64, AWQ layouts and 256-token tiles keep 64-k steps."""
+    assert _plan(pkg, 64, 4096, 4096)["steps"] * _plan(pkg, 64, 4096, 4096)["ksplit"] == 4096 // 128
+    assert _plan(pkg, 128, 28672, 4096)["steps"] == 4096 // 128
+    assert _plan(pkg, 64, 4096, 4096, group=64)["steps"] * _plan(pkg, 64, 4096, 4096, group=64)["ksplit"] == 4096 // 64
+    assert _plan(pkg, 64, 4096, 4096, awq=1)["steps"] * _plan(pkg, 64, 4096, 4096, awq=1)["ksplit"] == 4096 // 64
+    assert _plan(pkg, 1024, 4096, 4096)["steps"] == 4096 // 64
+    for m, n, k in [(16, 4096, 4096), (64, 28672, 4096), (128, 4096, 14336)]:
+        p = _plan(pkg, m, n, k)
+        assert p["sd"] == 2 and p["sd"] >= p["ng"]           # two sub-tiles x ring of two beside the accumulators: 256 TMEM columns
+        assert max(32, p["nmma"] * p["tt"]) + 2 * 32 * p["sd"] <= 256
