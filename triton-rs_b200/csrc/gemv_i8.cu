@@ -459,7 +459,11 @@ int gemv_i8_launch(const GemmArgs &g) {
     const int units = g.k / unit_rows;
     // enough CTAs for ~2 per SM, cluster size a power of two <= 8, no warp without a unit
     int ksplit = 1;
-    while (ksplit < 8 && colblocks * ksplit < 2 * sm_count() && ksplit * 2 * kwarps <= units) ksplit *= 2;
+    while (ksplit < 8 && colblocks * ksplit < 2 * sm_count() && ksplit * 2 * kwarps <= units) {
+        // AWQ with 256-column blocks: never past two CTAs per SM (4096 x 28672: 224 CTAs 16.7 us, 448 CTAs 18.2 us)
+        if (g.format == FMT_AWQ && awq_cols == 256 && colblocks * ksplit * 2 > 2 * sm_count()) break;
+        ksplit *= 2;
+    }
     {   // tuning override
         const int v = env_int("B200K_GEMV_KSPLIT", 0);
         if ((v == 1 || v == 2 || v == 4 || v == 8) && v * kwarps <= units) ksplit = v;
