@@ -460,8 +460,8 @@ int gemv_i8_launch(const GemmArgs &g) {
     // enough CTAs for ~2 per SM, cluster size a power of two <= 8, no warp without a unit
     int ksplit = 1;
     while (ksplit < 8 && colblocks * ksplit < 2 * sm_count() && ksplit * 2 * kwarps <= units) {
-        // AWQ with 256-column blocks: never past two CTAs per SM (4096 x 28672: 224 CTAs 16.7 us, 448 CTAs 18.2 us)
-        if (g.format == FMT_AWQ && awq_cols == 256 && colblocks * ksplit * 2 > 2 * sm_count()) break;
+        // 256-column blocks: never past two CTAs per SM (4096 x 28672: AWQ 224 CTAs 16.7 us, 448 CTAs 18.2 us; GPTQ 12.6 and 14.4 us)
+        if ((g.format == FMT_AWQ ? awq_cols == 256 : cw == 2) && colblocks * ksplit * 2 > 2 * sm_count()) break;
         ksplit *= 2;
     }
     {   // tuning override
